@@ -1,0 +1,409 @@
+// The C ABI of include/dooms_cuda.h over the C++ decoder, the GGUF reader and the single-kernel launchers.
+#include "dooms_cuda.h"
+
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "cuda_llama_decoder.h"
+#include "gguf.h"
+#include "kernels/kernels.h"
+#include "nccl_dyn.h"
+
+using namespace dooms;
+
+struct dooms_cuda_llama { std::unique_ptr<CudaLlamaDecoder> dec; };
+struct dooms_gguf { std::unique_ptr<GgufFile> file; };
+
+namespace {
+
+thread_local std::string g_last_error;
+
+// dooms::Code -> the C numbering (the reference's src/api/c_api.cpp:36-47: OutOfRange folds into InvalidArgument).
+int32_t c_code(Code c) {
+    switch (c) {
+        case Code::Ok: return DOOMS_OK;
+        case Code::InvalidArgument: case Code::OutOfRange: return DOOMS_INVALID_ARGUMENT;
+        case Code::NotFound: return DOOMS_NOT_FOUND;
+        case Code::DataLoss: return DOOMS_DATA_LOSS;
+        case Code::Unsupported: return DOOMS_UNSUPPORTED;
+        case Code::ResourceExhausted: return DOOMS_RESOURCE_EXHAUSTED;
+        case Code::IoError: return DOOMS_IO_ERROR;
+        case Code::Internal: return DOOMS_INTERNAL;
+    }
+    return DOOMS_INTERNAL;
+}
+int32_t fail(int32_t code, std::string message) { g_last_error = std::move(message); return code; }
+int32_t done(const Status & st) {
+    if (st.is_ok()) return DOOMS_OK;
+    return fail(c_code(st.code()), st.message());
+}
+// struct_size lets a newer library accept an older caller's smaller struct; zero (an uninitialised caller) is rejected.
+template <class T>
+bool struct_ok(const T * p, const char * name, int32_t * code) {
+    if (!p) { *code = fail(DOOMS_INVALID_ARGUMENT, std::string(name) + " is NULL"); return false; }
+    if (p->struct_size < sizeof(size_t) * 2) { *code = fail(DOOMS_INVALID_ARGUMENT, std::string(name) + ".struct_size is not set"); return false; }
+    return true;
+}
+
+bool ref_of(const dooms_weight_ref & r, WeightRef * out, std::string * err) {
+    if (r.data && !dtype_valid(r.dtype)) { *err = "a weight has dtype " + std::to_string(r.dtype) + ", which is not a dooms_dtype"; return false; }
+    out->data = r.data;
+    out->dtype = r.data ? static_cast<DType>(r.dtype) : DType::F32;
+    out->rows = r.rows;
+    out->cols = r.cols;
+    return true;
+}
+
+CudaOptions options_of(const dooms_cuda_options * o) {
+    CudaOptions c;
+    if (!o) return c;
+    c.device = o->device;
+    c.tp_rank = o->tp_rank;
+    c.tp_size = o->tp_size < 1 ? 1 : o->tp_size;
+    c.nccl_unique_id = o->nccl_unique_id;
+    c.nccl_library = o->nccl_library;
+    c.operand_bf16 = o->operand_bf16 != 0;
+    c.use_graphs = o->use_graphs != 0;
+    return c;
+}
+
+void fill_tensor(const GgufFile & f, const GgufTensorInfo & t, dooms_gguf_tensor * out) {
+    out->name = t.name.c_str();
+    out->dtype = static_cast<int32_t>(t.dtype);
+    out->rank = t.rank;
+    for (int d = 0; d < 4; d++) out->shape[d] = d < t.rank ? t.shape[d] : 0;
+    out->offset = t.offset;
+    out->nbytes = t.nbytes;
+    out->data = f.tensor_data(t);
+}
+
+// Scratch of the single-kernel entry points that need some (argmax partial results): one small buffer per device, made on first use.
+struct DeviceScratch { void * ptr = nullptr; size_t bytes = 0; };
+std::mutex g_scratch_mutex;
+DeviceScratch g_scratch[64];
+Status scratch_for(size_t bytes, void ** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return unsupported("no CUDA device"); }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    DeviceScratch & s = g_scratch[dev];
+    if (s.bytes < bytes) {
+        if (s.ptr) cudaFree(s.ptr);
+        s.ptr = nullptr;
+        s.bytes = 0;
+        if (cudaMalloc(&s.ptr, bytes) != cudaSuccess) { (void)cudaGetLastError(); return resource_exhausted("could not allocate kernel scratch memory"); }
+        s.bytes = bytes;
+    }
+    *out = s.ptr;
+    return Status();
+}
+
+int32_t launch_result(cudaError_t e, const char * what) {
+    if (e == cudaSuccess) return DOOMS_OK;
+    (void)cudaGetLastError();
+    if (e == cudaErrorInvalidValue) return fail(DOOMS_UNSUPPORTED, std::string(what) + ": a type or shape the kernel does not take");
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) return fail(DOOMS_UNSUPPORTED, std::string(what) + ": no CUDA device");
+    return fail(DOOMS_INTERNAL, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+bool matrix_dtype(int32_t dt) { return dt == DOOMS_F16 || dt == DOOMS_Q4_0 || dt == DOOMS_Q5_0 || dt == DOOMS_Q8_0 || dt == DOOMS_Q4_K || dt == DOOMS_Q6_K; }
+
+}  // namespace
+
+extern "C" {
+
+DOOMS_CUDA_API const char * dooms_cuda_last_error(void) { return g_last_error.c_str(); }
+
+DOOMS_CUDA_API const char * dooms_cuda_code_name(int32_t code) {
+    switch (code) {
+        case DOOMS_OK: return "Ok";
+        case DOOMS_INVALID_ARGUMENT: return "InvalidArgument";
+        case DOOMS_NOT_FOUND: return "NotFound";
+        case DOOMS_DATA_LOSS: return "DataLoss";
+        case DOOMS_UNSUPPORTED: return "Unsupported";
+        case DOOMS_RESOURCE_EXHAUSTED: return "ResourceExhausted";
+        case DOOMS_IO_ERROR: return "IoError";
+        case DOOMS_INTERNAL: return "Internal";
+    }
+    return "Unknown";
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return n;
+}
+
+DOOMS_CUDA_API int64_t dooms_dtype_block_elems(int32_t dtype) { const DTypeInfo * i = dtype_info(dtype); return i ? i->block_elems : 0; }
+DOOMS_CUDA_API int64_t dooms_dtype_block_bytes(int32_t dtype) { const DTypeInfo * i = dtype_info(dtype); return i ? i->block_bytes : 0; }
+DOOMS_CUDA_API const char * dooms_dtype_name(int32_t dtype) { const DTypeInfo * i = dtype_info(dtype); return i ? i->name : "unknown"; }
+DOOMS_CUDA_API int32_t dooms_dtype_bytes(int32_t dtype, int64_t n, uint64_t * out) {
+    if (!dtype_valid(dtype) || !out) return fail(DOOMS_INVALID_ARGUMENT, "unknown dtype or NULL output");
+    auto r = dtype_bytes(static_cast<DType>(dtype), n);
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value();
+    return DOOMS_OK;
+}
+
+// ---------------------------------------------------------------- GGUF
+
+DOOMS_CUDA_API int32_t dooms_gguf_open(const char * path, dooms_gguf ** out) {
+    if (!path || !out) return fail(DOOMS_INVALID_ARGUMENT, "path or out is NULL");
+    auto r = GgufFile::open(path);
+    if (!r.is_ok()) return done(r.status());
+    *out = new dooms_gguf{std::make_unique<GgufFile>(std::move(r).value())};
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_parse(const void * data, size_t size, dooms_gguf ** out) {
+    if (!out) return fail(DOOMS_INVALID_ARGUMENT, "out is NULL");
+    auto r = GgufFile::parse(static_cast<const uint8_t *>(data), size);
+    if (!r.is_ok()) return done(r.status());
+    *out = new dooms_gguf{std::make_unique<GgufFile>(std::move(r).value())};
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API void dooms_gguf_close(dooms_gguf * f) { delete f; }
+DOOMS_CUDA_API uint32_t dooms_gguf_version(const dooms_gguf * f) { return f ? f->file->version() : 0; }
+DOOMS_CUDA_API uint64_t dooms_gguf_alignment(const dooms_gguf * f) { return f ? f->file->alignment() : 0; }
+DOOMS_CUDA_API int64_t dooms_gguf_tensor_count(const dooms_gguf * f) { return f ? static_cast<int64_t>(f->file->tensors().size()) : 0; }
+DOOMS_CUDA_API int32_t dooms_gguf_tensor_at(const dooms_gguf * f, int64_t index, dooms_gguf_tensor * out) {
+    if (!f || !out) return fail(DOOMS_INVALID_ARGUMENT, "file or out is NULL");
+    if (index < 0 || index >= static_cast<int64_t>(f->file->tensors().size())) return fail(DOOMS_INVALID_ARGUMENT, "tensor index out of range");
+    fill_tensor(*f->file, f->file->tensors()[static_cast<size_t>(index)], out);
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_find_tensor(const dooms_gguf * f, const char * name, dooms_gguf_tensor * out) {
+    if (!f || !name || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, name or out is NULL");
+    auto r = f->file->find_tensor(name);
+    if (!r.is_ok()) return done(r.status());
+    fill_tensor(*f->file, *r.value(), out);
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_get_string(const dooms_gguf * f, const char * key, const char ** out) {
+    if (!f || !key || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, key or out is NULL");
+    auto it = f->file->metadata().find(key);
+    auto r = f->file->get_string(key);
+    if (!r.is_ok()) return done(r.status());
+    *out = it->second.s.c_str();   // owned by the file
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_get_uint(const dooms_gguf * f, const char * key, uint64_t * out) {
+    if (!f || !key || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, key or out is NULL");
+    auto r = f->file->get_uint(key);
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value();
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_get_int(const dooms_gguf * f, const char * key, int64_t * out) {
+    if (!f || !key || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, key or out is NULL");
+    auto r = f->file->get_int(key);
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value();
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_get_float(const dooms_gguf * f, const char * key, double * out) {
+    if (!f || !key || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, key or out is NULL");
+    auto r = f->file->get_float(key);
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value();
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_gguf_get_bool(const dooms_gguf * f, const char * key, int32_t * out) {
+    if (!f || !key || !out) return fail(DOOMS_INVALID_ARGUMENT, "file, key or out is NULL");
+    auto r = f->file->get_bool(key);
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value() ? 1 : 0;
+    return DOOMS_OK;
+}
+
+// ---------------------------------------------------------------- decoder
+
+DOOMS_CUDA_API int32_t dooms_cuda_llama_create(const dooms_llama_config * config, const dooms_llama_weights * weights, const dooms_cuda_options * options,
+                                               dooms_cuda_llama ** out) {
+    int32_t code = DOOMS_OK;
+    if (!struct_ok(config, "config", &code) || !struct_ok(weights, "weights", &code)) return code;
+    if (options && !struct_ok(options, "options", &code)) return code;
+    if (!out) return fail(DOOMS_INVALID_ARGUMENT, "out is NULL");
+    LlamaDecoderConfig c;
+    c.n_layer = config->n_layer; c.n_embd = config->n_embd; c.n_head = config->n_head; c.n_head_kv = config->n_head_kv; c.head_dim = config->head_dim;
+    c.n_ff = config->n_ff; c.n_vocab = config->n_vocab; c.rope_base = config->rope_base; c.rope_neox = config->rope_neox != 0; c.rms_eps = config->rms_eps;
+    c.n_ctx = config->n_ctx; c.n_batch = config->n_batch; c.spin_wait = config->spin_wait != 0; c.prefill_tile = config->prefill_tile;
+    LlamaDecoderWeights w;
+    std::string err;
+    bool ok = ref_of(weights->token_embd, &w.token_embd, &err) && ref_of(weights->output_norm, &w.output_norm, &err) && ref_of(weights->output, &w.output, &err);
+    if (ok && weights->n_layers > 0 && !weights->layers) { ok = false; err = "weights.layers is NULL"; }
+    for (int32_t l = 0; ok && l < weights->n_layers; l++) {
+        const dooms_llama_layer_weights & s = weights->layers[l];
+        LlamaLayerWeights L;
+        ok = ref_of(s.attn_norm, &L.attn_norm, &err) && ref_of(s.attn_q, &L.attn_q, &err) && ref_of(s.attn_k, &L.attn_k, &err) && ref_of(s.attn_v, &L.attn_v, &err) &&
+             ref_of(s.attn_qkv, &L.attn_qkv, &err) && ref_of(s.attn_q_bias, &L.attn_q_bias, &err) && ref_of(s.attn_k_bias, &L.attn_k_bias, &err) &&
+             ref_of(s.attn_v_bias, &L.attn_v_bias, &err) && ref_of(s.attn_qkv_bias, &L.attn_qkv_bias, &err) && ref_of(s.attn_output, &L.attn_output, &err) &&
+             ref_of(s.ffn_norm, &L.ffn_norm, &err) && ref_of(s.ffn_gate, &L.ffn_gate, &err) && ref_of(s.ffn_up, &L.ffn_up, &err) && ref_of(s.ffn_down, &L.ffn_down, &err);
+        w.layers.push_back(L);
+    }
+    if (!ok) return fail(DOOMS_INVALID_ARGUMENT, err);
+    auto r = CudaLlamaDecoder::create(c, w, options_of(options));
+    if (!r.is_ok()) return done(r.status());
+    *out = new dooms_cuda_llama{std::move(r).value()};
+    return DOOMS_OK;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_llama_load(const char * gguf_path, const dooms_native_llama_options * options, const dooms_cuda_options * cuda_options,
+                                             dooms_cuda_llama ** out) {
+    int32_t code = DOOMS_OK;
+    if (!gguf_path || !out) return fail(DOOMS_INVALID_ARGUMENT, "gguf_path or out is NULL");
+    if (options && !struct_ok(options, "options", &code)) return code;
+    if (cuda_options && !struct_ok(cuda_options, "cuda_options", &code)) return code;
+    NativeLlamaOptions o;
+    if (options) { o.n_ctx = options->n_ctx; o.n_batch = options->n_batch; o.spin_wait = options->spin_wait != 0; o.prefill_tile = options->prefill_tile; }
+    auto r = load_native_llama(gguf_path, o, options_of(cuda_options));
+    if (!r.is_ok()) return done(r.status());
+    *out = new dooms_cuda_llama{std::move(r).value()};
+    return DOOMS_OK;
+}
+
+DOOMS_CUDA_API void dooms_cuda_llama_destroy(dooms_cuda_llama * d) { delete d; }
+
+DOOMS_CUDA_API int32_t dooms_cuda_llama_config(const dooms_cuda_llama * d, dooms_llama_config * out) {
+    if (!d || !out) return fail(DOOMS_INVALID_ARGUMENT, "decoder or out is NULL");
+    const LlamaDecoderConfig & c = d->dec->config();
+    std::memset(out, 0, sizeof *out);
+    out->struct_size = sizeof *out;
+    out->n_layer = c.n_layer; out->n_embd = c.n_embd; out->n_head = c.n_head; out->n_head_kv = c.n_head_kv; out->head_dim = c.head_dim; out->n_ff = c.n_ff;
+    out->n_vocab = c.n_vocab; out->rope_base = c.rope_base; out->rope_neox = c.rope_neox ? 1 : 0; out->rms_eps = c.rms_eps; out->n_ctx = c.n_ctx;
+    out->n_batch = c.n_batch; out->spin_wait = c.spin_wait ? 1 : 0; out->prefill_tile = c.prefill_tile;
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_position(const dooms_cuda_llama * d) { return d ? d->dec->position() : 0; }
+DOOMS_CUDA_API int32_t dooms_cuda_llama_reset(dooms_cuda_llama * d) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    d->dec->reset();
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_tokens(dooms_cuda_llama * d, const int32_t * tokens, int32_t n) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->eval_tokens(tokens, n));
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_embeddings(dooms_cuda_llama * d, const float * embeddings, int32_t n) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->eval_embeddings(embeddings, n));
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_pending_token(dooms_cuda_llama * d, int32_t * out) {
+    if (!d || !out) return fail(DOOMS_INVALID_ARGUMENT, "decoder or out is NULL");
+    auto r = d->dec->pending_token();
+    if (!r.is_ok()) return done(r.status());
+    *out = r.value();
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_logits(dooms_cuda_llama * d, float * out, int64_t capacity) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->logits_into(out, capacity));
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_generate(dooms_cuda_llama * d, int32_t max_tokens, int32_t depth, dooms_token_callback callback, void * user) {
+    if (!d || !callback) return fail(DOOMS_INVALID_ARGUMENT, "decoder or callback is NULL");
+    return done(d->dec->generate(max_tokens, depth, [&](int32_t tok) { return callback(tok, user) != 0; }));
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_profile_pass(dooms_cuda_llama * d, int32_t rows, dooms_kernel_time * out, int32_t capacity, int32_t * count) {
+    if (!d || !count) return fail(DOOMS_INVALID_ARGUMENT, "decoder or count is NULL");
+    auto r = d->dec->profile_pass(rows);
+    if (!r.is_ok()) return done(r.status());
+    const auto & v = r.value();
+    if (static_cast<int32_t>(v.size()) > capacity || (!out && !v.empty())) {
+        *count = static_cast<int32_t>(v.size());
+        return fail(DOOMS_RESOURCE_EXHAUSTED, "profile_pass needs room for " + std::to_string(v.size()) + " entries");
+    }
+    for (size_t i = 0; i < v.size(); i++) out[i] = dooms_kernel_time{v[i].kind, v[i].dispatches, v[i].gpu_ms};
+    *count = static_cast<int32_t>(v.size());
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, dooms_cuda_timings * out) {
+    int32_t code = DOOMS_OK;
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    if (!struct_ok(out, "out", &code)) return code;
+    const CudaLlamaDecoder::Timings t = d->dec->timings();
+    out->last_eval_ms = t.last_eval_ms; out->last_generate_ms = t.last_generate_ms; out->last_eval_launches = t.last_eval_launches;
+    out->last_generate_launches = t.last_generate_launches; out->weight_bytes = t.weight_bytes; out->kv_bytes = t.kv_bytes;
+    return DOOMS_OK;
+}
+
+// ---------------------------------------------------------------- single kernels
+
+DOOMS_CUDA_API int32_t dooms_cuda_dequantize(int32_t dtype, const void * d_blocks, int64_t rows, int64_t cols, float * d_out, void * stream) {
+    if (!matrix_dtype(dtype)) return fail(DOOMS_UNSUPPORTED, "dequantize takes f16, q4_0, q5_0, q8_0, q4_K and q6_K");
+    if (!d_blocks || !d_out || rows < 0 || cols < 1 || cols % dooms_dtype_block_elems(dtype) != 0 || cols > INT32_MAX) {
+        return fail(DOOMS_INVALID_ARGUMENT, "dequantize: NULL pointer or rows that are not whole blocks");
+    }
+    if (rows == 0) return DOOMS_OK;
+    return launch_result(cuda::launch_dequantize(dtype, d_blocks, rows, cols, d_out, static_cast<cudaStream_t>(stream)), "dequantize");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const float * d_x, float * d_y, const float * d_bias, int64_t rows, int64_t cols,
+                                         uint32_t flags, void * stream) {
+    if (!matrix_dtype(dtype)) return fail(DOOMS_UNSUPPORTED, "matvec takes f16, q4_0, q5_0, q8_0, q4_K and q6_K");
+    if (!d_w || !d_x || !d_y || rows < 0 || cols < 32 || cols % 32 != 0 || cols % dooms_dtype_block_elems(dtype) != 0 || cols > INT32_MAX ||
+        ((flags & cuda::kFlagBias) && !d_bias) || (flags & ~(cuda::kFlagAccumulate | cuda::kFlagBias))) {
+        return fail(DOOMS_INVALID_ARGUMENT, "matvec: NULL pointer, unknown flag, or rows that are not whole blocks of at least 32 elements");
+    }
+    if (rows == 0) return DOOMS_OK;
+    return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, static_cast<cudaStream_t>(stream)), "matvec");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
+                                          void * stream) {
+    if (!matrix_dtype(dtype)) return fail(DOOMS_UNSUPPORTED, "gate_up takes f16, q4_0, q5_0, q8_0, q4_K and q6_K");
+    if (!d_wg || !d_wu || !d_x || !d_h || rows < 0 || cols < 32 || cols % 32 != 0 || cols % dooms_dtype_block_elems(dtype) != 0 || cols > INT32_MAX) {
+        return fail(DOOMS_INVALID_ARGUMENT, "gate_up: NULL pointer or rows that are not whole blocks of at least 32 elements");
+    }
+    if (rows == 0) return DOOMS_OK;
+    return launch_result(cuda::launch_gate_up(dtype, d_wg, d_wu, d_x, d_h, rows, cols, static_cast<cudaStream_t>(stream)), "gate_up");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream) {
+    if (!d_x || !d_gamma || !d_out || rows < 0 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX || !(eps > 0.f)) {
+        return fail(DOOMS_INVALID_ARGUMENT, "rms_norm: NULL pointer, bad shape or eps <= 0");
+    }
+    if (rows == 0) return DOOMS_OK;
+    return launch_result(cuda::launch_rms_norm(d_x, d_gamma, d_out, nullptr, int(rows), int(cols), eps, static_cast<cudaStream_t>(stream)), "rms_norm");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_argmax(const float * d_logits, int64_t n, int32_t * d_out, void * stream) {
+    if (!d_logits || !d_out || n < 1 || n > INT32_MAX) return fail(DOOMS_INVALID_ARGUMENT, "argmax: NULL pointer or n outside [1, 2^31)");
+    void * part = nullptr;
+    const Status st = scratch_for(size_t(cuda::argmax_blocks(n)) * 8, &part);
+    if (!st.is_ok()) return done(st);
+    return launch_result(cuda::launch_argmax_plain(d_logits, n, d_out, part, static_cast<cudaStream_t>(stream)), "argmax");
+}
+
+DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_t head_dim, int32_t n_keys) {
+    if (n_head < 1 || head_dim < 1 || n_keys < 1) return 0;
+    return int64_t(cuda::attention_splits(n_head, n_keys)) * n_head * (2 + head_dim) * 4;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void * d_kc, const void * d_vc, float * d_out, void * d_scratch, int32_t n_head,
+                                                   int32_t n_head_kv, int32_t head_dim, int32_t n_keys, void * stream) {
+    if (!d_q || !d_kc || !d_vc || !d_out || !d_scratch || n_head < 1 || n_head_kv < 1 || n_head % n_head_kv != 0 || n_keys < 1) {
+        return fail(DOOMS_INVALID_ARGUMENT, "attention_decode: NULL pointer or bad head counts");
+    }
+    if (head_dim < 4 || head_dim > 256 || (head_dim & (head_dim - 1)) != 0) return fail(DOOMS_UNSUPPORTED, "attention_decode: head_dim must be a power of two in [4, 256]");
+    const cuda::AttnShape s{n_head, n_head_kv, head_dim, n_head * head_dim, n_head_kv * head_dim, n_head * head_dim, 0, 10000.f};
+    const int splits = cuda::attention_splits(n_head, n_keys);
+    return launch_result(cuda::launch_attention_decode(d_q, d_kc, d_vc, d_out, static_cast<float *>(d_scratch), nullptr, n_keys, splits, s,
+                                                       static_cast<cudaStream_t>(stream)), "attention_decode");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_nccl_unique_id(const char * nccl_library, void * out128) {
+    if (!out128) return fail(DOOMS_INVALID_ARGUMENT, "out128 is NULL");
+    static NcclApi api;
+    const Status st = load_nccl(nccl_library, &api);
+    if (!st.is_ok()) return done(st);
+    NcclUniqueId id;
+    const int rc = api.GetUniqueId(&id);
+    if (rc != 0) return fail(DOOMS_INTERNAL, std::string("ncclGetUniqueId: ") + api.GetErrorString(rc));
+    std::memcpy(out128, &id, sizeof id);
+    return DOOMS_OK;
+}
+
+}  // extern "C"

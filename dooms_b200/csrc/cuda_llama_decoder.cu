@@ -1,0 +1,718 @@
+#include "cuda_llama_decoder.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <deque>
+#include <string>
+#include <utility>
+
+#include "kernels/kernels.h"
+#include "nccl_dyn.h"
+
+namespace dooms {
+
+using cuda::AttnShape;
+using cuda::DevState;
+using cuda::kFlagAccumulate;
+using cuda::kFlagBias;
+
+namespace {
+
+constexpr size_t kWeightAlign = 256;   // offset alignment of each tensor inside the weight buffer
+constexpr size_t kWeightTail = 256;    // slack after the last tensor: kernels that read rows as 16-byte spans may run a few bytes past a matrix
+constexpr int kMaxHeadDim = 256;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool is_matrix_type(DType t) {
+    return t == DType::F16 || t == DType::Q4_0 || t == DType::Q5_0 || t == DType::Q8_0 || t == DType::Q4_K || t == DType::Q6_K;
+}
+
+std::string cuda_msg(const char * what, cudaError_t e) { return std::string(what) + ": " + cudaGetErrorString(e); }
+
+// A matrix in the device weight buffer.
+struct MatDev {
+    const uint8_t * ptr = nullptr;
+    DType dt = DType::F16;
+    int64_t rows = 0, cols = 0;
+    int64_t bytes() const { return rows * static_cast<int64_t>(dtype_bytes(dt, cols).value()); }
+};
+// q, k and v are one concatenated matrix when they share a type; otherwise one part each (rows row0.. of the qkv output).
+struct QkvPart { MatDev w; int32_t row0 = 0; };
+struct LayerDev {
+    const float * attn_norm = nullptr, * ffn_norm = nullptr, * qkv_bias = nullptr;
+    std::vector<QkvPart> qkv;
+    MatDev attn_output, ffn_gate, ffn_up, ffn_down;
+};
+
+float half_bits_to_float(uint16_t h) { __half v; std::memcpy(&v, &h, 2); return __half2float(v); }
+
+}  // namespace
+
+struct CudaLlamaDecoder::Impl {
+    LlamaDecoderConfig cfg;
+    CudaOptions opt;
+    int tp = 1, rank = 0;
+    // this rank's share
+    int32_t nh = 0, nkv = 0, q_width = 0, kv_width = 0, qkv_width = 0, ff = 0, vocab_rows = 0, vocab_row0 = 0, vocab_stride = 0;
+    cudaStream_t stream = nullptr;
+    uint8_t * weights = nullptr;
+    size_t weight_bytes = 0, matrix_bytes = 0;
+    MatDev token_embd, output;
+    const float * output_norm = nullptr;
+    std::vector<LayerDev> layers;
+    __half * kc = nullptr, * vc = nullptr;
+    size_t cache_layer_elems = 0, kv_bytes = 0;
+    float * x = nullptr, * xn = nullptr, * qkv = nullptr, * attn = nullptr, * h = nullptr, * red = nullptr, * logits_buf = nullptr, * part = nullptr;
+    void * argmax_part = nullptr;
+    int32_t * tokens = nullptr, * in_tokens = nullptr, * host_tokens = nullptr, * host_in = nullptr;
+    float * host_x = nullptr;     // pinned staging for eval_embeddings
+    DevState * state = nullptr;
+    int splits = 1;
+    int32_t pos = 0;
+    bool has_pending = false;
+    // decode graph
+    cudaGraphExec_t step_graph = nullptr;
+    std::vector<cudaEvent_t> step_events;
+    cudaEvent_t ev_a = nullptr, ev_b = nullptr;
+    Timings tm;
+    int64_t launches = 0;
+    // profiling
+    std::vector<CudaLlamaDecoder::KernelTime> * profile = nullptr;
+    // tensor parallelism
+    NcclApi nccl;
+    NcclComm comm = nullptr;
+    Status failed;   // the first device error; every later call returns it
+
+    ~Impl() {
+        if (stream) cudaStreamSynchronize(stream);
+        if (comm) nccl.CommDestroy(comm);
+        if (step_graph) cudaGraphExecDestroy(step_graph);
+        for (cudaEvent_t e : step_events) cudaEventDestroy(e);
+        if (ev_a) cudaEventDestroy(ev_a);
+        if (ev_b) cudaEventDestroy(ev_b);
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part,
+                         argmax_part, (void *)tokens, (void *)in_tokens, (void *)state}) {
+            if (p) cudaFree(p);
+        }
+        for (void * p : {(void *)host_tokens, (void *)host_in, (void *)host_x}) if (p) cudaFreeHost(p);
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    Status check(cudaError_t e, const char * what) {
+        if (e == cudaSuccess) return Status();
+        Status st = internal_error(cuda_msg(what, e));
+        if (failed.is_ok()) failed = st;
+        return st;
+    }
+
+    Status wait_idle() {
+        if (!failed.is_ok()) return failed;
+        return check(cudaStreamSynchronize(stream), "a CUDA kernel of the decoder failed");
+    }
+
+    // Every launch goes through here: counted, and timed on its own when a profile is being taken.
+    template <class F>
+    void run(const char * kind, F && f) {
+        if (!failed.is_ok()) return;
+        if (profile) {
+            cudaEventRecord(ev_a, stream);
+            const cudaError_t e = f();
+            cudaEventRecord(ev_b, stream);
+            cudaEventSynchronize(ev_b);
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev_a, ev_b);
+            (void)check(e, kind);
+            for (auto & k : *profile) if (std::strcmp(k.kind, kind) == 0) { k.dispatches++; k.gpu_ms += ms; return; }
+            profile->push_back({kind, 1, ms});
+            return;
+        }
+        launches++;
+        (void)check(f(), kind);
+    }
+
+    AttnShape attn_shape() const {
+        return AttnShape{nh, nkv, cfg.head_dim, qkv_width, kv_width, q_width, cfg.rope_neox ? 1 : 0, cfg.rope_base};
+    }
+
+    void all_reduce(float * buf, size_t count) {
+        if (tp == 1) return;
+        run("all_reduce", [&] { return nccl.AllReduce(buf, buf, count, NcclApi::kFloat32, NcclApi::kSum, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown; });
+    }
+
+    void matvec(const char * kind, const MatDev & w, const float * in, float * out, const float * bias, uint32_t flags) {
+        run(kind, [&] { return cuda::launch_matvec(int(w.dt), w.ptr, in, out, bias, w.rows, w.cols, flags, stream); });
+    }
+    void matmul(const char * kind, const MatDev & w, const MatDev * w2, const float * in, int64_t in_stride, float * out, int64_t out_stride, const float * bias, int M,
+                uint32_t flags) {
+        run(kind, [&] { return cuda::launch_matmul_tile(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, in, in_stride, out, out_stride, bias, M, w.rows, w.cols, flags, stream); });
+    }
+    // x += partial sums of the other ranks' shares: with one GPU the projection accumulated into x directly.
+    void reduce_into_x(int M) {
+        if (tp == 1) return;
+        const size_t n = size_t(M) * size_t(cfg.n_embd);
+        all_reduce(red, n);
+        run("residual", [&] { return cuda::launch_add(x, red, int64_t(n), stream); });
+    }
+
+    // All layers for M positions starting at state->pos whose input rows are in x; then the logits and the greedy token of the last row
+    // (encode_forward, metal_llama_decoder.mm:311-385).
+    void forward(int M, bool advance) {
+        const int E = cfg.n_embd;
+        const AttnShape as = attn_shape();
+        const bool single = tp == 1;
+        for (size_t l = 0; l < layers.size(); l++) {
+            const LayerDev & L = layers[l];
+            __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
+            float * o_dst = single ? x : red;
+            const uint32_t o_flags = single ? kFlagAccumulate : 0u;
+            run("norm", [&] { return cuda::launch_rms_norm(x, L.attn_norm, xn, nullptr, M, E, cfg.rms_eps, stream); });
+            if (M == 1) {
+                for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
+                run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, state, 0, splits, as, stream); });
+                matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
+                reduce_into_x(1);
+                run("norm", [&] { return cuda::launch_rms_norm(x, L.ffn_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
+                run("gate_up", [&] { return cuda::launch_gate_up(int(L.ffn_gate.dt), L.ffn_gate.ptr, L.ffn_up.ptr, xn, h, L.ffn_gate.rows, L.ffn_gate.cols, stream); });
+                matvec("ffn_down", L.ffn_down, h, o_dst, nullptr, o_flags);
+                reduce_into_x(1);
+            } else {
+                for (const QkvPart & q : L.qkv) {
+                    matmul("qkv", q.w, nullptr, xn, E, qkv + q.row0, qkv_width, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, L.qkv_bias ? kFlagBias : 0u);
+                }
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
+                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, state, M, as, stream); });
+                matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
+                reduce_into_x(M);
+                run("norm", [&] { return cuda::launch_rms_norm(x, L.ffn_norm, xn, nullptr, M, E, cfg.rms_eps, stream); });
+                matmul("gate_up", L.ffn_gate, &L.ffn_up, xn, E, h, ff, nullptr, M, 0u);
+                matmul("ffn_down", L.ffn_down, nullptr, h, ff, o_dst, E, nullptr, M, o_flags);
+                reduce_into_x(M);
+            }
+        }
+        // The logits of the last row only (metal_llama_decoder.mm:375).
+        run("norm", [&] { return cuda::launch_rms_norm(x + size_t(M - 1) * E, output_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
+        if (output.rows > 0) matvec("output", output, xn, logits_buf + vocab_row0, nullptr, 0u);
+        if (tp > 1) {
+            run("all_gather", [&] {
+                return nccl.AllGather(logits_buf + vocab_row0, logits_buf, size_t(vocab_stride), NcclApi::kFloat32, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown;
+            });
+        }
+        run("argmax", [&] { return cuda::launch_argmax(logits_buf, int64_t(vocab_stride) * tp, tokens, host_tokens, state, argmax_part, advance ? 1 : 0, stream); });
+    }
+
+    void embed(const int32_t * ids, const int32_t * index, int rows) {
+        run("embed", [&] { return cuda::launch_embed(int(token_embd.dt), token_embd.ptr, ids, index, x, rows, cfg.n_embd, stream); });
+    }
+
+    // One chunk whose rows are in x (or whose ids are in in_tokens); the last row's greedy token lands in tokens[0] (run_chunk, metal_llama_decoder.mm:402-414).
+    void run_chunk(int rows, bool from_tokens) {
+        run("state", [&] { return cuda::launch_set_state(state, pos, 0, 0, stream); });
+        if (from_tokens) embed(in_tokens, nullptr, rows);
+        forward(rows, false);
+        pos += rows;
+        has_pending = true;
+    }
+
+    // One decode step: embeds tokens[state->tok_in], writes its greedy token to tokens[state->tok_out], advances the state.
+    void decode_step_launches() {
+        embed(tokens, &state->tok_in, 1);
+        forward(1, true);
+    }
+
+    Status ensure_step_graph() {
+        if (step_graph || !opt.use_graphs) return Status();
+        DOOMS_RETURN_IF_ERROR(wait_idle());
+        const int64_t before = launches;
+        cudaGraph_t graph = nullptr;
+        DOOMS_RETURN_IF_ERROR(check(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture"));
+        decode_step_launches();
+        const cudaError_t e = cudaStreamEndCapture(stream, &graph);
+        step_launches = launches - before;
+        launches = before;
+        if (!failed.is_ok()) { if (graph) cudaGraphDestroy(graph); return failed; }
+        DOOMS_RETURN_IF_ERROR(check(e, "cudaStreamEndCapture"));
+        const cudaError_t ie = cudaGraphInstantiate(&step_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        return check(ie, "cudaGraphInstantiate");
+    }
+    int64_t step_launches = 0;
+
+    void queue_decode_step() {
+        if (step_graph) {
+            launches += step_launches;
+            (void)check(cudaGraphLaunch(step_graph, stream), "cudaGraphLaunch");
+        } else {
+            decode_step_launches();
+        }
+    }
+};
+
+namespace cuda {
+cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream);
+}
+
+CudaLlamaDecoder::CudaLlamaDecoder(std::unique_ptr<Impl> impl) : impl_(std::move(impl)) {}
+CudaLlamaDecoder::~CudaLlamaDecoder() = default;
+
+const LlamaDecoderConfig & CudaLlamaDecoder::config() const { return impl_->cfg; }
+int32_t CudaLlamaDecoder::position() const { return impl_->pos; }
+CudaLlamaDecoder::Timings CudaLlamaDecoder::timings() const { return impl_->tm; }
+
+Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDecoderConfig & c, const LlamaDecoderWeights & w, const CudaOptions & opt) {
+    // The argument checks of the reference's create (metal_llama_decoder.mm:426-494), in its order and with its codes.
+    if (c.n_layer < 1 || c.n_embd < 4 || c.n_head < 1 || c.n_head_kv < 1 || c.head_dim < 2 || c.n_ff < 4 || c.n_vocab < 1 || c.n_ctx < 1 || c.n_batch < 1 ||
+        !(c.rope_base > 0.f) || !(c.rms_eps > 0.f)) {
+        return invalid_argument("llama decoder config: every size must be positive, rope_base and rms_eps > 0");
+    }
+    if (c.n_head % c.n_head_kv != 0) return invalid_argument("n_head must be a multiple of n_head_kv");
+    if (c.prefill_tile < 0 || c.prefill_tile > 2) return invalid_argument("prefill_tile must be 0 (automatic), 1 (CUDA-core tiles) or 2 (tensor-core tiles)");
+    if (c.head_dim < 4 || c.head_dim > kMaxHeadDim || (c.head_dim & (c.head_dim - 1)) != 0) {
+        return unsupported("head_dim must be a power of two in [4, " + std::to_string(kMaxHeadDim) + "], got " + std::to_string(c.head_dim));
+    }
+    if (c.n_embd % 4 != 0 || c.n_ff % 4 != 0 || (c.n_head * c.head_dim) % 4 != 0) return unsupported("n_embd, n_ff and n_head*head_dim must be multiples of 4");
+    if (static_cast<int64_t>(w.layers.size()) != c.n_layer) {
+        return invalid_argument("expected " + std::to_string(c.n_layer) + " layers of weights, got " + std::to_string(w.layers.size()));
+    }
+    if (opt.tp_size < 1 || opt.tp_rank < 0 || opt.tp_rank >= opt.tp_size) return invalid_argument("tp_rank must be in [0, tp_size)");
+
+    const int64_t E = c.n_embd, F = c.n_ff, V = c.n_vocab, Qw = int64_t(c.n_head) * c.head_dim, KVw = int64_t(c.n_head_kv) * c.head_dim;
+    auto check = [](const WeightRef & r, int64_t rows, int64_t cols, bool matrix, const std::string & name) -> Status {
+        if (!r.data) return invalid_argument("weight '" + name + "' is missing");
+        if (r.rows != rows || r.cols != cols) {
+            return invalid_argument("weight '" + name + "' is " + std::to_string(r.rows) + "x" + std::to_string(r.cols) + ", expected " + std::to_string(rows) + "x" +
+                                    std::to_string(cols));
+        }
+        if (!dtype_valid(static_cast<int32_t>(r.dtype))) return invalid_argument("weight '" + name + "' has an unknown dtype");
+        if (matrix && !is_matrix_type(r.dtype)) {
+            return unsupported("weight '" + name + "' is " + dtype_name(r.dtype) + "; the CUDA decoder takes f16, q4_0, q5_0, q8_0, q4_K and q6_K matrices");
+        }
+        if (matrix && r.cols % dtype_block_elems(r.dtype) != 0) return invalid_argument("weight '" + name + "' rows are not whole " + dtype_name(r.dtype) + " blocks");
+        if (matrix && r.dtype == DType::F16 && r.cols % 32 != 0) return unsupported("f16 weight '" + name + "' needs rows that are a multiple of 32 elements");
+        if (!matrix && r.dtype != DType::F32 && r.dtype != DType::F16) return unsupported("norm '" + name + "' is " + dtype_name(r.dtype) + "; expected f32 or f16");
+        return Status();
+    };
+    Status st = check(w.token_embd, V, E, true, "token_embd");
+    if (st.is_ok()) st = check(w.output_norm, 1, E, false, "output_norm");
+    if (st.is_ok()) st = check(w.output, V, E, true, "output");
+    for (int32_t l = 0; l < c.n_layer && st.is_ok(); l++) {
+        const LlamaLayerWeights & L = w.layers[size_t(l)];
+        const std::string b = "blk." + std::to_string(l) + ".";
+        st = check(L.attn_norm, 1, E, false, b + "attn_norm");
+        if (st.is_ok()) {
+            if (L.attn_qkv.data) st = check(L.attn_qkv, Qw + 2 * KVw, E, true, b + "attn_qkv");
+            else {
+                st = check(L.attn_q, Qw, E, true, b + "attn_q");
+                if (st.is_ok()) st = check(L.attn_k, KVw, E, true, b + "attn_k");
+                if (st.is_ok()) st = check(L.attn_v, KVw, E, true, b + "attn_v");
+            }
+        }
+        if (st.is_ok()) {
+            const bool split = L.attn_q_bias.data || L.attn_k_bias.data || L.attn_v_bias.data;
+            if (split && L.attn_qkv_bias.data) st = invalid_argument(b + "attn: give attn_qkv_bias or attn_q/k/v_bias, not both");
+            else if (L.attn_qkv_bias.data) st = check(L.attn_qkv_bias, 1, Qw + 2 * KVw, false, b + "attn_qkv_bias");
+            else if (split) {
+                st = check(L.attn_q_bias, 1, Qw, false, b + "attn_q_bias");
+                if (st.is_ok()) st = check(L.attn_k_bias, 1, KVw, false, b + "attn_k_bias");
+                if (st.is_ok()) st = check(L.attn_v_bias, 1, KVw, false, b + "attn_v_bias");
+            }
+        }
+        if (st.is_ok()) st = check(L.attn_output, E, Qw, true, b + "attn_output");
+        if (st.is_ok()) st = check(L.ffn_norm, 1, E, false, b + "ffn_norm");
+        if (st.is_ok()) st = check(L.ffn_gate, F, E, true, b + "ffn_gate");
+        if (st.is_ok()) st = check(L.ffn_up, F, E, true, b + "ffn_up");
+        if (st.is_ok()) st = check(L.ffn_down, E, F, true, b + "ffn_down");
+        if (st.is_ok() && L.ffn_gate.dtype != L.ffn_up.dtype) {
+            st = unsupported(b + "ffn_gate is " + dtype_name(L.ffn_gate.dtype) + " and ffn_up " + dtype_name(L.ffn_up.dtype) + "; the fused gate/up kernel takes one type");
+        }
+    }
+    if (!st.is_ok()) return st;
+
+    // This rank's share under tensor parallelism: whole heads, and column shards that are whole blocks.
+    const int tp = opt.tp_size;
+    if (c.n_head % tp != 0 || c.n_head_kv % tp != 0 || c.n_ff % tp != 0) {
+        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs needs n_head, n_head_kv and n_ff to be multiples of it");
+    }
+    for (const LlamaLayerWeights & L : w.layers) {
+        if ((Qw / tp) % dtype_block_elems(L.attn_output.dtype) != 0 || (F / tp) % dtype_block_elems(L.ffn_down.dtype) != 0) {
+            return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs would cut attn_output or ffn_down inside a quantization block");
+        }
+    }
+
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) { (void)cudaGetLastError(); return unsupported("no CUDA device"); }
+    if (opt.device < 0 || opt.device >= n_dev) return invalid_argument("CUDA device " + std::to_string(opt.device) + " does not exist");
+    if (cudaSetDevice(opt.device) != cudaSuccess) return unsupported(cuda_msg("cannot use the CUDA device", cudaGetLastError()));
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, opt.device) != cudaSuccess) return unsupported("cannot query the CUDA device");
+    if (prop.major != 10) return unsupported(std::string("the kernels are built for sm_100a (B200); device is ") + prop.name);
+
+    auto impl = std::make_unique<Impl>();
+    Impl & m = *impl;
+    m.cfg = c;
+    m.opt = opt;
+    m.tp = tp;
+    m.rank = opt.tp_rank;
+    m.nh = c.n_head / tp;
+    m.nkv = c.n_head_kv / tp;
+    m.q_width = m.nh * c.head_dim;
+    m.kv_width = m.nkv * c.head_dim;
+    m.qkv_width = m.q_width + 2 * m.kv_width;
+    m.ff = c.n_ff / tp;
+    m.vocab_stride = int32_t((V + tp - 1) / tp);
+    m.vocab_row0 = m.vocab_stride * m.rank;
+    m.vocab_rows = int32_t(std::max<int64_t>(0, std::min<int64_t>(m.vocab_stride, V - m.vocab_row0)));
+
+    if (cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking) != cudaSuccess) return internal_error(cuda_msg("cudaStreamCreate", cudaGetLastError()));
+    cudaEventCreate(&m.ev_a);
+    cudaEventCreate(&m.ev_b);
+
+    if (tp > 1) {
+        if (!opt.nccl_unique_id) return invalid_argument("tp_size > 1 needs the group's nccl_unique_id");
+        DOOMS_RETURN_IF_ERROR(load_nccl(opt.nccl_library, &m.nccl));
+        NcclUniqueId id;
+        std::memcpy(&id, opt.nccl_unique_id, sizeof id);
+        const int rc = m.nccl.CommInitRank(&m.comm, tp, id, m.rank);
+        if (rc != 0) return internal_error(std::string("ncclCommInitRank: ") + m.nccl.GetErrorString(rc));
+    }
+
+    // ---- the packed weight buffer: matrices as they are in the file (this rank's rows / column blocks), norms and biases as f32 ----
+    struct Piece { const WeightRef * src; int64_t row0, rows, col0, cols; };   // a slice of a host tensor
+    struct Plan { size_t off; std::vector<Piece> pieces; bool vector; };
+    std::vector<Plan> plans;
+    size_t total = 0;
+    auto reserve = [&](size_t bytes) { const size_t off = total; total = align_up(total + bytes, kWeightAlign); return off; };
+    auto piece_bytes = [](const Piece & p) { return size_t(p.rows) * size_t(dtype_bytes(p.src->dtype, p.cols).value()); };
+    auto plan_mat = [&](std::vector<Piece> pieces, MatDev * out) {
+        size_t bytes = 0;
+        int64_t rows = 0;
+        for (const Piece & p : pieces) { bytes += piece_bytes(p); rows += p.rows; }
+        const size_t off = reserve(bytes);
+        out->ptr = reinterpret_cast<const uint8_t *>(off);   // an offset until the buffer exists
+        out->dt = pieces[0].src->dtype;
+        out->rows = rows;
+        out->cols = pieces[0].cols;
+        m.matrix_bytes += bytes;
+        plans.push_back({off, std::move(pieces), false});
+    };
+    auto plan_vec = [&](std::vector<Piece> pieces, const float ** out) {
+        int64_t n = 0;
+        for (const Piece & p : pieces) n += p.cols;
+        const size_t off = reserve(size_t(n) * sizeof(float));
+        *out = reinterpret_cast<const float *>(off);
+        plans.push_back({off, std::move(pieces), true});
+    };
+    auto whole = [](const WeightRef & r) { return Piece{&r, 0, r.rows, 0, r.cols}; };
+    auto rows_of = [](const WeightRef & r, int64_t row0, int64_t rows) { return Piece{&r, row0, rows, 0, r.cols}; };
+    auto cols_of = [](const WeightRef & r, int64_t col0, int64_t cols) { return Piece{&r, 0, r.rows, col0, cols}; };
+
+    plan_mat({whole(w.token_embd)}, &m.token_embd);
+    const bool tied = w.output.data == w.token_embd.data && w.output.dtype == w.token_embd.dtype;
+    if (tied) {
+        m.output = m.token_embd;   // the rank's vocabulary rows are addressed inside the table below
+    } else if (m.vocab_rows > 0) {
+        plan_mat({rows_of(w.output, m.vocab_row0, m.vocab_rows)}, &m.output);
+    }
+    plan_vec({whole(w.output_norm)}, &m.output_norm);
+    m.layers.resize(size_t(c.n_layer));
+    const int64_t ql = m.q_width, kvl = m.kv_width, q0 = int64_t(m.rank) * ql, kv0 = int64_t(m.rank) * kvl;
+    for (int32_t l = 0; l < c.n_layer; l++) {
+        const LlamaLayerWeights & L = w.layers[size_t(l)];
+        LayerDev & o = m.layers[size_t(l)];
+        plan_vec({whole(L.attn_norm)}, &o.attn_norm);
+        if (L.attn_qkv.data) {
+            QkvPart p;
+            plan_mat({rows_of(L.attn_qkv, q0, ql), rows_of(L.attn_qkv, Qw + kv0, kvl), rows_of(L.attn_qkv, Qw + KVw + kv0, kvl)}, &p.w);
+            o.qkv.push_back(p);
+        } else if (L.attn_q.dtype == L.attn_k.dtype && L.attn_k.dtype == L.attn_v.dtype) {
+            QkvPart p;
+            plan_mat({rows_of(L.attn_q, q0, ql), rows_of(L.attn_k, kv0, kvl), rows_of(L.attn_v, kv0, kvl)}, &p.w);
+            o.qkv.push_back(p);
+        } else {
+            QkvPart a, b, d;
+            plan_mat({rows_of(L.attn_q, q0, ql)}, &a.w);
+            plan_mat({rows_of(L.attn_k, kv0, kvl)}, &b.w);
+            plan_mat({rows_of(L.attn_v, kv0, kvl)}, &d.w);
+            a.row0 = 0; b.row0 = int32_t(ql); d.row0 = int32_t(ql + kvl);
+            o.qkv.push_back(a); o.qkv.push_back(b); o.qkv.push_back(d);
+        }
+        if (L.attn_qkv_bias.data) {
+            plan_vec({cols_of(L.attn_qkv_bias, q0, ql), cols_of(L.attn_qkv_bias, Qw + kv0, kvl), cols_of(L.attn_qkv_bias, Qw + KVw + kv0, kvl)}, &o.qkv_bias);
+        } else if (L.attn_q_bias.data) {
+            plan_vec({cols_of(L.attn_q_bias, q0, ql), cols_of(L.attn_k_bias, kv0, kvl), cols_of(L.attn_v_bias, kv0, kvl)}, &o.qkv_bias);
+        }
+        plan_mat({cols_of(L.attn_output, q0, ql)}, &o.attn_output);
+        plan_vec({whole(L.ffn_norm)}, &o.ffn_norm);
+        plan_mat({rows_of(L.ffn_gate, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_gate);
+        plan_mat({rows_of(L.ffn_up, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_up);
+        plan_mat({cols_of(L.ffn_down, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_down);
+    }
+    total += kWeightTail;
+    m.weight_bytes = total;
+
+    auto dev_alloc = [&](void ** p, size_t bytes, const char * what) -> Status {
+        const cudaError_t e = cudaMalloc(p, std::max<size_t>(bytes, 16));
+        if (e != cudaSuccess) { (void)cudaGetLastError(); return resource_exhausted(std::string("could not allocate ") + std::to_string(bytes) + " bytes for " + what); }
+        return Status();
+    };
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.weights), total, "the decoder weights"));
+    cudaMemset(m.weights + total - kWeightTail, 0, kWeightTail);
+    auto fix = [&](MatDev & d) { d.ptr = m.weights + reinterpret_cast<size_t>(d.ptr); };
+    auto fixv = [&](const float *& p) { p = reinterpret_cast<const float *>(m.weights + reinterpret_cast<size_t>(p)); };
+    fix(m.token_embd);
+    if (tied) {
+        m.output = m.token_embd;
+        m.output.ptr += size_t(m.vocab_row0) * size_t(dtype_bytes(m.output.dt, E).value());
+        m.output.rows = m.vocab_rows;
+    } else if (m.vocab_rows > 0) fix(m.output);
+    fixv(m.output_norm);
+    for (LayerDev & o : m.layers) {
+        fixv(o.attn_norm); fixv(o.ffn_norm);
+        if (o.qkv_bias) fixv(o.qkv_bias);
+        for (QkvPart & p : o.qkv) fix(p.w);
+        fix(o.attn_output); fix(o.ffn_gate); fix(o.ffn_up); fix(o.ffn_down);
+    }
+    // qkv_bias == offset 0 cannot happen (token_embd is first), so a null pointer still means "no bias".
+
+    std::vector<float> vec_tmp;
+    for (const Plan & pl : plans) {
+        uint8_t * dst = m.weights + pl.off;
+        for (const Piece & p : pl.pieces) {
+            const WeightRef & r = *p.src;
+            cudaError_t e = cudaSuccess;
+            if (pl.vector) {
+                vec_tmp.resize(size_t(p.cols));
+                for (int64_t i = 0; i < p.cols; i++) {
+                    const uint8_t * s = static_cast<const uint8_t *>(r.data);
+                    if (r.dtype == DType::F32) std::memcpy(&vec_tmp[size_t(i)], s + (p.col0 + i) * 4, 4);
+                    else { uint16_t hb; std::memcpy(&hb, s + (p.col0 + i) * 2, 2); vec_tmp[size_t(i)] = half_bits_to_float(hb); }
+                }
+                e = cudaMemcpy(dst, vec_tmp.data(), size_t(p.cols) * 4, cudaMemcpyHostToDevice);
+                dst += size_t(p.cols) * 4;
+            } else {
+                const size_t src_row = size_t(dtype_bytes(r.dtype, r.cols).value()), width = size_t(dtype_bytes(r.dtype, p.cols).value());
+                const size_t col_off = size_t(dtype_bytes(r.dtype, p.col0).value());
+                const uint8_t * s = static_cast<const uint8_t *>(r.data) + size_t(p.row0) * src_row + col_off;
+                if (width == src_row) e = cudaMemcpy(dst, s, width * size_t(p.rows), cudaMemcpyHostToDevice);
+                else e = cudaMemcpy2D(dst, width, s, src_row, width, size_t(p.rows), cudaMemcpyHostToDevice);
+                dst += width * size_t(p.rows);
+            }
+            if (e != cudaSuccess) return internal_error(cuda_msg("copying the weights to the device", e));
+        }
+    }
+
+    // ---- activations for the largest chunk, the KV cache, the logits and the token ring ----
+    const size_t B = size_t(c.n_batch);
+    m.cache_layer_elems = size_t(c.n_ctx) * size_t(m.kv_width);
+    m.kv_bytes = 2 * size_t(c.n_layer) * m.cache_layer_elems * sizeof(__half);
+    m.splits = cuda::attention_splits(m.nh, c.n_ctx);
+    const size_t part_floats = size_t(m.splits) * size_t(m.nh) * size_t(2 + c.head_dim);
+    const size_t logits_floats = size_t(m.vocab_stride) * size_t(tp);
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.kc), m.kv_bytes / 2, "the key cache"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.vc), m.kv_bytes / 2, "the value cache"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.x), B * size_t(E) * 4, "the residual rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xn), B * size_t(E) * 4, "the normalized rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.qkv), B * size_t(m.qkv_width) * 4, "the q/k/v rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn), B * size_t(m.q_width) * 4, "the attention rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h), B * size_t(m.ff) * 4, "the feed-forward rows"));
+    if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(&m.argmax_part, size_t(cuda::argmax_blocks(int64_t(logits_floats))) * 8, "the argmax partial results"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tokens), (size_t(c.n_ctx) + 2) * 4, "the token ring"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.in_tokens), B * 4, "the input tokens"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.state), sizeof(DevState), "the position state"));
+    cudaMemset(m.state, 0, sizeof(DevState));
+    cudaMemset(m.tokens, 0, (size_t(c.n_ctx) + 2) * 4);
+    {   // vocabulary padding rows (tp does not divide n_vocab) never win the argmax
+        std::vector<float> ninf(logits_floats, -INFINITY);
+        cudaMemcpy(m.logits_buf, ninf.data(), logits_floats * 4, cudaMemcpyHostToDevice);
+    }
+    if (cudaHostAlloc(reinterpret_cast<void **>(&m.host_tokens), (size_t(c.n_ctx) + 2) * 4, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void **>(&m.host_in), B * 4, cudaHostAllocDefault) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void **>(&m.host_x), B * size_t(E) * 4, cudaHostAllocDefault) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return resource_exhausted("could not allocate pinned host memory for the decoder");
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
+    m.tm.weight_bytes = int64_t(m.matrix_bytes);
+    m.tm.kv_bytes = int64_t(m.kv_bytes);
+    return std::unique_ptr<CudaLlamaDecoder>(new CudaLlamaDecoder(std::move(impl)));
+}
+
+void CudaLlamaDecoder::reset() {
+    (void)impl_->wait_idle();
+    impl_->pos = 0;
+    impl_->has_pending = false;
+}
+
+Status CudaLlamaDecoder::eval_embeddings(const float * embeddings, int32_t n) {
+    Impl & m = *impl_;
+    if (!embeddings || n < 1) return invalid_argument("no embeddings to evaluate");
+    const int64_t total = int64_t(n) * m.cfg.n_embd;
+    for (int64_t i = 0; i < total; i++) if (!std::isfinite(embeddings[i])) return invalid_argument("the embeddings contain NaN or Inf");
+    if (int64_t(m.pos) + n > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
+    cudaSetDevice(m.opt.device);
+    m.launches = 0;
+    bool first = true;
+    for (int32_t start = 0; start < n; start += m.cfg.n_batch) {
+        DOOMS_RETURN_IF_ERROR(m.wait_idle());   // the staging rows are rewritten by the host
+        const int32_t rows = std::min(m.cfg.n_batch, n - start);
+        const size_t bytes = size_t(rows) * size_t(m.cfg.n_embd) * 4;
+        std::memcpy(m.host_x, embeddings + int64_t(start) * m.cfg.n_embd, bytes);
+        if (first) { cudaEventRecord(m.ev_a, m.stream); first = false; }
+        (void)m.check(cudaMemcpyAsync(m.x, m.host_x, bytes, cudaMemcpyHostToDevice, m.stream), "copying the embeddings to the device");
+        m.run_chunk(rows, false);
+    }
+    cudaEventRecord(m.ev_b, m.stream);
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, m.ev_a, m.ev_b);
+    m.tm.last_eval_ms = ms;
+    m.tm.last_eval_launches = m.launches;
+    return Status();
+}
+
+Status CudaLlamaDecoder::eval_tokens(const std::vector<int32_t> & ids) { return eval_tokens(ids.data(), int32_t(ids.size())); }
+
+Status CudaLlamaDecoder::eval_tokens(const int32_t * ids, int32_t n) {
+    Impl & m = *impl_;
+    if (!ids || n < 1) return invalid_argument("no tokens to evaluate");
+    for (int32_t i = 0; i < n; i++) {
+        if (ids[i] < 0 || ids[i] >= m.cfg.n_vocab) {
+            return invalid_argument("token " + std::to_string(ids[i]) + " is outside the vocabulary [0, " + std::to_string(m.cfg.n_vocab) + ")");
+        }
+    }
+    if (int64_t(m.pos) + n > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
+    cudaSetDevice(m.opt.device);
+    m.launches = 0;
+    bool first = true;
+    for (int32_t start = 0; start < n; start += m.cfg.n_batch) {
+        DOOMS_RETURN_IF_ERROR(m.wait_idle());   // the staging ids are rewritten by the host
+        const int32_t rows = std::min(m.cfg.n_batch, n - start);
+        std::memcpy(m.host_in, ids + start, size_t(rows) * 4);
+        if (first) { cudaEventRecord(m.ev_a, m.stream); first = false; }
+        (void)m.check(cudaMemcpyAsync(m.in_tokens, m.host_in, size_t(rows) * 4, cudaMemcpyHostToDevice, m.stream), "copying the tokens to the device");
+        m.run_chunk(rows, true);
+    }
+    cudaEventRecord(m.ev_b, m.stream);
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, m.ev_a, m.ev_b);
+    m.tm.last_eval_ms = ms;
+    m.tm.last_eval_launches = m.launches;
+    return Status();
+}
+
+Result<int32_t> CudaLlamaDecoder::pending_token() {
+    Impl & m = *impl_;
+    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    return m.host_tokens[0];
+}
+
+Status CudaLlamaDecoder::logits_into(float * out, int64_t capacity) {
+    Impl & m = *impl_;
+    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
+    if (!out || capacity < m.cfg.n_vocab) return resource_exhausted("logits need room for " + std::to_string(m.cfg.n_vocab) + " floats");
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    cudaSetDevice(m.opt.device);
+    return m.check(cudaMemcpy(out, m.logits_buf, size_t(m.cfg.n_vocab) * 4, cudaMemcpyDeviceToHost), "reading the logits");
+}
+
+Result<std::vector<float>> CudaLlamaDecoder::logits() {
+    std::vector<float> v(size_t(impl_->cfg.n_vocab));
+    Status st = logits_into(v.data(), int64_t(v.size()));
+    if (!st.is_ok()) return st;
+    return v;
+}
+
+Status CudaLlamaDecoder::generate(int32_t max_tokens, int32_t depth, const std::function<bool(int32_t)> & on_token) {
+    Impl & m = *impl_;
+    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
+    if (max_tokens < 1 || depth < 1) return invalid_argument("max_tokens and depth must be >= 1");
+    // Step i (1 <= i < max_tokens) writes the cache at position base + i - 1 and its token into tokens[i] (metal_llama_decoder.mm:745-747).
+    const int32_t base = m.pos;
+    if (int64_t(base) + max_tokens - 1 > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
+    cudaSetDevice(m.opt.device);
+    DOOMS_RETURN_IF_ERROR(m.ensure_step_graph());
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());   // tokens[0] (the pending token) is final; steps queued by an earlier generate() are done
+    while (m.step_events.size() < size_t(depth) + 1) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        m.step_events.push_back(e);
+    }
+    m.launches = 0;
+    m.run("state", [&] { return cuda::launch_set_state(m.state, base, 0, 1, m.stream); });
+    cudaEventRecord(m.ev_a, m.stream);
+    std::deque<int> inflight;   // event slots; inflight[k] marks the step that produces tokens[produced + k]; -1: already complete
+    inflight.push_back(-1);
+    int32_t produced = 0, next = 1;
+    size_t slot = 0;
+    int last_slot = -1;   // the event of the step that produced the last delivered token
+    Status st;
+    while (true) {
+        while (next < max_tokens && next - produced <= depth) {
+            m.queue_decode_step();
+            const int s = int(slot++ % m.step_events.size());
+            cudaEventRecord(m.step_events[size_t(s)], m.stream);
+            inflight.push_back(s);
+            next++;
+        }
+        const int s = inflight.front();
+        inflight.pop_front();
+        if (s >= 0) {
+            cudaError_t e;
+            if (m.cfg.spin_wait) { while ((e = cudaEventQuery(m.step_events[size_t(s)])) == cudaErrorNotReady) {} }
+            else e = cudaEventSynchronize(m.step_events[size_t(s)]);
+            if (e != cudaSuccess) { st = m.check(e, "a decode step failed"); break; }
+            last_slot = s;
+        }
+        if (!m.failed.is_ok()) { st = m.failed; break; }
+        const int32_t token = m.host_tokens[produced];
+        produced++;
+        if (!on_token(token) || produced == max_tokens) break;
+    }
+    // Steps queued past the stopping point still run; every later call starts by waiting for the stream, so they never overlap with new work.
+    if (st.is_ok()) {
+        // Device time up to the step of the last delivered token: steps queued past it are not the caller's.
+        float ms = 0.f;
+        if (last_slot >= 0) cudaEventElapsedTime(&ms, m.ev_a, m.step_events[size_t(last_slot)]);
+        m.tm.last_generate_ms = ms;
+        m.tm.last_generate_launches = m.launches;
+    } else {
+        (void)cudaStreamSynchronize(m.stream);
+    }
+    m.pos = base + produced - 1;
+    m.has_pending = false;
+    return st;
+}
+
+Result<std::vector<CudaLlamaDecoder::KernelTime>> CudaLlamaDecoder::profile_pass(int32_t rows) {
+    Impl & m = *impl_;
+    if (rows < 1 || rows > m.cfg.n_batch) return invalid_argument("rows must be in [1, n_batch]");
+    if (rows == 1 && !m.has_pending) return invalid_argument("nothing has been evaluated yet");
+    if (m.pos + rows > m.cfg.n_ctx) return resource_exhausted("the cache is too full");
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    cudaSetDevice(m.opt.device);
+    if (rows > 1) {
+        for (int32_t i = 0; i < rows; i++) m.host_in[i] = i % m.cfg.n_vocab;
+        (void)m.check(cudaMemcpyAsync(m.in_tokens, m.host_in, size_t(rows) * 4, cudaMemcpyHostToDevice, m.stream), "copying the tokens to the device");
+    }
+    std::vector<KernelTime> times;
+    m.profile = &times;
+    // tokens[0] holds the pending token; the pass writes its own token to tokens[1] and leaves position() alone.
+    (void)m.check(cuda::launch_set_state(m.state, m.pos, 0, 1, m.stream), "state");
+    m.embed(rows == 1 ? m.tokens : m.in_tokens, nullptr, rows);
+    m.forward(rows, false);
+    m.profile = nullptr;
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    return times;
+}
+
+}  // namespace dooms

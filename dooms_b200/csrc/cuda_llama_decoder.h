@@ -1,0 +1,101 @@
+#pragma once
+// A llama / qwen2 text decoder on hand-written CUDA kernels for B200 (sm_100a). The class keeps the method set, argument meaning and error behaviour of the
+// reference's MetalLlamaDecoder (src/backend/metal/metal_llama_decoder.h:63-106) so that its callers (src/pipeline/llm_pipeline.cpp:60,187-212,
+// bench/bench_llm.cpp:92-114) compile against either: create / config / position / reset / eval_embeddings / eval_tokens / pending_token / logits /
+// generate / profile_pass. Activations are f32, weight matrices stay in their GGUF block format in device memory (f16, q4_0, q5_0, q8_0, q4_K, q6_K),
+// the KV cache is f16 in device memory. This header exposes no CUDA type. There is no CPU fallback: create() fails with Unsupported without a device.
+#include <cstdint>
+#include <functional>
+#include <memory>
+#include <vector>
+
+#include "dtype.h"
+#include "status.h"
+
+namespace dooms {
+
+// A tensor in host memory; copied at creation, not referenced afterwards (src/backend/weight_ref.h:11-15). Row-major [rows][cols], cols = input width.
+struct WeightRef {
+    const void * data = nullptr;
+    DType dtype = DType::F32;
+    int64_t rows = 0, cols = 0;
+};
+
+// metal_llama_decoder.h:20-39
+struct LlamaDecoderConfig {
+    int32_t n_layer = 0, n_embd = 0, n_head = 0, n_head_kv = 0, head_dim = 0, n_ff = 0, n_vocab = 0;
+    float rope_base = 0.f;
+    bool rope_neox = false;
+    float rms_eps = 0.f;
+    int32_t n_ctx = 0, n_batch = 0;
+    bool spin_wait = true;      // generate(): poll the step's event on the calling thread instead of sleeping in the driver
+    int32_t prefill_tile = 0;   // 0 automatic, 1 CUDA-core tiles, 2 tcgen05 tensor-core tiles (when the widths allow)
+};
+
+// metal_llama_decoder.h:42-58
+struct LlamaLayerWeights {
+    WeightRef attn_norm;
+    WeightRef attn_q, attn_k, attn_v, attn_qkv;
+    WeightRef attn_q_bias, attn_k_bias, attn_v_bias, attn_qkv_bias;
+    WeightRef attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down;
+};
+struct LlamaDecoderWeights {
+    WeightRef token_embd, output_norm, output;
+    std::vector<LlamaLayerWeights> layers;
+};
+
+// Where and how this process's share of the model runs (no counterpart in the reference, which has one GPU).
+struct CudaOptions {
+    int32_t device = 0;
+    int32_t tp_rank = 0, tp_size = 1;        // tensor parallelism: q/k/v/gate/up split by output rows, attn_output/ffn_down by input columns
+    const void * nccl_unique_id = nullptr;   // 128 bytes shared by the ranks of the group (tp_size > 1)
+    const char * nccl_library = nullptr;
+    bool operand_bf16 = false;               // tensor-core prefill operands: f16 (the reference's rounding) or bf16
+    bool use_graphs = true;                  // decode steps replay a captured CUDA graph
+};
+
+class CudaLlamaDecoder {
+public:
+    //   Unsupported  no CUDA device, a weight type the kernels do not take, a head_dim that is not a power of two in [4, 256]
+    //   InvalidArgument  the weights do not have the shapes the config implies
+    //   ResourceExhausted  device memory
+    static Result<std::unique_ptr<CudaLlamaDecoder>> create(const LlamaDecoderConfig & config, const LlamaDecoderWeights & weights,
+                                                            const CudaOptions & options = CudaOptions());
+    ~CudaLlamaDecoder();
+    CudaLlamaDecoder(const CudaLlamaDecoder &) = delete;
+    CudaLlamaDecoder & operator=(const CudaLlamaDecoder &) = delete;
+
+    const LlamaDecoderConfig & config() const;
+    int32_t position() const;
+    void reset();
+    Status eval_embeddings(const float * embeddings, int32_t n);
+    Status eval_tokens(const std::vector<int32_t> & tokens);
+    Status eval_tokens(const int32_t * tokens, int32_t n);
+    Result<int32_t> pending_token();
+    Result<std::vector<float>> logits();
+    Status logits_into(float * out, int64_t capacity);
+    Status generate(int32_t max_tokens, int32_t depth, const std::function<bool(int32_t)> & on_token);
+
+    struct KernelTime { const char * kind; int32_t dispatches; double gpu_ms; };
+    Result<std::vector<KernelTime>> profile_pass(int32_t rows = 1);
+
+    // Device-side measurements of the last calls (CUDA events on the decoder's stream).
+    struct Timings { double last_eval_ms = 0, last_generate_ms = 0; int64_t last_eval_launches = 0, last_generate_launches = 0, weight_bytes = 0, kv_bytes = 0; };
+    Timings timings() const;
+
+private:
+    struct Impl;
+    explicit CudaLlamaDecoder(std::unique_ptr<Impl> impl);
+    std::unique_ptr<Impl> impl_;
+};
+
+struct NativeLlamaOptions {   // src/pipeline/native_llama.h:15-20
+    int32_t n_ctx = 2048, n_batch = 512;
+    bool spin_wait = true;
+    int32_t prefill_tile = 0;
+};
+//   NotFound  no such file     Unsupported  not a GGUF this decoder runs     InvalidArgument  bad options or inconsistent metadata
+Result<std::unique_ptr<CudaLlamaDecoder>> load_native_llama(const std::string & path, const NativeLlamaOptions & options = NativeLlamaOptions(),
+                                                            const CudaOptions & cuda = CudaOptions());
+
+}  // namespace dooms

@@ -1,0 +1,69 @@
+#pragma once
+// Launchers of the decoder's CUDA kernels (internal interface between the host-side decoder and the .cu files). Every launcher enqueues on `stream` and
+// returns the CUDA error of the launch; nothing here allocates or synchronizes unless it says so.
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace dooms {
+namespace cuda {
+
+// Position state of a sequence, kept in device memory so that a captured decode step can be replayed without new arguments: the kernels read it, the last
+// kernel of a step advances it.
+struct DevState {
+    int32_t pos;       // cache position of the first row of the current call
+    int32_t tok_in;    // index into the token ring of the token a decode step embeds
+    int32_t tok_out;   // index into the token ring where the step's greedy token goes
+    int32_t error;     // set non-zero by a kernel that found an inconsistency (never cleared by kernels)
+};
+
+enum : uint32_t { kFlagAccumulate = 2, kFlagBias = 4 };   // the reference's MatvecParams / GemmParams flags (metal_llama_decoder.mm:51)
+
+cudaError_t launch_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t tok_out, cudaStream_t stream);
+
+// x[row][:] = table[ids[(index ? *index : 0) + row]][:], rows x E (embedq<Q>, llama_kernels.h:1289-1296).
+cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const int32_t * index, float * x, int rows, int E, cudaStream_t stream);
+
+// out[r][:] = x[r][:] * rsqrt(mean(x[r]^2) + eps) * gamma (norm_vec, llama_kernels.h:1272-1286). out16 (optional) also receives the rows as f16.
+cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, int rows, int E, float eps, cudaStream_t stream);
+
+// y[r] (+)= W[r] . x (+ bias[r]) (matvec1q<Q>, llama_kernels.h:1197-1230).
+cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
+// h[r] = silu(Wg[r] . x) * (Wu[r] . x) (gate_up1q<Q>, llama_kernels.h:1232-1269).
+cudaError_t launch_gate_up(int dt, const void * Wg, const void * Wu, const float * x, float * h, int64_t rows, int64_t cols, cudaStream_t stream);
+
+// Y[m][n] (+)= X[m] . W[n] (+ bias[n]) for M rows (matmulq<16,16,Q>, llama_kernels.h:1397-1429), CUDA-core tiles, f32 operands. With W2 the kernel computes
+// silu(X . W[n]) * (X . W2[n]) instead (matmul_gate_upq, llama_kernels.h:1431-1468).
+cudaError_t launch_matmul_tile(int dt, const void * W, const void * W2, const float * X, int64_t x_stride, float * Y, int64_t y_stride, const float * bias,
+                               int M, int64_t N, int64_t K, uint32_t flags, cudaStream_t stream);
+
+// x[i] += y[i].
+cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream);
+
+// Whole matrix to f32, bit for bit the block formulas (dequant_half<Q>, llama_kernels.h:1474-1480).
+cudaError_t launch_dequantize(int dt, const void * blocks, int64_t rows, int64_t cols, float * out, cudaStream_t stream);
+
+struct AttnShape { int n_head, n_head_kv, head_dim, qkv_stride, kv_stride, out_stride, neox; float rope_base; };
+
+// Rotates q in place, rotates k into the f16 key cache and copies v into the f16 value cache for M rows at positions st->pos + t
+// (rope_store, llama_kernels.h:521-545).
+cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, int M, const AttnShape & s, cudaStream_t stream);
+
+// One query row against cache positions 0 .. st->pos (attention_split + attention_combine, llama_kernels.h:860-929). The cache is cut into `splits`
+// ranges; part holds splits x n_head x (2 + head_dim) floats.
+int attention_splits(int n_head, int n_ctx);
+cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, const DevState * st, int n_keys_fixed,
+                                    int splits, const AttnShape & s, cudaStream_t stream);
+
+// Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
+cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, const DevState * st, int M, const AttnShape & s,
+                                     cudaStream_t stream);
+
+// tokens[st->tok_out] = first index of the maximum of logits[0..n) (NaN never wins); the token also goes to host_tokens[st->tok_out] when that is set
+// (mapped pinned memory). With advance the state moves one decode step forward (pos, tok_in, tok_out += 1). part: argmax_blocks(n) x 2 words.
+int argmax_blocks(int64_t n);
+cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int32_t * host_tokens, DevState * st, void * part, int advance, cudaStream_t stream);
+// The same reduction without a state: *out = argmax.
+cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream);
+
+}  // namespace cuda
+}  // namespace dooms

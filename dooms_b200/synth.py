@@ -1,0 +1,186 @@
+"""Synthetic llama / qwen2 GGUF models: the benchmark configurations' shapes and quantization plans with seeded random weights.
+
+Stands in for the public checkpoints the reference benchmarks (none of their weights are used): matrices are drawn N(0, 0.02) and quantized per tensor
+plan, norm gains U(0.7, 1.3), q/k/v biases N(0, 0.02), as the reference's tests draw theirs (tests/unit/test_metal_llama_decoder.cpp:41-53). Each tensor
+has its own seed (base seed, tensor index), so a tensor's bytes do not depend on which others were generated. Small models draw from numpy's PCG64; with
+device="cuda" the draws come from torch's CUDA generator instead (fast enough for 8B / 32B shapes; a different but equally seeded stream).
+"""
+from __future__ import annotations
+
+import dataclasses
+from pathlib import Path
+from typing import Callable
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from .gguf_io import GgufWriter
+from .quantize import quantize
+
+
+@dataclasses.dataclass
+class ModelSpec:
+    name: str
+    arch: str                # "llama" or "qwen2"
+    n_layer: int
+    n_embd: int
+    n_head: int
+    n_head_kv: int
+    n_ff: int
+    n_vocab: int
+    rope_base: float
+    rms_eps: float
+    context_length: int
+    tied: bool
+    bias: bool
+    plan: Callable[[str, int], int]      # (tensor kind, layer) -> dtype; kinds: token_embd, output, attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down
+    weight_std: float = 0.02
+    embd_std: float = 0.02
+    bias_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+    def matrices(self):
+        """(gguf name, kind, layer, rows, cols) of every weight matrix, in file order."""
+        E, F, V = self.n_embd, self.n_ff, self.n_vocab
+        Q, KV = self.n_head * self.head_dim, self.n_head_kv * self.head_dim
+        out = [("token_embd.weight", "token_embd", -1, V, E)]
+        if not self.tied:
+            out.append(("output.weight", "output", -1, V, E))
+        for l in range(self.n_layer):
+            b = f"blk.{l}."
+            out += [(b + "attn_q.weight", "attn_q", l, Q, E), (b + "attn_k.weight", "attn_k", l, KV, E), (b + "attn_v.weight", "attn_v", l, KV, E),
+                    (b + "attn_output.weight", "attn_output", l, E, Q), (b + "ffn_gate.weight", "ffn_gate", l, F, E), (b + "ffn_up.weight", "ffn_up", l, F, E),
+                    (b + "ffn_down.weight", "ffn_down", l, E, F)]
+        return out
+
+    def matrix_bytes(self) -> int:
+        """Bytes of weight matrices a decode step reads: every layer matrix plus the output matrix (the tied table when there is no separate one)."""
+        total = 0
+        for name, kind, l, rows, cols in self.matrices():
+            if kind == "token_embd" and not self.tied:
+                continue
+            dt = self.plan(kind, l)
+            total += rows * cols // L.BLOCK_ELEMS[dt] * L.BLOCK_BYTES[dt]
+        return total
+
+
+def pure(dtype: int):
+    return lambda kind, layer: dtype
+
+
+def q4_k_m_small(kind: str, layer: int) -> int:
+    """The Q4_K_M-style mix on rows of 896 elements, which are not whole 256-element super-blocks: llama-quantize's fallback types there, as the reference
+    describes them (metal_llama_decoder.mm:83 "Q4_K_M files mix q5_0 and q8_0 there"; test plan at tests/unit/test_metal_llama_decoder.cpp:390)."""
+    even = layer % 2 == 0
+    return {"token_embd": L.Q8_0, "output": L.Q8_0, "attn_q": L.Q5_0, "attn_k": L.Q5_0, "attn_v": L.Q8_0 if even else L.Q5_0, "attn_output": L.Q5_0,
+            "ffn_gate": L.Q5_0, "ffn_up": L.Q5_0, "ffn_down": L.Q6_K if even else L.Q4_K}[kind]
+
+
+def q4_k_m_large(kind: str, layer: int) -> int:
+    """Q4_K everywhere; Q6_K for the output / token table and for attn_v and ffn_down in even layers."""
+    if kind in ("token_embd", "output"):
+        return L.Q6_K
+    if kind in ("attn_v", "ffn_down") and layer % 2 == 0:
+        return L.Q6_K
+    return L.Q4_K
+
+
+def config_spec(index: int) -> ModelSpec:
+    """The benchmark configurations 0-3 (4 reuses the model of 0)."""
+    if index in (0, 4):
+        return ModelSpec("qwen2.5-0.5b-arch-q4_0", "qwen2", 24, 896, 14, 2, 4864, 151936, 1e6, 1e-6, 32768, True, True, pure(L.Q4_0))
+    if index == 1:
+        return ModelSpec("qwen2.5-0.5b-arch-q4_k_m", "qwen2", 24, 896, 14, 2, 4864, 151936, 1e6, 1e-6, 32768, True, True, q4_k_m_small)
+    if index == 2:
+        return ModelSpec("llama-3-8b-arch-q4_0", "llama", 32, 4096, 32, 8, 14336, 128256, 5e5, 1e-5, 8192, False, False, pure(L.Q4_0))
+    if index == 3:
+        return ModelSpec("qwen2.5-32b-arch-q4_k_m", "qwen2", 64, 5120, 40, 8, 27648, 152064, 1e6, 1e-6, 32768, False, True, q4_k_m_large)
+    raise ValueError(index)
+
+
+def tiny_spec(dtype_plan, arch: str = "qwen2", n_embd: int = 256, n_head: int = 4, n_head_kv: int = 2, n_ff: int = 2304, n_vocab: int = 50, n_layer: int = 2,
+              context_length: int = 1024, tied: bool = False) -> ModelSpec:
+    """The shape of the reference's quantized test model (tests/unit/test_metal_llama_decoder.cpp:279-285): E 256, 4 / 2 heads of 64, F 2304, V 50."""
+    return ModelSpec("tiny", arch, n_layer, n_embd, n_head, n_head_kv, n_ff, n_vocab, 10000.0, 1e-5, context_length, tied, arch == "qwen2", dtype_plan,
+                     weight_std=0.15, embd_std=1.0, bias_std=0.3)
+
+
+def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
+    if device == "cpu":
+        g = np.random.Generator(np.random.PCG64(seed))
+        return torch.from_numpy(g.standard_normal(shape, dtype=np.float32) * np.float32(std))
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
+
+
+def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu") -> dict:
+    """Writes the model as a GGUF file; returns {"matrix_bytes": ...}."""
+    md = {
+        "general.architecture": spec.arch,
+        "general.name": spec.name,
+        f"{spec.arch}.block_count": spec.n_layer,
+        f"{spec.arch}.embedding_length": spec.n_embd,
+        f"{spec.arch}.attention.head_count": spec.n_head,
+        f"{spec.arch}.attention.head_count_kv": spec.n_head_kv,
+        f"{spec.arch}.feed_forward_length": spec.n_ff,
+        f"{spec.arch}.context_length": spec.context_length,
+        f"{spec.arch}.rope.freq_base": float(spec.rope_base),
+        f"{spec.arch}.attention.layer_norm_rms_epsilon": float(spec.rms_eps),
+    }
+    tensors = []
+    counter = [0]
+
+    def next_seed() -> int:
+        counter[0] += 1
+        return seed * 1_000_003 + counter[0]
+
+    def matrix(kind, layer, rows, cols):
+        s = next_seed()
+        dt = spec.plan(kind, layer)
+        std = spec.embd_std if kind == "token_embd" else spec.weight_std
+
+        def produce():
+            out = []
+            step = max(1, (1 << 26) // cols)          # 64M elements at a time
+            for r0 in range(0, rows, step):
+                r1 = min(rows, r0 + step)
+                out.append(quantize(dt, _normal((r1 - r0, cols), std, s * 131 + r0, device)).cpu().numpy())
+            return np.concatenate(out, axis=0)
+        return dt, produce
+
+    def vector(n, kind):
+        s = next_seed()
+
+        def produce():
+            g = np.random.Generator(np.random.PCG64(s))
+            if kind == "norm":
+                return g.uniform(0.7, 1.3, n).astype(np.float32)
+            return (g.standard_normal(n, dtype=np.float32) * np.float32(spec.bias_std)).astype(np.float32)
+        return produce
+
+    E = spec.n_embd
+    Q, KV = spec.n_head * spec.head_dim, spec.n_head_kv * spec.head_dim
+    for name, kind, layer, rows, cols in spec.matrices():
+        if kind == "attn_q":
+            tensors.append((f"blk.{layer}.attn_norm.weight", L.F32, [E], vector(E, "norm")))
+        if kind == "ffn_gate":
+            tensors.append((f"blk.{layer}.ffn_norm.weight", L.F32, [E], vector(E, "norm")))
+        dt, produce = matrix(kind, layer, rows, cols)
+        tensors.append((name, dt, [rows, cols], produce))
+        if spec.bias and kind in ("attn_q", "attn_k", "attn_v"):
+            tensors.append((name.replace(".weight", ".bias"), L.F32, [rows], vector(rows, "bias")))
+        if kind == "token_embd":
+            tensors.append(("output_norm.weight", L.F32, [E], vector(E, "norm")))
+    GgufWriter().write(path, md, tensors)
+    return {"matrix_bytes": spec.matrix_bytes()}
+
+
+def prompt_tokens(n: int, n_vocab: int, seed: int) -> np.ndarray:
+    """n seeded uniform token ids in [0, n_vocab)."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    return g.integers(0, n_vocab, n, dtype=np.int32)

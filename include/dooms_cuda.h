@@ -1,0 +1,203 @@
+#ifndef DOOMS_CUDA_H
+#define DOOMS_CUDA_H
+/* C ABI of the CUDA (sm_100a) backend for the llama / qwen2 GGUF decoder.
+ *
+ * This is the boundary a dooms.cpp build binds instead of its Metal decoder: the entry points below carry the method set of
+ * dooms::MetalLlamaDecoder (src/backend/metal/metal_llama_decoder.h:63-106) and of load_native_llama (src/pipeline/native_llama.h:15-23) over plain
+ * pointers and sizes. No C++, CUDA or torch type appears in a signature.
+ *
+ *  - Every function returns a dooms_code (the reference's values, include/dooms/dooms_c.h:23-32); DOOMS_OK is 0. On failure
+ *    dooms_cuda_last_error() returns a message for the calling thread, valid until that thread's next call.
+ *  - Handles are not thread-safe: one caller at a time per handle (metal_llama_decoder.h:61-62).
+ *  - Weight pointers are HOST memory (for example a mapped GGUF file). They are copied to device memory at creation and never referenced afterwards
+ *    (src/backend/weight_ref.h:9). Quantized blocks are uploaded byte for byte.
+ *  - There is no CPU fallback: without a CUDA device every entry point that computes fails with DOOMS_UNSUPPORTED.
+ *  - Structs start with struct_size (set it to sizeof(the struct)); zero is rejected (src/api/c_api.cpp:96-102).
+ */
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DOOMS_CUDA_API __attribute__((visibility("default")))
+
+typedef enum dooms_code {
+    DOOMS_OK = 0,
+    DOOMS_INVALID_ARGUMENT = 1,
+    DOOMS_NOT_FOUND = 2,
+    DOOMS_DATA_LOSS = 3,
+    DOOMS_UNSUPPORTED = 4,
+    DOOMS_RESOURCE_EXHAUSTED = 5,
+    DOOMS_IO_ERROR = 6,
+    DOOMS_INTERNAL = 7
+} dooms_code;
+
+/* Element types, numbered like dooms::DType (src/core/dtype.h:15). The quantized ones are ggml block formats (src/core/dtype.cpp:17-29). */
+typedef enum dooms_dtype {
+    DOOMS_F32 = 0, DOOMS_F16 = 1, DOOMS_BF16 = 2, DOOMS_I32 = 3,
+    DOOMS_Q4_0 = 4, DOOMS_Q5_0 = 5, DOOMS_Q8_0 = 6, DOOMS_Q4_K = 7, DOOMS_Q6_K = 8
+} dooms_dtype;
+
+/* dooms::WeightRef (src/backend/weight_ref.h:11-15): a row-major [rows][cols] host tensor, cols = input width; vectors have rows = 1. */
+typedef struct dooms_weight_ref {
+    const void * data;
+    int32_t dtype;       /* a dooms_dtype */
+    int64_t rows, cols;
+} dooms_weight_ref;
+
+/* dooms::LlamaDecoderConfig (metal_llama_decoder.h:20-39). */
+typedef struct dooms_llama_config {
+    size_t struct_size;
+    int32_t n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab;
+    float rope_base;
+    int32_t rope_neox;      /* 0: adjacent rotary pairs (llama); 1: split halves (qwen2) */
+    float rms_eps;
+    int32_t n_ctx;          /* positions the KV cache holds */
+    int32_t n_batch;        /* largest prefill chunk */
+    int32_t spin_wait;      /* generate(): poll for each token instead of sleeping */
+    int32_t prefill_tile;   /* 0: automatic; 1: the CUDA-core tile kernel; 2: the tcgen05 tensor-core kernel (when the widths allow) */
+} dooms_llama_config;
+
+/* dooms::LlamaLayerWeights (metal_llama_decoder.h:42-51). Unused refs have data == NULL. */
+typedef struct dooms_llama_layer_weights {
+    dooms_weight_ref attn_norm;
+    dooms_weight_ref attn_q, attn_k, attn_v, attn_qkv;
+    dooms_weight_ref attn_q_bias, attn_k_bias, attn_v_bias, attn_qkv_bias;
+    dooms_weight_ref attn_output;
+    dooms_weight_ref ffn_norm;
+    dooms_weight_ref ffn_gate, ffn_up, ffn_down;
+} dooms_llama_layer_weights;
+
+/* dooms::LlamaDecoderWeights (metal_llama_decoder.h:53-58). output.data == token_embd.data means tied. */
+typedef struct dooms_llama_weights {
+    size_t struct_size;
+    dooms_weight_ref token_embd, output_norm, output;
+    const dooms_llama_layer_weights * layers;
+    int32_t n_layers;
+} dooms_llama_weights;
+
+/* Placement; no counterpart in the reference (it has one GPU and no distributed code). */
+typedef struct dooms_cuda_options {
+    size_t struct_size;
+    int32_t device;          /* CUDA device ordinal of this process */
+    int32_t tp_rank;         /* tensor-parallel rank and degree; 0 / 1 for one GPU */
+    int32_t tp_size;
+    const void * nccl_unique_id;   /* tp_size > 1: the 128-byte ncclUniqueId every rank of the group passes (rank 0 makes it with dooms_cuda_nccl_unique_id) */
+    const char * nccl_library;     /* path of libnccl.so.2 to load; NULL: the dynamic loader's search path */
+    int32_t operand_bf16;    /* prefill tensor-core operands: 0 = f16 (the reference's rounding, llama_kernels.h:197), 1 = bf16 */
+    int32_t use_graphs;      /* 1: decode steps replay a CUDA graph; 0: plain launches */
+} dooms_cuda_options;
+
+/* dooms::NativeLlamaOptions (src/pipeline/native_llama.h:15-20). */
+typedef struct dooms_native_llama_options {
+    size_t struct_size;
+    int32_t n_ctx, n_batch, spin_wait, prefill_tile;
+} dooms_native_llama_options;
+
+/* MetalLlamaDecoder::KernelTime (metal_llama_decoder.h:99). `kind` points at a string literal. */
+typedef struct dooms_kernel_time {
+    const char * kind;
+    int32_t dispatches;
+    double gpu_ms;
+} dooms_kernel_time;
+
+typedef struct dooms_cuda_llama dooms_cuda_llama;
+
+DOOMS_CUDA_API const char * dooms_cuda_last_error(void);
+DOOMS_CUDA_API const char * dooms_cuda_code_name(int32_t code);                  /* code_name, src/core/status.h:25 */
+DOOMS_CUDA_API int32_t dooms_cuda_device_count(void);                            /* 0 without a usable CUDA device */
+
+/* Block tables: dtype_block_elems / dtype_block_bytes / dtype_bytes (src/core/dtype.cpp:45-52). */
+DOOMS_CUDA_API int64_t dooms_dtype_block_elems(int32_t dtype);
+DOOMS_CUDA_API int64_t dooms_dtype_block_bytes(int32_t dtype);
+DOOMS_CUDA_API int32_t dooms_dtype_bytes(int32_t dtype, int64_t n, uint64_t * out);
+DOOMS_CUDA_API const char * dooms_dtype_name(int32_t dtype);
+
+/* ---- GGUF reader: GgufFile (src/format/gguf.h:63-100, src/format/gguf.cpp:179-317). Host only. ---- */
+typedef struct dooms_gguf dooms_gguf;
+typedef struct dooms_gguf_tensor {
+    const char * name;       /* owned by the file handle */
+    int32_t dtype;
+    int32_t rank;
+    int64_t shape[4];        /* row-major, outermost first (the file stores the reverse) */
+    uint64_t offset;         /* from the start of the file */
+    uint64_t nbytes;
+    const void * data;       /* inside the mapping; valid while the handle lives */
+} dooms_gguf_tensor;
+DOOMS_CUDA_API int32_t dooms_gguf_open(const char * path, dooms_gguf ** out);                         /* GgufFile::open */
+DOOMS_CUDA_API int32_t dooms_gguf_parse(const void * data, size_t size, dooms_gguf ** out);            /* GgufFile::parse; data must outlive the handle */
+DOOMS_CUDA_API void dooms_gguf_close(dooms_gguf * f);
+DOOMS_CUDA_API uint32_t dooms_gguf_version(const dooms_gguf * f);
+DOOMS_CUDA_API uint64_t dooms_gguf_alignment(const dooms_gguf * f);
+DOOMS_CUDA_API int64_t dooms_gguf_tensor_count(const dooms_gguf * f);
+DOOMS_CUDA_API int32_t dooms_gguf_tensor_at(const dooms_gguf * f, int64_t index, dooms_gguf_tensor * out);
+DOOMS_CUDA_API int32_t dooms_gguf_find_tensor(const dooms_gguf * f, const char * name, dooms_gguf_tensor * out);   /* find_tensor + tensor_data */
+DOOMS_CUDA_API int32_t dooms_gguf_get_string(const dooms_gguf * f, const char * key, const char ** out);
+DOOMS_CUDA_API int32_t dooms_gguf_get_uint(const dooms_gguf * f, const char * key, uint64_t * out);
+DOOMS_CUDA_API int32_t dooms_gguf_get_int(const dooms_gguf * f, const char * key, int64_t * out);
+DOOMS_CUDA_API int32_t dooms_gguf_get_float(const dooms_gguf * f, const char * key, double * out);
+DOOMS_CUDA_API int32_t dooms_gguf_get_bool(const dooms_gguf * f, const char * key, int32_t * out);
+
+/* ---- The decoder: MetalLlamaDecoder's methods (metal_llama_decoder.h:63-106). ---- */
+/* create (metal_llama_decoder.mm:425-689). options may be NULL (device 0, one GPU, f16 operands, graphs on). */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_create(const dooms_llama_config * config, const dooms_llama_weights * weights, const dooms_cuda_options * options,
+                                               dooms_cuda_llama ** out);
+/* load_native_llama (src/pipeline/native_llama.cpp:9-102): GGUF metadata -> config, tensor names -> weights, then create. */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_load(const char * gguf_path, const dooms_native_llama_options * options, const dooms_cuda_options * cuda_options,
+                                             dooms_cuda_llama ** out);
+DOOMS_CUDA_API void dooms_cuda_llama_destroy(dooms_cuda_llama * d);
+DOOMS_CUDA_API int32_t dooms_cuda_llama_config(const dooms_cuda_llama * d, dooms_llama_config * out);   /* config() */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_position(const dooms_cuda_llama * d);                            /* position() */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_reset(dooms_cuda_llama * d);                                     /* reset(), .mm:691-695 */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_tokens(dooms_cuda_llama * d, const int32_t * tokens, int32_t n);        /* .mm:712-724 */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_embeddings(dooms_cuda_llama * d, const float * embeddings, int32_t n);  /* .mm:697-710 */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_pending_token(dooms_cuda_llama * d, int32_t * out);                           /* .mm:726-731 */
+/* logits() (.mm:733-739): n_vocab floats of the last evaluated position into out (capacity floats; too small: DOOMS_RESOURCE_EXHAUSTED). */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_logits(dooms_cuda_llama * d, float * out, int64_t capacity);
+/* generate() (.mm:741-787). callback returns non-zero to continue, zero to stop (the reference's `bool on_token(int32_t)`). */
+typedef int32_t (*dooms_token_callback)(int32_t token, void * user);
+DOOMS_CUDA_API int32_t dooms_cuda_llama_generate(dooms_cuda_llama * d, int32_t max_tokens, int32_t depth, dooms_token_callback callback, void * user);
+/* profile_pass() (.mm:789-812): per-kind device time of one forward pass over `rows` positions; *count receives the number of entries written. */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_profile_pass(dooms_cuda_llama * d, int32_t rows, dooms_kernel_time * out, int32_t capacity, int32_t * count);
+
+/* Measurement helpers without a counterpart in the reference's class: device time (CUDA events on the decoder's stream) of the last eval_* call and of
+ * the last generate() call, and the number of kernels those calls launched. */
+typedef struct dooms_cuda_timings {
+    size_t struct_size;
+    double last_eval_ms;         /* device time of the last eval_tokens / eval_embeddings call, all chunks */
+    double last_generate_ms;     /* device time from the first queued decode step to the last delivered token */
+    int64_t last_eval_launches;
+    int64_t last_generate_launches;
+    int64_t weight_bytes;        /* bytes of weight matrices resident on this GPU */
+    int64_t kv_bytes;            /* bytes of the KV cache on this GPU */
+} dooms_cuda_timings;
+DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, dooms_cuda_timings * out);
+
+/* ---- Single kernels on DEVICE pointers, for parity tests and roofline measurement. `stream` is a cudaStream_t (NULL: the default stream). ---- */
+/* dequant_half<Q> / Q::elem (llama_kernels.h:1012-1154, 1474-1480): rows x cols blocks -> f32 values, bit for bit the block formulas. */
+DOOMS_CUDA_API int32_t dooms_cuda_dequantize(int32_t dtype, const void * d_blocks, int64_t rows, int64_t cols, float * d_out, void * stream);
+/* matvec1q<Q> (llama_kernels.h:1197-1230): y[r] (+)= W[r] . x (+ bias[r]). flags: 2 accumulate into y, 4 add bias (MatvecParams flags, .mm:51). */
+DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const float * d_x, float * d_y, const float * d_bias, int64_t rows, int64_t cols,
+                                         uint32_t flags, void * stream);
+/* gate_up1q<Q> (llama_kernels.h:1232-1269): h[r] = silu(Wg[r] . x) * (Wu[r] . x). */
+DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
+                                          void * stream);
+/* norm_vec (llama_kernels.h:1272-1286): xn = x * rsqrt(mean(x^2) + eps) * gamma for `rows` rows of `cols`. */
+DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream);
+/* argmax (llama_kernels.h:949-975) with the host rule that NaN never wins (src/core/argmax.h:15-16): *d_out = lowest index of the maximum. */
+DOOMS_CUDA_API int32_t dooms_cuda_argmax(const float * d_logits, int64_t n, int32_t * d_out, void * stream);
+/* attention_split + attention_combine (llama_kernels.h:860-929): one query token, n_keys cached positions, grouped-query heads. q f32 [n_head][head_dim]
+ * (already rotated), kc / vc f16 [n_keys][n_head_kv*head_dim], out f32 [n_head][head_dim]. d_scratch: dooms_cuda_attention_scratch_bytes(...) bytes. */
+DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_t head_dim, int32_t n_keys);
+DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void * d_kc, const void * d_vc, float * d_out, void * d_scratch, int32_t n_head,
+                                                   int32_t n_head_kv, int32_t head_dim, int32_t n_keys, void * stream);
+
+/* Tensor-parallel set-up helper: fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and sends the bytes to the other ranks). */
+DOOMS_CUDA_API int32_t dooms_cuda_nccl_unique_id(const char * nccl_library, void * out128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,194 @@
+"""Parity of the CUDA decoder with the CPU checker, through the C ABI, on the cases the reference's own decoder test runs
+(tests/unit/test_metal_llama_decoder.cpp:311-626): tolerances, prompts and structural cases are the reference's."""
+import numpy as np
+import pytest
+
+from dooms_b200 import CudaLlamaDecoder, DoomsError, synth
+from dooms_b200 import _lib as L
+from oracle import binding as ob
+
+from helpers import K_PROMPT, QUANT_PLANS, collect, oracle_greedy, rel_l2, tiny_f16, write
+
+pytestmark = pytest.mark.gpu
+
+BATCHED_TOL = 3e-3     # prompt in one call: the reference's bound for its half-rounded prefill tiles (test_metal_llama_decoder.cpp:327)
+SINGLE_TOL = 1e-4      # one token per call: f32 activations on exact weights (test_metal_llama_decoder.cpp:335)
+
+
+def check_prompt_and_generation(path, n_ctx, n_batch, n_gen, depth, **kw):
+    dec = CudaLlamaDecoder.load(path, n_ctx, n_batch, **kw)
+    o = ob.OracleDecoder(path, n_ctx)
+    want = o.eval_tokens(K_PROMPT)
+    dec.eval_tokens(K_PROMPT)
+    assert rel_l2(dec.logits(), want) < BATCHED_TOL
+    assert dec.pending_token() == ob.argmax(want)
+    dec.reset()
+    for t in K_PROMPT:
+        dec.eval_tokens([t])
+    single = rel_l2(dec.logits(), want)
+    assert single < SINGLE_TOL, single
+    assert dec.pending_token() == ob.argmax(want)
+    assert dec.position() == len(K_PROMPT)
+    want_tokens = oracle_greedy(o, want, n_gen)
+    got = collect(dec, n_gen, depth)
+    assert got == want_tokens
+    assert dec.position() == len(K_PROMPT) + n_gen - 1      # the last token was not fed back
+    dec.close()
+
+
+def test_prompt_logits_and_greedy_generation_match_the_oracle(model_dir):
+    path = write(model_dir, "tiny_llama", tiny_f16(), 1)
+    check_prompt_and_generation(path, 128, 64, 24, 3)
+
+
+def test_qwen_style_block_matches_the_oracle(model_dir):
+    path = write(model_dir, "tiny_qwen", tiny_f16(qwen=True), 4)
+    check_prompt_and_generation(path, 128, 64, 16, 2)
+
+
+@pytest.mark.parametrize("plan", list(QUANT_PLANS))
+@pytest.mark.parametrize("tile", [1, 2])
+def test_quantized_matrices_match_the_oracle(model_dir, plan, tile):
+    path = write(model_dir, "quant_" + plan.replace(" ", "_"), synth.tiny_spec(QUANT_PLANS[plan]), 11)
+    check_prompt_and_generation(path, 128, 64, 16, 2, prefill_tile=tile)
+
+
+@pytest.mark.parametrize("plan", list(QUANT_PLANS))
+def test_longer_prompts_in_one_call(model_dir, plan):
+    """120 and 330 tokens in one call, then a decode step (test_metal_llama_decoder.cpp:426-456)."""
+    path = write(model_dir, "quant_" + plan.replace(" ", "_"), synth.tiny_spec(QUANT_PLANS[plan]), 11)
+    dec = CudaLlamaDecoder.load(path, 400, 400)
+    for n in (120, 330):
+        prompt = [(i * 13 + 5) % 50 for i in range(n)]
+        o = ob.OracleDecoder(path, 400)
+        want = o.eval_tokens(prompt)
+        dec.reset()
+        dec.eval_tokens(prompt)
+        assert rel_l2(dec.logits(), want) < BATCHED_TOL
+        assert dec.pending_token() == ob.argmax(want)
+        nxt = ob.argmax(want)
+        want = o.eval_tokens([nxt])
+        dec.eval_tokens([nxt])
+        assert rel_l2(dec.logits(), want) < BATCHED_TOL
+
+
+@pytest.mark.parametrize("qwen", [False, True])
+def test_long_context_decode_matches_the_oracle(model_dir, qwen):
+    """Decode steps from position 520 on, where the cache is attended in several splits (test_metal_llama_decoder.cpp:467-495); head_dim 64."""
+    spec = synth.tiny_spec(synth.pure(L.F16), arch="qwen2" if qwen else "llama", n_embd=256, n_head=4, n_head_kv=2, n_ff=2208 if qwen else 96)
+    path = write(model_dir, f"long_{qwen}", spec, 21 if qwen else 22)
+    dec = CudaLlamaDecoder.load(path, 600, 64)
+    o = ob.OracleDecoder(path, 600)
+    prompt = [(i * 7 + 3) % 50 for i in range(520)]
+    want = o.eval_tokens(prompt)
+    dec.eval_tokens(prompt)
+    worst, t = 0.0, ob.argmax(want)
+    for _ in range(24):
+        want = o.eval_tokens([t])
+        dec.eval_tokens([t])
+        worst = max(worst, rel_l2(dec.logits(), want))
+        assert dec.pending_token() == ob.argmax(want)
+        t = ob.argmax(want)
+    assert worst < BATCHED_TOL
+
+
+@pytest.mark.parametrize("variant", range(4))
+@pytest.mark.parametrize("tile", [1, 2, 3])
+def test_both_prefill_kernels_match_the_oracle(model_dir, variant, tile):
+    """A 45-token prompt (no multiple of any tile), llama and qwen blocks, head_dim 16 and 64; tile 3 = the tensor-core kernel fed in chunks of 20
+    (test_metal_llama_decoder.cpp:499-532)."""
+    qwen, hd = variant % 2 == 1, 16 if variant < 2 else 64
+    spec = synth.tiny_spec(synth.pure(L.F16), arch="qwen2" if qwen else "llama", n_embd=4 * hd, n_head=4, n_head_kv=2, n_ff=2208 if qwen else 96)
+    path = write(model_dir, f"prefill_{variant}", spec, 5)
+    prompt = [(i * 7 + 3) % 50 for i in range(45)]
+    o = ob.OracleDecoder(path, 128)
+    want = o.eval_tokens(prompt)
+    want_tokens = oracle_greedy(o, want, 8)
+    dec = CudaLlamaDecoder.load(path, 128, 20 if tile == 3 else 64, prefill_tile=2 if tile == 3 else tile)
+    dec.eval_tokens(prompt)
+    assert rel_l2(dec.logits(), want) < BATCHED_TOL
+    assert collect(dec, 8, 1) == want_tokens
+
+
+def test_bad_prefill_tile_is_refused(model_dir):
+    path = write(model_dir, "tiny_llama", tiny_f16(), 1)
+    with pytest.raises(DoomsError) as e:
+        CudaLlamaDecoder.load(path, 128, 64, prefill_tile=3)
+    assert e.value.code == L.INVALID_ARGUMENT
+
+
+def test_chunked_prefill_embeddings_and_queue_depth_give_the_same_tokens(model_dir):
+    """test_metal_llama_decoder.cpp:534-564"""
+    path = write(model_dir, "tiny_llama2", tiny_f16(), 2)
+    a = CudaLlamaDecoder.load(path, 128, 64)
+    b = CudaLlamaDecoder.load(path, 128, 4)          # the prompt split into chunks of 4
+    a.eval_tokens(K_PROMPT)
+    base = collect(a, 16, 1)
+    b.eval_tokens(K_PROMPT)
+    assert collect(b, 16, 6) == base
+    o = ob.OracleDecoder(path, 128)
+    emb = np.stack([o.embedding(t) for t in K_PROMPT])
+    a.reset()
+    assert a.position() == 0
+    a.eval_embeddings(emb)
+    assert collect(a, 16, 2) == base
+    # continuing after a generation: feeding the last delivered token gives what a longer generation would have produced next
+    a.reset()
+    a.eval_tokens(K_PROMPT)
+    first = collect(a, 8, 4)
+    a.eval_tokens([first[-1]])
+    assert a.pending_token() == base[8]
+    # with and without CUDA graphs
+    c = CudaLlamaDecoder.load(path, 128, 64, use_graphs=False)
+    c.eval_tokens(K_PROMPT)
+    assert collect(c, 16, 3) == base
+
+
+def test_stopping_early_and_errors(model_dir):
+    """test_metal_llama_decoder.cpp:566-608"""
+    spec = tiny_f16()
+    path = write(model_dir, "tiny_llama3", spec, 3)
+    d = CudaLlamaDecoder.load(path, 32, 8)
+
+    def code_of(fn):
+        with pytest.raises(DoomsError) as e:
+            fn()
+        return e.value.code
+
+    assert code_of(d.pending_token) == L.INVALID_ARGUMENT
+    assert code_of(d.logits) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.generate(4, 2, lambda t: True)) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.eval_tokens([])) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.eval_tokens([-1])) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.eval_tokens([50])) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.eval_embeddings(None, 1)) == L.INVALID_ARGUMENT
+    nan_row = np.zeros((1, 64), dtype=np.float32)
+    nan_row[0, 0] = np.nan
+    assert code_of(lambda: d.eval_embeddings(nan_row)) == L.INVALID_ARGUMENT
+    d.eval_tokens(K_PROMPT)
+    assert code_of(lambda: d.generate(0, 1, lambda t: True)) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.generate(4, 0, lambda t: True)) == L.INVALID_ARGUMENT
+    assert code_of(lambda: d.generate(32, 1, lambda t: True)) == L.RESOURCE_EXHAUSTED      # 11 + 31 > 32
+    calls = []
+    d.generate(10, 4, lambda t: calls.append(t) or len(calls) < 3)
+    assert len(calls) == 3
+    assert d.position() == len(K_PROMPT) + 2
+    d.reset()
+    assert code_of(lambda: d.eval_tokens([1] * 40)) == L.RESOURCE_EXHAUSTED
+
+
+def test_profile_pass_reports_every_kind(model_dir):
+    path = write(model_dir, "tiny_llama", tiny_f16(), 1)
+    d = CudaLlamaDecoder.load(path, 128, 64)
+    with pytest.raises(DoomsError):
+        d.profile_pass(1)                      # nothing evaluated yet
+    d.eval_tokens(K_PROMPT)
+    before = d.position()
+    kinds = {k["kind"]: k for k in d.profile_pass(1)}
+    for kind in ("embed", "qkv", "attention", "attn_output", "gate_up", "ffn_down", "output", "argmax"):
+        assert kind in kinds and kinds[kind]["dispatches"] >= 1 and kinds[kind]["gpu_ms"] >= 0
+    assert d.position() == before
+    kinds = {k["kind"] for k in d.profile_pass(16)}
+    assert {"embed", "qkv", "attention", "gate_up"} <= kinds
+    with pytest.raises(DoomsError):
+        d.profile_pass(65)
