@@ -94,7 +94,8 @@ def test_gate_up_matches_the_oracle(dtype):
     u = oracle_matrix(dtype, bu, rows, cols).astype(np.float64) @ x
     want = g / (1 + np.exp(-g)) * u
     d_h = torch.empty(rows, dtype=torch.float32, device="cuda")
-    L.check(L.lib().dooms_cuda_gate_up(dtype, dev(bg).data_ptr(), dev(bu).data_ptr(), dev(x).data_ptr(), d_h.data_ptr(), rows, cols, None))
+    d_g, d_u, d_x = dev(bg), dev(bu), dev(x)          # named: the device buffers must outlive the launch
+    L.check(L.lib().dooms_cuda_gate_up(dtype, d_g.data_ptr(), d_u.data_ptr(), d_x.data_ptr(), d_h.data_ptr(), rows, cols, None))
     torch.cuda.synchronize()
     got = d_h.cpu().numpy()
     assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 1e-5
@@ -107,14 +108,16 @@ def test_rms_norm_matches_the_oracle():
     xd = x.astype(np.float64)
     want = xd / np.sqrt((xd ** 2).mean(axis=1, keepdims=True) + 1e-6) * gamma
     d_out = torch.empty(5, 896, dtype=torch.float32, device="cuda")
-    L.check(L.lib().dooms_cuda_rms_norm(dev(x).data_ptr(), dev(gamma).data_ptr(), d_out.data_ptr(), 5, 896, 1e-6, None))
+    d_x, d_g = dev(x), dev(gamma)
+    L.check(L.lib().dooms_cuda_rms_norm(d_x.data_ptr(), d_g.data_ptr(), d_out.data_ptr(), 5, 896, 1e-6, None))
     torch.cuda.synchronize()
     assert np.abs(d_out.cpu().numpy() - want).max() < 1e-5
 
 
 def gpu_argmax(v):
     d_out = torch.zeros(1, dtype=torch.int32, device="cuda")
-    L.check(L.lib().dooms_cuda_argmax(dev(v).data_ptr(), v.size, d_out.data_ptr(), None))
+    d_v = dev(v)
+    L.check(L.lib().dooms_cuda_argmax(d_v.data_ptr(), v.size, d_out.data_ptr(), None))
     torch.cuda.synchronize()
     return int(d_out.item())
 
@@ -155,7 +158,8 @@ def test_split_attention_matches_the_oracle(n_head, n_head_kv, head_dim, n_keys)
     nbytes = L.lib().dooms_cuda_attention_scratch_bytes(n_head, head_dim, n_keys)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     d_out = torch.empty(n_head, head_dim, dtype=torch.float32, device="cuda")
-    L.check(L.lib().dooms_cuda_attention_decode(dev(q).data_ptr(), dev(kc).data_ptr(), dev(vc).data_ptr(), d_out.data_ptr(), scratch.data_ptr(), n_head,
+    d_q, d_k, d_v = dev(q), dev(kc), dev(vc)
+    L.check(L.lib().dooms_cuda_attention_decode(d_q.data_ptr(), d_k.data_ptr(), d_v.data_ptr(), d_out.data_ptr(), scratch.data_ptr(), n_head,
                                                 n_head_kv, head_dim, n_keys, None))
     torch.cuda.synchronize()
     assert np.abs(d_out.cpu().numpy() - want).max() < 2e-5
