@@ -110,6 +110,21 @@ int32_t launch_result(cudaError_t e, const char * what) {
     return fail(DOOMS_INTERNAL, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// The staged q4_0 GEMV on an f32 input: split the input into the per-device scratch, then the kernel. The scratch is shared by every call on the device, so
+// calls on different streams must not overlap.
+int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t st,
+                  const char * what) {
+    void * scratch = nullptr;
+    const size_t xq_bytes = (cuda::quantized_x_bytes(cols) + 15) & ~size_t(15);
+    const Status ss = scratch_for(xq_bytes + 16, &scratch);
+    if (!ss.is_ok()) return done(ss);
+    int32_t * error = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(scratch) + xq_bytes);
+    cudaError_t e = cudaMemsetAsync(error, 0, 4, st);
+    if (e == cudaSuccess) e = cuda::launch_quantize_x(x, cols, scratch, st);
+    if (e == cudaSuccess) e = cuda::launch_gemv_q4_0(w, w2, scratch, y, bias, rows, cols, flags, error, st);
+    return launch_result(e, what);
+}
+
 bool matrix_dtype(int32_t dt) { return dt == DOOMS_F16 || dt == DOOMS_Q4_0 || dt == DOOMS_Q5_0 || dt == DOOMS_Q8_0 || dt == DOOMS_Q4_K || dt == DOOMS_Q6_K; }
 
 }  // namespace
@@ -348,7 +363,9 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
         return fail(DOOMS_INVALID_ARGUMENT, "matvec: NULL pointer, unknown flag, or rows that are not whole blocks of at least 32 elements");
     }
     if (rows == 0) return DOOMS_OK;
-    return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, static_cast<cudaStream_t>(stream)), "matvec");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, st, "matvec");
+    return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, st), "matvec");
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
@@ -358,7 +375,11 @@ DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, cons
         return fail(DOOMS_INVALID_ARGUMENT, "gate_up: NULL pointer or rows that are not whole blocks of at least 32 elements");
     }
     if (rows == 0) return DOOMS_OK;
-    return launch_result(cuda::launch_gate_up(dtype, d_wg, d_wu, d_x, d_h, rows, cols, static_cast<cudaStream_t>(stream)), "gate_up");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_wg, rows, cols) && cuda::gemv_q4_0_supported(d_wu, rows, cols)) {
+        return fast_q4_0(d_wg, d_wu, d_x, d_h, nullptr, rows, cols, 0u, st, "gate_up");
+    }
+    return launch_result(cuda::launch_gate_up(dtype, d_wg, d_wu, d_x, d_h, rows, cols, st), "gate_up");
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream) {

@@ -69,9 +69,12 @@ struct CudaLlamaDecoder::Impl {
     size_t cache_layer_elems = 0, kv_bytes = 0;
     float * x = nullptr, * xn = nullptr, * qkv = nullptr, * attn = nullptr, * h = nullptr, * red = nullptr, * logits_buf = nullptr, * part = nullptr;
     void * argmax_part = nullptr;
+    uint8_t * xq = nullptr;        // the current projection input split into int8 limbs (the staged q4_0 GEMV's operand)
+    const float * xq_of = nullptr; // which f32 vector xq currently holds
     int32_t * tokens = nullptr, * in_tokens = nullptr, * host_tokens = nullptr, * host_in = nullptr;
     float * host_x = nullptr;     // pinned staging for eval_embeddings
     DevState * state = nullptr;
+    int32_t * host_error = nullptr;   // mapped pinned word a kernel sets when a bounded wait ran out
     int splits = 1;
     int32_t pos = 0;
     bool has_pending = false;
@@ -96,10 +99,10 @@ struct CudaLlamaDecoder::Impl {
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
         for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part,
-                         argmax_part, (void *)tokens, (void *)in_tokens, (void *)state}) {
+                         argmax_part, (void *)xq, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
-        for (void * p : {(void *)host_tokens, (void *)host_in, (void *)host_x}) if (p) cudaFreeHost(p);
+        for (void * p : {(void *)host_tokens, (void *)host_in, (void *)host_x, (void *)host_error}) if (p) cudaFreeHost(p);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -112,7 +115,12 @@ struct CudaLlamaDecoder::Impl {
 
     Status wait_idle() {
         if (!failed.is_ok()) return failed;
-        return check(cudaStreamSynchronize(stream), "a CUDA kernel of the decoder failed");
+        DOOMS_RETURN_IF_ERROR(check(cudaStreamSynchronize(stream), "a CUDA kernel of the decoder failed"));
+        if (host_error && *host_error != 0) {   // a kernel gave up on a bounded wait and said so
+            failed = internal_error("a decoder kernel timed out waiting for a bulk copy (error flag " + std::to_string(*host_error) + ")");
+            return failed;
+        }
+        return Status();
     }
 
     // Every launch goes through here: counted, and timed on its own when a profile is being taken.
@@ -144,8 +152,28 @@ struct CudaLlamaDecoder::Impl {
         run("all_reduce", [&] { return nccl.AllReduce(buf, buf, count, NcclApi::kFloat32, NcclApi::kSum, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown; });
     }
 
+    bool fast(const MatDev & w) const { return w.dt == DType::Q4_0 && cuda::gemv_q4_0_supported(w.ptr, w.rows, w.cols); }
+    // The staged q4_0 kernels read their input split into int8 limbs; one split serves every projection of the same input.
+    void split_input(const float * in, int64_t cols) {
+        if (xq_of == in) return;
+        run("split", [&] { return cuda::launch_quantize_x(in, cols, xq, stream); });
+        xq_of = in;
+    }
     void matvec(const char * kind, const MatDev & w, const float * in, float * out, const float * bias, uint32_t flags) {
+        if (fast(w)) {
+            split_input(in, w.cols);
+            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, xq, out, bias, w.rows, w.cols, flags, host_error, stream); });
+            return;
+        }
         run(kind, [&] { return cuda::launch_matvec(int(w.dt), w.ptr, in, out, bias, w.rows, w.cols, flags, stream); });
+    }
+    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, float * out) {
+        if (fast(wg) && fast(wu)) {
+            split_input(in, wg.cols);
+            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, xq, out, nullptr, wg.rows, wg.cols, 0u, host_error, stream); });
+            return;
+        }
+        run("gate_up", [&] { return cuda::launch_gate_up(int(wg.dt), wg.ptr, wu.ptr, in, out, wg.rows, wg.cols, stream); });
     }
     void matmul(const char * kind, const MatDev & w, const MatDev * w2, const float * in, int64_t in_stride, float * out, int64_t out_stride, const float * bias, int M,
                 uint32_t flags) {
@@ -171,14 +199,18 @@ struct CudaLlamaDecoder::Impl {
             float * o_dst = single ? x : red;
             const uint32_t o_flags = single ? kFlagAccumulate : 0u;
             run("norm", [&] { return cuda::launch_rms_norm(x, L.attn_norm, xn, nullptr, M, E, cfg.rms_eps, stream); });
+            xq_of = nullptr;   // every producer of a projection input invalidates the split copy
             if (M == 1) {
                 for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
                 run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, state, 0, splits, as, stream); });
+                xq_of = nullptr;
                 matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
                 run("norm", [&] { return cuda::launch_rms_norm(x, L.ffn_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
-                run("gate_up", [&] { return cuda::launch_gate_up(int(L.ffn_gate.dt), L.ffn_gate.ptr, L.ffn_up.ptr, xn, h, L.ffn_gate.rows, L.ffn_gate.cols, stream); });
+                xq_of = nullptr;
+                gate_up(L.ffn_gate, L.ffn_up, xn, h);
+                xq_of = nullptr;
                 matvec("ffn_down", L.ffn_down, h, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
             } else {
@@ -197,6 +229,7 @@ struct CudaLlamaDecoder::Impl {
         }
         // The logits of the last row only (metal_llama_decoder.mm:375).
         run("norm", [&] { return cuda::launch_rms_norm(x + size_t(M - 1) * E, output_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
+        xq_of = nullptr;
         if (output.rows > 0) matvec("output", output, xn, logits_buf + vocab_row0, nullptr, 0u);
         if (tp > 1) {
             run("all_gather", [&] {
@@ -523,6 +556,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
+                                    "the split projection input"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(&m.argmax_part, size_t(cuda::argmax_blocks(int64_t(logits_floats))) * 8, "the argmax partial results"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tokens), (size_t(c.n_ctx) + 2) * 4, "the token ring"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.in_tokens), B * 4, "the input tokens"));
@@ -535,10 +570,12 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     }
     if (cudaHostAlloc(reinterpret_cast<void **>(&m.host_tokens), (size_t(c.n_ctx) + 2) * 4, cudaHostAllocMapped) != cudaSuccess ||
         cudaHostAlloc(reinterpret_cast<void **>(&m.host_in), B * 4, cudaHostAllocDefault) != cudaSuccess ||
+        cudaHostAlloc(reinterpret_cast<void **>(&m.host_error), 64, cudaHostAllocMapped) != cudaSuccess ||
         cudaHostAlloc(reinterpret_cast<void **>(&m.host_x), B * size_t(E) * 4, cudaHostAllocDefault) != cudaSuccess) {
         (void)cudaGetLastError();
         return resource_exhausted("could not allocate pinned host memory for the decoder");
     }
+    *m.host_error = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
     m.tm.weight_bytes = int64_t(m.matrix_bytes);
     m.tm.kv_bytes = int64_t(m.kv_bytes);

@@ -1,0 +1,369 @@
+// Decode GEMV on q4_0 rows, built for HBM speed on B200.
+//
+// The work per weight has to stay near one instruction for the kernel to keep up with ~44 GB/s per SM, so the dot products run on the tensor cores'
+// integer path and the CUDA cores only unpack nibbles and apply block scales:
+//   * The input vector arrives pre-split (k_quantize_x): per 32-element block a power-of-two scale s and, for every element, the 28-bit fixed-point value
+//     X = rint(x / s * 2^26) cut into four balanced base-128 digits (int8 "limbs"). Elements within 8x of the block's largest keep every f32 bit; the rest
+//     are exact to 2^-27 of it, so the product sums are exact integers and the only rounding left is the f32 accumulation over blocks.
+//   * A weight nibble q becomes the int8 value 16 (q - 8) with two logic ops per four weights (shift the nibble into the byte's high half, flip its top
+//     bit), exactly the operand layout mma.m16n8k32.s8 wants for a q4_0 block: low nibbles are elements 0..15, high nibbles 16..31.
+//   * One MMA per block: 16 rows x 32 elements x (4 limbs of this block | 4 limbs of the next block's slot). Two consecutive blocks accumulate into one
+//     8-column fragment so that all 32 lanes have one (row, block, limb pair) to scale: acc += float(c_lo + 128 c_hi) * (d * s * 2^-30 or 2^-16).
+//   * Each warp owns 16 rows and streams them through its own ring of shared-memory stages filled by 1-D bulk (TMA) copies of the rows' bytes exactly as
+//     they lie in the GGUF file (18-byte blocks, 2-byte aligned): no repacking, 16-byte aligned covers, per-row padding that keeps the 8 rows of a
+//     fragment on different banks. No block-wide synchronisation after the prologue.
+// The block formulas are the reference's (src/backend/metal/llama_kernels.h:1012-1040: value = d (q - 8)); matvec1q / gate_up1q there are the kernels this
+// replaces (llama_kernels.h:1197-1269).
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace dooms {
+namespace cuda {
+
+using namespace dooms::dev;
+
+namespace {
+
+constexpr int kTileRows = 16;
+constexpr int kBlockBytes = 18;
+constexpr int kMaxPieces = 10;      // 16-byte pieces of a stage one lane copies: 16 rows x at most 20 pieces per row / 32 lanes
+
+struct GemvQ40Params {
+    const uint8_t * W;      // rows x (cols / 32) blocks
+    const uint8_t * W2;     // gate/up: the second matrix (up); nullptr for a plain projection
+    const uint8_t * xq;     // the split input: (cols / 32) x 128 limb bytes, then (cols / 32) x 2 floats
+    float * y;
+    const float * bias;
+    int64_t rows;
+    int cols;
+    uint32_t flags;
+    int cbk;                // blocks per chunk (even)
+    int nchunks;            // chunks per row
+    int stride;             // bytes between the rows of a stage (multiple of 16, = 16 mod 128)
+    int upr;                // 16-byte pieces copied per row of a stage (the aligned cover of a chunk)
+};
+
+__device__ __forceinline__ float warp_max_f(float v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// x[K] (f32) -> xq. One warp per 32-element block.
+__global__ void __launch_bounds__(256) k_quantize_x(const float * x, int nb, uint8_t * xq) {
+    const int lane = threadIdx.x % 32;
+    const int blk = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (blk >= nb) return;
+    const float v = x[blk * 32 + lane];
+    const float amax = warp_max_f(fabsf(v));
+    uint32_t eb = (__float_as_uint(amax) >> 23) & 0xFFu;       // biased exponent of the largest magnitude
+    eb = max(eb, 30u);                                         // blocks below 2^-97 are treated as that small: their limbs come out zero
+    eb = min(eb, 250u);
+    const float inv = __uint_as_float((279u - eb) << 23);      // 2^26 / s with s = 2^(eb - 126) > amax
+    int X = __float2int_rn(v * inv);
+    int l[4];
+    #pragma unroll
+    for (int i = 0; i < 3; i++) { l[i] = ((X + 64) & 127) - 64; X = (X - l[i]) >> 7; }
+    l[3] = X;
+    const int pos = ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);      // lane t of a fragment finds its 8 bytes of a limb contiguous at 8 t
+    uint8_t * dst = xq + size_t(blk) * 128;
+    #pragma unroll
+    for (int i = 0; i < 4; i++) dst[i * 32 + pos] = uint8_t(int8_t(l[i]));
+    if (lane == 0) {
+        float * sx = reinterpret_cast<float *>(xq + size_t(nb) * 128) + blk * 2;
+        sx[0] = __uint_as_float((eb - 29u) << 23);             // s * 2^-26 / 16: the weights carry a factor 16
+        sx[1] = __uint_as_float((eb - 15u) << 23);             // the same for the upper limb pair (x 2^14)
+    }
+}
+
+
+// One pair of consecutive blocks (even block at byte PAIR * 36 of the chunk row, odd block 18 bytes later) of the lane's two rows. Rows and chunks start
+// 4-byte aligned (an even number of 18-byte blocks each), so the even block's quants straddle two words and the odd block's are one aligned word.
+template <int PAIR>
+__device__ __forceinline__ void pair_step(uint32_t a0, uint32_t a1, uint32_t d0a, uint32_t d1a, uint32_t ba, uint32_t sa, bool first, float & acc0, float & acc1) {
+    constexpr int O = PAIR * 36;
+    const uint2 bv = lds64<PAIR * 256>(ba);
+    const float sx = ldsf<PAIR * 16>(sa);
+    const uint32_t e0 = __byte_perm(lds32<O>(a0), lds32<O + 4>(a0), 0x5432), e1 = __byte_perm(lds32<O>(a1), lds32<O + 4>(a1), 0x5432);
+    const uint32_t o0 = lds32<O + 20>(a0), o1 = lds32<O + 20>(a1);
+    const float d0 = half_bits_to_float(lds16<O>(d0a)), d1 = half_bits_to_float(lds16<O>(d1a));
+    int c[4];
+    mma_s8_16832_zero(c, lop3_and_xor(e0 << 4, 0xF0F0F0F0u, 0x80808080u), lop3_and_xor(e1 << 4, 0xF0F0F0F0u, 0x80808080u),
+                      lop3_and_xor(e0, 0xF0F0F0F0u, 0x80808080u), lop3_and_xor(e1, 0xF0F0F0F0u, 0x80808080u), first ? bv.x : 0u, first ? bv.y : 0u);
+    mma_s8_16832(c, lop3_and_xor(o0 << 4, 0xF0F0F0F0u, 0x80808080u), lop3_and_xor(o1 << 4, 0xF0F0F0F0u, 0x80808080u),
+                 lop3_and_xor(o0, 0xF0F0F0F0u, 0x80808080u), lop3_and_xor(o1, 0xF0F0F0F0u, 0x80808080u), first ? 0u : bv.x, first ? 0u : bv.y);
+    acc0 = fmaf(float(c[0] + 128 * c[1]), d0 * sx, acc0);
+    acc1 = fmaf(float(c[2] + 128 * c[3]), d1 * sx, acc1);
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Grid: one block per SM, each with an equal share of the rows (so every SM pulls the same number of bytes, to within a row). A block's rows form tiles of
+// 16; the units of work are (tile, matrix, chunk of the row), dealt round-robin to the block's warps, each of which streams its units through its own ring
+// of stages with 16-byte asynchronous copies (commit / wait groups: a waiting warp sleeps in hardware, there is no polling and nothing that can hang).
+// In a stage copy lanes 2r and 2r+1 fetch row r, 32 bytes per step (whole sectors), so a lane keeps one source pointer and the loop has no bookkeeping.
+// A warp adds what it computed for a (tile, matrix) into its own slot of a small shared table; after one block-wide barrier the table's slots are summed
+// in a fixed order, so the result does not depend on timing.
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
+    const int nb = p.cols / 32;
+    const int nmat = p.W2 ? 2 : 1;
+    const uint32_t RB = uint32_t(nb) * kBlockBytes;
+    const uint32_t CB = uint32_t(p.cbk) * kBlockBytes;
+
+    // this block's rows
+    const int64_t R0 = p.rows * blockIdx.x / gridDim.x, R1 = p.rows * (blockIdx.x + 1) / gridDim.x;
+    const int nrows = int(R1 - R0);
+    const int ntiles = (nrows + kTileRows - 1) / kTileRows;
+    const int total_units = ntiles * nmat * p.nchunks;
+    const int my_units = warp < total_units ? (total_units - warp - 1) / WARPS + 1 : 0;
+
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t xl = smem_base;                                                  // limbs: nb x 128, then the block scales: nb x 2 floats
+    const uint32_t sxp = xl + uint32_t(nb) * 128u;
+    const uint32_t stride = uint32_t(p.stride);
+    const uint32_t stage_bytes = uint32_t(kTileRows) * stride;
+    const uint32_t stages_base = xl + ((uint32_t(nb) * 136u + 127u) & ~127u);
+    const uint32_t my_stages = stages_base + uint32_t(warp) * STAGES * stage_bytes;
+    float * partial = reinterpret_cast<float *>(smem + (stages_base - smem_base) + size_t(WARPS) * STAGES * stage_bytes);   // [tile][mat][warp][16]
+
+    // Unit u of this warp is unit warp + u WARPS of the block: (tile * nmat + mat) = that / nchunks, chunk = that % nchunks. Going to the next unit adds
+    // WARPS: a fixed step in the chunk index plus a carry.
+    const int step_tm = WARPS / p.nchunks, step_chunk = WARPS % p.nchunks;
+    int f_tm = warp / p.nchunks, f_chunk = warp % p.nchunks, f_slot = 0;      // the unit being fetched
+    int u_tm = f_tm, u_chunk = f_chunk, u_slot = 0;                           // the unit being used
+
+    // Stage copy: a stage is 16 rows x p.upr 16-byte pieces (the aligned cover of the chunk's bytes), dealt to the lanes in order, so that one instruction
+    // copies 512 consecutive bytes of a row or two. Which (row, piece) a lane copies is the same for every stage: a table of packed (source offset from
+    // the tile's first row << 13 | offset in the stage), built once. Rows past the block's range repeat its last row (the same bytes again: no extra
+    // traffic from memory; their results are dropped), which only the block's last tile needs: it has its own table.
+    uint32_t tab[kMaxPieces], tab_last[kMaxPieces];
+    {
+        const int last = nrows - 1 - (ntiles - 1) * kTileRows;
+        int row = 0, col = lane;
+        #pragma unroll
+        for (int k = 0; k < kMaxPieces; k++) {
+            while (col >= p.upr) { col -= p.upr; row++; }
+            const uint32_t dst = uint32_t(row) * stride + uint32_t(col) * 16u;
+            tab[k] = row < kTileRows ? ((uint32_t(row) * RB + uint32_t(col) * 16u) << 13) | dst : 0xFFFFFFFFu;
+            tab_last[k] = row < kTileRows ? ((uint32_t(min(row, last)) * RB + uint32_t(col) * 16u) << 13) | dst : 0xFFFFFFFFu;
+            col += 32;
+        }
+    }
+    auto fetch = [&]() {
+        const int tile = nmat == 2 ? f_tm >> 1 : f_tm, mat = nmat == 2 ? f_tm & 1 : 0;
+        const uint8_t * base = (mat ? p.W2 : p.W) + (R0 + tile * kTileRows) * int64_t(RB) + uint32_t(f_chunk) * CB;      // the tile's first row, this chunk
+        const uint32_t lo = uint32_t(reinterpret_cast<uintptr_t>(base));
+        const uint32_t dst0 = my_stages + uint32_t(f_slot) * stage_bytes;
+        const bool is_last = tile == ntiles - 1;
+        #pragma unroll
+        for (int k = 0; k < kMaxPieces; k++) {
+            const uint32_t e = is_last ? tab_last[k] : tab[k];
+            if (e != 0xFFFFFFFFu) {
+                const uint32_t off = e >> 13;
+                cp_async16(dst0 + (e & 0x1FFFu), base + (int32_t(off) - int32_t((lo + off) & 15u)));
+            }
+        }
+        f_chunk += step_chunk;
+        f_tm += step_tm;
+        if (f_chunk >= p.nchunks) { f_chunk -= p.nchunks; f_tm++; }
+        if (++f_slot == STAGES) f_slot = 0;
+    };
+
+    int fetched = 0;
+    // the split input first (its own group), then the first STAGES - 1 stages
+    for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
+    cp_async_commit();
+    #pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        if (fetched < my_units) { fetch(); fetched++; }
+        cp_async_commit();
+    }
+    for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
+    cp_async_wait<STAGES - 1>();      // the split input has landed (this thread's part)
+    __syncthreads();
+
+    const bool first = g < 4;
+    const uint32_t b_lane = xl + uint32_t(g >> 2) * 128u + uint32_t(g & 3) * 32u + uint32_t(t) * 8u;
+    const uint32_t s_lane = sxp + uint32_t(t >> 1) * 8u + uint32_t(t & 1) * 4u;
+    const uint32_t row_lane0 = uint32_t(g) * stride, row_lane1 = uint32_t(g + 8) * stride;
+    const uint32_t w_lo = uint32_t(reinterpret_cast<uintptr_t>(p.W)) + uint32_t(R0) * RB, w2_lo = uint32_t(reinterpret_cast<uintptr_t>(p.W2)) + uint32_t(R0) * RB;
+    const int npairs = p.cbk / 2;
+    float acc0 = 0.f, acc1 = 0.f;
+    int acc_tm = u_tm;
+    // Adds the lane quad's sums for rows g, g + 8 of (tile, matrix) acc_tm into this warp's slot of the table.
+    auto flush = [&]() {
+        float s0 = acc0, s1 = acc1;
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        if (t == 0) {
+            float * dst = partial + (acc_tm * WARPS + warp) * kTileRows;
+            dst[g] += s0;
+            dst[g + 8] += s1;
+        }
+        acc0 = 0.f;
+        acc1 = 0.f;
+    };
+    for (int u = 0; u < my_units; u++) {
+        cp_async_wait<STAGES - 2>();      // stage u has landed (this lane's pieces) ...
+        __syncwarp();                     // ... and every lane's; also: every lane is done reading the slot refilled next
+        if (fetched < my_units) { fetch(); fetched++; }
+        cp_async_commit();
+        if (u_tm != acc_tm) { flush(); acc_tm = u_tm; }
+        const int tile = nmat == 2 ? u_tm >> 1 : u_tm;
+        // where the rows' bytes start inside their stage rows: the low four address bits of each row's chunk
+        const int last = nrows - 1 - tile * kTileRows;
+        const uint32_t lo = ((nmat == 2 && (u_tm & 1)) ? w2_lo : w_lo) + uint32_t(tile * kTileRows) * RB + uint32_t(u_chunk) * CB;
+        const uint32_t st = my_stages + uint32_t(u_slot) * stage_bytes;
+        const uint32_t row0 = st + row_lane0 + ((lo + uint32_t(min(g, last)) * RB) & 15u);
+        const uint32_t row1 = st + row_lane1 + ((lo + uint32_t(min(g + 8, last)) * RB) & 15u);
+        uint32_t a0 = row0 + 4u * t, a1 = row1 + 4u * t, d0a = row0 + 18u * (t >> 1), d1a = row1 + 18u * (t >> 1);
+        uint32_t ba = b_lane + uint32_t(u_chunk * p.cbk) * 128u, sa = s_lane + uint32_t(u_chunk * p.cbk) * 8u;
+        int pr = (p.flags & 0x100u) ? npairs : 0;      // TEMPORARY probe: skip the arithmetic, keep the copies
+        #pragma unroll 1
+        for (; pr + 4 <= npairs; pr += 4) {
+            pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+            pair_step<1>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+            pair_step<2>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+            pair_step<3>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+            a0 += 144; a1 += 144; d0a += 144; d1a += 144; ba += 1024; sa += 64;
+        }
+        #pragma unroll 1
+        for (; pr < npairs; pr++) {
+            pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+            a0 += 36; a1 += 36; d0a += 36; d1a += 36; ba += 256; sa += 16;
+        }
+        u_chunk += step_chunk;
+        u_tm += step_tm;
+        if (u_chunk >= p.nchunks) { u_chunk -= p.nchunks; u_tm++; }
+        if (++u_slot == STAGES) u_slot = 0;
+    }
+    cp_async_wait<0>();
+    if (my_units > 0) flush();
+    __syncthreads();
+    // the rows of this block: the warps' shares summed in warp order, then the epilogue
+    for (int r = threadIdx.x; r < nrows; r += WARPS * 32) {
+        const float * src = partial + size_t(r / kTileRows) * nmat * WARPS * kTileRows + (r % kTileRows);
+        float s = 0.f, s2 = 0.f;
+        #pragma unroll
+        for (int w = 0; w < WARPS; w++) s += src[w * kTileRows];
+        if (nmat == 2) {
+            #pragma unroll
+            for (int w = 0; w < WARPS; w++) s2 += src[(WARPS + w) * kTileRows];
+            s = s / (1.f + expf(-s)) * s2;
+        }
+        const int64_t row = R0 + r;
+        if (p.flags & kFlagBias) s += p.bias[row];
+        p.y[row] = (p.flags & kFlagAccumulate) ? p.y[row] + s : s;
+    }
+}
+
+constexpr size_t kSmemLimit = 224 * 1024;
+constexpr int kMaxTilesPerBlock = 8;        // the table of per-warp sums holds this many 16-row tiles of two matrices
+constexpr size_t partial_bytes(int warps) { return size_t(kMaxTilesPerBlock) * 2 * warps * kTileRows * sizeof(float); }
+
+struct Plan { int cbk, nchunks, stride, stages, warps; size_t smem; bool ok; };
+
+// Chunks of an even number of blocks that divides the row; the row stride in a stage is an odd multiple of 16 bytes so that the 8 rows of a fragment fall
+// on different banks. Preference: 16 warps (four per scheduler hide the latencies of the unpack / MMA / scale chain) with at least two stages each and
+// chunks as close to 16 blocks as shared memory allows; 8 warps otherwise.
+Plan plan_for(int64_t cols) {
+    Plan best{};
+    const int nb = int(cols / 32);
+    if (cols % 64 != 0 || nb < 2) return best;
+    const size_t fixed = (size_t(nb) * 136 + 127) & ~size_t(127);
+    const char * force = getenv("DOOMS_GEMV_CBK");
+    const char * force_warps = getenv("DOOMS_GEMV_WARPS");
+    int best_score = -1;
+    for (int warps : {16, 8}) {
+        if (force_warps && warps != atoi(force_warps)) continue;
+        for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
+            if (nb % cbk) continue;
+            if (force && cbk != atoi(force)) continue;
+            int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
+            if (stride % 32 != 16) stride += 16;
+            if ((cbk * kBlockBytes + 30) / 16 * kTileRows > kMaxPieces * 32 || kTileRows * stride >= (1 << 13)) continue;
+            int stages = 0;
+            for (int st = 4; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps) <= kSmemLimit) { stages = st; break; }
+            if (!stages) continue;
+            const int score = (warps == 16 ? 10000 : 0) + cbk * 100 + stages;
+            if (score > best_score) {
+                best_score = score;
+                best = Plan{cbk, nb / cbk, stride, stages, warps, fixed + size_t(warps) * stages * kTileRows * stride + partial_bytes(warps), true};
+            }
+        }
+    }
+    return best;
+}
+
+template <int WARPS, int STAGES>
+cudaError_t launch_with(const GemvQ40Params & p, size_t smem, unsigned grid, cudaStream_t stream) {
+    static int configured_device = -1;      // the attribute is per function and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
+        if (e != cudaSuccess) return e;
+        configured_device = dev;
+    }
+    k_gemv_q4_0<WARPS, STAGES><<<grid, WARPS * 32, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols) {
+    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols).ok;
+}
+
+size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }
+
+cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
+    const int nb = int(cols / 32);
+    k_quantize_x<<<(nb + 7) / 8, 256, 0, stream>>>(x, nb, static_cast<uint8_t *>(xq));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
+                             int32_t * error, cudaStream_t stream) {
+    const Plan pl = plan_for(cols);
+    if (!pl.ok) return cudaErrorInvalidValue;
+    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), y, bias, rows, int(cols), flags,
+                    pl.cbk, pl.nchunks, pl.stride, 0};
+    (void)error;
+    if (getenv("DOOMS_GEMV_NOCOMPUTE")) p.flags |= 0x100u;
+    // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
+    const int64_t row_bytes = cols / 32 * kBlockBytes;
+    const int chunk_bytes = pl.cbk * kBlockBytes;
+    p.upr = (row_bytes % 16 == 0 && chunk_bytes % 16 == 0) ? chunk_bytes / 16 : (chunk_bytes + 30) / 16;
+    // one block per SM; more (whole multiples) only when a block's share would exceed the table of kMaxTilesPerBlock tiles
+    const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
+    const int64_t waves = (rows + 148 * max_rows - 1) / (148 * max_rows);
+    const unsigned grid = unsigned(std::min<int64_t>(148 * waves, rows));
+    if (pl.warps == 16) {
+        switch (pl.stages) {
+            case 4: return launch_with<16, 4>(p, pl.smem, grid, stream);
+            case 3: return launch_with<16, 3>(p, pl.smem, grid, stream);
+            default: return launch_with<16, 2>(p, pl.smem, grid, stream);
+        }
+    }
+    switch (pl.stages) {
+        case 4: return launch_with<8, 4>(p, pl.smem, grid, stream);
+        case 3: return launch_with<8, 3>(p, pl.smem, grid, stream);
+        default: return launch_with<8, 2>(p, pl.smem, grid, stream);
+    }
+}
+
+}  // namespace cuda
+}  // namespace dooms

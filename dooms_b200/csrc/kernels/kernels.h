@@ -65,5 +65,15 @@ cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int
 // The same reduction without a state: *out = argmax.
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream);
 
+// ---- the fast decode GEMV on q4_0 rows (gemv_q4_0.cu) ----
+// The input vector split into int8 limbs: quantized_x_bytes(cols) bytes at a 16-byte aligned address, written by launch_quantize_x.
+size_t quantized_x_bytes(int64_t cols);
+cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream);
+// Whether launch_gemv_q4_0 takes this matrix: a 16-byte aligned base and rows of an even number of blocks that fit the kernel's shared memory plan.
+bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
+// y[r] (+)= W[r] . x (+ bias[r]); with W2: y[r] = silu(W[r] . x) * (W2[r] . x). x comes as xq. *error is set to 1 if a bulk copy never arrived.
+cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
+                             int32_t * error, cudaStream_t stream);
+
 }  // namespace cuda
 }  // namespace dooms
