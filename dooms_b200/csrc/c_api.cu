@@ -387,7 +387,7 @@ DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_ga
         return fail(DOOMS_INVALID_ARGUMENT, "rms_norm: NULL pointer, bad shape or eps <= 0");
     }
     if (rows == 0) return DOOMS_OK;
-    return launch_result(cuda::launch_rms_norm(d_x, d_gamma, d_out, nullptr, int(rows), int(cols), eps, static_cast<cudaStream_t>(stream)), "rms_norm");
+    return launch_result(cuda::launch_rms_norm(d_x, d_gamma, d_out, nullptr, nullptr, int(rows), int(cols), eps, static_cast<cudaStream_t>(stream)), "rms_norm");
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_argmax(const float * d_logits, int64_t n, int32_t * d_out, void * stream) {

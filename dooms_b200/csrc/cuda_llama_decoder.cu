@@ -167,6 +167,13 @@ struct CudaLlamaDecoder::Impl {
         }
         run(kind, [&] { return cuda::launch_matvec(int(w.dt), w.ptr, in, out, bias, w.rows, w.cols, flags, stream); });
     }
+    // xn = RMS-normalized rows; with split (one row) the kernel also leaves the row split for the staged q4_0 kernels (every producer of a projection
+    // input invalidates the split copy).
+    void norm(const float * in, const float * gamma, int M, bool split) {
+        const bool do_split = split && M == 1 && cfg.n_embd % 32 == 0;
+        run("norm", [&] { return cuda::launch_rms_norm(in, gamma, xn, nullptr, do_split ? xq : nullptr, M, cfg.n_embd, cfg.rms_eps, stream); });
+        xq_of = do_split ? xn : nullptr;
+    }
     void gate_up(const MatDev & wg, const MatDev & wu, const float * in, float * out) {
         if (fast(wg) && fast(wu)) {
             split_input(in, wg.cols);
@@ -198,8 +205,9 @@ struct CudaLlamaDecoder::Impl {
             __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
             float * o_dst = single ? x : red;
             const uint32_t o_flags = single ? kFlagAccumulate : 0u;
-            run("norm", [&] { return cuda::launch_rms_norm(x, L.attn_norm, xn, nullptr, M, E, cfg.rms_eps, stream); });
-            xq_of = nullptr;   // every producer of a projection input invalidates the split copy
+            bool qkv_fast = false;
+            for (const QkvPart & q : L.qkv) qkv_fast = qkv_fast || fast(q.w);
+            norm(x, L.attn_norm, M, qkv_fast);
             if (M == 1) {
                 for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
@@ -207,8 +215,7 @@ struct CudaLlamaDecoder::Impl {
                 xq_of = nullptr;
                 matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
-                run("norm", [&] { return cuda::launch_rms_norm(x, L.ffn_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
-                xq_of = nullptr;
+                norm(x, L.ffn_norm, 1, fast(L.ffn_gate) && fast(L.ffn_up));
                 gate_up(L.ffn_gate, L.ffn_up, xn, h);
                 xq_of = nullptr;
                 matvec("ffn_down", L.ffn_down, h, o_dst, nullptr, o_flags);
@@ -221,15 +228,14 @@ struct CudaLlamaDecoder::Impl {
                 run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, state, M, as, stream); });
                 matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
-                run("norm", [&] { return cuda::launch_rms_norm(x, L.ffn_norm, xn, nullptr, M, E, cfg.rms_eps, stream); });
+                norm(x, L.ffn_norm, M, false);
                 matmul("gate_up", L.ffn_gate, &L.ffn_up, xn, E, h, ff, nullptr, M, 0u);
                 matmul("ffn_down", L.ffn_down, nullptr, h, ff, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
             }
         }
         // The logits of the last row only (metal_llama_decoder.mm:375).
-        run("norm", [&] { return cuda::launch_rms_norm(x + size_t(M - 1) * E, output_norm, xn, nullptr, 1, E, cfg.rms_eps, stream); });
-        xq_of = nullptr;
+        norm(x + size_t(M - 1) * E, output_norm, 1, output.rows > 0 && fast(output));
         if (output.rows > 0) matvec("output", output, xn, logits_buf + vocab_row0, nullptr, 0u);
         if (tp > 1) {
             run("all_gather", [&] {

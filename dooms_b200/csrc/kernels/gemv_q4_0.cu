@@ -9,18 +9,18 @@
 //     bit), exactly the operand layout mma.m16n8k32.s8 wants for a q4_0 block: low nibbles are elements 0..15, high nibbles 16..31.
 //   * One MMA per block: 16 rows x 32 elements x (4 limbs of this block | 4 limbs of the next block's slot). Two consecutive blocks accumulate into one
 //     8-column fragment so that all 32 lanes have one (row, block, limb pair) to scale: acc += float(c_lo + 128 c_hi) * (d * s * 2^-30 or 2^-16).
-//   * Each warp owns 16 rows and streams them through its own ring of shared-memory stages filled by 1-D bulk (TMA) copies of the rows' bytes exactly as
-//     they lie in the GGUF file (18-byte blocks, 2-byte aligned): no repacking, 16-byte aligned covers, per-row padding that keeps the 8 rows of a
-//     fragment on different banks. No block-wide synchronisation after the prologue.
+//   * Each warp streams (16 rows x a chunk of the row) units through its own ring of shared-memory stages filled by 16-byte asynchronous copies of the
+//     rows' bytes exactly as they lie in the GGUF file (18-byte blocks, 2-byte aligned): no repacking, 16-byte aligned covers, a row stride in the stage
+//     that keeps the 8 rows of a fragment on different banks. One block-wide barrier after the prologue, one before the epilogue.
 // The block formulas are the reference's (src/backend/metal/llama_kernels.h:1012-1040: value = d (q - 8)); matvec1q / gate_up1q there are the kernels this
 // replaces (llama_kernels.h:1197-1269).
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "kernels.h"
 #include "ptx.cuh"
+#include "xsplit.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -48,39 +48,13 @@ struct GemvQ40Params {
     int upr;                // 16-byte pieces copied per row of a stage (the aligned cover of a chunk)
 };
 
-__device__ __forceinline__ float warp_max_f(float v) {
-    #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
 // x[K] (f32) -> xq. One warp per 32-element block.
 __global__ void __launch_bounds__(256) k_quantize_x(const float * x, int nb, uint8_t * xq) {
     const int lane = threadIdx.x % 32;
     const int blk = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (blk >= nb) return;
-    const float v = x[blk * 32 + lane];
-    const float amax = warp_max_f(fabsf(v));
-    uint32_t eb = (__float_as_uint(amax) >> 23) & 0xFFu;       // biased exponent of the largest magnitude
-    eb = max(eb, 30u);                                         // blocks below 2^-97 are treated as that small: their limbs come out zero
-    eb = min(eb, 250u);
-    const float inv = __uint_as_float((279u - eb) << 23);      // 2^26 / s with s = 2^(eb - 126) > amax
-    int X = __float2int_rn(v * inv);
-    int l[4];
-    #pragma unroll
-    for (int i = 0; i < 3; i++) { l[i] = ((X + 64) & 127) - 64; X = (X - l[i]) >> 7; }
-    l[3] = X;
-    const int pos = ((lane & 15) >> 2) * 8 + (lane >> 4) * 4 + (lane & 3);      // lane t of a fragment finds its 8 bytes of a limb contiguous at 8 t
-    uint8_t * dst = xq + size_t(blk) * 128;
-    #pragma unroll
-    for (int i = 0; i < 4; i++) dst[i * 32 + pos] = uint8_t(int8_t(l[i]));
-    if (lane == 0) {
-        float * sx = reinterpret_cast<float *>(xq + size_t(nb) * 128) + blk * 2;
-        sx[0] = __uint_as_float((eb - 29u) << 23);             // s * 2^-26 / 16: the weights carry a factor 16
-        sx[1] = __uint_as_float((eb - 15u) << 23);             // the same for the upper limb pair (x 2^14)
-    }
+    split_block(x[blk * 32 + lane], lane, blk, nb, xq);
 }
-
 
 // One pair of consecutive blocks (even block at byte PAIR * 36 of the chunk row, odd block 18 bytes later) of the lane's two rows. Rows and chunks start
 // 4-byte aligned (an even number of 18-byte blocks each), so the even block's quants straddle two words and the odd block's are one aligned word.
@@ -110,7 +84,6 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Grid: one block per SM, each with an equal share of the rows (so every SM pulls the same number of bytes, to within a row). A block's rows form tiles of
 // 16; the units of work are (tile, matrix, chunk of the row), dealt round-robin to the block's warps, each of which streams its units through its own ring
 // of stages with 16-byte asynchronous copies (commit / wait groups: a waiting warp sleeps in hardware, there is no polling and nothing that can hang).
-// In a stage copy lanes 2r and 2r+1 fetch row r, 32 bytes per step (whole sectors), so a lane keeps one source pointer and the loop has no bookkeeping.
 // A warp adds what it computed for a (tile, matrix) into its own slot of a small shared table; after one block-wide barrier the table's slots are summed
 // in a fixed order, so the result does not depend on timing.
 template <int WARPS, int STAGES>
@@ -230,7 +203,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         const uint32_t row1 = st + row_lane1 + ((lo + uint32_t(min(g + 8, last)) * RB) & 15u);
         uint32_t a0 = row0 + 4u * t, a1 = row1 + 4u * t, d0a = row0 + 18u * (t >> 1), d1a = row1 + 18u * (t >> 1);
         uint32_t ba = b_lane + uint32_t(u_chunk * p.cbk) * 128u, sa = s_lane + uint32_t(u_chunk * p.cbk) * 8u;
-        int pr = (p.flags & 0x100u) ? npairs : 0;      // TEMPORARY probe: skip the arithmetic, keep the copies
+        int pr = 0;
         #pragma unroll 1
         for (; pr + 4 <= npairs; pr += 4) {
             pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
@@ -283,14 +256,10 @@ Plan plan_for(int64_t cols) {
     const int nb = int(cols / 32);
     if (cols % 64 != 0 || nb < 2) return best;
     const size_t fixed = (size_t(nb) * 136 + 127) & ~size_t(127);
-    const char * force = getenv("DOOMS_GEMV_CBK");
-    const char * force_warps = getenv("DOOMS_GEMV_WARPS");
     int best_score = -1;
     for (int warps : {16, 8}) {
-        if (force_warps && warps != atoi(force_warps)) continue;
         for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
             if (nb % cbk) continue;
-            if (force && cbk != atoi(force)) continue;
             int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
             if (stride % 32 != 16) stride += 16;
             if ((cbk * kBlockBytes + 30) / 16 * kTileRows > kMaxPieces * 32 || kTileRows * stride >= (1 << 13)) continue;
@@ -342,7 +311,6 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, f
     GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), y, bias, rows, int(cols), flags,
                     pl.cbk, pl.nchunks, pl.stride, 0};
     (void)error;
-    if (getenv("DOOMS_GEMV_NOCOMPUTE")) p.flags |= 0x100u;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
     const int chunk_bytes = pl.cbk * kBlockBytes;

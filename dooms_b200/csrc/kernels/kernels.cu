@@ -6,6 +6,7 @@
 #include <math_constants.h>
 
 #include "quant.cuh"
+#include "xsplit.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -65,7 +66,8 @@ __global__ void k_embed(const uint8_t * table, const int32_t * ids, const int32_
 
 // ---------------------------------------------------------------- RMS norm
 
-__global__ void k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, int E, float eps) {
+// xq (optional, one row only, E a multiple of 32): the normalized row also split for the staged q4_0 GEMV (xsplit.cuh).
+__global__ void k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, uint8_t * xq, int E, float eps) {
     __shared__ float red[32];
     const float * xr = x + int64_t(blockIdx.x) * E;
     float ss = 0.f;
@@ -76,6 +78,16 @@ __global__ void k_rms_norm(const float * x, const float * gamma, float * out, __
     float total = 0.f;
     for (int w = 0; w < int(blockDim.x) / 32; w++) total += red[w];
     const float inv = rsqrtf(total / float(E) + eps);
+    if (xq) {      // whole 32-element blocks per warp, so that a warp can split its block
+        const int lane = threadIdx.x % 32, nb = E / 32;
+        for (int blk = threadIdx.x / 32; blk < nb; blk += blockDim.x / 32) {
+            const int i = blk * 32 + lane;
+            const float v = xr[i] * inv * gamma[i];
+            if (out) out[i] = v;
+            split_block(v, lane, blk, nb, xq);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         const float v = xr[i] * inv * gamma[i];
         if (out) out[int64_t(blockIdx.x) * E + i] = v;
@@ -387,8 +399,9 @@ cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const 
     return ok ? cudaGetLastError() : cudaErrorInvalidValue;
 }
 
-cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, int rows, int E, float eps, cudaStream_t stream) {
-    k_rms_norm<<<rows, 256, 0, stream>>>(x, gamma, out, static_cast<__half *>(out16), E, eps);
+cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, void * xq, int rows, int E, float eps, cudaStream_t stream) {
+    if (xq && (rows != 1 || E % 32 != 0)) return cudaErrorInvalidValue;
+    k_rms_norm<<<rows, 256, 0, stream>>>(x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
     return cudaGetLastError();
 }
 

@@ -23,8 +23,9 @@ cudaError_t launch_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t
 // x[row][:] = table[ids[(index ? *index : 0) + row]][:], rows x E (embedq<Q>, llama_kernels.h:1289-1296).
 cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const int32_t * index, float * x, int rows, int E, cudaStream_t stream);
 
-// out[r][:] = x[r][:] * rsqrt(mean(x[r]^2) + eps) * gamma (norm_vec, llama_kernels.h:1272-1286). out16 (optional) also receives the rows as f16.
-cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, int rows, int E, float eps, cudaStream_t stream);
+// out[r][:] = x[r][:] * rsqrt(mean(x[r]^2) + eps) * gamma (norm_vec, llama_kernels.h:1272-1286). out16 (optional) also receives the rows as f16; xq
+// (optional, one row, E a multiple of 32) the row split for the staged q4_0 GEMV.
+cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, void * xq, int rows, int E, float eps, cudaStream_t stream);
 
 // y[r] (+)= W[r] . x (+ bias[r]) (matvec1q<Q>, llama_kernels.h:1197-1230).
 cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
