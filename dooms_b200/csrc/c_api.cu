@@ -382,6 +382,27 @@ DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, cons
     return launch_result(cuda::launch_gate_up(dtype, d_wg, d_wu, d_x, d_h, rows, cols, st), "gate_up");
 }
 
+DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const void * d_w2, const void * d_x16, float * d_y, const float * d_bias,
+                                         int32_t tokens, int64_t rows, int64_t cols, uint32_t flags, void * stream) {
+    if (!matrix_dtype(dtype)) return fail(DOOMS_UNSUPPORTED, "matmul takes f16, q4_0, q5_0, q8_0, q4_K and q6_K");
+    if (!d_w || !d_x16 || !d_y || tokens < 1 || rows < 1 || cols < 64 || cols % 64 != 0 || cols % dooms_dtype_block_elems(dtype) != 0 || cols > INT32_MAX ||
+        ((flags & cuda::kFlagBias) && !d_bias) || (flags & ~(cuda::kFlagAccumulate | cuda::kFlagBias)) || (d_w2 && flags)) {
+        return fail(DOOMS_INVALID_ARGUMENT, "matmul: NULL pointer, unknown flag, or rows that are not whole blocks and a multiple of 64 elements");
+    }
+    void * scratch = nullptr;
+    const Status ss = scratch_for(256, &scratch);
+    if (!ss.is_ok()) return done(ss);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cuda::TensorMap map;
+    cudaError_t e = cuda::make_activation_map(&map, d_x16, tokens, cols);
+    if (e != cudaSuccess) return launch_result(e, "matmul (tensor map)");
+    e = cudaMemsetAsync(scratch, 0, 4, st);
+    if (e == cudaSuccess) {
+        e = cuda::launch_gemm_tc(dtype, d_w, d_w2, &map, d_y, nullptr, d_bias, tokens, rows, cols, rows, 0, flags, static_cast<int32_t *>(scratch), st);
+    }
+    return launch_result(e, "matmul");
+}
+
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream) {
     if (!d_x || !d_gamma || !d_out || rows < 0 || cols < 1 || rows > INT32_MAX || cols > INT32_MAX || !(eps > 0.f)) {
         return fail(DOOMS_INVALID_ARGUMENT, "rms_norm: NULL pointer, bad shape or eps <= 0");

@@ -69,6 +69,9 @@ struct CudaLlamaDecoder::Impl {
     size_t cache_layer_elems = 0, kv_bytes = 0;
     float * x = nullptr, * xn = nullptr, * qkv = nullptr, * attn = nullptr, * h = nullptr, * red = nullptr, * logits_buf = nullptr, * part = nullptr;
     void * argmax_part = nullptr;
+    __half * xn16 = nullptr, * attn16 = nullptr, * h16 = nullptr;   // f16 activations of a prefill chunk, the tensor-core GEMM's token operands
+    cuda::TensorMap map_xn, map_attn, map_h;
+    bool tc_capable = false;       // every reduction length is a multiple of 64 and the TMA descriptors exist
     uint8_t * xq = nullptr;        // the current projection input split into int8 limbs (the staged q4_0 GEMV's operand)
     const float * xq_of = nullptr; // which f32 vector xq currently holds
     int32_t * tokens = nullptr, * in_tokens = nullptr, * host_tokens = nullptr, * host_in = nullptr;
@@ -99,7 +102,7 @@ struct CudaLlamaDecoder::Impl {
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
         for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part,
-                         argmax_part, (void *)xq, (void *)tokens, (void *)in_tokens, (void *)state}) {
+                         argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
         for (void * p : {(void *)host_tokens, (void *)host_in, (void *)host_x, (void *)host_error}) if (p) cudaFreeHost(p);
@@ -169,9 +172,11 @@ struct CudaLlamaDecoder::Impl {
     }
     // xn = RMS-normalized rows; with split (one row) the kernel also leaves the row split for the staged q4_0 kernels (every producer of a projection
     // input invalidates the split copy).
-    void norm(const float * in, const float * gamma, int M, bool split) {
+    void norm(const float * in, const float * gamma, int M, bool split, bool f16_only = false) {
         const bool do_split = split && M == 1 && cfg.n_embd % 32 == 0;
-        run("norm", [&] { return cuda::launch_rms_norm(in, gamma, xn, nullptr, do_split ? xq : nullptr, M, cfg.n_embd, cfg.rms_eps, stream); });
+        run("norm", [&] {
+            return cuda::launch_rms_norm(in, gamma, f16_only ? nullptr : xn, f16_only ? xn16 : nullptr, do_split ? xq : nullptr, M, cfg.n_embd, cfg.rms_eps, stream);
+        });
         xq_of = do_split ? xn : nullptr;
     }
     void gate_up(const MatDev & wg, const MatDev & wu, const float * in, float * out) {
@@ -185,6 +190,14 @@ struct CudaLlamaDecoder::Impl {
     void matmul(const char * kind, const MatDev & w, const MatDev * w2, const float * in, int64_t in_stride, float * out, int64_t out_stride, const float * bias, int M,
                 uint32_t flags) {
         run(kind, [&] { return cuda::launch_matmul_tile(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, in, in_stride, out, out_stride, bias, M, w.rows, w.cols, flags, stream); });
+    }
+    // Y[m][row0 + n] (+)= X16[m] . W[n] on the tensor cores; X16 is the f16 activation buffer behind map.
+    void gemm_tc(const char * kind, const MatDev & w, const MatDev * w2, const cuda::TensorMap & map, float * out, __half * out16, const float * bias, int M,
+                 int64_t out_stride, int64_t out16_stride, uint32_t flags) {
+        run(kind, [&] {
+            return cuda::launch_gemm_tc(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, &map, out, out16, bias, M, w.rows, w.cols, out_stride, out16_stride, flags,
+                                        host_error, stream);
+        });
     }
     // x += partial sums of the other ranks' shares: with one GPU the projection accumulated into x directly.
     void reduce_into_x(int M) {
@@ -207,7 +220,8 @@ struct CudaLlamaDecoder::Impl {
             const uint32_t o_flags = single ? kFlagAccumulate : 0u;
             bool qkv_fast = false;
             for (const QkvPart & q : L.qkv) qkv_fast = qkv_fast || fast(q.w);
-            norm(x, L.attn_norm, M, qkv_fast);
+            const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
+            norm(x, L.attn_norm, M, qkv_fast, use_tc);
             if (M == 1) {
                 for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
@@ -220,12 +234,25 @@ struct CudaLlamaDecoder::Impl {
                 xq_of = nullptr;
                 matvec("ffn_down", L.ffn_down, h, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
+            } else if (use_tc) {
+                // (the chunk's norm above wrote xn16)
+                for (const QkvPart & q : L.qkv) {
+                    gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
+                }
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
+                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, attn16, state, M, as, stream); });
+                gemm_tc("attn_output", L.attn_output, nullptr, map_attn, o_dst, nullptr, nullptr, M, E, 0, o_flags);
+                reduce_into_x(M);
+                norm(x, L.ffn_norm, M, false, true);
+                gemm_tc("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, M, 0, ff, 0u);
+                gemm_tc("ffn_down", L.ffn_down, nullptr, map_h, o_dst, nullptr, nullptr, M, E, 0, o_flags);
+                reduce_into_x(M);
             } else {
                 for (const QkvPart & q : L.qkv) {
                     matmul("qkv", q.w, nullptr, xn, E, qkv + q.row0, qkv_width, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, L.qkv_bias ? kFlagBias : 0u);
                 }
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
-                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, state, M, as, stream); });
+                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, nullptr, state, M, as, stream); });
                 matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
                 norm(x, L.ffn_norm, M, false);
@@ -564,6 +591,20 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
                                     "the split projection input"));
+    if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xn16), B * size_t(E) * 2, "the f16 normalized rows"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn16), B * size_t(m.q_width) * 2, "the f16 attention rows"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h16), B * size_t(m.ff) * 2, "the f16 feed-forward rows"));
+        m.tc_capable = cuda::make_activation_map(&m.map_xn, m.xn16, int64_t(B), E) == cudaSuccess &&
+                       cuda::make_activation_map(&m.map_attn, m.attn16, int64_t(B), m.q_width) == cudaSuccess &&
+                       cuda::make_activation_map(&m.map_h, m.h16, int64_t(B), m.ff) == cudaSuccess;
+        for (const LayerDev & L : m.layers) {
+            for (const QkvPart & q : L.qkv) m.tc_capable = m.tc_capable && cuda::gemm_tc_supported(int(q.w.dt), q.w.ptr, q.w.rows, q.w.cols);
+            for (const MatDev * w : {&L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down}) {
+                m.tc_capable = m.tc_capable && cuda::gemm_tc_supported(int(w->dt), w->ptr, w->rows, w->cols);
+            }
+        }
+    }
     DOOMS_RETURN_IF_ERROR(dev_alloc(&m.argmax_part, size_t(cuda::argmax_blocks(int64_t(logits_floats))) * 8, "the argmax partial results"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tokens), (size_t(c.n_ctx) + 2) * 4, "the token ring"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.in_tokens), B * 4, "the input tokens"));

@@ -1,0 +1,348 @@
+// Prefill GEMM on the 5th-generation tensor cores: Y[m][n] (+)= sum_k X[m][k] * W[n][k] with W in its GGUF block format, dequantized tile by tile into
+// shared memory and multiplied with tcgen05.mma, accumulators in tensor memory.
+//
+//   * One block of threads computes 128 weight rows x up to 256 tokens. The weight tile is the MMA's A operand (M = 128: one weight row per TMEM lane), the
+//     token tile its B operand (N = 128 or 256), both K-major f16 in the 128-byte swizzled layout; D[n][m] lives in 256 TMEM columns (gate/up: two
+//     accumulators, all 512 columns).
+//   * Per 64-wide k step: the token tile (f16 activations written by the producing kernel) arrives by TMA (cp.async.bulk.tensor.2d, no multicast); 256
+//     producer threads read the weight rows' raw blocks from global memory (two threads per row, 32 elements each), dequantize them to f16 exactly as the
+//     reference's tiles do (half(Q::elem), src/backend/metal/llama_kernels.h:1027-1035, 197) and store them swizzled; one thread issues the four k = 16
+//     MMAs and commits the stage back to the producers. Stages are handed over through mbarriers; every wait is bounded and reports failure instead of
+//     hanging.
+//   * Epilogue: the producer warps read their TMEM lanes (tcgen05.ld 32x32b), add bias / the residual, or apply silu(gate) * up, and write coalesced
+//     rows of Y (f32) or of the f16 activation buffer the next GEMM reads.
+// Replaces matmul_bigq / matmul_gate_up_bigq and the dequant_half + matmul_big pair of the reference (llama_kernels.h:1320-1382, 1474-1480).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "kernels.h"
+#include "ptx.cuh"
+#include "quant.cuh"
+
+namespace dooms {
+namespace cuda {
+
+using namespace dooms::dev;
+
+namespace {
+
+constexpr int kRowsW = 128;         // weight rows per block = MMA M
+constexpr int kStepK = 64;          // k elements per stage: one 128-byte swizzle row of f16
+constexpr int kProducerWarps = 8;   // two threads per weight row
+constexpr int kThreads = (kProducerWarps + 2) * 32;   // + the TMA warp and the MMA warp
+constexpr uint32_t kTileWBytes = kRowsW * kStepK * 2; // 16 KB
+
+// ---- tcgen05 / TMA wrappers ----
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap * map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                   "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzled layout: rows of 128 bytes, groups of 8 rows 1024 bytes apart (the tile base is
+// 1024-byte aligned). A k = 16 slice inside the 128-byte row is addressed by adding its byte offset to the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// Instruction descriptor, kind::f16: f32 accumulator, A and B of type `bf16 ? bf16 : f16`, both K-major, M = 128, N = n.
+__host__ __device__ inline uint32_t idesc_f16(int n, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(kRowsW >> 4) << 24);
+}
+
+// ---- dequantization of one thread's 32 elements (elements k0 .. k0+31 of a weight row, k0 a multiple of 32) to four 16-byte chunks of f16 ----
+
+// Generic: element by element with the block formulas, rounded to f16 as the reference's tiles are (half(Q::elem)).
+template <int DT>
+__device__ __forceinline__ void dequant32(const uint8_t * row, uint32_t k0, uint4 (&out)[4]) {
+    #pragma unroll
+    for (int c = 0; c < 4; c++) {
+        uint32_t w[4];
+        #pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const __half2 h = __floats2half2_rn(elem<DT>(row, k0 + 8 * c + 2 * i), elem<DT>(row, k0 + 8 * c + 2 * i + 1));
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        out[c] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// q4_0: one 18-byte block. (1024 + q) is built as an f16 bit pattern, 1032 subtracted (exact), the block scale multiplied in f16: the rounding of the exact
+// product d (q - 8), the same value half(d * (q - 8)) has.
+__device__ __forceinline__ uint32_t h2_sub_mul(uint32_t v, __half2 d2) {
+    const __half2 k1032 = __half2half2(__ushort_as_half(0x6408));      // 1032.0
+    const __half2 r = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v), k1032), d2);
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+template <>
+__device__ __forceinline__ void dequant32<kQ4_0>(const uint8_t * row, uint32_t k0, uint4 (&out)[4]) {
+    const uint16_t * b = reinterpret_cast<const uint16_t *>(row + size_t(k0 / 32) * 18);
+    uint16_t raw[9];
+    #pragma unroll
+    for (int i = 0; i < 9; i++) raw[i] = __ldg(b + i);
+    const __half2 d2 = __half2half2(__ushort_as_half(raw[0]));
+    uint32_t lo[8], hi[8];      // half2 pairs of elements (2i, 2i+1) and (16+2i, 16+2i+1)
+    #pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t two = raw[1 + i];                                  // bytes 2i, 2i+1 of qs
+        const uint32_t t = (two & 0xFFu) | ((two & 0xFF00u) << 8);        // [b0, 0, b1, 0]
+        lo[i] = h2_sub_mul((t & 0x000F000Fu) | 0x64006400u, d2);
+        hi[i] = h2_sub_mul(((t >> 4) & 0x000F000Fu) | 0x64006400u, d2);
+    }
+    out[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    out[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+    out[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    out[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+}
+
+struct GemmTcParams {
+    const uint8_t * W;
+    const uint8_t * W2;        // gate/up: the up matrix
+    float * Y;                 // f32 output rows [m][y_stride] (nullptr when only the f16 output is wanted)
+    __half * Y16;              // f16 output rows [m][y16_stride] (gate/up: the activations the down projection reads)
+    const float * bias;
+    int64_t N;                 // weight rows
+    int K, M;                  // reduction length, tokens
+    int64_t y_stride, y16_stride;
+    uint32_t flags;
+    int T;                     // tokens per block: 128 or 256
+    int32_t * error;
+};
+
+// Shared memory: [stage][W tile | W2 tile | X tile], then the mbarriers and the TMEM base address.
+template <int DT, bool GATE>
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const GemmTcParams p) {
+    constexpr int NMAT = GATE ? 2 : 1;
+    constexpr int STAGES = GATE ? 3 : 4;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t tile_x_bytes = uint32_t(p.T) * 128u;
+    const uint32_t stage_bytes = NMAT * kTileWBytes + tile_x_bytes;
+    const uint32_t bars = smem0 + STAGES * stage_bytes;       // full_x[S], full_w[S], empty[S], acc_full
+    const uint32_t full_x = bars, full_w = bars + 8 * STAGES, empty = bars + 16 * STAGES, acc_full = bars + 24 * STAGES, tmem_slot = acc_full + 8;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int64_t n0 = int64_t(blockIdx.x) * kRowsW;
+    const int m0 = blockIdx.y * p.T;
+    const int ksteps = p.K / kStepK;
+    const uint32_t ncols = GATE ? 512u : 256u;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full_x + 8 * s, 1); mbar_init(full_w + 8 * s, kProducerWarps * 32); mbar_init(empty + 8 * s, 1); }
+        mbar_init(acc_full, 1);
+        mbar_init_fence();
+    }
+    if (warp == kProducerWarps + 1) {      // the MMA warp owns the tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    bool ok = true;
+
+    if (warp < kProducerWarps) {
+        // ---- weight producers: row r of the tile, elements 32 half .. 32 half + 31 of each k step ----
+        const int r = (warp & 3) * 32 + lane, half = warp >> 2;
+        const int64_t row = min(n0 + r, p.N - 1);
+        const int64_t RB = row_bytes_of(DT, p.K);
+        const uint8_t * wrow[NMAT];
+        wrow[0] = p.W + row * RB;
+        if (GATE) wrow[NMAT - 1] = p.W2 + row * RB;
+        const uint32_t dst_row = uint32_t(r) * 128u;
+        for (int ks = 0; ks < ksteps && ok; ks++) {
+            const int s = ks % STAGES;
+            if (ks >= STAGES) ok = mbar_wait(empty + 8 * s, uint32_t(ks / STAGES - 1) & 1u);
+            if (!ok) break;
+            #pragma unroll
+            for (int mtx = 0; mtx < NMAT; mtx++) {
+                uint4 v[4];
+                dequant32<DT>(wrow[mtx], uint32_t(ks * kStepK + half * 32), v);
+                const uint32_t tile = smem0 + s * stage_bytes + mtx * kTileWBytes + dst_row;
+                #pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const uint32_t chunk = uint32_t(half * 4 + c) ^ uint32_t(r & 7);
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + chunk * 16u), "r"(v[c].x), "r"(v[c].y), "r"(v[c].z), "r"(v[c].w) : "memory");
+                }
+            }
+            fence_async_smem();      // the generic-proxy stores above must be visible to the tensor core's (asynchronous proxy) reads
+            mbar_arrive(full_w + 8 * s);
+        }
+    } else if (warp == kProducerWarps) {
+        // ---- TMA producer: the token tile of each k step (rows past the activation buffer are filled with zeros by the copy) ----
+        if (lane == 0) {
+            for (int ks = 0; ks < ksteps && ok; ks++) {
+                const int s = ks % STAGES;
+                if (ks >= STAGES) ok = mbar_wait(empty + 8 * s, uint32_t(ks / STAGES - 1) & 1u);
+                if (!ok) break;
+                const uint32_t dst = smem0 + s * stage_bytes + NMAT * kTileWBytes;
+                mbar_arrive_expect_tx(full_x + 8 * s, tile_x_bytes);
+                for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, ks * kStepK, m0 + part * 128, full_x + 8 * s);
+            }
+        }
+    } else {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            const uint32_t idesc = idesc_f16(p.T, false);
+            for (int ks = 0; ks < ksteps && ok; ks++) {
+                const int s = ks % STAGES;
+                const uint32_t ph = uint32_t(ks / STAGES) & 1u;
+                ok = mbar_wait(full_x + 8 * s, ph) && mbar_wait(full_w + 8 * s, ph);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t wt = smem0 + s * stage_bytes, xt = wt + NMAT * kTileWBytes;
+                #pragma unroll
+                for (int kk = 0; kk < kStepK / 16; kk++) {
+                    const uint64_t bdesc = smem_desc_sw128(xt + kk * 32);
+                    #pragma unroll
+                    for (int mtx = 0; mtx < NMAT; mtx++) {
+                        tc_mma_f16(tmem_base + mtx * 256u, smem_desc_sw128(wt + mtx * kTileWBytes + kk * 32), bdesc, idesc, (ks | kk) ? 1u : 0u);
+                    }
+                }
+                tc_commit(empty + 8 * s);      // arrives when the MMAs above have read the stage
+            }
+            if (ok) tc_commit(acc_full);       // ... and this one when every MMA has written the accumulators
+        }
+    }
+    __syncwarp();
+    ok = __all_sync(0xffffffffu, ok);
+
+    // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its weight rows) and half of the token columns ----
+    if (warp < kProducerWarps) {
+        if (ok) ok = mbar_wait(acc_full, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3, colhalf = warp >> 2;
+            const int64_t n = n0 + q * 32 + lane;
+            const int cols_per_warp = p.T / 2;
+            const float bias = (p.flags & kFlagBias) && n < p.N ? p.bias[n] : 0.f;
+            for (int c0 = colhalf * cols_per_warp; c0 < (colhalf + 1) * cols_per_warp; c0 += 32) {
+                if (m0 + c0 >= p.M) break;      // warp-uniform
+                uint32_t acc[32], acc2[32];
+                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0);
+                tc_ld32(taddr, acc);
+                if (GATE) tc_ld32(taddr + 256u, acc2);
+                if (n < p.N) {
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int m = m0 + c0 + j;
+                        if (m >= p.M) continue;
+                        float v = __uint_as_float(acc[j]);
+                        if (GATE) v = v / (1.f + expf(-v)) * __uint_as_float(acc2[j]);
+                        else v += bias;
+                        if (p.Y) {
+                            float * y = p.Y + int64_t(m) * p.y_stride + n;
+                            *y = (p.flags & kFlagAccumulate) ? *y + v : v;
+                        }
+                        if (p.Y16) p.Y16[int64_t(m) * p.y16_stride + n] = __float2half_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0 && p.error) *p.error = 2;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kProducerWarps + 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ncols) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void * sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+template <int DT>
+cudaError_t launch_dt(const CUtensorMap & map, const GemmTcParams & p, bool gate, cudaStream_t stream) {
+    const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
+    const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
+    const dim3 grid(unsigned((p.N + kRowsW - 1) / kRowsW), unsigned((p.M + p.T - 1) / p.T));
+    static int configured[2] = {-1, -1};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured[gate] != dev) {
+        const cudaError_t e = gate ? cudaFuncSetAttribute(k_gemm_tc<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
+                                   : cudaFuncSetAttribute(k_gemm_tc<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[gate] = dev;
+    }
+    if (gate) k_gemm_tc<DT, true><<<grid, kThreads, smem, stream>>>(map, p);
+    else k_gemm_tc<DT, false><<<grid, kThreads, smem, stream>>>(map, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+static_assert(sizeof(TensorMap) == sizeof(CUtensorMap) && alignof(TensorMap) >= alignof(CUtensorMap), "TensorMap must hold a CUtensorMap");
+
+cudaError_t make_activation_map(TensorMap * out, const void * base, int64_t rows, int64_t cols) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(kStepK), 128u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
+    (void)W;
+    const bool type_ok = dt == kF16 || dt == kQ4_0 || dt == kQ5_0 || dt == kQ8_0 || dt == kQ4_K || dt == kQ6_K;
+    return type_ok && N >= 1 && K >= kStepK && K % kStepK == 0;
+}
+
+cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
+                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream) {
+    if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
+    GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
+                   flags, M > 128 ? 256 : 128, error};
+    const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
+    const bool gate = W2 != nullptr;
+    switch (dt) {
+        case kF16: return launch_dt<kF16>(map, p, gate, stream);
+        case kQ4_0: return launch_dt<kQ4_0>(map, p, gate, stream);
+        case kQ5_0: return launch_dt<kQ5_0>(map, p, gate, stream);
+        case kQ8_0: return launch_dt<kQ8_0>(map, p, gate, stream);
+        case kQ4_K: return launch_dt<kQ4_K>(map, p, gate, stream);
+        case kQ6_K: return launch_dt<kQ6_K>(map, p, gate, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace cuda
+}  // namespace dooms

@@ -248,7 +248,7 @@ constexpr int kMaxDimsPerLane = 8;   // head_dim <= 256
 
 // One block per (head, split, query row): the block's warps share the split's key range, each with its own running softmax, merged in shared memory.
 // part entry: (max, sum, values[head_dim]) unnormalised; direct: splits == 1, the normalised result goes straight to out.
-__global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, const __half * kc, const __half * vc, float * out, float * part,
+__global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, const __half * kc, const __half * vc, float * out, __half * out16, float * part,
                                                                const DevState * st, int n_keys_fixed, int splits, int direct, AttnShape p) {
     __shared__ float qs[256];
     __shared__ float wm[kAttnWarps], wl[kAttnWarps];
@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, 
         float a = 0.f;
         for (int w = 0; w < kAttnWarps; w++) a += wo[w][e] * wgt[w];
         dst[e] = direct ? a / total : a;
+        if (direct && out16) out16[int64_t(t) * p.out_stride + h * hd + e] = __float2half_rn(a / total);
     }
     if (!direct && threadIdx.x == 0) { dst[-2] = mx; dst[-1] = total; }
 }
@@ -459,18 +460,19 @@ int attention_splits(int n_head, int n_ctx) {
 cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, const DevState * st, int n_keys_fixed,
                                     int splits, const AttnShape & s, cudaStream_t stream) {
     const dim3 grid(s.n_head, splits, 1);
-    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(q, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, part, st, n_keys_fixed, splits,
-                                                      splits == 1 ? 1 : 0, s);
+    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(q, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, nullptr, part, st, n_keys_fixed,
+                                                      splits, splits == 1 ? 1 : 0, s);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || splits == 1) return e;
     k_attention_combine<<<dim3(s.n_head, 1), s.head_dim, 0, stream>>>(part, out, splits, s);
     return cudaGetLastError();
 }
 
-cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, const DevState * st, int M, const AttnShape & s,
-                                     cudaStream_t stream) {
+cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,
+                                     const AttnShape & s, cudaStream_t stream) {
     const dim3 grid(s.n_head, 1, M);
-    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(qkv, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, nullptr, st, 0, 1, 1, s);
+    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(qkv, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, static_cast<__half *>(out16), nullptr,
+                                                      st, 0, 1, 1, s);
     return cudaGetLastError();
 }
 

@@ -56,8 +56,9 @@ cudaError_t launch_attention_decode(const float * q, const void * kc, const void
                                     int splits, const AttnShape & s, cudaStream_t stream);
 
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
-cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, const DevState * st, int M, const AttnShape & s,
-                                     cudaStream_t stream);
+// out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.
+cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,
+                                     const AttnShape & s, cudaStream_t stream);
 
 // tokens[st->tok_out] = first index of the maximum of logits[0..n) (NaN never wins); the token also goes to host_tokens[st->tok_out] when that is set
 // (mapped pinned memory). With advance the state moves one decode step forward (pos, tok_in, tok_out += 1). part: argmax_blocks(n) x 2 words.
@@ -75,6 +76,16 @@ bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
 // y[r] (+)= W[r] . x (+ bias[r]); with W2: y[r] = silu(W[r] . x) * (W2[r] . x). x comes as xq. *error is set to 1 if a bulk copy never arrived.
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
                              int32_t * error, cudaStream_t stream);
+
+// ---- the tensor-core prefill GEMM (gemm_tc.cu) ----
+// A TMA descriptor of an f16 activation buffer [rows][cols] (cols a multiple of 64), opaque here so that this header needs no driver types.
+struct alignas(64) TensorMap { unsigned char bytes[128]; };
+cudaError_t make_activation_map(TensorMap * out, const void * base, int64_t rows, int64_t cols);
+bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K);
+// Y[m][n] (+)= X[m] . W[n] (+ bias[n]) for M tokens; X is the f16 buffer behind xmap. With W2: silu(X . W[n]) * (X . W2[n]). Y (f32) and / or Y16 (f16)
+// receive the result. *error is set to 2 if a pipeline wait ran out.
+cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
+                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream);
 
 }  // namespace cuda
 }  // namespace dooms

@@ -184,6 +184,11 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
 /* gate_up1q<Q> (llama_kernels.h:1232-1269): h[r] = silu(Wg[r] . x) * (Wu[r] . x). */
 DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
                                           void * stream);
+/* matmul_bigq<Q> / matmul_gate_up_bigq<Q> (llama_kernels.h:1320-1382) on the tcgen05 tensor cores: Y[t][r] (+)= sum_k X[t][k] W[r][k] (+ bias[r]) for
+ * `tokens` rows of X, an f16 [tokens][cols] device buffer (cols a multiple of 64; operands are rounded to f16 as the reference's tiles, llama_kernels.h:197).
+ * With d_w2: Y[t][r] = silu(X[t] . W[r]) * (X[t] . W2[r]). Y is f32 [tokens][rows]. flags as dooms_cuda_matvec. */
+DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const void * d_w2, const void * d_x16, float * d_y, const float * d_bias,
+                                         int32_t tokens, int64_t rows, int64_t cols, uint32_t flags, void * stream);
 /* norm_vec (llama_kernels.h:1272-1286): xn = x * rsqrt(mean(x^2) + eps) * gamma for `rows` rows of `cols`. */
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream);
 /* argmax (llama_kernels.h:949-975) with the host rule that NaN never wins (src/core/argmax.h:15-16): *d_out = lowest index of the maximum. */

@@ -173,3 +173,35 @@ def test_kernel_entry_points_reject_bad_arguments():
     assert lib.dooms_cuda_matvec(L.Q4_0, 1, 1, 1, None, 4, 64, 4, None) == L.INVALID_ARGUMENT  # bias flag without a bias
     assert lib.dooms_cuda_argmax(None, 5, None, None) == L.INVALID_ARGUMENT
     assert lib.dooms_cuda_attention_decode(1, 1, 1, 1, 1, 4, 2, 24, 8, None) == L.UNSUPPORTED
+
+
+@pytest.mark.parametrize("dtype", MATRIX_TYPES)
+@pytest.mark.parametrize("shape", [(45, 300, 256), (130, 128, 512), (1, 129, 64), (257, 256, 1024)])
+@pytest.mark.parametrize("gate", [False, True])
+def test_tensor_core_matmul_matches_the_oracle(dtype, shape, gate):
+    """The tcgen05 prefill GEMM against float64 products of the checker's dequantized weights rounded to f16 (the operand rounding of the reference's
+    tiles, src/backend/metal/llama_kernels.h:186-199); tokens and rows that are no multiple of the 128-wide tiles."""
+    tokens, rows, cols = shape
+    if cols % L.BLOCK_ELEMS[dtype]:
+        pytest.skip("rows are not whole blocks of this type")
+    g = np.random.default_rng(3)
+    bw, bw2 = random_blocks(dtype, rows, cols, 21), random_blocks(dtype, rows, cols, 22)
+    x16 = g.standard_normal((tokens, cols)).astype(np.float16)
+    bias = g.standard_normal(rows).astype(np.float32)
+    y0 = g.standard_normal((tokens, rows)).astype(np.float32)
+    w = oracle_matrix(dtype, bw, rows, cols).astype(np.float16).astype(np.float64)
+    base = x16.astype(np.float64) @ w.T
+    d_w, d_w2, d_x, d_b = dev(bw), dev(bw2), dev(x16), dev(bias)
+    if gate:
+        u = x16.astype(np.float64) @ oracle_matrix(dtype, bw2, rows, cols).astype(np.float16).astype(np.float64).T
+        cases = [(0, base / (1 + np.exp(-base)) * u)]
+    else:
+        cases = [(0, base), (4, base + bias), (2, base + y0), (6, base + bias + y0)]
+    for flags, want in cases:
+        d_y = dev(y0.copy())
+        L.check(L.lib().dooms_cuda_matmul(dtype, d_w.data_ptr(), d_w2.data_ptr() if gate else None, d_x.data_ptr(), d_y.data_ptr(), d_b.data_ptr(), tokens,
+                                          rows, cols, flags, None))
+        torch.cuda.synchronize()
+        got = d_y.cpu().numpy().astype(np.float64)
+        assert np.isfinite(got).all()
+        assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 2e-5, flags
