@@ -432,7 +432,7 @@ DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void
     if (head_dim < 4 || head_dim > 256 || (head_dim & (head_dim - 1)) != 0) return fail(DOOMS_UNSUPPORTED, "attention_decode: head_dim must be a power of two in [4, 256]");
     const cuda::AttnShape s{n_head, n_head_kv, head_dim, n_head * head_dim, n_head_kv * head_dim, n_head * head_dim, 0, 10000.f};
     const int splits = cuda::attention_splits(n_head, n_keys);
-    return launch_result(cuda::launch_attention_decode(d_q, d_kc, d_vc, d_out, static_cast<float *>(d_scratch), nullptr, n_keys, splits, s,
+    return launch_result(cuda::launch_attention_decode(d_q, d_kc, d_vc, d_out, static_cast<float *>(d_scratch), nullptr, nullptr, n_keys, splits, s,
                                                        static_cast<cudaStream_t>(stream)), "attention_decode");
 }
 

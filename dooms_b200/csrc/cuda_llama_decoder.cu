@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <string>
@@ -225,8 +226,9 @@ struct CudaLlamaDecoder::Impl {
             if (M == 1) {
                 for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
-                run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, state, 0, splits, as, stream); });
-                xq_of = nullptr;
+                const bool split_attn = fast(L.attn_output) && splits > 1 && cfg.head_dim % 32 == 0;
+                run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
+                xq_of = split_attn ? attn : nullptr;
                 matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
                 norm(x, L.ffn_norm, 1, fast(L.ffn_gate) && fast(L.ffn_up));

@@ -66,32 +66,62 @@ __global__ void k_embed(const uint8_t * table, const int32_t * ids, const int32_
 
 // ---------------------------------------------------------------- RMS norm
 
-// xq (optional, one row only, E a multiple of 32): the normalized row also split for the staged q4_0 GEMV (xsplit.cuh).
-__global__ void k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, uint8_t * xq, int E, float eps) {
+// One block of 1024 threads per row. Every thread loads its elements (and their gains) up front, so the loads are in flight together instead of one round
+// trip to L2 per loop iteration; rows wider than kNormMaxPerThread x 1024 take the looping path. Element i belongs to thread (i / 32) % 32 * 32 + i % 32
+// of pass i / 1024: a warp holds whole 32-element blocks, which is what the split for the staged q4_0 GEMV needs.
+// xq (optional, one row only, E a multiple of 32): the normalized row also split for that kernel (xsplit.cuh).
+constexpr int kNormThreads = 1024, kNormMaxPerThread = 8;
+__global__ void __launch_bounds__(kNormThreads) k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, uint8_t * xq, int E, float eps) {
     __shared__ float red[32];
     const float * xr = x + int64_t(blockIdx.x) * E;
+    const int64_t obase = int64_t(blockIdx.x) * E;
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
-    ss = warp_sum(ss);
-    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
-    __syncthreads();
-    float total = 0.f;
-    for (int w = 0; w < int(blockDim.x) / 32; w++) total += red[w];
-    const float inv = rsqrtf(total / float(E) + eps);
-    if (xq) {      // whole 32-element blocks per warp, so that a warp can split its block
-        const int lane = threadIdx.x % 32, nb = E / 32;
-        for (int blk = threadIdx.x / 32; blk < nb; blk += blockDim.x / 32) {
-            const int i = blk * 32 + lane;
-            const float v = xr[i] * inv * gamma[i];
-            if (out) out[i] = v;
-            split_block(v, lane, blk, nb, xq);
+    if (E <= kNormThreads * kNormMaxPerThread) {
+        float v[kNormMaxPerThread], g[kNormMaxPerThread];
+        #pragma unroll
+        for (int k = 0; k < kNormMaxPerThread; k++) {
+            const int i = k * kNormThreads + threadIdx.x;
+            v[k] = i < E ? xr[i] : 0.f;
+            g[k] = i < E ? gamma[i] : 0.f;
+        }
+        #pragma unroll
+        for (int k = 0; k < kNormMaxPerThread; k++) ss += v[k] * v[k];
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float total = 0.f;
+        #pragma unroll
+        for (int w = 0; w < 32; w++) total += red[w];
+        const float inv = rsqrtf(total / float(E) + eps);
+        #pragma unroll
+        for (int k = 0; k < kNormMaxPerThread; k++) {
+            const int i = k * kNormThreads + threadIdx.x;
+            if (i - lane >= E) break;      // warp-uniform: the whole 32-element block is past the row
+            const float r = v[k] * inv * g[k];
+            if (i < E) {
+                if (out) out[obase + i] = r;
+                if (out16) out16[obase + i] = __float2half_rn(r);
+            }
+            if (xq) split_block(r, lane, i / 32, E / 32, xq);
         }
         return;
     }
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        const float v = xr[i] * inv * gamma[i];
-        if (out) out[int64_t(blockIdx.x) * E + i] = v;
-        if (out16) out16[int64_t(blockIdx.x) * E + i] = __float2half_rn(v);
+    for (int i = threadIdx.x; i < E; i += kNormThreads) { const float t = xr[i]; ss += t * t; }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < 32; w++) total += red[w];
+    const float inv = rsqrtf(total / float(E) + eps);
+    for (int i0 = warp * 32; i0 < E; i0 += kNormThreads) {
+        const int i = i0 + lane;
+        const float r = i < E ? xr[i] * inv * gamma[i] : 0.f;
+        if (i < E) {
+            if (out) out[obase + i] = r;
+            if (out16) out16[obase + i] = __float2half_rn(r);
+        }
+        if (xq) split_block(r, lane, i / 32, E / 32, xq);
     }
 }
 
@@ -310,7 +340,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, 
 }
 
 // out[t][h] = merge of the splits' partial results (attention_combine, llama_kernels.h:914-929). grid (n_head, M), head_dim threads.
-__global__ void k_attention_combine(const float * part, float * out, int splits, AttnShape p) {
+__global__ void k_attention_combine(const float * part, float * out, uint8_t * xq, int splits, AttnShape p) {
     const int h = blockIdx.x, t = blockIdx.y, hd = p.head_dim, i = threadIdx.x;
     const float * base = part + (int64_t(t) * p.n_head + h) * splits * (2 + hd);
     float mx = -CUDART_INF_F;
@@ -323,7 +353,10 @@ __global__ void k_attention_combine(const float * part, float * out, int splits,
         total += ps[1] * w;
         acc += ps[2 + i] * w;
     }
-    out[int64_t(t) * p.out_stride + h * hd + i] = acc / total;
+    const float r = acc / total;
+    out[int64_t(t) * p.out_stride + h * hd + i] = r;
+    // the row as the staged q4_0 GEMV wants it (head_dim a multiple of 32: a warp holds whole 32-element blocks)
+    if (xq) split_block(r, i % 32, (h * hd + i) / 32, p.n_head * hd / 32, xq);
 }
 
 // ---------------------------------------------------------------- argmax
@@ -402,7 +435,7 @@ cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const 
 
 cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, void * xq, int rows, int E, float eps, cudaStream_t stream) {
     if (xq && (rows != 1 || E % 32 != 0)) return cudaErrorInvalidValue;
-    k_rms_norm<<<rows, 256, 0, stream>>>(x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
+    k_rms_norm<<<rows, kNormThreads, 0, stream>>>(x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
     return cudaGetLastError();
 }
 
@@ -457,14 +490,15 @@ int attention_splits(int n_head, int n_ctx) {
     return std::max(1, std::min(want, (n_ctx + 63) / 64));
 }
 
-cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, const DevState * st, int n_keys_fixed,
-                                    int splits, const AttnShape & s, cudaStream_t stream) {
+cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, void * xq, const DevState * st,
+                                    int n_keys_fixed, int splits, const AttnShape & s, cudaStream_t stream) {
+    if (xq && (splits == 1 || s.head_dim % 32 != 0)) return cudaErrorInvalidValue;
     const dim3 grid(s.n_head, splits, 1);
     k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(q, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, nullptr, part, st, n_keys_fixed,
                                                       splits, splits == 1 ? 1 : 0, s);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || splits == 1) return e;
-    k_attention_combine<<<dim3(s.n_head, 1), s.head_dim, 0, stream>>>(part, out, splits, s);
+    k_attention_combine<<<dim3(s.n_head, 1), s.head_dim, 0, stream>>>(part, out, static_cast<uint8_t *>(xq), splits, s);
     return cudaGetLastError();
 }
 

@@ -52,8 +52,9 @@ cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState 
 // One query row against cache positions 0 .. st->pos (attention_split + attention_combine, llama_kernels.h:860-929). The cache is cut into `splits`
 // ranges; part holds splits x n_head x (2 + head_dim) floats.
 int attention_splits(int n_head, int n_ctx);
-cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, const DevState * st, int n_keys_fixed,
-                                    int splits, const AttnShape & s, cudaStream_t stream);
+// xq (optional; needs splits > 1 and head_dim a multiple of 32): the output row also split for the staged q4_0 GEMV.
+cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, void * xq, const DevState * st,
+                                    int n_keys_fixed, int splits, const AttnShape & s, cudaStream_t stream);
 
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
 // out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.

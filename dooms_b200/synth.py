@@ -35,6 +35,7 @@ class ModelSpec:
     tied: bool
     bias: bool
     plan: Callable[[str, int], int]      # (tensor kind, layer) -> dtype; kinds: token_embd, output, attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down
+    random_blocks: bool = False          # quantized matrices as random block bytes with power-of-two scales (every value exact in f16), see random_blocks()
     weight_std: float = 0.02
     embd_std: float = 0.02
     bias_std: float = 0.02
@@ -103,10 +104,36 @@ def config_spec(index: int) -> ModelSpec:
 
 
 def tiny_spec(dtype_plan, arch: str = "qwen2", n_embd: int = 256, n_head: int = 4, n_head_kv: int = 2, n_ff: int = 2304, n_vocab: int = 50, n_layer: int = 2,
-              context_length: int = 1024, tied: bool = False) -> ModelSpec:
+              context_length: int = 1024, tied: bool = False, random_blocks: bool = False) -> ModelSpec:
     """The shape of the reference's quantized test model (tests/unit/test_metal_llama_decoder.cpp:279-285): E 256, 4 / 2 heads of 64, F 2304, V 50."""
     return ModelSpec("tiny", arch, n_layer, n_embd, n_head, n_head_kv, n_ff, n_vocab, 10000.0, 1e-5, context_length, tied, arch == "qwen2", dtype_plan,
-                     weight_std=0.15, embd_std=1.0, bias_std=0.3)
+                     random_blocks=random_blocks, weight_std=0.15, embd_std=1.0, bias_std=0.3)
+
+
+def random_blocks(dtype: int, rows: int, cols: int, seed: int) -> np.ndarray:
+    """Random block bytes with power-of-two scales sized for weights of std ~0.14, so that every dequantized value is exact in f16: the reference test's
+    random_quant (tests/unit/test_metal_llama_decoder.cpp:226-254). With such weights a half-rounded operand tile loses nothing on the weight side."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    nb = rows * cols // L.BLOCK_ELEMS[dtype]
+    b = g.integers(0, 256, (nb, L.BLOCK_BYTES[dtype]), dtype=np.uint8)
+
+    def put_half(off, value):
+        b[:, off:off + 2] = np.array([value], dtype=np.float16).view(np.uint8)
+    if dtype == L.Q4_0:
+        put_half(0, 1 / 32)
+    elif dtype == L.Q5_0:
+        put_half(0, 1 / 64)
+    elif dtype == L.Q8_0:
+        put_half(0, 1 / 512)
+    elif dtype == L.Q4_K:
+        put_half(0, 1 / 1024)
+        put_half(2, 1 / 1024)
+    elif dtype == L.Q6_K:
+        b[:, 192:208] = g.integers(-63, 64, (nb, 16)).astype(np.int8).view(np.uint8)      # |scale| <= 63: |scale * q| < 2048, exact in f16
+        put_half(208, 1 / 4096)
+    else:
+        raise ValueError(dtype)
+    return b.reshape(rows, -1)
 
 
 def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
@@ -145,6 +172,8 @@ def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu
         std = spec.embd_std if kind == "token_embd" else spec.weight_std
 
         def produce():
+            if spec.random_blocks and dt != L.F16:
+                return random_blocks(dt, rows, cols, s)
             out = []
             step = max(1, (1 << 26) // cols)          # 64M elements at a time
             for r0 in range(0, rows, step):
