@@ -113,6 +113,7 @@ SIGNATURES = {
     "dooms_cuda_matmul": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
     "dooms_cuda_rms_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "dooms_cuda_argmax": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "dooms_cuda_argmax_noalloc": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "dooms_cuda_attention_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "dooms_cuda_attention_decode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "dooms_cuda_nccl_unique_id": (C.c_int32, [C.c_char_p, C.c_void_p]),

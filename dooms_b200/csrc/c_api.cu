@@ -125,6 +125,13 @@ int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, c
     return launch_result(e, what);
 }
 
+// Scratch of dooms_cuda_argmax_noalloc: the per-block partial results (8 bytes each) for up to DOOMS_CUDA_ARGMAX_NOALLOC_MAX logits. It is part of the
+// library's device image, so no call ever allocates. In host code the name below is only a handle for cudaGetSymbolAddress, never a device address.
+constexpr int kNoAllocParts = DOOMS_CUDA_ARGMAX_NOALLOC_MAX / 4096;
+static __device__ __align__(256) unsigned long long g_argmax_noalloc_scratch[kNoAllocParts];
+void * g_argmax_noalloc_ptr[64];      // the array's device address, per device, looked up on the first call there
+std::mutex g_argmax_noalloc_mutex;
+
 bool matrix_dtype(int32_t dt) { return dt == DOOMS_F16 || dt == DOOMS_Q4_0 || dt == DOOMS_Q5_0 || dt == DOOMS_Q8_0 || dt == DOOMS_Q4_K || dt == DOOMS_Q6_K; }
 
 }  // namespace
@@ -417,6 +424,29 @@ DOOMS_CUDA_API int32_t dooms_cuda_argmax(const float * d_logits, int64_t n, int3
     const Status st = scratch_for(size_t(cuda::argmax_blocks(n)) * 8, &part);
     if (!st.is_ok()) return done(st);
     return launch_result(cuda::launch_argmax_plain(d_logits, n, d_out, part, static_cast<cudaStream_t>(stream)), "argmax");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_argmax_noalloc(const float * d_logits, int64_t n, int32_t * d_out, void * stream) {
+    if (!d_logits || !d_out || n < 1) return fail(DOOMS_INVALID_ARGUMENT, "argmax_noalloc: NULL pointer or n < 1");
+    if (n > DOOMS_CUDA_ARGMAX_NOALLOC_MAX || cuda::argmax_blocks(n) > kNoAllocParts) {
+        return fail(DOOMS_INVALID_ARGUMENT, "argmax_noalloc: n = " + std::to_string(n) + " exceeds the fixed scratch, which holds the partial results of at most " +
+                                            std::to_string(DOOMS_CUDA_ARGMAX_NOALLOC_MAX) + " logits; use dooms_cuda_argmax");
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { (void)cudaGetLastError(); return fail(DOOMS_UNSUPPORTED, "argmax_noalloc: no CUDA device"); }
+    void * part = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_argmax_noalloc_mutex);
+        if (!g_argmax_noalloc_ptr[dev]) {      // once per device, with that device current
+            void * p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_argmax_noalloc_scratch);
+            if (e != cudaSuccess || !p) { (void)cudaGetLastError(); return fail(DOOMS_INTERNAL, std::string("argmax_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e)); }
+            g_argmax_noalloc_ptr[dev] = p;
+        }
+        part = g_argmax_noalloc_ptr[dev];
+    }
+    // every partial result read by the final pass is written by the first pass of the same call: nothing in the array has to start at zero
+    return launch_result(cuda::launch_argmax_plain(d_logits, n, d_out, part, static_cast<cudaStream_t>(stream)), "argmax_noalloc");
 }
 
 DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_t head_dim, int32_t n_keys) {

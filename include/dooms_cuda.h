@@ -193,6 +193,14 @@ DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const 
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream);
 /* argmax (llama_kernels.h:949-975) with the host rule that NaN never wins (src/core/argmax.h:15-16): *d_out = lowest index of the maximum. */
 DOOMS_CUDA_API int32_t dooms_cuda_argmax(const float * d_logits, int64_t n, int32_t * d_out, void * stream);
+/* No counterpart in the reference. The same reduction as dooms_cuda_argmax for callers that must not allocate device memory: code running where a
+ * cudaMalloc is forbidden or would stall (inside a latency-critical serving loop that has handed all free device memory to a KV-cache pool, or a host
+ * runtime that pre-plans its memory and treats any later allocation as a fault). Its partial results live in a fixed array inside the library's device
+ * image (2 KB per GPU that loads the library, held until the process exits), which limits n to DOOMS_CUDA_ARGMAX_NOALLOC_MAX logits; larger n is refused
+ * with DOOMS_INVALID_ARGUMENT. The first call on each device looks up the array's device address (no allocation, but a driver call): make that first
+ * call before starting any stream capture. All calls on a device share the array: two calls that overlap on the GPU (different streams) race. */
+#define DOOMS_CUDA_ARGMAX_NOALLOC_MAX 1048576
+DOOMS_CUDA_API int32_t dooms_cuda_argmax_noalloc(const float * d_logits, int64_t n, int32_t * d_out, void * stream);
 /* attention_split + attention_combine (llama_kernels.h:860-929): one query token, n_keys cached positions, grouped-query heads. q f32 [n_head][head_dim]
  * (already rotated), kc / vc f16 [n_keys][n_head_kv*head_dim], out f32 [n_head][head_dim]. d_scratch: dooms_cuda_attention_scratch_bytes(...) bytes. */
 DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_t head_dim, int32_t n_keys);
