@@ -192,6 +192,15 @@ struct CudaLlamaDecoder::Impl {
                 uint32_t flags) {
         run(kind, [&] { return cuda::launch_matmul_tile(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, in, in_stride, out, out_stride, bias, M, w.rows, w.cols, flags, stream); });
     }
+    // Causal attention of a chunk: flash attention on the tensor cores for head_dim 64 / 128 (the reference's attention_prefill), the CUDA-core kernel
+    // otherwise, or when prefill_tile = 1 asks for the plain kernels.
+    void prefill_attention(__half * kcl, __half * vcl, __half * out16, int M, const AttnShape & as) {
+        if (cfg.prefill_tile != 1 && cuda::attention_flash_supported(as)) {
+            run("attention", [&] { return cuda::launch_attention_flash(qkv, kcl, vcl, attn, out16, state, M, as, stream); });
+        } else {
+            run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, out16, state, M, as, stream); });
+        }
+    }
     // Y[m][row0 + n] (+)= X16[m] . W[n] on the tensor cores; X16 is the f16 activation buffer behind map.
     void gemm_tc(const char * kind, const MatDev & w, const MatDev * w2, const cuda::TensorMap & map, float * out, __half * out16, const float * bias, int M,
                  int64_t out_stride, int64_t out16_stride, uint32_t flags) {
@@ -242,7 +251,7 @@ struct CudaLlamaDecoder::Impl {
                     gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
                 }
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
-                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, attn16, state, M, as, stream); });
+                prefill_attention(kcl, vcl, attn16, M, as);
                 gemm_tc("attn_output", L.attn_output, nullptr, map_attn, o_dst, nullptr, nullptr, M, E, 0, o_flags);
                 reduce_into_x(M);
                 norm(x, L.ffn_norm, M, false, true);
@@ -254,7 +263,7 @@ struct CudaLlamaDecoder::Impl {
                     matmul("qkv", q.w, nullptr, xn, E, qkv + q.row0, qkv_width, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, L.qkv_bias ? kFlagBias : 0u);
                 }
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
-                run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, nullptr, state, M, as, stream); });
+                prefill_attention(kcl, vcl, nullptr, M, as);
                 matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
                 norm(x, L.ffn_norm, M, false);

@@ -61,6 +61,11 @@ cudaError_t launch_attention_decode(const float * q, const void * kc, const void
 cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,
                                      const AttnShape & s, cudaStream_t stream);
 
+// The same on the tensor cores (attention_flash.cu) for head_dim 64 or 128.
+bool attention_flash_supported(const AttnShape & s);
+cudaError_t launch_attention_flash(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M, const AttnShape & s,
+                                   cudaStream_t stream);
+
 // tokens[st->tok_out] = first index of the maximum of logits[0..n) (NaN never wins); the token also goes to host_tokens[st->tok_out] when that is set
 // (mapped pinned memory). With advance the state moves one decode step forward (pos, tok_in, tok_out += 1). part: argmax_blocks(n) x 2 words.
 int argmax_blocks(int64_t n);
