@@ -70,6 +70,10 @@ class GgufTensor(C.Structure):
                 ("nbytes", C.c_uint64), ("data", C.c_void_p)]
 
 
+class TpShare(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t)] + [(n, C.c_int64) for n in ("q_row0", "q_rows", "kv_row0", "kv_rows", "ff_row0", "ff_rows", "vocab_row0", "vocab_rows")]
+
+
 TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int32, C.c_int32, C.c_void_p)
 
 # name -> (restype, argtypes); every symbol include/dooms_cuda.h declares
@@ -116,6 +120,7 @@ SIGNATURES = {
     "dooms_cuda_argmax_noalloc": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "dooms_cuda_attention_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "dooms_cuda_attention_decode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "dooms_cuda_tp_share": (C.c_int32, [C.POINTER(LlamaConfig), C.c_int32, C.c_int32, C.POINTER(TpShare)]),
     "dooms_cuda_nccl_unique_id": (C.c_int32, [C.c_char_p, C.c_void_p]),
 }
 

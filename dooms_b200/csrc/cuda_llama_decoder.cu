@@ -334,6 +334,24 @@ namespace cuda {
 cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream);
 }
 
+Result<TpShare> tp_share(const LlamaDecoderConfig & c, int32_t rank, int32_t tp) {
+    if (tp < 1 || rank < 0 || rank >= tp) return invalid_argument("tp_rank must be in [0, tp_size)");
+    if (c.n_head < 1 || c.n_head_kv < 1 || c.n_head % tp != 0 || c.n_head_kv % tp != 0 || c.n_ff % tp != 0) {
+        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs needs n_head, n_head_kv and n_ff to be multiples of it");
+    }
+    TpShare s;
+    s.q_rows = int64_t(c.n_head / tp) * c.head_dim;
+    s.q_row0 = s.q_rows * rank;
+    s.kv_rows = int64_t(c.n_head_kv / tp) * c.head_dim;
+    s.kv_row0 = s.kv_rows * rank;
+    s.ff_rows = c.n_ff / tp;
+    s.ff_row0 = s.ff_rows * rank;
+    const int64_t stride = (int64_t(c.n_vocab) + tp - 1) / tp;
+    s.vocab_row0 = stride * rank;
+    s.vocab_rows = std::max<int64_t>(0, std::min<int64_t>(stride, int64_t(c.n_vocab) - s.vocab_row0));
+    return s;
+}
+
 CudaLlamaDecoder::CudaLlamaDecoder(std::unique_ptr<Impl> impl) : impl_(std::move(impl)) {}
 CudaLlamaDecoder::~CudaLlamaDecoder() = default;
 
@@ -412,9 +430,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
 
     // This rank's share under tensor parallelism: whole heads, and column shards that are whole blocks.
     const int tp = opt.tp_size;
-    if (c.n_head % tp != 0 || c.n_head_kv % tp != 0 || c.n_ff % tp != 0) {
-        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs needs n_head, n_head_kv and n_ff to be multiples of it");
-    }
+    const Result<TpShare> share = tp_share(c, opt.tp_rank, tp);
+    if (!share.is_ok()) return share.status();
     for (const LlamaLayerWeights & L : w.layers) {
         if ((Qw / tp) % dtype_block_elems(L.attn_output.dtype) != 0 || (F / tp) % dtype_block_elems(L.ffn_down.dtype) != 0) {
             return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs would cut attn_output or ffn_down inside a quantization block");
@@ -440,10 +457,10 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.q_width = m.nh * c.head_dim;
     m.kv_width = m.nkv * c.head_dim;
     m.qkv_width = m.q_width + 2 * m.kv_width;
-    m.ff = c.n_ff / tp;
+    m.ff = int32_t(share.value().ff_rows);
     m.vocab_stride = int32_t((V + tp - 1) / tp);
-    m.vocab_row0 = m.vocab_stride * m.rank;
-    m.vocab_rows = int32_t(std::max<int64_t>(0, std::min<int64_t>(m.vocab_stride, V - m.vocab_row0)));
+    m.vocab_row0 = int32_t(share.value().vocab_row0);
+    m.vocab_rows = int32_t(share.value().vocab_rows);
 
     if (cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking) != cudaSuccess) return internal_error(cuda_msg("cudaStreamCreate", cudaGetLastError()));
     cudaEventCreate(&m.ev_a);

@@ -54,6 +54,11 @@ struct CudaOptions {
     bool use_graphs = true;                  // decode steps replay a captured CUDA graph
 };
 
+// A rank's share of the model under tensor parallelism: whole heads, a slice of the feed-forward width, a slice of the vocabulary.
+struct TpShare { int64_t q_row0 = 0, q_rows = 0, kv_row0 = 0, kv_rows = 0, ff_row0 = 0, ff_rows = 0, vocab_row0 = 0, vocab_rows = 0; };
+//   InvalidArgument  tp_rank outside [0, tp_size)     Unsupported  n_head, n_head_kv or n_ff is not a multiple of tp_size
+Result<TpShare> tp_share(const LlamaDecoderConfig & config, int32_t tp_rank, int32_t tp_size);
+
 class CudaLlamaDecoder {
 public:
     //   Unsupported  no CUDA device, a weight type the kernels do not take, a head_dim that is not a power of two in [4, 256]

@@ -4,7 +4,7 @@
 //   * One block of threads computes 128 weight rows x up to 256 tokens. The weight tile is the MMA's A operand (M = 128: one weight row per TMEM lane), the
 //     token tile its B operand (N = 128 or 256), both K-major f16 in the 128-byte swizzled layout; D[n][m] lives in 256 TMEM columns (gate/up: two
 //     accumulators, all 512 columns).
-//   * Per 64-wide k step: the token tile (f16 activations written by the producing kernel) arrives by TMA (cp.async.bulk.tensor.2d, no multicast); 256
+//   * Per 64-wide k step: the token tile (f16 activations written by the producing kernel) arrives by TMA (cp.async.bulk.tensor.2d, one block of threads per copy); 256
 //     producer threads read the weight rows' raw blocks from global memory (two threads per row, 32 elements each), dequantize them to f16 exactly as the
 //     reference's tiles do (half(Q::elem), src/backend/metal/llama_kernels.h:1027-1035, 197) and store them swizzled; one thread issues the four k = 16
 //     MMAs and commits the stage back to the producers. Stages are handed over through mbarriers; every wait is bounded and reports failure instead of

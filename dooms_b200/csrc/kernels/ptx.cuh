@@ -1,6 +1,6 @@
 #pragma once
 // Thin wrappers over the sm_100a PTX this backend uses directly: mbarriers, 1-D bulk (TMA) copies into shared memory, warp-level integer MMA.
-// No bulk copy here uses cluster multicast. Every wait is bounded: it gives up after a fixed number of polls and reports failure to the caller.
+// Every copy here targets the issuing block only. Every wait is bounded: it gives up after a fixed number of polls and reports failure to the caller.
 #include <cstdint>
 
 namespace dooms {

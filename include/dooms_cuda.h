@@ -207,6 +207,16 @@ DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_
 DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void * d_kc, const void * d_vc, float * d_out, void * d_scratch, int32_t n_head,
                                                    int32_t n_head_kv, int32_t head_dim, int32_t n_keys, void * stream);
 
+/* This rank's share of the model under tensor parallelism (no counterpart in the reference): rows [q_row0, q_row0 + q_rows) of attn_q and the same
+ * columns of attn_output, rows [kv_row0, ..) of attn_k / attn_v (whole heads; the KV cache holds only these heads), rows [ff_row0, ..) of ffn_gate /
+ * ffn_up and the same columns of ffn_down, rows [vocab_row0, ..) of the output matrix. The partial sums of attn_output and ffn_down are all-reduced.
+ * Host only. DOOMS_UNSUPPORTED when the heads or n_ff do not divide by tp_size. */
+typedef struct dooms_tp_share {
+    size_t struct_size;
+    int64_t q_row0, q_rows, kv_row0, kv_rows, ff_row0, ff_rows, vocab_row0, vocab_rows;
+} dooms_tp_share;
+DOOMS_CUDA_API int32_t dooms_cuda_tp_share(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, dooms_tp_share * out);
+
 /* Tensor-parallel set-up helper: fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and sends the bytes to the other ranks). */
 DOOMS_CUDA_API int32_t dooms_cuda_nccl_unique_id(const char * nccl_library, void * out128);
 
