@@ -207,6 +207,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if os.environ.get("DOOMS_BENCH_WATCHDOG"):      # dump every thread's stack and exit if the run is still going after this many seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["DOOMS_BENCH_WATCHDOG"]), exit=True)
 
     if args.impl == "reference":
         run_reference_arm(args, rank, world, None)
@@ -273,6 +276,7 @@ def main():
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     sum_prefill_ms, sum_decode_ms, sum_wall = [float(v) for v in stats.cpu()]
+    dec.close()      # every rank at the same point: tearing down the tensor-parallel group is collective
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()

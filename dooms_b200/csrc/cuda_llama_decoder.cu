@@ -97,8 +97,8 @@ struct CudaLlamaDecoder::Impl {
 
     ~Impl() {
         if (stream) cudaStreamSynchronize(stream);
+        if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
         if (comm) nccl.CommDestroy(comm);
-        if (step_graph) cudaGraphExecDestroy(step_graph);
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);

