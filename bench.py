@@ -234,7 +234,8 @@ def main():
         box = [nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         uid = box[0]
-    dec = CudaLlamaDecoder.load(path, n_prompt + n_gen + 16, n_batch, device=local, tp_rank=rank, tp_size=world, nccl_unique_id=uid)
+    dec = CudaLlamaDecoder.load(path, n_prompt + n_gen + 16, n_batch, device=local, tp_rank=rank, tp_size=world, nccl_unique_id=uid,
+                                use_graphs=os.environ.get("DOOMS_BENCH_NO_GRAPHS") is None)
     prompt = synth.prompt_tokens(n_prompt, spec.n_vocab, 2000 + config)
     tokens: list[int] = []
 

@@ -20,6 +20,7 @@
 
 #include "kernels.h"
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "xsplit.cuh"
 
 namespace dooms {
@@ -50,6 +51,8 @@ struct GemvQ40Params {
 
 // x[K] (f32) -> xq. One warp per 32-element block.
 __global__ void __launch_bounds__(256) k_quantize_x(const float * x, int nb, uint8_t * xq) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x % 32;
     const int blk = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (blk >= nb) return;
@@ -155,16 +158,19 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     };
 
     int fetched = 0;
-    // the split input first (its own group), then the first STAGES - 1 stages
-    for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
-    cp_async_commit();
+    // The first STAGES - 1 stages of weights are asked for at once: they do not depend on the kernel before this one, which may still be running (this
+    // kernel is launched early, see launch.cuh). Only then wait for that kernel, and fetch the split input it (or one before it) wrote, as one more group.
+    pdl_trigger();
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (fetched < my_units) { fetch(); fetched++; }
         cp_async_commit();
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
-    cp_async_wait<STAGES - 1>();      // the split input has landed (this thread's part)
+    pdl_wait();
+    for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
+    cp_async_commit();
+    cp_async_wait<0>();               // the split input has landed (this thread's part), and with it the first stages
     __syncthreads();
 
     const bool first = g < 4;
@@ -286,8 +292,8 @@ cudaError_t launch_with(const GemvQ40Params & p, size_t smem, unsigned grid, cud
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
-    k_gemv_q4_0<WARPS, STAGES><<<grid, WARPS * 32, smem, stream>>>(p);
-    return cudaGetLastError();
+    static const bool early = [] { const char * e = getenv("DOOMS_PDL_GEMV"); return !(e && *e == '0'); }();
+    return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
 }
 
 }  // namespace
@@ -300,8 +306,7 @@ size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }
 
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
     const int nb = int(cols / 32);
-    k_quantize_x<<<(nb + 7) / 8, 256, 0, stream>>>(x, nb, static_cast<uint8_t *>(xq));
-    return cudaGetLastError();
+    return launch_pdl(k_quantize_x, dim3((nb + 7) / 8), dim3(256), 0, stream, x, nb, static_cast<uint8_t *>(xq));
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,

@@ -6,6 +6,7 @@
 #include <math_constants.h>
 
 #include "quant.cuh"
+#include "launch.cuh"
 #include "xsplit.cuh"
 
 namespace dooms {
@@ -48,6 +49,8 @@ struct GlobalX {
 // ---------------------------------------------------------------- state
 
 __global__ void k_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t tok_out) {
+    pdl_trigger();
+    pdl_wait();
     st->pos = pos;
     st->tok_in = tok_in;
     st->tok_out = tok_out;
@@ -57,6 +60,8 @@ __global__ void k_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t 
 
 template <int DT>
 __global__ void k_embed(const uint8_t * table, const int32_t * ids, const int32_t * index, float * x, int E) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= E) return;
@@ -72,6 +77,8 @@ __global__ void k_embed(const uint8_t * table, const int32_t * ids, const int32_
 // xq (optional, one row only, E a multiple of 32): the normalized row also split for that kernel (xsplit.cuh).
 constexpr int kNormThreads = 1024, kNormMaxPerThread = 8;
 __global__ void __launch_bounds__(kNormThreads) k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, uint8_t * xq, int E, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[32];
     const float * xr = x + int64_t(blockIdx.x) * E;
     const int64_t obase = int64_t(blockIdx.x) * E;
@@ -131,6 +138,8 @@ constexpr int kMvWarps = 4;
 
 template <int DT>
 __global__ void __launch_bounds__(kMvWarps * 32) k_matvec(const uint8_t * W, const float * x, float * y, const float * bias, int64_t rows, int cols, uint32_t flags) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int64_t r = int64_t(blockIdx.x) * kMvWarps + warp;
     if (r >= rows) return;
@@ -147,6 +156,8 @@ __global__ void __launch_bounds__(kMvWarps * 32) k_matvec(const uint8_t * W, con
 
 template <int DT>
 __global__ void __launch_bounds__(kMvWarps * 32) k_gate_up(const uint8_t * Wg, const uint8_t * Wu, const float * x, float * h, int64_t rows, int cols) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int64_t r = int64_t(blockIdx.x) * kMvWarps + warp;
     if (r >= rows) return;
@@ -246,6 +257,8 @@ __device__ __forceinline__ void rope_sincos(int pos, int i, int hd, float base, 
 
 // grid (n_head + 2 * n_head_kv, M), head_dim / 2 threads: slots are query heads (rotated in place), key heads (rotated into the cache), value heads (copied).
 __global__ void k_rope_store(float * qkv, __half * kc, __half * vc, const DevState * st, AttnShape p) {
+    pdl_trigger();
+    pdl_wait();
     const int slot = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = p.head_dim;
     const int pos = st->pos + t;
     const int e0 = p.neox ? i : 2 * i, e1 = p.neox ? i + hd / 2 : 2 * i + 1;
@@ -280,6 +293,8 @@ constexpr int kMaxDimsPerLane = 8;   // head_dim <= 256
 // part entry: (max, sum, values[head_dim]) unnormalised; direct: splits == 1, the normalised result goes straight to out.
 __global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, const __half * kc, const __half * vc, float * out, __half * out16, float * part,
                                                                const DevState * st, int n_keys_fixed, int splits, int direct, AttnShape p) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float qs[256];
     __shared__ float wm[kAttnWarps], wl[kAttnWarps];
     __shared__ float wo[kAttnWarps][256];
@@ -341,6 +356,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attention(const float * q, 
 
 // out[t][h] = merge of the splits' partial results (attention_combine, llama_kernels.h:914-929). grid (n_head, M), head_dim threads.
 __global__ void k_attention_combine(const float * part, float * out, uint8_t * xq, int splits, AttnShape p) {
+    pdl_trigger();
+    pdl_wait();
     const int h = blockIdx.x, t = blockIdx.y, hd = p.head_dim, i = threadIdx.x;
     const float * base = part + (int64_t(t) * p.n_head + h) * splits * (2 + hd);
     float mx = -CUDART_INF_F;
@@ -393,6 +410,8 @@ __device__ __forceinline__ Best block_best(Best b) {
 constexpr int kArgmaxThreads = 256, kArgmaxPerBlock = 4096;
 
 __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_part(const float * logits, int64_t n, Best * part) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t begin = int64_t(blockIdx.x) * kArgmaxPerBlock, end = min(n, begin + kArgmaxPerBlock);
     Best b{0.f, -1};
     for (int64_t i = begin + threadIdx.x; i < end; i += kArgmaxThreads) {
@@ -405,6 +424,8 @@ __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_part(const float * lo
 
 __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_final(const Best * part, int nparts, int32_t * tokens, int32_t * host_tokens, DevState * st,
                                                                  int32_t * plain_out, int advance) {
+    pdl_trigger();
+    pdl_wait();
     Best b{0.f, -1};
     for (int i = threadIdx.x; i < nparts; i += kArgmaxThreads) if (better(part[i].v, part[i].i, b.v, b.i)) b = part[i];
     b = block_best(b);
@@ -423,36 +444,37 @@ __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_final(const Best * pa
 // ---------------------------------------------------------------- launchers
 
 cudaError_t launch_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t tok_out, cudaStream_t stream) {
-    k_set_state<<<1, 1, 0, stream>>>(st, pos, tok_in, tok_out);
-    return cudaGetLastError();
+    return launch_pdl(k_set_state, dim3(1), dim3(1), 0, stream, st, pos, tok_in, tok_out);
 }
 
 cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const int32_t * index, float * x, int rows, int E, cudaStream_t stream) {
     const dim3 grid((E + 255) / 256, rows);
-    const bool ok = dispatch_mat(dt, [&]<int DT>() { k_embed<DT><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(table), ids, index, x, E); });
-    return ok ? cudaGetLastError() : cudaErrorInvalidValue;
+    cudaError_t e = cudaSuccess;
+    const bool ok = dispatch_mat(dt, [&]<int DT>() { e = launch_pdl(k_embed<DT>, grid, dim3(256), 0, stream, static_cast<const uint8_t *>(table), ids, index, x, E); });
+    return ok ? e : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, void * xq, int rows, int E, float eps, cudaStream_t stream) {
     if (xq && (rows != 1 || E % 32 != 0)) return cudaErrorInvalidValue;
-    k_rms_norm<<<rows, kNormThreads, 0, stream>>>(x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
-    return cudaGetLastError();
+    return launch_pdl(k_rms_norm, dim3(rows), dim3(kNormThreads), 0, stream, x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
 }
 
 cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
+    cudaError_t e = cudaSuccess;
     const bool ok = dispatch_mat(dt, [&]<int DT>() {
-        k_matvec<DT><<<grid, kMvWarps * 32, 0, stream>>>(static_cast<const uint8_t *>(W), x, y, bias, rows, int(cols), flags);
+        e = launch_pdl(k_matvec<DT>, dim3(grid), dim3(kMvWarps * 32), 0, stream, static_cast<const uint8_t *>(W), x, y, bias, rows, int(cols), flags);
     });
-    return ok ? cudaGetLastError() : cudaErrorInvalidValue;
+    return ok ? e : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_gate_up(int dt, const void * Wg, const void * Wu, const float * x, float * h, int64_t rows, int64_t cols, cudaStream_t stream) {
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
+    cudaError_t e = cudaSuccess;
     const bool ok = dispatch_mat(dt, [&]<int DT>() {
-        k_gate_up<DT><<<grid, kMvWarps * 32, 0, stream>>>(static_cast<const uint8_t *>(Wg), static_cast<const uint8_t *>(Wu), x, h, rows, int(cols));
+        e = launch_pdl(k_gate_up<DT>, dim3(grid), dim3(kMvWarps * 32), 0, stream, static_cast<const uint8_t *>(Wg), static_cast<const uint8_t *>(Wu), x, h, rows, int(cols));
     });
-    return ok ? cudaGetLastError() : cudaErrorInvalidValue;
+    return ok ? e : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_matmul_tile(int dt, const void * W, const void * W2, const float * X, int64_t x_stride, float * Y, int64_t y_stride, const float * bias,
@@ -480,8 +502,7 @@ cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t strea
 
 cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, int M, const AttnShape & s, cudaStream_t stream) {
     const dim3 grid(s.n_head + 2 * s.n_head_kv, M);
-    k_rope_store<<<grid, s.head_dim / 2, 0, stream>>>(qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), st, s);
-    return cudaGetLastError();
+    return launch_pdl(k_rope_store, grid, dim3(s.head_dim / 2), 0, stream, qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), st, s);
 }
 
 int attention_splits(int n_head, int n_ctx) {
@@ -494,36 +515,35 @@ cudaError_t launch_attention_decode(const float * q, const void * kc, const void
                                     int n_keys_fixed, int splits, const AttnShape & s, cudaStream_t stream) {
     if (xq && (splits == 1 || s.head_dim % 32 != 0)) return cudaErrorInvalidValue;
     const dim3 grid(s.n_head, splits, 1);
-    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(q, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, nullptr, part, st, n_keys_fixed,
-                                                      splits, splits == 1 ? 1 : 0, s);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(k_attention, grid, dim3(kAttnWarps * 32), 0, stream, q, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out,
+                               static_cast<__half *>(nullptr), part, st, n_keys_fixed, splits, splits == 1 ? 1 : 0, s);
     if (e != cudaSuccess || splits == 1) return e;
-    k_attention_combine<<<dim3(s.n_head, 1), s.head_dim, 0, stream>>>(part, out, static_cast<uint8_t *>(xq), splits, s);
-    return cudaGetLastError();
+    return launch_pdl(k_attention_combine, dim3(s.n_head, 1), dim3(s.head_dim), 0, stream, static_cast<const float *>(part), out, static_cast<uint8_t *>(xq), splits, s);
 }
 
 cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,
                                      const AttnShape & s, cudaStream_t stream) {
     const dim3 grid(s.n_head, 1, M);
-    k_attention<<<grid, kAttnWarps * 32, 0, stream>>>(qkv, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out, static_cast<__half *>(out16), nullptr,
-                                                      st, 0, 1, 1, s);
-    return cudaGetLastError();
+    return launch_pdl(k_attention, grid, dim3(kAttnWarps * 32), 0, stream, qkv, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out,
+                      static_cast<__half *>(out16), static_cast<float *>(nullptr), st, 0, 1, 1, s);
 }
 
 int argmax_blocks(int64_t n) { return int((n + kArgmaxPerBlock - 1) / kArgmaxPerBlock); }
 
 cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int32_t * host_tokens, DevState * st, void * part, int advance, cudaStream_t stream) {
     const int blocks = argmax_blocks(n);
-    k_argmax_part<<<blocks, kArgmaxThreads, 0, stream>>>(logits, n, static_cast<Best *>(part));
-    k_argmax_final<<<1, kArgmaxThreads, 0, stream>>>(static_cast<const Best *>(part), blocks, tokens, host_tokens, st, nullptr, advance);
-    return cudaGetLastError();
+    const cudaError_t e = launch_pdl(k_argmax_part, dim3(blocks), dim3(kArgmaxThreads), 0, stream, logits, n, static_cast<Best *>(part));
+    if (e != cudaSuccess) return e;
+    return launch_pdl(k_argmax_final, dim3(1), dim3(kArgmaxThreads), 0, stream, static_cast<const Best *>(part), blocks, tokens, host_tokens, st,
+                      static_cast<int32_t *>(nullptr), advance);
 }
 
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream) {
     const int blocks = argmax_blocks(n);
-    k_argmax_part<<<blocks, kArgmaxThreads, 0, stream>>>(logits, n, static_cast<Best *>(part));
-    k_argmax_final<<<1, kArgmaxThreads, 0, stream>>>(static_cast<const Best *>(part), blocks, nullptr, nullptr, nullptr, out, 0);
-    return cudaGetLastError();
+    const cudaError_t e = launch_pdl(k_argmax_part, dim3(blocks), dim3(kArgmaxThreads), 0, stream, logits, n, static_cast<Best *>(part));
+    if (e != cudaSuccess) return e;
+    return launch_pdl(k_argmax_final, dim3(1), dim3(kArgmaxThreads), 0, stream, static_cast<const Best *>(part), blocks, static_cast<int32_t *>(nullptr),
+                      static_cast<int32_t *>(nullptr), static_cast<DevState *>(nullptr), out, 0);
 }
 
 }  // namespace cuda
