@@ -451,7 +451,8 @@ DOOMS_CUDA_API int32_t dooms_cuda_argmax_noalloc(const float * d_logits, int64_t
 
 DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_t head_dim, int32_t n_keys) {
     if (n_head < 1 || head_dim < 1 || n_keys < 1) return 0;
-    return int64_t(cuda::attention_splits(n_head, n_keys)) * n_head * (2 + head_dim) * 4;
+    // enough for either kernel: the grouped-query one uses at most one range per SM
+    return int64_t(std::max(cuda::attention_splits(n_head, n_keys), cuda::attention_gqa_splits(1, n_keys))) * n_head * (2 + head_dim) * 4;
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void * d_kc, const void * d_vc, float * d_out, void * d_scratch, int32_t n_head,
@@ -461,6 +462,15 @@ DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void
     }
     if (head_dim < 4 || head_dim > 256 || (head_dim & (head_dim - 1)) != 0) return fail(DOOMS_UNSUPPORTED, "attention_decode: head_dim must be a power of two in [4, 256]");
     const cuda::AttnShape s{n_head, n_head_kv, head_dim, n_head * head_dim, n_head_kv * head_dim, n_head * head_dim, 0, 10000.f};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cuda::attention_gqa_supported(s) && (reinterpret_cast<uintptr_t>(d_kc) & 15u) == 0 && (reinterpret_cast<uintptr_t>(d_vc) & 15u) == 0) {
+        // q alone is read of the row, so d_q stands for the whole row
+        const int gs = cuda::attention_gqa_splits(n_head_kv, n_keys);
+        const cudaError_t e = cuda::launch_attention_gqa(d_q, const_cast<void *>(d_kc), const_cast<void *>(d_vc), static_cast<float *>(d_scratch), nullptr, nullptr,
+                                                         n_keys, gs, s, st);
+        if (e != cudaSuccess) return launch_result(e, "attention_decode");
+        return launch_result(cuda::launch_attention_combine(static_cast<const float *>(d_scratch), d_out, nullptr, gs, s, st), "attention_decode");
+    }
     const int splits = cuda::attention_splits(n_head, n_keys);
     return launch_result(cuda::launch_attention_decode(d_q, d_kc, d_vc, d_out, static_cast<float *>(d_scratch), nullptr, nullptr, n_keys, splits, s,
                                                        static_cast<cudaStream_t>(stream)), "attention_decode");

@@ -80,6 +80,9 @@ struct CudaLlamaDecoder::Impl {
     DevState * state = nullptr;
     int32_t * host_error = nullptr;   // mapped pinned word a kernel sets when a bounded wait ran out
     int splits = 1;
+    bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
+    int gqa_splits = 1;
+    double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
     int32_t pos = 0;
     bool has_pending = false;
     // decode graph
@@ -102,7 +105,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -234,9 +237,14 @@ struct CudaLlamaDecoder::Impl {
             norm(x, L.attn_norm, M, qkv_fast, use_tc);
             if (M == 1) {
                 for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
-                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
-                const bool split_attn = fast(L.attn_output) && splits > 1 && cfg.head_dim % 32 == 0;
-                run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
+                const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
+                if (gqa) {
+                    run("attention", [&] { return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, stream); });
+                    run("attention_combine", [&] { return cuda::launch_attention_combine(part, attn, split_attn ? xq : nullptr, gqa_splits, as, stream); });
+                } else {
+                    run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
+                    run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
+                }
                 xq_of = split_attn ? attn : nullptr;
                 matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
@@ -605,7 +613,9 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.cache_layer_elems = size_t(c.n_ctx) * size_t(m.kv_width);
     m.kv_bytes = 2 * size_t(c.n_layer) * m.cache_layer_elems * sizeof(__half);
     m.splits = cuda::attention_splits(m.nh, c.n_ctx);
-    const size_t part_floats = size_t(m.splits) * size_t(m.nh) * size_t(2 + c.head_dim);
+    m.gqa = cuda::attention_gqa_supported(m.attn_shape());
+    m.gqa_splits = cuda::attention_gqa_splits(m.nkv, c.n_ctx);
+    const size_t part_floats = size_t(std::max(m.splits, m.gqa_splits)) * size_t(m.nh) * size_t(2 + c.head_dim);
     const size_t logits_floats = size_t(m.vocab_stride) * size_t(tp);
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.kc), m.kv_bytes / 2, "the key cache"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.vc), m.kv_bytes / 2, "the value cache"));
@@ -617,6 +627,12 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
+    {
+        std::vector<double> freq(size_t(c.head_dim / 2));
+        for (size_t i = 0; i < freq.size(); i++) freq[i] = std::pow(double(c.rope_base), -2.0 * double(i) / double(c.head_dim));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.inv_freq), freq.size() * sizeof(double), "the rotary frequencies"));
+        if (cudaMemcpy(m.inv_freq, freq.data(), freq.size() * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) return internal_error("copying the rotary frequencies");
+    }
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
                                     "the split projection input"));
     if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {

@@ -1,0 +1,288 @@
+// Decode attention for one new token, grouped-query aware: the query heads that share a key/value head are processed together, so every cached key and value
+// row is read from device memory once per step, in 16-byte coalesced asynchronous copies, by a grid of (key/value head, range of positions) blocks that
+// covers all SMs. The kernel also does what used to be a launch of its own before it: it rotates the new token's query and key (rope_store,
+// src/backend/metal/llama_kernels.h:521-545), writes the rotated key and the value into the f16 cache, and uses them from shared memory in the same pass.
+// Each block leaves an unnormalised partial result (max, sum, values) per query head; k_attention_combine merges the ranges (attention_split /
+// attention_combine, llama_kernels.h:860-929).
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include <algorithm>
+
+#include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace dooms {
+namespace cuda {
+
+using namespace dooms::dev;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTileKeys = 64;
+constexpr int kStages = 2;
+
+struct AttnDecodeParams {
+    const float * qkv;        // the new token's row: query heads, then key heads, then value heads
+    __half * kc;
+    __half * vc;
+    float * part;             // [n_head][splits][2 + head_dim]
+    const DevState * st;
+    const double * inv_freq;  // head_dim / 2 rotary frequencies; nullptr: q is used as it is and nothing is written to the cache
+    int n_keys_fixed, splits;
+    AttnShape s;
+};
+
+__device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// D: head_dim (64 or 128). GP: query heads per key/value head, rounded up to 1, 2, 4 or 8.
+template <int D, int GP>
+__global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeParams p) {
+    constexpr int KP = D * 2 + 16;                      // bytes between key rows in a stage: 16-byte loads of 8 consecutive rows fall on different banks
+    constexpr int VP = D * 2;
+    constexpr int STAGE = kTileKeys * (KP + VP);
+    constexpr int HQ = kThreads / kTileKeys;            // threads per key in the score phase: 4, each with the heads hq, hq + 4
+    constexpr int HPT = (GP + HQ - 1) / HQ;             // heads per thread there
+    constexpr int OUT_IT = (GP * D / 2 + kThreads - 1) / kThreads;   // (head, dim pair) outputs per thread
+    extern __shared__ __align__(128) uint8_t smem[];
+    float * qs = reinterpret_cast<float *>(smem);                      // [GP][D], scaled
+    float * sc = qs + GP * D;                                          // [GP][kTileKeys] scores, then probabilities
+    float * corr = sc + GP * kTileKeys;                                // [GP]
+    uint8_t * stages = smem + ((GP * D + GP * kTileKeys + GP) * 4 + 127) / 128 * 128;
+    const uint32_t stages_u = smem_u32(stages);
+
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int kvh = blockIdx.x, split = blockIdx.y;
+    const int G = p.s.n_head / p.s.n_head_kv;
+    const bool fuse = p.inv_freq != nullptr;
+    const int pos = fuse ? p.st->pos : 0;
+    const int n_keys = p.n_keys_fixed > 0 ? p.n_keys_fixed : pos + 1;
+    // ranges of whole tiles, the same for every head: at least one tile per range, so short contexts leave the later ranges empty
+    const int tiles_total = (n_keys + kTileKeys - 1) / kTileKeys;
+    const int tiles_per = (tiles_total + p.splits - 1) / p.splits;
+    const int j_begin = min(n_keys, split * tiles_per * kTileKeys), j_end = min(n_keys, j_begin + tiles_per * kTileKeys);
+    const int ntiles = (j_end - j_begin + kTileKeys - 1) / kTileKeys;
+
+    auto fetch = [&](int tile) {
+        const int j0 = j_begin + tile * kTileKeys, cnt = min(kTileKeys, j_end - j0);
+        const uint32_t base = stages_u + uint32_t(tile % kStages) * STAGE;
+        constexpr int PIECES = D * 2 / 16;      // 16-byte pieces per row
+        for (int i = tid; i < cnt * PIECES; i += kThreads) {
+            const int r = i / PIECES, c = i % PIECES;
+            cp16(base + r * KP + c * 16, p.kc + int64_t(j0 + r) * p.s.kv_stride + kvh * D + c * 8);
+            cp16(base + kTileKeys * KP + r * VP + c * 16, p.vc + int64_t(j0 + r) * p.s.kv_stride + kvh * D + c * 8);
+        }
+    };
+    if (ntiles > 0) fetch(0);
+    cp_commit();
+    if (ntiles > 1) fetch(1);
+    cp_commit();
+
+    // the group's queries: rotated (when asked), scaled
+    const float scale = rsqrtf(float(D));
+    for (int i = tid; i < GP * D / 2; i += kThreads) {
+        const int hq = i / (D / 2), d = i % (D / 2);
+        const int e0 = p.s.neox ? d : 2 * d, e1 = p.s.neox ? d + D / 2 : 2 * d + 1;
+        float r0 = 0.f, r1 = 0.f;
+        if (hq < G) {
+            const float * x = p.qkv + (kvh * G + hq) * D;
+            r0 = x[e0];
+            r1 = x[e1];
+            if (fuse) {
+                double sd, cd;
+                sincos(double(pos) * p.inv_freq[d], &sd, &cd);
+                const float c = float(cd), s = float(sd), a = r0, b = r1;
+                r0 = a * c - b * s;
+                r1 = a * s + b * c;
+            }
+        }
+        qs[hq * D + e0] = r0 * scale;
+        qs[hq * D + e1] = r1 * scale;
+    }
+
+    float m_run = -CUDART_INF_F, l_run = 0.f;      // of head `warp` (warps below GP)
+    float acc[OUT_IT][2];
+    #pragma unroll
+    for (int it = 0; it < OUT_IT; it++) acc[it][0] = acc[it][1] = 0.f;
+
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int j0 = j_begin + tile * kTileKeys, cnt = min(kTileKeys, j_end - j0);
+        uint8_t * ks = stages + (tile % kStages) * STAGE;
+        uint8_t * vs = ks + kTileKeys * KP;
+        cp_wait<kStages - 1>();
+        __syncthreads();
+        if (fuse && pos >= j0 && pos < j0 + cnt) {
+            // the new token's own key and value: into the cache and over the (stale) row that was just copied from it
+            const int r = pos - j0;
+            if (tid < D / 2) {
+                const int d = tid;
+                const int e0 = p.s.neox ? d : 2 * d, e1 = p.s.neox ? d + D / 2 : 2 * d + 1;
+                const float * x = p.qkv + (p.s.n_head + kvh) * D;
+                double sd, cd;
+                sincos(double(pos) * p.inv_freq[d], &sd, &cd);
+                const float c = float(cd), s = float(sd), a = x[e0], b = x[e1];
+                const __half h0 = __float2half_rn(a * c - b * s), h1 = __float2half_rn(a * s + b * c);
+                __half * dst = p.kc + int64_t(pos) * p.s.kv_stride + kvh * D;
+                __half * row = reinterpret_cast<__half *>(ks + r * KP);
+                dst[e0] = h0; dst[e1] = h1;
+                row[e0] = h0; row[e1] = h1;
+            } else if (tid >= 64 && tid < 64 + D) {
+                const int e = tid - 64;
+                const __half hv = __float2half_rn(p.qkv[(p.s.n_head + p.s.n_head_kv + kvh) * D + e]);
+                p.vc[int64_t(pos) * p.s.kv_stride + kvh * D + e] = hv;
+                reinterpret_cast<__half *>(vs + r * VP)[e] = hv;
+            }
+            __syncthreads();
+        }
+        // scores: thread (key, hq) for heads hq, hq + HQ, ...
+        {
+            const int key = tid % kTileKeys, hq0 = tid / kTileKeys;
+            float a[HPT];
+            #pragma unroll
+            for (int i = 0; i < HPT; i++) a[i] = 0.f;
+            if (key < cnt && hq0 < G) {
+                const uint4 * krow = reinterpret_cast<const uint4 *>(ks + key * KP);
+                #pragma unroll 4
+                for (int c = 0; c < D / 8; c++) {
+                    const uint4 kv = krow[c];
+                    const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x)), k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
+                    const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.z)), k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.w));
+                    #pragma unroll
+                    for (int i = 0; i < HPT; i++) {
+                        if (hq0 + i * HQ < GP) {
+                            const float4 qa = *reinterpret_cast<const float4 *>(qs + (hq0 + i * HQ) * D + c * 8);
+                            const float4 qb = *reinterpret_cast<const float4 *>(qs + (hq0 + i * HQ) * D + c * 8 + 4);
+                            a[i] += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
+                        }
+                    }
+                }
+            }
+            #pragma unroll
+            for (int i = 0; i < HPT; i++) if (hq0 + i * HQ < GP) sc[(hq0 + i * HQ) * kTileKeys + key] = key < cnt ? a[i] : -CUDART_INF_F;
+        }
+        __syncthreads();
+        // running softmax: warp w owns head w
+        if (warp < GP) {
+            const float s0 = sc[warp * kTileKeys + lane], s1 = sc[warp * kTileKeys + 32 + lane];
+            float mx = fmaxf(s0, s1);
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m_run, mx);
+            const float p0 = lane < cnt ? expf(s0 - m_new) : 0.f, p1 = 32 + lane < cnt ? expf(s1 - m_new) : 0.f;
+            float sum = p0 + p1;
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float cf = expf(m_run - m_new);        // 0 on the first tile
+            l_run = l_run * cf + sum;
+            m_run = m_new;
+            sc[warp * kTileKeys + lane] = p0;
+            sc[warp * kTileKeys + 32 + lane] = p1;
+            if (lane == 0) corr[warp] = cf;
+        }
+        __syncthreads();
+        // values: thread owns (head, dim pair) outputs
+        #pragma unroll
+        for (int it = 0; it < OUT_IT; it++) {
+            const int idx = tid + it * kThreads;
+            if (idx < GP * D / 2) {
+                const int hq = idx / (D / 2), dp = idx % (D / 2);
+                const float cf = corr[hq];
+                float a0 = acc[it][0] * cf, a1 = acc[it][1] * cf;
+                const float * pr = sc + hq * kTileKeys;
+                const __half2 * vcol = reinterpret_cast<const __half2 *>(vs) + dp;
+                if (cnt == kTileKeys) {
+                    #pragma unroll 4
+                    for (int k = 0; k < kTileKeys; k += 4) {
+                        const float4 pk = *reinterpret_cast<const float4 *>(pr + k);
+                        const float2 v0 = __half22float2(vcol[(k + 0) * (D / 2)]), v1 = __half22float2(vcol[(k + 1) * (D / 2)]);
+                        const float2 v2 = __half22float2(vcol[(k + 2) * (D / 2)]), v3 = __half22float2(vcol[(k + 3) * (D / 2)]);
+                        a0 += pk.x * v0.x; a1 += pk.x * v0.y;
+                        a0 += pk.y * v1.x; a1 += pk.y * v1.y;
+                        a0 += pk.z * v2.x; a1 += pk.z * v2.y;
+                        a0 += pk.w * v3.x; a1 += pk.w * v3.y;
+                    }
+                } else {
+                    // rows past cnt hold old bytes: their probabilities are 0, but 0 x NaN is not
+                    for (int k = 0; k < cnt; k++) {
+                        const float2 v = __half22float2(vcol[k * (D / 2)]);
+                        a0 += pr[k] * v.x; a1 += pr[k] * v.y;
+                    }
+                }
+                acc[it][0] = a0;
+                acc[it][1] = a1;
+            }
+        }
+        __syncthreads();                       // the stage and the scores are free again
+        if (tile + kStages < ntiles) fetch(tile + kStages);
+        cp_commit();
+    }
+    cp_wait<0>();
+    // partial results (an empty range leaves sum = 0, which the merge skips)
+    #pragma unroll
+    for (int it = 0; it < OUT_IT; it++) {
+        const int idx = tid + it * kThreads;
+        if (idx < GP * D / 2) {
+            const int hq = idx / (D / 2), dp = idx % (D / 2);
+            if (hq < G) {
+                float * dst = p.part + (int64_t(kvh * G + hq) * p.splits + split) * (2 + D) + 2;
+                dst[2 * dp] = acc[it][0];
+                dst[2 * dp + 1] = acc[it][1];
+            }
+        }
+    }
+    if (warp < G && lane == 0) {
+        float * dst = p.part + (int64_t(kvh * G + warp) * p.splits + split) * (2 + D);
+        dst[0] = m_run;
+        dst[1] = l_run;
+    }
+}
+
+template <int D, int GP>
+cudaError_t launch_one(const AttnDecodeParams & p, cudaStream_t stream) {
+    constexpr size_t smem = ((GP * D + GP * kTileKeys + GP) * 4 + 127) / 128 * 128 + size_t(kStages) * kTileKeys * (D * 4 + 16);
+    static int configured_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_device != dev) {
+        const cudaError_t e = cudaFuncSetAttribute(k_attention_decode<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        configured_device = dev;
+    }
+    return launch_pdl(k_attention_decode<D, GP>, dim3(p.s.n_head_kv, p.splits), dim3(kThreads), smem, stream, p);
+}
+
+template <int D>
+cudaError_t launch_group(const AttnDecodeParams & p, int G, cudaStream_t stream) {
+    if (G == 1) return launch_one<D, 1>(p, stream);
+    if (G == 2) return launch_one<D, 2>(p, stream);
+    if (G <= 4) return launch_one<D, 4>(p, stream);
+    return launch_one<D, 8>(p, stream);
+}
+
+}  // namespace
+
+bool attention_gqa_supported(const AttnShape & s) {
+    return (s.head_dim == 64 || s.head_dim == 128) && s.n_head % s.n_head_kv == 0 && s.n_head / s.n_head_kv <= 8 && s.kv_stride % 8 == 0;
+}
+
+int attention_gqa_splits(int n_head_kv, int n_ctx) {
+    // about one block per SM, and no more ranges than the context has tiles
+    const int want = std::max(1, (148 + n_head_kv - 1) / n_head_kv);
+    return std::max(1, std::min(want, (n_ctx + kTileKeys - 1) / kTileKeys));
+}
+
+cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
+                                 int splits, const AttnShape & s, cudaStream_t stream) {
+    if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1)) return cudaErrorInvalidValue;
+    const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s};
+    return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
+}
+
+}  // namespace cuda
+}  // namespace dooms

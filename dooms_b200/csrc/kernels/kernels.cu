@@ -521,6 +521,11 @@ cudaError_t launch_attention_decode(const float * q, const void * kc, const void
     return launch_pdl(k_attention_combine, dim3(s.n_head, 1), dim3(s.head_dim), 0, stream, static_cast<const float *>(part), out, static_cast<uint8_t *>(xq), splits, s);
 }
 
+cudaError_t launch_attention_combine(const float * part, float * out, void * xq, int splits, const AttnShape & s, cudaStream_t stream) {
+    if (xq && s.head_dim % 32 != 0) return cudaErrorInvalidValue;
+    return launch_pdl(k_attention_combine, dim3(s.n_head, 1), dim3(s.head_dim), 0, stream, part, out, static_cast<uint8_t *>(xq), splits, s);
+}
+
 cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,
                                      const AttnShape & s, cudaStream_t stream) {
     const dim3 grid(s.n_head, 1, M);

@@ -56,6 +56,18 @@ int attention_splits(int n_head, int n_ctx);
 cudaError_t launch_attention_decode(const float * q, const void * kc, const void * vc, float * out, float * part, void * xq, const DevState * st,
                                     int n_keys_fixed, int splits, const AttnShape & s, cudaStream_t stream);
 
+// The merge of the ranges alone: out[h] from part[h][splits][2 + head_dim]; xq (optional) receives the row split for the staged q4_0 GEMV.
+cudaError_t launch_attention_combine(const float * part, float * out, void * xq, int splits, const AttnShape & s, cudaStream_t stream);
+
+// Grouped-query decode attention (attention_decode.cu), head_dim 64 or 128, at most 8 query heads per key/value head, cache rows 16-byte aligned. qkv is
+// the new token's row (query, key and value heads). With inv_freq (head_dim / 2 rotary frequencies base^(-2i / head_dim)) the kernel rotates the query and
+// the key itself and writes key and value into the cache at st->pos (no launch_rope_store before it); without, q is used as it is, the cache is only read
+// and n_keys_fixed gives the number of positions. Leaves part[n_head][splits][2 + head_dim] for launch_attention_combine.
+bool attention_gqa_supported(const AttnShape & s);
+int attention_gqa_splits(int n_head_kv, int n_ctx);
+cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
+                                 int splits, const AttnShape & s, cudaStream_t stream);
+
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
 // out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.
 cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,

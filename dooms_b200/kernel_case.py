@@ -1,0 +1,156 @@
+"""One kernel on one small case, through the C ABI: a correctness check plus CUDA-event timing, sized for a profiler capture.
+
+    python -m dooms_b200.kernel_case gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
+    python -m dooms_b200.kernel_case gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
+    python -m dooms_b200.kernel_case launches <ncu csv>                                     per-kernel totals and shares of an ncu launch list
+
+The GEMV case walks over several distinct matrices so that every launch reads its weights from device memory, not from L2.
+"""
+import argparse
+import collections
+import csv
+import re
+import sys
+
+
+def _gemv(args):
+    import torch
+    from . import _lib as L
+    from .quantize import quantize
+    lib = L.lib()
+    gen = torch.Generator(device='cuda').manual_seed(1)
+    dt = L.DTYPE_NAMES.index(args.dtype)
+    mats = []
+    for _ in range(args.mats):
+        g = quantize(dt, torch.randn(args.rows, args.cols, device='cuda', generator=gen) * 0.02)
+        u = quantize(dt, torch.randn(args.rows, args.cols, device='cuda', generator=gen) * 0.02) if args.gate else None
+        mats.append((g, u))
+    x = torch.randn(args.cols, device='cuda', generator=gen)
+    y = torch.empty(args.rows, device='cuda')
+    st = torch.cuda.current_stream().cuda_stream
+
+    def launch(g, u):
+        if args.gate:
+            L.check(lib.dooms_cuda_gate_up(dt, g.data_ptr(), u.data_ptr(), x.data_ptr(), y.data_ptr(), args.rows, args.cols, st))
+        else:
+            L.check(lib.dooms_cuda_matvec(dt, g.data_ptr(), x.data_ptr(), y.data_ptr(), None, args.rows, args.cols, 0, st))
+
+    # check the last matrix against the dequantized product in f64
+    g, u = mats[-1]
+    launch(g, u)
+    wd = torch.empty(args.rows, args.cols, device='cuda')
+    L.check(lib.dooms_cuda_dequantize(dt, g.data_ptr(), args.rows, args.cols, wd.data_ptr(), st))
+    ref = wd.double() @ x.double()
+    if args.gate:
+        L.check(lib.dooms_cuda_dequantize(dt, u.data_ptr(), args.rows, args.cols, wd.data_ptr(), st))
+        ref = torch.nn.functional.silu(ref) * (wd.double() @ x.double())
+    err = (y.double() - ref).abs().max().item()
+    print(f'max abs error against the f64 product: {err:.3e}')
+    assert err < 1e-3, err
+    nbytes = (2 if args.gate else 1) * g.numel()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.reps):
+        a.record()
+        for g, u in mats:
+            launch(g, u)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / len(mats)
+        print(f'{us:.1f} us per call (input split + GEMV), {nbytes / us / 1e3:.0f} GB/s of weight bytes ({nbytes / 1e6:.1f} MB per call)')
+
+
+def _gemm(args):
+    import torch
+    from . import _lib as L
+    from .quantize import quantize
+    lib = L.lib()
+    gen = torch.Generator(device='cuda').manual_seed(1)
+    dt = L.Q4_0
+    M, N, K = args.tokens, args.rows, args.cols
+    w = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02)
+    w2 = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02) if args.gate else None
+    x = torch.randn(M, K, device='cuda', generator=gen).half()
+    y = torch.zeros(M, N, device='cuda')
+    st = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        L.check(lib.dooms_cuda_matmul(dt, w.data_ptr(), w2.data_ptr() if args.gate else None, x.data_ptr(), y.data_ptr(), None, M, N, K, 0, st))
+
+    launch()
+    wd = torch.empty(N, K, device='cuda')
+    L.check(lib.dooms_cuda_dequantize(dt, w.data_ptr(), N, K, wd.data_ptr(), st))
+    ref = x.float() @ wd.half().float().T
+    if args.gate:
+        L.check(lib.dooms_cuda_dequantize(dt, w2.data_ptr(), N, K, wd.data_ptr(), st))
+        ref = torch.nn.functional.silu(ref) * (x.float() @ wd.half().float().T)
+    rel = ((y - ref).norm() / ref.norm()).item()
+    print(f'relative error against the f16-operand product: {rel:.2e}')
+    assert rel < 2e-3, rel
+    flops = 2.0 * M * N * K * (2 if args.gate else 1)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(args.reps):
+        a.record()
+        for _ in range(4):
+            launch()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / 4
+        print(f'{ms * 1e3:.1f} us per call, {flops / ms / 1e9:.1f} TFLOP/s')
+
+
+def summarize_launches(path, out=sys.stdout):
+    """Totals per kernel of an `ncu --metrics gpu__time_duration.sum --csv` launch list."""
+    header, agg = None, collections.OrderedDict()
+    for row in csv.reader(open(path, newline='')):
+        if header is None:
+            if 'Kernel Name' in row:
+                header = row
+            continue
+        if len(row) < len(header):
+            continue
+        d = dict(zip(header, row))
+        if d.get('Metric Name') != 'gpu__time_duration.sum':
+            continue
+        name = re.sub(r'\(.*', '', d['Kernel Name'])
+        name = re.sub(r'^void |dooms::cuda::|\(anonymous namespace\)::|<unnamed>::', '', name)
+        value = float(d['Metric Value'].replace(',', ''))
+        us = value / 1000 if d['Metric Unit'] in ('ns', 'nsecond') else value
+        slot = agg.setdefault(name, [0, 0.0])
+        slot[0] += 1
+        slot[1] += us
+    total = sum(v[1] for v in agg.values())
+    print(f'{sum(v[0] for v in agg.values())} launches, {total:.1f} us in total', file=out)
+    print(f'{"total us":>10} {"share":>6} {"launches":>8} {"us each":>9}  kernel', file=out)
+    for name, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+        print(f'{us:10.1f} {100 * us / total:5.1f}% {n:8d} {us / n:9.2f}  {name[:100]}', file=out)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest='case', required=True)
+    g = sub.add_parser('gemv')
+    g.add_argument('--rows', type=int, default=14336)
+    g.add_argument('--cols', type=int, default=4096)
+    g.add_argument('--gate', action='store_true')
+    g.add_argument('--mats', type=int, default=4)
+    g.add_argument('--reps', type=int, default=3)
+    g.add_argument('--dtype', default='q4_0')
+    m = sub.add_parser('gemm')
+    m.add_argument('--tokens', type=int, default=2048)
+    m.add_argument('--rows', type=int, default=4096)
+    m.add_argument('--cols', type=int, default=4096)
+    m.add_argument('--gate', action='store_true')
+    m.add_argument('--reps', type=int, default=3)
+    l = sub.add_parser('launches')
+    l.add_argument('csv')
+    args = ap.parse_args(argv)
+    if args.case == 'gemv':
+        _gemv(args)
+    elif args.case == 'gemm':
+        _gemm(args)
+    else:
+        summarize_launches(args.csv)
+
+
+if __name__ == '__main__':
+    main()

@@ -141,7 +141,8 @@ def test_argmax_first_index_ties_and_nan():
     assert gpu_argmax(zeros) == 0
 
 
-@pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_keys", [(14, 2, 64, 1), (14, 2, 64, 700), (32, 8, 128, 2304), (4, 2, 16, 45), (40, 8, 128, 8448)])
+@pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_keys", [(14, 2, 64, 1), (14, 2, 64, 700), (32, 8, 128, 2304), (4, 2, 16, 45), (40, 8, 128, 8448),
+                                                               (6, 6, 64, 130), (16, 2, 128, 64), (4, 2, 64, 65), (24, 2, 64, 300)])
 def test_split_attention_matches_the_oracle(n_head, n_head_kv, head_dim, n_keys):
     g = np.random.default_rng(n_keys)
     q = g.standard_normal((n_head, head_dim)).astype(np.float32)
