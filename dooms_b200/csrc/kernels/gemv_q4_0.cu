@@ -17,6 +17,8 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "ptx.cuh"
@@ -47,6 +49,8 @@ struct GemvQ40Params {
     int nchunks;            // chunks per row
     int stride;             // bytes between the rows of a stage (multiple of 16, = 16 mod 128)
     int upr;                // 16-byte pieces copied per row of a stage (the aligned cover of a chunk)
+    int rows_q, rows_r;     // rows / grid and rows % grid: block b has rows_q + (b < rows_r) rows starting at b rows_q + min(b, rows_r)
+    uint32_t inv_upr, inv_nchunks;   // 65536 / d + 1: (j * inv) >> 16 = j / d for the small j divided here
 };
 
 // x[K] (f32) -> xq. One warp per 32-element block.
@@ -99,8 +103,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     const uint32_t CB = uint32_t(p.cbk) * kBlockBytes;
 
     // this block's rows
-    const int64_t R0 = p.rows * blockIdx.x / gridDim.x, R1 = p.rows * (blockIdx.x + 1) / gridDim.x;
-    const int nrows = int(R1 - R0);
+    const int nrows = p.rows_q + (int(blockIdx.x) < p.rows_r ? 1 : 0);
+    const int64_t R0 = int64_t(blockIdx.x) * p.rows_q + min(int(blockIdx.x), p.rows_r);
     const int ntiles = (nrows + kTileRows - 1) / kTileRows;
     const int total_units = ntiles * nmat * p.nchunks;
     const int my_units = warp < total_units ? (total_units - warp - 1) / WARPS + 1 : 0;
@@ -116,39 +120,45 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
 
     // Unit u of this warp is unit warp + u WARPS of the block: (tile * nmat + mat) = that / nchunks, chunk = that % nchunks. Going to the next unit adds
     // WARPS: a fixed step in the chunk index plus a carry.
-    const int step_tm = WARPS / p.nchunks, step_chunk = WARPS % p.nchunks;
-    int f_tm = warp / p.nchunks, f_chunk = warp % p.nchunks, f_slot = 0;      // the unit being fetched
+    const int step_tm = int((uint32_t(WARPS) * p.inv_nchunks) >> 16), step_chunk = WARPS - step_tm * p.nchunks;
+    int f_tm = int((uint32_t(warp) * p.inv_nchunks) >> 16), f_chunk = warp - f_tm * p.nchunks, f_slot = 0;      // the unit being fetched
     int u_tm = f_tm, u_chunk = f_chunk, u_slot = 0;                           // the unit being used
 
     // Stage copy: a stage is 16 rows x p.upr 16-byte pieces (the aligned cover of the chunk's bytes), dealt to the lanes in order, so that one instruction
     // copies 512 consecutive bytes of a row or two. Which (row, piece) a lane copies is the same for every stage: a table of packed (source offset from
-    // the tile's first row << 13 | offset in the stage), built once. Rows past the block's range repeat its last row (the same bytes again: no extra
-    // traffic from memory; their results are dropped), which only the block's last tile needs: it has its own table.
-    uint32_t tab[kMaxPieces], tab_last[kMaxPieces];
-    {
-        const int last = nrows - 1 - (ntiles - 1) * kTileRows;
-        int row = 0, col = lane;
-        #pragma unroll
-        for (int k = 0; k < kMaxPieces; k++) {
-            while (col >= p.upr) { col -= p.upr; row++; }
-            const uint32_t dst = uint32_t(row) * stride + uint32_t(col) * 16u;
-            tab[k] = row < kTileRows ? ((uint32_t(row) * RB + uint32_t(col) * 16u) << 13) | dst : 0xFFFFFFFFu;
-            tab_last[k] = row < kTileRows ? ((uint32_t(min(row, last)) * RB + uint32_t(col) * 16u) << 13) | dst : 0xFFFFFFFFu;
-            col += 32;
-        }
+    // the tile's first row << 13 | offset in the stage), built once, plus the pieces' rows as 4-bit fields: the block's last tile may have fewer than 16
+    // rows, and the pieces of the missing ones are not copied (what those rows of the stage hold is computed on and dropped).
+    uint32_t tab[kMaxPieces], piece_rows[2] = {0u, 0u};
+    #pragma unroll
+    for (int k = 0; k < kMaxPieces; k++) {
+        const uint32_t j = uint32_t(lane) + 32u * k;
+        const uint32_t row = (j * p.inv_upr) >> 16, col = j - row * uint32_t(p.upr);
+        tab[k] = row < uint32_t(kTileRows) ? ((row * RB + col * 16u) << 13) | (row * stride + col * 16u) : 0xFFFFFFFFu;
+        piece_rows[k / 8] |= (row & 15u) << (4 * (k % 8));
     }
+    const int last_rows = nrows - 1 - (ntiles - 1) * kTileRows;      // the last tile's last row
     auto fetch = [&]() {
         const int tile = nmat == 2 ? f_tm >> 1 : f_tm, mat = nmat == 2 ? f_tm & 1 : 0;
         const uint8_t * base = (mat ? p.W2 : p.W) + (R0 + tile * kTileRows) * int64_t(RB) + uint32_t(f_chunk) * CB;      // the tile's first row, this chunk
         const uint32_t lo = uint32_t(reinterpret_cast<uintptr_t>(base));
         const uint32_t dst0 = my_stages + uint32_t(f_slot) * stage_bytes;
-        const bool is_last = tile == ntiles - 1;
-        #pragma unroll
-        for (int k = 0; k < kMaxPieces; k++) {
-            const uint32_t e = is_last ? tab_last[k] : tab[k];
-            if (e != 0xFFFFFFFFu) {
-                const uint32_t off = e >> 13;
-                cp_async16(dst0 + (e & 0x1FFFu), base + (int32_t(off) - int32_t((lo + off) & 15u)));
+        if (tile != ntiles - 1) {
+            #pragma unroll
+            for (int k = 0; k < kMaxPieces; k++) {
+                const uint32_t e = tab[k];
+                if (e != 0xFFFFFFFFu) {
+                    const uint32_t off = e >> 13;
+                    cp_async16(dst0 + (e & 0x1FFFu), base + (int32_t(off) - int32_t((lo + off) & 15u)));
+                }
+            }
+        } else {
+            #pragma unroll
+            for (int k = 0; k < kMaxPieces; k++) {
+                const uint32_t e = tab[k];
+                if (e != 0xFFFFFFFFu && int((piece_rows[k / 8] >> (4 * (k % 8))) & 15u) <= last_rows) {
+                    const uint32_t off = e >> 13;
+                    cp_async16(dst0 + (e & 0x1FFFu), base + (int32_t(off) - int32_t((lo + off) & 15u)));
+                }
             }
         }
         f_chunk += step_chunk;
@@ -250,32 +260,39 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
 
 constexpr size_t kSmemLimit = 224 * 1024;
 constexpr int kMaxTilesPerBlock = 8;        // the table of per-warp sums holds this many 16-row tiles of two matrices
-constexpr size_t partial_bytes(int warps) { return size_t(kMaxTilesPerBlock) * 2 * warps * kTileRows * sizeof(float); }
+constexpr size_t partial_bytes(int warps, int nmat) { return size_t(kMaxTilesPerBlock) * nmat * warps * kTileRows * sizeof(float); }
 
 struct Plan { int cbk, nchunks, stride, stages, warps; size_t smem; bool ok; };
 
 // Chunks of an even number of blocks that divides the row; the row stride in a stage is an odd multiple of 16 bytes so that the 8 rows of a fragment fall
-// on different banks. Preference: 16 warps (four per scheduler hide the latencies of the unpack / MMA / scale chain) with at least two stages each and
-// chunks as close to 16 blocks as shared memory allows; 8 warps otherwise.
-Plan plan_for(int64_t cols) {
+// on different banks.
+constexpr int kMaxStages = 6;
+Plan plan_for(int64_t cols, int nmat) {
     Plan best{};
     const int nb = int(cols / 32);
     if (cols % 64 != 0 || nb < 2) return best;
     const size_t fixed = (size_t(nb) * 136 + 127) & ~size_t(127);
-    int best_score = -1;
+    int64_t best_score = -1;
+    int fw = 0, fc = 0, fs = 0;
+    if (const char * f = getenv("DOOMS_GEMV_FORCE")) sscanf(f, "%d:%d:%d", &fw, &fc, &fs);
     for (int warps : {16, 8}) {
+        if (fw && warps != fw) continue;
         for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
             if (nb % cbk) continue;
+            if (fc && cbk != fc && nb % fc == 0) continue;
             int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
             if (stride % 32 != 16) stride += 16;
             if ((cbk * kBlockBytes + 30) / 16 * kTileRows > kMaxPieces * 32 || kTileRows * stride >= (1 << 13)) continue;
             int stages = 0;
-            for (int st = 4; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps) <= kSmemLimit) { stages = st; break; }
+            for (int st = kMaxStages; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps, nmat) <= kSmemLimit) { stages = st; break; }
             if (!stages) continue;
-            const int score = (warps == 16 ? 10000 : 0) + cbk * 100 + stages;
+            if (fs && fs <= stages) stages = fs;
+            // Measured on B200 (8B shapes, back-to-back launches over distinct matrices): the kernel is bound by instruction issue and shared-memory
+            // bandwidth more than by the bytes in flight, so the longest chunk (fewest per-unit fixed costs) wins, then 16 warps over 8, then stages.
+            const int64_t score = int64_t(cbk) * 1000 + (warps == 16 ? 100 : 0) + stages;
             if (score > best_score) {
                 best_score = score;
-                best = Plan{cbk, nb / cbk, stride, stages, warps, fixed + size_t(warps) * stages * kTileRows * stride + partial_bytes(warps), true};
+                best = Plan{cbk, nb / cbk, stride, stages, warps, fixed + size_t(warps) * stages * kTileRows * stride + partial_bytes(warps, nmat), true};
             }
         }
     }
@@ -296,10 +313,21 @@ cudaError_t launch_with(const GemvQ40Params & p, size_t smem, unsigned grid, cud
     return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
 }
 
+template <int WARPS>
+cudaError_t launch_stages(const GemvQ40Params & p, const Plan & pl, unsigned grid, cudaStream_t stream) {
+    switch (pl.stages) {
+        case 6: return launch_with<WARPS, 6>(p, pl.smem, grid, stream);
+        case 5: return launch_with<WARPS, 5>(p, pl.smem, grid, stream);
+        case 4: return launch_with<WARPS, 4>(p, pl.smem, grid, stream);
+        case 3: return launch_with<WARPS, 3>(p, pl.smem, grid, stream);
+        default: return launch_with<WARPS, 2>(p, pl.smem, grid, stream);
+    }
+}
+
 }  // namespace
 
 bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols) {
-    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols).ok;
+    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 1).ok;
 }
 
 size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }
@@ -311,10 +339,10 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
                              int32_t * error, cudaStream_t stream) {
-    const Plan pl = plan_for(cols);
+    const Plan pl = plan_for(cols, W2 ? 2 : 1);
     if (!pl.ok) return cudaErrorInvalidValue;
     GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), y, bias, rows, int(cols), flags,
-                    pl.cbk, pl.nchunks, pl.stride, 0};
+                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 0u, 0u};
     (void)error;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
@@ -324,18 +352,11 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, f
     const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
     const int64_t waves = (rows + 148 * max_rows - 1) / (148 * max_rows);
     const unsigned grid = unsigned(std::min<int64_t>(148 * waves, rows));
-    if (pl.warps == 16) {
-        switch (pl.stages) {
-            case 4: return launch_with<16, 4>(p, pl.smem, grid, stream);
-            case 3: return launch_with<16, 3>(p, pl.smem, grid, stream);
-            default: return launch_with<16, 2>(p, pl.smem, grid, stream);
-        }
-    }
-    switch (pl.stages) {
-        case 4: return launch_with<8, 4>(p, pl.smem, grid, stream);
-        case 3: return launch_with<8, 3>(p, pl.smem, grid, stream);
-        default: return launch_with<8, 2>(p, pl.smem, grid, stream);
-    }
+    p.rows_q = int(rows / grid);
+    p.rows_r = int(rows % grid);
+    p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
+    p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
+    return pl.warps == 16 ? launch_stages<16>(p, pl, grid, stream) : launch_stages<8>(p, pl, grid, stream);
 }
 
 }  // namespace cuda
