@@ -460,6 +460,7 @@ cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, v
 }
 
 cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
+    if (gemv_blocks_supported(dt, W, x, rows, cols)) return launch_gemv_blocks(dt, W, nullptr, x, y, bias, rows, cols, flags, stream);
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
     cudaError_t e = cudaSuccess;
     const bool ok = dispatch_mat(dt, [&]<int DT>() {
@@ -469,6 +470,9 @@ cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, co
 }
 
 cudaError_t launch_gate_up(int dt, const void * Wg, const void * Wu, const float * x, float * h, int64_t rows, int64_t cols, cudaStream_t stream) {
+    if (gemv_blocks_supported(dt, Wg, x, rows, cols) && gemv_blocks_supported(dt, Wu, x, rows, cols)) {
+        return launch_gemv_blocks(dt, Wg, Wu, x, h, nullptr, rows, cols, 0u, stream);
+    }
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
     cudaError_t e = cudaSuccess;
     const bool ok = dispatch_mat(dt, [&]<int DT>() {

@@ -86,6 +86,12 @@ cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream);
 
 // ---- the fast decode GEMV on q4_0 rows (gemv_q4_0.cu) ----
+// The streaming GEMV for any block format (gemv_blocks.cu): y (+)= W x (+ bias), or with W2 the fused gate/up h = silu(W x) * (W2 x). Takes 16-byte aligned
+// W and x and rows of whole blocks that fit its shared-memory plan; launch_matvec / launch_gate_up use it whenever it takes the call.
+bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows, int64_t cols);
+cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols,
+                               uint32_t flags, cudaStream_t stream);
+
 // The input vector split into int8 limbs: quantized_x_bytes(cols) bytes at a 16-byte aligned address, written by launch_quantize_x.
 size_t quantized_x_bytes(int64_t cols);
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream);
