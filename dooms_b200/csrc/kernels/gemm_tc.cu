@@ -5,7 +5,7 @@
 //     token tile its B operand (N = 128 or 256), both K-major f16 in the 128-byte swizzled layout; D[n][m] lives in 256 TMEM columns (gate/up: two
 //     accumulators, all 512 columns).
 //   * Per 64-wide k step: the token tile (f16 activations written by the producing kernel) arrives by TMA (cp.async.bulk.tensor.2d, one block of threads per copy); 256
-//     producer threads read the weight rows' raw blocks from global memory (two threads per row, 32 elements each), dequantize them to f16 exactly as the
+//     producer threads read the weight rows' raw blocks from global memory (two threads per row; q4_0 rows in 144-byte groups of 16-byte loads), dequantize them to f16 exactly as the
 //     reference's tiles do (half(Q::elem), src/backend/metal/llama_kernels.h:1027-1035, 197) and store them swizzled; one thread issues the four k = 16
 //     MMAs and commits the stage back to the producers. Stages are handed over through mbarriers; every wait is bounded and reports failure instead of
 //     hanging.
@@ -60,6 +60,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Polls the count of consumed steps (a word in shared memory that only grows) until it reaches `want`; bounded like mbar_wait.
+__device__ __forceinline__ bool wait_consumed(uint32_t addr, int want) {
+    for (uint32_t i = 0; i < kMaxPolls; i++) {
+        uint32_t v;
+        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        if (int(v) >= want) { __threadfence_block(); return true; }
+    }
+    return false;
+}
+
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzled layout: rows of 128 bytes, groups of 8 rows 1024 bytes apart (the tile base is
 // 1024-byte aligned). A k = 16 slice inside the 128-byte row is addressed by adding its byte offset to the start address.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -95,12 +105,8 @@ __device__ __forceinline__ uint32_t h2_sub_mul(uint32_t v, __half2 d2) {
     const __half2 r = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&v), k1032), d2);
     return *reinterpret_cast<const uint32_t *>(&r);
 }
-template <>
-__device__ __forceinline__ void dequant32<kQ4_0>(const uint8_t * row, uint32_t k0, uint4 (&out)[4]) {
-    const uint16_t * b = reinterpret_cast<const uint16_t *>(row + size_t(k0 / 32) * 18);
-    uint16_t raw[9];
-    #pragma unroll
-    for (int i = 0; i < 9; i++) raw[i] = __ldg(b + i);
+// raw: the block's nine 16-bit words (scale, then the quants two bytes at a time)
+__device__ __forceinline__ void dequant_q4_0_words(const uint16_t (&raw)[9], uint4 (&out)[4]) {
     const __half2 d2 = __half2half2(__ushort_as_half(raw[0]));
     uint32_t lo[8], hi[8];      // half2 pairs of elements (2i, 2i+1) and (16+2i, 16+2i+1)
     #pragma unroll
@@ -115,6 +121,25 @@ __device__ __forceinline__ void dequant32<kQ4_0>(const uint8_t * row, uint32_t k
     out[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     out[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
 }
+template <>
+__device__ __forceinline__ void dequant32<kQ4_0>(const uint8_t * row, uint32_t k0, uint4 (&out)[4]) {
+    const uint16_t * b = reinterpret_cast<const uint16_t *>(row + size_t(k0 / 32) * 18);
+    uint16_t raw[9];
+    #pragma unroll
+    for (int i = 0; i < 9; i++) raw[i] = __ldg(b + i);
+    dequant_q4_0_words(raw, out);
+}
+// Block B (0..7) of a 256-element group held in registers as 36 32-bit words (144 bytes): its 16-bit words are 9 B .. 9 B + 8 of the group's 72.
+template <int B>
+__device__ __forceinline__ void dequant_q4_0_group(const uint32_t (&w)[36], uint4 (&out)[4]) {
+    uint16_t raw[9];
+    #pragma unroll
+    for (int i = 0; i < 9; i++) {
+        constexpr int base = 9 * B;
+        raw[i] = uint16_t(((base + i) & 1) ? w[(base + i) >> 1] >> 16 : w[(base + i) >> 1] & 0xFFFFu);
+    }
+    dequant_q4_0_words(raw, out);
+}
 
 struct GemmTcParams {
     const uint8_t * W;
@@ -127,6 +152,7 @@ struct GemmTcParams {
     int64_t y_stride, y16_stride;
     uint32_t flags;
     int T;                     // tokens per block: 128 or 256
+    int wide;                  // q4_0 rows of whole 256-element groups at 16-byte aligned addresses: the producers load 144-byte groups with 16-byte loads
     int32_t * error;
 };
 
@@ -141,6 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const uint32_t stage_bytes = NMAT * kTileWBytes + tile_x_bytes;
     const uint32_t bars = smem0 + STAGES * stage_bytes;       // full_x[S], full_w[S], empty[S], acc_full
     const uint32_t full_x = bars, full_w = bars + 8 * STAGES, empty = bars + 16 * STAGES, acc_full = bars + 24 * STAGES, tmem_slot = acc_full + 8;
+    const uint32_t consumed = tmem_slot + 4;       // steps whose stage is free again, counted by the tracker lane
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int64_t n0 = int64_t(blockIdx.x) * kRowsW;
     const int m0 = blockIdx.y * p.T;
@@ -148,8 +175,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const uint32_t ncols = GATE ? 512u : 256u;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(full_x + 8 * s, 1); mbar_init(full_w + 8 * s, kProducerWarps * 32); mbar_init(empty + 8 * s, 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(full_x + 8 * s, 1); mbar_init(full_w + 8 * s, p.wide ? kProducerWarps * 16 : kProducerWarps * 32); mbar_init(empty + 8 * s, 1); }
         mbar_init(acc_full, 1);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(consumed), "r"(0u) : "memory");
         mbar_init_fence();
     }
     if (warp == kProducerWarps + 1) {      // the MMA warp owns the tensor memory
@@ -163,8 +191,57 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
     bool ok = true;
 
-    if (warp < kProducerWarps) {
-        // ---- weight producers: row r of the tile, elements 32 half .. 32 half + 31 of each k step ----
+    if (warp < kProducerWarps && DT == kQ4_0 && p.wide) {
+        // ---- weight producers, q4_0 rows of whole 256-element groups: the two threads of a row take the groups (four k steps each) in turn. A group is
+        // 144 consecutive bytes, fetched with nine 16-byte loads per matrix before anything is computed, so that the other thread's stores overlap this
+        // thread's loads; the thread then fills its four stages, a whole 128-byte row of the tile per step. ----
+        const int r = (warp & 3) * 32 + lane, half = warp >> 2;
+        const int64_t row = min(n0 + r, p.N - 1);
+        const int64_t RB = row_bytes_of(DT, p.K);
+        const uint8_t * wrow[NMAT];
+        wrow[0] = p.W + row * RB;
+        if (GATE) wrow[NMAT - 1] = p.W2 + row * RB;
+        const uint32_t dst_row = uint32_t(r) * 128u;
+        const int groups = ksteps / 4;
+        for (int g = half; g < groups && ok; g += 2) {
+            uint32_t raw[NMAT][36];
+            #pragma unroll
+            for (int mtx = 0; mtx < NMAT; mtx++) {
+                const uint4 * src = reinterpret_cast<const uint4 *>(wrow[mtx] + size_t(g) * 144);
+                #pragma unroll
+                for (int i = 0; i < 9; i++) {
+                    const uint4 v = __ldg(src + i);
+                    raw[mtx][4 * i] = v.x; raw[mtx][4 * i + 1] = v.y; raw[mtx][4 * i + 2] = v.z; raw[mtx][4 * i + 3] = v.w;
+                }
+            }
+            auto step = [&]<int J>() {
+                // A thread comes back to a stage only every eighth step while the stage's barrier completes a phase every STAGES steps: a parity wait
+                // would be ambiguous, so these threads wait on the count of steps whose stage the tensor core has finished reading (see the tracker).
+                const int ks = g * 4 + J, s = ks % STAGES;
+                if (ks >= STAGES) ok = ok && wait_consumed(consumed, ks - STAGES + 1);
+                if (!ok) return;
+                #pragma unroll
+                for (int mtx = 0; mtx < NMAT; mtx++) {
+                    uint4 v[8];
+                    dequant_q4_0_group<2 * J>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[0]));
+                    dequant_q4_0_group<2 * J + 1>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[4]));
+                    const uint32_t tile = smem0 + s * stage_bytes + mtx * kTileWBytes + dst_row;
+                    #pragma unroll
+                    for (int c = 0; c < 8; c++) {
+                        const uint32_t chunk = uint32_t(c) ^ uint32_t(r & 7);
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + chunk * 16u), "r"(v[c].x), "r"(v[c].y), "r"(v[c].z), "r"(v[c].w) : "memory");
+                    }
+                }
+                fence_async_smem();
+                mbar_arrive(full_w + 8 * s);
+            };
+            step.template operator()<0>();
+            step.template operator()<1>();
+            step.template operator()<2>();
+            step.template operator()<3>();
+        }
+    } else if (warp < kProducerWarps) {
+        // ---- weight producers, any format: row r of the tile, elements 32 half .. 32 half + 31 of each k step ----
         const int r = (warp & 3) * 32 + lane, half = warp >> 2;
         const int64_t row = min(n0 + r, p.N - 1);
         const int64_t RB = row_bytes_of(DT, p.K);
@@ -200,6 +277,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 const uint32_t dst = smem0 + s * stage_bytes + NMAT * kTileWBytes;
                 mbar_arrive_expect_tx(full_x + 8 * s, tile_x_bytes);
                 for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, ks * kStepK, m0 + part * 128, full_x + 8 * s);
+            }
+        } else if (lane == 1 && p.wide) {
+            // ---- tracker: passes through every phase of the stages' "empty" barriers in order and publishes the number of steps consumed ----
+            for (int ks = 0; ks < ksteps && ok; ks++) {
+                ok = mbar_wait(empty + 8 * (ks % STAGES), uint32_t(ks / STAGES) & 1u);
+                if (ok) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(consumed), "r"(uint32_t(ks + 1)) : "memory");
             }
         }
     } else {
@@ -330,7 +413,8 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
                            int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream) {
     if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
-                   flags, M > 128 ? 256 : 128, error};
+                   flags, M > 128 ? 256 : 128, 0, error};
+    p.wide = dt == kQ4_0 && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
     switch (dt) {
