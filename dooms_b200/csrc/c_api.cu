@@ -110,19 +110,10 @@ int32_t launch_result(cudaError_t e, const char * what) {
     return fail(DOOMS_INTERNAL, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-// The staged q4_0 GEMV on an f32 input: split the input into the per-device scratch, then the kernel. The scratch is shared by every call on the device, so
-// calls on different streams must not overlap.
+// The staged q4_0 GEMV on an f32 input: every block splits the input for itself in its prologue, so the call is one launch and needs no scratch.
 int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t st,
                   const char * what) {
-    void * scratch = nullptr;
-    const size_t xq_bytes = (cuda::quantized_x_bytes(cols) + 15) & ~size_t(15);
-    const Status ss = scratch_for(xq_bytes + 16, &scratch);
-    if (!ss.is_ok()) return done(ss);
-    int32_t * error = reinterpret_cast<int32_t *>(static_cast<uint8_t *>(scratch) + xq_bytes);
-    cudaError_t e = cudaMemsetAsync(error, 0, 4, st);
-    if (e == cudaSuccess) e = cuda::launch_quantize_x(x, cols, scratch, st);
-    if (e == cudaSuccess) e = cuda::launch_gemv_q4_0(w, w2, scratch, y, bias, rows, cols, flags, error, st);
-    return launch_result(e, what);
+    return launch_result(cuda::launch_gemv_q4_0(w, w2, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, st), what);
 }
 
 // Scratch of dooms_cuda_argmax_noalloc: the per-block partial results (8 bytes each) for up to DOOMS_CUDA_ARGMAX_NOALLOC_MAX logits. It is part of the

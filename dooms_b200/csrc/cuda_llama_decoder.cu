@@ -160,18 +160,30 @@ struct CudaLlamaDecoder::Impl {
     }
 
     bool fast(const MatDev & w) const { return w.dt == DType::Q4_0 && cuda::gemv_q4_0_supported(w.ptr, w.rows, w.cols); }
-    // The staged q4_0 kernels read their input split into int8 limbs; one split serves every projection of the same input.
-    void split_input(const float * in, int64_t cols) {
-        if (xq_of == in) return;
-        run("split", [&] { return cuda::launch_quantize_x(in, cols, xq, stream); });
-        xq_of = in;
+    // One-token projection of `in`, RMS-normalized with gamma first when gamma is given. The streaming kernels do the norm (and the q4_0 kernel the split of
+    // its input into int8 limbs) in their prologue; only shapes they do not take go through a norm launch and the row-per-warp kernel. A producer that
+    // already wrote the split of `in` (the attention merge) leaves it in xq and says so in xq_of.
+    // The q4_0 kernel splits an f32 input in its prologue, every block for itself. That beats a launch of its own for the model-width inputs (with the norm
+    // folded in); for the feed-forward-width input of ffn_down (3.5x longer) one split kernel ahead of the projection measured 0.2 ms per token faster on
+    // the 8B shape, so long plain inputs are still split once, by a kernel.
+    void prepare_fast_input(const float *& in, const float *& gamma, int64_t cols) {
+        if (!gamma && xq_of != in && cols >= 8192) {
+            run("split", [&] { return cuda::launch_quantize_x(in, cols, xq, stream); });
+            xq_of = in;
+        }
     }
-    void matvec(const char * kind, const MatDev & w, const float * in, float * out, const float * bias, uint32_t flags) {
+    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags) {
         if (fast(w)) {
-            split_input(in, w.cols);
-            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, xq, out, bias, w.rows, w.cols, flags, host_error, stream); });
+            prepare_fast_input(in, gamma, w.cols);
+            const void * split = (xq_of == in && !gamma) ? xq : nullptr;
+            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
             return;
         }
+        if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
+            run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
+            return;
+        }
+        if (gamma) { norm(in, gamma, 1, false); in = xn; }
         run(kind, [&] { return cuda::launch_matvec(int(w.dt), w.ptr, in, out, bias, w.rows, w.cols, flags, stream); });
     }
     // xn = RMS-normalized rows; with split (one row) the kernel also leaves the row split for the staged q4_0 kernels (every producer of a projection
@@ -183,12 +195,18 @@ struct CudaLlamaDecoder::Impl {
         });
         xq_of = do_split ? xn : nullptr;
     }
-    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, float * out) {
+    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out) {
         if (fast(wg) && fast(wu)) {
-            split_input(in, wg.cols);
-            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, xq, out, nullptr, wg.rows, wg.cols, 0u, host_error, stream); });
+            prepare_fast_input(in, gamma, wg.cols);
+            const void * split = (xq_of == in && !gamma) ? xq : nullptr;
+            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream); });
             return;
         }
+        if (cuda::gemv_blocks_supported(int(wg.dt), wg.ptr, in, wg.rows, wg.cols) && cuda::gemv_blocks_supported(int(wu.dt), wu.ptr, in, wu.rows, wu.cols)) {
+            run("gate_up", [&] { return cuda::launch_gemv_blocks(int(wg.dt), wg.ptr, wu.ptr, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream); });
+            return;
+        }
+        if (gamma) { norm(in, gamma, 1, false); in = xn; }
         run("gate_up", [&] { return cuda::launch_gate_up(int(wg.dt), wg.ptr, wu.ptr, in, out, wg.rows, wg.cols, stream); });
     }
     void matmul(const char * kind, const MatDev & w, const MatDev * w2, const float * in, int64_t in_stride, float * out, int64_t out_stride, const float * bias, int M,
@@ -231,34 +249,33 @@ struct CudaLlamaDecoder::Impl {
             __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
             float * o_dst = single ? x : red;
             const uint32_t o_flags = single ? kFlagAccumulate : 0u;
-            bool qkv_fast = false;
-            for (const QkvPart & q : L.qkv) qkv_fast = qkv_fast || fast(q.w);
             const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
-            norm(x, L.attn_norm, M, qkv_fast, use_tc);
+            if (M > 1) norm(x, L.attn_norm, M, false, use_tc);
             if (M == 1) {
-                for (const QkvPart & q : L.qkv) matvec("qkv", q.w, xn, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
+                for (const QkvPart & q : L.qkv) {
+                    matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
+                }
                 const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
                 if (gqa) {
                     run("attention", [&] { return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, stream); });
                     run("attention_combine", [&] { return cuda::launch_attention_combine(part, attn, split_attn ? xq : nullptr, gqa_splits, as, stream); });
                 } else {
-                    run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, 1, as, stream); });
+                    run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, 1, as, stream); });
                     run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
                 }
                 xq_of = split_attn ? attn : nullptr;
-                matvec("attn_output", L.attn_output, attn, o_dst, nullptr, o_flags);
-                reduce_into_x(1);
-                norm(x, L.ffn_norm, 1, fast(L.ffn_gate) && fast(L.ffn_up));
-                gate_up(L.ffn_gate, L.ffn_up, xn, h);
+                matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags);
                 xq_of = nullptr;
-                matvec("ffn_down", L.ffn_down, h, o_dst, nullptr, o_flags);
+                reduce_into_x(1);
+                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h);
+                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
             } else if (use_tc) {
                 // (the chunk's norm above wrote xn16)
                 for (const QkvPart & q : L.qkv) {
                     gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
                 }
-                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, M, as, stream); });
                 prefill_attention(kcl, vcl, attn16, M, as);
                 gemm_tc("attn_output", L.attn_output, nullptr, map_attn, o_dst, nullptr, nullptr, M, E, 0, o_flags);
                 reduce_into_x(M);
@@ -270,7 +287,7 @@ struct CudaLlamaDecoder::Impl {
                 for (const QkvPart & q : L.qkv) {
                     matmul("qkv", q.w, nullptr, xn, E, qkv + q.row0, qkv_width, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, M, L.qkv_bias ? kFlagBias : 0u);
                 }
-                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, M, as, stream); });
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, M, as, stream); });
                 prefill_attention(kcl, vcl, nullptr, M, as);
                 matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
@@ -281,8 +298,7 @@ struct CudaLlamaDecoder::Impl {
             }
         }
         // The logits of the last row only (metal_llama_decoder.mm:375).
-        norm(x + size_t(M - 1) * E, output_norm, 1, output.rows > 0 && fast(output));
-        if (output.rows > 0) matvec("output", output, xn, logits_buf + vocab_row0, nullptr, 0u);
+        if (output.rows > 0) matvec("output", output, x + size_t(M - 1) * E, output_norm, logits_buf + vocab_row0, nullptr, 0u);
         if (tp > 1) {
             run("all_gather", [&] {
                 return nccl.AllGather(logits_buf + vocab_row0, logits_buf, size_t(vocab_stride), NcclApi::kFloat32, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown;

@@ -41,6 +41,8 @@ struct GemvBlocksParams {
     const uint8_t * W;
     const uint8_t * W2;     // gate/up: the second matrix (up)
     const float * x;
+    const float * gamma;    // optional: RMS-normalize x first
+    float eps;
     float * y;
     const float * bias;
     int cols;
@@ -133,6 +135,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
+    if (p.gamma) {
+        // x[i] * rsqrt(mean(x^2) + eps) * gamma[i] (norm_vec, llama_kernels.h:1272-1286), in place in shared memory, by every block for itself
+        __shared__ float red[WARPS];
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) ss += xs[i] * xs[i];
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float total = 0.f;
+        #pragma unroll
+        for (int w = 0; w < WARPS; w++) total += red[w];
+        const float inv = rsqrtf(total / float(p.cols) + p.eps);
+        for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) xs[i] = xs[i] * inv * p.gamma[i];
+        __syncthreads();
+    }
 
     const int row = lane & 15, half = lane >> 4;
     constexpr int UPB = BE / 32;                  // 32-element groups per block
@@ -271,9 +289,9 @@ bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows,
     return plan_for(fmt_be(dt), fmt_bb(dt), cols, 2).ok;
 }
 
-cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols,
-                               uint32_t flags, cudaStream_t stream) {
-    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u};
+cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, const float * gamma, float eps, float * y, const float * bias,
+                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
+    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, gamma, eps, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u};
     switch (dt) {
         case kF16: return launch_dt<kF16>(p, rows, stream);
         case kQ4_0: return launch_dt<kQ4_0>(p, rows, stream);

@@ -39,7 +39,10 @@ constexpr int kMaxPieces = 10;      // 16-byte pieces of a stage one lane copies
 struct GemvQ40Params {
     const uint8_t * W;      // rows x (cols / 32) blocks
     const uint8_t * W2;     // gate/up: the second matrix (up); nullptr for a plain projection
-    const uint8_t * xq;     // the split input: (cols / 32) x 128 limb bytes, then (cols / 32) x 2 floats
+    const uint8_t * xq;     // the split input: (cols / 32) x 128 limb bytes, then (cols / 32) x 2 floats; nullptr: the block splits x itself
+    const float * x;        // the input as f32 (xq == nullptr)
+    const float * gamma;    // with x: RMS-normalize it first, x[i] * rsqrt(mean(x^2) + eps) * gamma[i] (norm_vec, llama_kernels.h:1272-1286); nullptr: as it is
+    float eps;
     float * y;
     const float * bias;
     int64_t rows;
@@ -178,9 +181,44 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
-    for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
-    cp_async_commit();
-    cp_async_wait<0>();               // the split input has landed (this thread's part), and with it the first stages
+    if (p.xq) {
+        for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
+        cp_async_commit();
+        cp_async_wait<0>();               // the split input has landed (this thread's part), and with it the first stages
+    } else {
+        // every block normalizes (when asked) and splits the whole input itself, while its first stages are on their way: a 16 KB read from L2 and about
+        // forty instructions per 32 elements, instead of a launch of its own and a round trip through device memory
+        float inv = 1.f;
+        if (p.gamma) {
+            __shared__ float red[WARPS];
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) { const float v = p.x[i]; ss += v * v; }
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float total = 0.f;
+            #pragma unroll
+            for (int w = 0; w < WARPS; w++) total += red[w];
+            inv = rsqrtf(total / float(p.cols) + p.eps);
+        }
+        for (int blk0 = warp; blk0 < nb; blk0 += WARPS * 8) {       // eight loads on their way before the first block is split
+            float v[8], gm[8];
+            #pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int blk = blk0 + j * WARPS;
+                v[j] = blk < nb ? p.x[blk * 32 + lane] : 0.f;
+                gm[j] = (p.gamma && blk < nb) ? p.gamma[blk * 32 + lane] : 1.f;
+            }
+            #pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int blk = blk0 + j * WARPS;
+                if (blk < nb) split_block(p.gamma ? v[j] * inv * gm[j] : v[j], lane, blk, nb, smem);
+            }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+    }
     __syncthreads();
 
     const bool first = g < 4;
@@ -337,13 +375,13 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
     return launch_pdl(k_quantize_x, dim3((nb + 7) / 8), dim3(256), 0, stream, x, nb, static_cast<uint8_t *>(xq));
 }
 
-cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
-                             int32_t * error, cudaStream_t stream) {
+cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
+                             int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
     const Plan pl = plan_for(cols, W2 ? 2 : 1);
     if (!pl.ok) return cudaErrorInvalidValue;
-    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), y, bias, rows, int(cols), flags,
+    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, y, bias, rows, int(cols), flags,
                     pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 0u, 0u};
-    (void)error;
+    if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
     const int chunk_bytes = pl.cbk * kBlockBytes;

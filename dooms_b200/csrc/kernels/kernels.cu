@@ -245,42 +245,37 @@ __global__ void k_add(float * x, const float * y, int64_t n) {
 
 // ---------------------------------------------------------------- rotary embedding + cache write
 
-// Angle of rotary pair i at position pos: pos * base^(-2i / head_dim) (rotate_pair, llama_kernels.h:513-518), evaluated in double so that positions in the
-// thousands keep their low bits.
-__device__ __forceinline__ void rope_sincos(int pos, int i, int hd, float base, float & c, float & s) {
-    const double theta = double(pos) * pow(double(base), -2.0 * double(i) / double(hd));
-    double sd, cd;
-    sincos(theta, &sd, &cd);
-    c = float(cd);
-    s = float(sd);
-}
-
-// grid (n_head + 2 * n_head_kv, M), head_dim / 2 threads: slots are query heads (rotated in place), key heads (rotated into the cache), value heads (copied).
-__global__ void k_rope_store(float * qkv, __half * kc, __half * vc, const DevState * st, AttnShape p) {
+// grid (M), head_dim / 2 x (up to 4) threads: a thread owns rotary pair i and every fourth slot; slots are query heads (rotated in place), key heads
+// (rotated into the cache), value heads (copied). The angle pos * inv_freq[i] and its sine / cosine are computed once per thread in double precision, so that
+// positions in the thousands keep their low bits (rotate_pair, llama_kernels.h:513-518).
+__global__ void k_rope_store(float * qkv, __half * kc, __half * vc, const DevState * st, const double * inv_freq, AttnShape p) {
     pdl_trigger();
     pdl_wait();
-    const int slot = blockIdx.x, t = blockIdx.y, i = threadIdx.x, hd = p.head_dim;
+    const int hd = p.head_dim, t = blockIdx.x, i = threadIdx.x % (hd / 2), lanes = blockDim.x / (hd / 2);
     const int pos = st->pos + t;
     const int e0 = p.neox ? i : 2 * i, e1 = p.neox ? i + hd / 2 : 2 * i + 1;
     float * row = qkv + int64_t(t) * p.qkv_stride;
-    if (slot < p.n_head + p.n_head_kv) {
-        float c, s;
-        rope_sincos(pos, i, hd, p.rope_base, c, s);
-        float * x = row + slot * hd;
-        const float a = x[e0], b = x[e1];
-        const float r0 = a * c - b * s, r1 = a * s + b * c;
-        if (slot < p.n_head) { x[e0] = r0; x[e1] = r1; }
-        else {
-            __half * dst = kc + int64_t(pos) * p.kv_stride + (slot - p.n_head) * hd;
-            dst[e0] = __float2half_rn(r0);
-            dst[e1] = __float2half_rn(r1);
+    double sd, cd;
+    sincos(double(pos) * inv_freq[i], &sd, &cd);
+    const float c = float(cd), s = float(sd);
+    for (int slot = threadIdx.x / (hd / 2); slot < p.n_head + 2 * p.n_head_kv; slot += lanes) {
+        if (slot < p.n_head + p.n_head_kv) {
+            float * x = row + slot * hd;
+            const float a = x[e0], b = x[e1];
+            const float r0 = a * c - b * s, r1 = a * s + b * c;
+            if (slot < p.n_head) { x[e0] = r0; x[e1] = r1; }
+            else {
+                __half * dst = kc + int64_t(pos) * p.kv_stride + (slot - p.n_head) * hd;
+                dst[e0] = __float2half_rn(r0);
+                dst[e1] = __float2half_rn(r1);
+            }
+        } else {
+            const int kvh = slot - p.n_head - p.n_head_kv;
+            const float * x = row + (p.n_head + p.n_head_kv + kvh) * hd;
+            __half * dst = vc + int64_t(pos) * p.kv_stride + kvh * hd;
+            dst[e0] = __float2half_rn(x[e0]);
+            dst[e1] = __float2half_rn(x[e1]);
         }
-    } else {
-        const int kvh = slot - p.n_head - p.n_head_kv;
-        const float * x = row + (p.n_head + p.n_head_kv + kvh) * hd;
-        __half * dst = vc + int64_t(pos) * p.kv_stride + kvh * hd;
-        dst[e0] = __float2half_rn(x[e0]);
-        dst[e1] = __float2half_rn(x[e1]);
     }
 }
 
@@ -460,7 +455,7 @@ cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, v
 }
 
 cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
-    if (gemv_blocks_supported(dt, W, x, rows, cols)) return launch_gemv_blocks(dt, W, nullptr, x, y, bias, rows, cols, flags, stream);
+    if (gemv_blocks_supported(dt, W, x, rows, cols)) return launch_gemv_blocks(dt, W, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, stream);
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
     cudaError_t e = cudaSuccess;
     const bool ok = dispatch_mat(dt, [&]<int DT>() {
@@ -471,7 +466,7 @@ cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, co
 
 cudaError_t launch_gate_up(int dt, const void * Wg, const void * Wu, const float * x, float * h, int64_t rows, int64_t cols, cudaStream_t stream) {
     if (gemv_blocks_supported(dt, Wg, x, rows, cols) && gemv_blocks_supported(dt, Wu, x, rows, cols)) {
-        return launch_gemv_blocks(dt, Wg, Wu, x, h, nullptr, rows, cols, 0u, stream);
+        return launch_gemv_blocks(dt, Wg, Wu, x, nullptr, 0.f, h, nullptr, rows, cols, 0u, stream);
     }
     const unsigned grid = unsigned((rows + kMvWarps - 1) / kMvWarps);
     cudaError_t e = cudaSuccess;
@@ -504,9 +499,10 @@ cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t strea
     return cudaGetLastError();
 }
 
-cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, int M, const AttnShape & s, cudaStream_t stream) {
-    const dim3 grid(s.n_head + 2 * s.n_head_kv, M);
-    return launch_pdl(k_rope_store, grid, dim3(s.head_dim / 2), 0, stream, qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), st, s);
+cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, const double * inv_freq, int M, const AttnShape & s, cudaStream_t stream) {
+    const int pairs = s.head_dim / 2;
+    const int lanes = std::max(1, std::min(4, 256 / pairs));
+    return launch_pdl(k_rope_store, dim3(M), dim3(pairs * lanes), 0, stream, qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), st, inv_freq, s);
 }
 
 int attention_splits(int n_head, int n_ctx) {

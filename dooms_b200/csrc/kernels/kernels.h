@@ -47,7 +47,8 @@ struct AttnShape { int n_head, n_head_kv, head_dim, qkv_stride, kv_stride, out_s
 
 // Rotates q in place, rotates k into the f16 key cache and copies v into the f16 value cache for M rows at positions st->pos + t
 // (rope_store, llama_kernels.h:521-545).
-cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, int M, const AttnShape & s, cudaStream_t stream);
+cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState * st, const double * inv_freq, int M, const AttnShape & s,
+                              cudaStream_t stream);   // inv_freq: head_dim / 2 rotary frequencies base^(-2i / head_dim)
 
 // One query row against cache positions 0 .. st->pos (attention_split + attention_combine, llama_kernels.h:860-929). The cache is cut into `splits`
 // ranges; part holds splits x n_head x (2 + head_dim) floats.
@@ -89,17 +90,20 @@ cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, 
 // The streaming GEMV for any block format (gemv_blocks.cu): y (+)= W x (+ bias), or with W2 the fused gate/up h = silu(W x) * (W2 x). Takes 16-byte aligned
 // W and x and rows of whole blocks that fit its shared-memory plan; launch_matvec / launch_gate_up use it whenever it takes the call.
 bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows, int64_t cols);
-cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols,
-                               uint32_t flags, cudaStream_t stream);
+// gamma (optional): the input is RMS-normalized in the block's prologue first, as for launch_gemv_q4_0.
+cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, const float * gamma, float eps, float * y, const float * bias,
+                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
 
 // The input vector split into int8 limbs: quantized_x_bytes(cols) bytes at a 16-byte aligned address, written by launch_quantize_x.
 size_t quantized_x_bytes(int64_t cols);
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream);
 // Whether launch_gemv_q4_0 takes this matrix: a 16-byte aligned base and rows of an even number of blocks that fit the kernel's shared memory plan.
 bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
-// y[r] (+)= W[r] . x (+ bias[r]); with W2: y[r] = silu(W[r] . x) * (W2[r] . x). x comes as xq. *error is set to 1 if a bulk copy never arrived.
-cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags,
-                             int32_t * error, cudaStream_t stream);
+// y[r] (+)= W[r] . x (+ bias[r]); with W2: y[r] = silu(W[r] . x) * (W2[r] . x). The input comes either split (xq, from launch_quantize_x or from a kernel
+// that writes the split itself) or as f32 (xq == nullptr, x != nullptr): then every block splits it in its prologue, after RMS-normalizing it when gamma is
+// given (x[i] * rsqrt(mean(x^2) + eps) * gamma[i]), which saves the norm's and the split's own launches in a decode step.
+cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
+                             int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
 
 // ---- the tensor-core prefill GEMM (gemm_tc.cu) ----
 // A TMA descriptor of an f16 activation buffer [rows][cols] (cols a multiple of 64), opaque here so that this header needs no driver types.
