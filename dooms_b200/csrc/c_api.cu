@@ -458,7 +458,7 @@ DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void
         // q alone is read of the row, so d_q stands for the whole row
         const int gs = cuda::attention_gqa_splits(n_head_kv, n_keys);
         const cudaError_t e = cuda::launch_attention_gqa(d_q, const_cast<void *>(d_kc), const_cast<void *>(d_vc), static_cast<float *>(d_scratch), nullptr, nullptr,
-                                                         n_keys, gs, s, st);
+                                                         n_keys, gs, s, nullptr, nullptr, nullptr, st);
         if (e != cudaSuccess) return launch_result(e, "attention_decode");
         return launch_result(cuda::launch_attention_combine(static_cast<const float *>(d_scratch), d_out, nullptr, gs, s, st), "attention_decode");
     }

@@ -83,6 +83,7 @@ struct CudaLlamaDecoder::Impl {
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
     int gqa_splits = 1;
     double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
+    int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
     int32_t pos = 0;
     bool has_pending = false;
     // decode graph
@@ -105,7 +106,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -257,8 +258,9 @@ struct CudaLlamaDecoder::Impl {
                 }
                 const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
                 if (gqa) {
-                    run("attention", [&] { return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, stream); });
-                    run("attention_combine", [&] { return cuda::launch_attention_combine(part, attn, split_attn ? xq : nullptr, gqa_splits, as, stream); });
+                    run("attention", [&] {
+                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream);
+                    });
                 } else {
                     run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, 1, as, stream); });
                     run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
@@ -649,6 +651,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.inv_freq), freq.size() * sizeof(double), "the rotary frequencies"));
         if (cudaMemcpy(m.inv_freq, freq.data(), freq.size() * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) return internal_error("copying the rotary frequencies");
     }
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn_counters), size_t(std::max(1, m.nkv)) * sizeof(int), "the attention counters"));
+    cudaMemset(m.attn_counters, 0, size_t(std::max(1, m.nkv)) * sizeof(int));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
                                     "the split projection input"));
     if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {

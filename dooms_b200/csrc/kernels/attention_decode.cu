@@ -12,6 +12,7 @@
 #include "kernels.h"
 #include "launch.cuh"
 #include "ptx.cuh"
+#include "xsplit.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -33,6 +34,11 @@ struct AttnDecodeParams {
     const double * inv_freq;  // head_dim / 2 rotary frequencies; nullptr: q is used as it is and nothing is written to the cache
     int n_keys_fixed, splits;
     AttnShape s;
+    // With counters (one zeroed int per key/value head, left zeroed): the block that finishes a key/value head's last range merges the ranges of its
+    // query heads itself (attention_combine, llama_kernels.h:914-929) into out, and into xq the row split for the staged q4_0 GEMV when xq is given.
+    int * counters;
+    float * out;
+    uint8_t * xq;
 };
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
@@ -48,6 +54,7 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
     constexpr int HQ = kThreads / kTileKeys;            // threads per key in the score phase: 4, each with the heads hq, hq + 4
     constexpr int HPT = (GP + HQ - 1) / HQ;             // heads per thread there
     constexpr int OUT_IT = (GP * D / 2 + kThreads - 1) / kThreads;   // (head, dim pair) outputs per thread
+    constexpr int MERGE_IT = (GP * D + kThreads - 1) / kThreads;     // single outputs per thread in the merge
     extern __shared__ __align__(128) uint8_t smem[];
     float * qs = reinterpret_cast<float *>(smem);                      // [GP][D], scaled
     float * sc = qs + GP * D;                                          // [GP][kTileKeys] scores, then probabilities
@@ -241,6 +248,61 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
         dst[0] = m_run;
         dst[1] = l_run;
     }
+    if (!p.counters) return;
+    // the last block of this key/value head to get here merges: its own writes are ordered before the count, the others' are visible after it
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int done = atomicAdd(p.counters + kvh, 1);
+        is_last = done == int(gridDim.y) - 1;
+        if (is_last) p.counters[kvh] = 0;          // ready for the next step; nobody else touches it any more in this launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // weights of the ranges, per head: warp w takes head w (the stage buffers are free now and hold them)
+    float * wts = reinterpret_cast<float *>(stages);            // [GP][splits]
+    float * tot = wts + GP * p.splits;                          // [GP]
+    if (warp < G) {
+        const float * base = p.part + int64_t(kvh * G + warp) * p.splits * (2 + D);
+        float mx = -CUDART_INF_F;
+        for (int sp = lane; sp < p.splits; sp += 32) if (__ldcg(base + sp * (2 + D) + 1) > 0.f) mx = fmaxf(mx, __ldcg(base + sp * (2 + D)));
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float total = 0.f;
+        for (int sp = lane; sp < p.splits; sp += 32) {
+            const float l = __ldcg(base + sp * (2 + D) + 1);
+            const float w = l > 0.f ? expf(__ldcg(base + sp * (2 + D)) - mx) : 0.f;      // an empty range weighs nothing
+            wts[warp * p.splits + sp] = w;
+            total += l * w;
+        }
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        if (lane == 0) tot[warp] = total;
+    }
+    __syncthreads();
+    #pragma unroll
+    for (int it = 0; it < MERGE_IT; it++) {
+        const int idx = tid + it * kThreads;            // (head, element): a warp holds 32 consecutive elements of one head
+        const int hq = idx / D, d = idx % D;
+        if (idx < GP * D && hq < G) {
+            const float * col = p.part + int64_t(kvh * G + hq) * p.splits * (2 + D) + 2 + d;
+            const float * w = wts + hq * p.splits;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            int sp = 0;
+            for (; sp + 4 <= p.splits; sp += 4) {       // independent loads: an empty range's values are finite (zeros) and its weight is 0
+                a0 += __ldcg(col + (sp + 0) * (2 + D)) * w[sp + 0];
+                a1 += __ldcg(col + (sp + 1) * (2 + D)) * w[sp + 1];
+                a2 += __ldcg(col + (sp + 2) * (2 + D)) * w[sp + 2];
+                a3 += __ldcg(col + (sp + 3) * (2 + D)) * w[sp + 3];
+            }
+            for (; sp < p.splits; sp++) a0 += __ldcg(col + sp * (2 + D)) * w[sp];
+            const float r = ((a0 + a1) + (a2 + a3)) / tot[hq];
+            p.out[(kvh * G + hq) * D + d] = r;
+            if (p.xq) split_block(r, lane, ((kvh * G + hq) * D + d) / 32, p.s.n_head * D / 32, p.xq);
+        }
+    }
 }
 
 template <int D, int GP>
@@ -278,9 +340,10 @@ int attention_gqa_splits(int n_head_kv, int n_ctx) {
 }
 
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
-                                 int splits, const AttnShape & s, cudaStream_t stream) {
-    if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1)) return cudaErrorInvalidValue;
-    const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s};
+                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream) {
+    if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1) || (counters && !out) || (xq && !counters)) return cudaErrorInvalidValue;
+    const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
+                             static_cast<uint8_t *>(xq)};
     return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
 }
 

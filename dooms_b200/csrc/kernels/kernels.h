@@ -66,8 +66,9 @@ cudaError_t launch_attention_combine(const float * part, float * out, void * xq,
 // and n_keys_fixed gives the number of positions. Leaves part[n_head][splits][2 + head_dim] for launch_attention_combine.
 bool attention_gqa_supported(const AttnShape & s);
 int attention_gqa_splits(int n_head_kv, int n_ctx);
+// With counters (n_head_kv zeroed ints, left zeroed) the last block of each key/value head merges the ranges itself into out (and xq): no combine launch.
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
-                                 int splits, const AttnShape & s, cudaStream_t stream);
+                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream);
 
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
 // out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.
