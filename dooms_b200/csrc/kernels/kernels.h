@@ -106,6 +106,23 @@ bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
                              int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
 
+// ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
+constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;
+struct PeerAllReduce {
+    float * inbox[kPeerMaxRanks];       // every rank's inbox [2][n][max_floats] as this process sees it (its own, and the peers' through CUDA IPC)
+    uint32_t * flags[kPeerMaxRanks];    // every rank's flags [2][n][kPeerMaxBlocks]
+    uint32_t * round;                   // this rank's count of rounds done (device memory, zero at start)
+    uint32_t * ticket;                  // this rank's count of blocks done in the current round
+    DevState * state;
+    int32_t * host_error;               // mapped host word the decoder polls (optional)
+    int rank, n, max_floats;
+};
+size_t peer_allreduce_inbox_bytes(int n_ranks, int max_floats);
+size_t peer_allreduce_flag_bytes(int n_ranks);
+// x[0..n) += sum over ranks of partial[0..n), the same bits on every rank. n a multiple of 4, at most max_floats. All ranks must call it the same number
+// of times; waits are bounded and end with state->error = 3.
+cudaError_t launch_allreduce_add(const PeerAllReduce & p, const float * partial, float * x, int n, cudaStream_t stream);
+
 // ---- the tensor-core prefill GEMM (gemm_tc.cu) ----
 // A TMA descriptor of an f16 activation buffer [rows][cols] (cols a multiple of 64), opaque here so that this header needs no driver types.
 struct alignas(64) TensorMap { unsigned char bytes[128]; };

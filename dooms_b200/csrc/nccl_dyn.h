@@ -21,7 +21,7 @@ struct NcclApi {
     int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
     const char * (*GetErrorString)(int) = nullptr;
-    static constexpr int kFloat32 = 7, kSum = 0;   // ncclFloat32, ncclSum
+    static constexpr int kFloat32 = 7, kInt8 = 0, kSum = 0;   // ncclFloat32, ncclInt8, ncclSum
 };
 
 inline Status load_nccl(const char * path, NcclApi * api) {

@@ -145,14 +145,16 @@ dist.destroy_process_group()
 
 
 @pytest.mark.gpu
-def test_tensor_parallel_decoder_matches_one_gpu(tmp_path):
+@pytest.mark.parametrize("allreduce", ["nccl", "peer"])
+def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, allreduce):
+    """Two ranks against one GPU: last-position logits and greedy tokens; with NCCL's all-reduce and with the peer-memory all-reduce + add kernel."""
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "child.py"
     script.write_text(NCCL_CHILD)
-    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0", DOOMS_TP_ALLREDUCE=allreduce)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                         "29534", str(script)], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
