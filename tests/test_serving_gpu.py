@@ -1,0 +1,30 @@
+"""Data-parallel serving of many sequences: every sequence's greedy tokens equal those of the same sequence run alone; the workload generator is seeded."""
+import numpy as np
+import pytest
+
+from dooms_b200 import CudaLlamaDecoder, serving, synth
+from dooms_b200 import _lib as L
+
+from helpers import write
+
+
+def test_workload_is_seeded_and_within_the_ranges():
+    a = serving.workload(40, 1000, 3000)
+    b = serving.workload(40, 1000, 3000)
+    assert all(np.array_equal(x[0], y[0]) and x[1] == y[1] for x, y in zip(a, b))
+    assert all(32 <= len(p) <= 4096 and 16 <= d <= 512 and p.min() >= 0 and p.max() < 1000 for p, d in a)
+    assert serving.workload(3, 1000, 1)[0][1] != a[0][1] or not np.array_equal(serving.workload(3, 1000, 1)[0][0], a[0][0])
+
+
+@pytest.mark.gpu
+def test_sequences_served_by_two_workers_equal_single_runs(model_dir):
+    import torch
+    path = write(model_dir, "serve_q4_0", synth.tiny_spec(synth.pure(L.Q4_0)), 5)
+    seqs = serving.workload(10, 50, 3000, prompt_range=(3, 70), decode_range=(2, 12))
+    devices = [0, 1] if torch.cuda.device_count() > 1 else [0, 0]       # two workers either way
+    tokens, stats = serving.serve(path, seqs, devices, n_ctx=96, n_batch=32)
+    assert stats["sequences"] == 10 and stats["generated_tokens"] == sum(d for _, d in seqs) and stats["decode_tok_s"] > 0
+    dec = CudaLlamaDecoder.load(path, 96, 32)
+    for (prompt, n_decode), got in zip(seqs, tokens):
+        assert serving.run_sequence(dec, prompt, n_decode)[0] == got
+    dec.close()
