@@ -141,6 +141,36 @@ __device__ __forceinline__ void dequant_q4_0_group(const uint32_t (&w)[36], uint
     dequant_q4_0_words(raw, out);
 }
 
+// q4_K: a 256-element super-block is 144 bytes too (d, dmin, 12 scale bytes, 128 quant bytes). k step J of the group = sub-blocks 2J (the low nibbles of
+// quant bytes 32J .. 32J+31) and 2J+1 (their high nibbles); every value goes through the same f32 roundings as elem<kQ4_K> before it is rounded to f16.
+template <int J>
+__device__ __forceinline__ void dequant_q4_K_group(const uint32_t (&w)[36], uint4 (&out)[8]) {
+    const float d = __half2float(__ushort_as_half(uint16_t(w[0] & 0xFFFFu))), dmin = __half2float(__ushort_as_half(uint16_t(w[0] >> 16)));
+    auto qb = [&](int j) -> uint32_t { return (w[1 + j / 4] >> (8 * (j % 4))) & 0xFFu; };      // scale byte j (an index known at compile time)
+    float ds[2], mm[2];
+    #pragma unroll
+    for (int s = 0; s < 2; s++) {
+        const int c = 2 * J + s;
+        uint32_t sc, mn;
+        if (c < 4) { sc = qb(c) & 63u; mn = qb(c + 4) & 63u; }
+        else { sc = (qb(c + 4) & 15u) | ((qb(c - 4) >> 6) << 4); mn = (qb(c + 4) >> 4) | ((qb(c) >> 6) << 4); }
+        ds[s] = __fmul_rn(d, float(sc));
+        mm[s] = __fmul_rn(dmin, float(mn));
+    }
+    auto pair = [&](uint32_t q0, uint32_t q1, float dsc, float m) -> uint32_t {
+        const __half2 h = __floats2half2_rn(__fsub_rn(__fmul_rn(dsc, float(q0)), m), __fsub_rn(__fmul_rn(dsc, float(q1)), m));
+        return *reinterpret_cast<const uint32_t *>(&h);
+    };
+    #pragma unroll
+    for (int c8 = 0; c8 < 4; c8++) {
+        const uint32_t a = w[4 + 8 * J + 2 * c8], b = w[4 + 8 * J + 2 * c8 + 1];      // quant bytes 8 c8 .. 8 c8 + 7 of this step
+        out[c8] = make_uint4(pair(a & 15u, (a >> 8) & 15u, ds[0], mm[0]), pair((a >> 16) & 15u, (a >> 24) & 15u, ds[0], mm[0]),
+                             pair(b & 15u, (b >> 8) & 15u, ds[0], mm[0]), pair((b >> 16) & 15u, (b >> 24) & 15u, ds[0], mm[0]));
+        out[4 + c8] = make_uint4(pair((a >> 4) & 15u, (a >> 12) & 15u, ds[1], mm[1]), pair((a >> 20) & 15u, a >> 28, ds[1], mm[1]),
+                                 pair((b >> 4) & 15u, (b >> 12) & 15u, ds[1], mm[1]), pair((b >> 20) & 15u, b >> 28, ds[1], mm[1]));
+    }
+}
+
 struct GemmTcParams {
     const uint8_t * W;
     const uint8_t * W2;        // gate/up: the up matrix
@@ -152,7 +182,7 @@ struct GemmTcParams {
     int64_t y_stride, y16_stride;
     uint32_t flags;
     int T;                     // tokens per block: 128 or 256
-    int wide;                  // q4_0 rows of whole 256-element groups at 16-byte aligned addresses: the producers load 144-byte groups with 16-byte loads
+    int wide;                  // q4_0 / q4_K rows of whole 256-element groups at 16-byte aligned addresses: the producers load 144-byte groups with 16-byte loads
     int32_t * error;
 };
 
@@ -191,8 +221,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
     bool ok = true;
 
-    if (warp < kProducerWarps && DT == kQ4_0 && p.wide) {
-        // ---- weight producers, q4_0 rows of whole 256-element groups: the two threads of a row take the groups (four k steps each) in turn. A group is
+    if (warp < kProducerWarps && (DT == kQ4_0 || DT == kQ4_K) && p.wide) {
+        // ---- weight producers, q4_0 / q4_K rows of whole 256-element groups (144 bytes in both formats): the two threads of a row take the groups (four k steps each) in turn. A group is
         // 144 consecutive bytes, fetched with nine 16-byte loads per matrix before anything is computed, so that the other thread's stores overlap this
         // thread's loads; the thread then fills its four stages, a whole 128-byte row of the tile per step. ----
         const int r = (warp & 3) * 32 + lane, half = warp >> 2;
@@ -223,8 +253,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 #pragma unroll
                 for (int mtx = 0; mtx < NMAT; mtx++) {
                     uint4 v[8];
-                    dequant_q4_0_group<2 * J>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[0]));
-                    dequant_q4_0_group<2 * J + 1>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[4]));
+                    if constexpr (DT == kQ4_K) {
+                        dequant_q4_K_group<J>(raw[mtx], v);
+                    } else {
+                        dequant_q4_0_group<2 * J>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[0]));
+                        dequant_q4_0_group<2 * J + 1>(raw[mtx], reinterpret_cast<uint4 (&)[4]>(v[4]));
+                    }
                     const uint32_t tile = smem0 + s * stage_bytes + mtx * kTileWBytes + dst_row;
                     #pragma unroll
                     for (int c = 0; c < 8; c++) {
@@ -414,7 +448,7 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
     if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
                    flags, M > 128 ? 256 : 128, 0, error};
-    p.wide = dt == kQ4_0 && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
+    p.wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
     switch (dt) {

@@ -59,9 +59,18 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-struct SharedX {
-    const float * base;
-    __device__ __forceinline__ float operator()(uint32_t i) const { return base[i]; }
+// The 32 input values of one group, fetched with eight 16-byte shared-memory loads (a broadcast: the lanes of a half-warp read the same group) and handed
+// to the formats' dot products by index: after inlining the indices are constants and the values stay in registers.
+struct GroupX {
+    float v[32];
+    uint32_t first;     // index of v[0] in the chunk
+    __device__ __forceinline__ void load(const float * chunk, uint32_t group) {
+        first = group * 32u;
+        const float4 * src = reinterpret_cast<const float4 *>(chunk + first);
+        #pragma unroll
+        for (int i = 0; i < 8; i++) { const float4 t = src[i]; v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w; }
+    }
+    __device__ __forceinline__ float operator()(uint32_t i) const { return v[i - first]; }
 };
 
 template <int DT, int WARPS, int STAGES>
@@ -173,8 +182,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
         const uint32_t lo = ((nmat == 2 && (u_tm & 1)) ? w2_lo : w_lo) + uint32_t(tile * kTileRows) * RB + uint32_t(u_chunk) * CB;
         // the lane's row of the stage; its bytes start at the low four address bits of the row's chunk
         const uint8_t * rp = smem + my_stages_off + uint32_t(u_slot) * stage_bytes + uint32_t(row) * stride + ((lo + uint32_t(row) * RB) & 15u);
-        const SharedX X{xs + size_t(u_chunk) * p.cbk * BE};
-        for (int gq = half; gq < groups; gq += 2) acc += UnitDot<DT>::dot(rp, uint32_t(gq), X);
+        const float * chunk_x = xs + size_t(u_chunk) * p.cbk * BE;
+        for (int gq = half; gq < groups; gq += 2) {
+            GroupX X;
+            X.load(chunk_x, uint32_t(gq));
+            acc += UnitDot<DT>::dot(rp, uint32_t(gq), X);
+        }
         u_chunk += step_chunk;
         u_tm += step_tm;
         if (u_chunk >= p.nchunks) { u_chunk -= p.nchunks; u_tm++; }

@@ -65,7 +65,7 @@ def _gemm(args):
     from .quantize import quantize
     lib = L.lib()
     gen = torch.Generator(device='cuda').manual_seed(1)
-    dt = L.Q4_0
+    dt = L.DTYPE_NAMES.index(args.dtype)
     M, N, K = args.tokens, args.rows, args.cols
     w = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02)
     w2 = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02) if args.gate else None
@@ -141,6 +141,7 @@ def main(argv=None):
     m.add_argument('--cols', type=int, default=4096)
     m.add_argument('--gate', action='store_true')
     m.add_argument('--reps', type=int, default=3)
+    m.add_argument('--dtype', default='q4_0')
     l = sub.add_parser('launches')
     l.add_argument('csv')
     args = ap.parse_args(argv)
