@@ -110,10 +110,17 @@ int32_t launch_result(cudaError_t e, const char * what) {
     return fail(DOOMS_INTERNAL, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-// The staged q4_0 GEMV on an f32 input: every block splits the input for itself in its prologue, so the call is one launch and needs no scratch.
-int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t st,
-                  const char * what) {
-    return launch_result(cuda::launch_gemv_q4_0(w, w2, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, st), what);
+// The integer tensor-core GEMV on an f32 input. Up to 8192 columns every block splits the input for itself in its prologue: one launch, no scratch. Longer
+// inputs are split once by a kernel into the per-device scratch (shared by every call on the device, so such calls must not overlap on different streams).
+int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, bool q4_k,
+                  cudaStream_t st, const char * what) {
+    if (cols < 8192) return launch_result(cuda::launch_gemv_q4_0(w, w2, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st), what);
+    void * scratch = nullptr;
+    const Status ss = scratch_for((cuda::quantized_x_bytes(cols) + 15) & ~size_t(15), &scratch);
+    if (!ss.is_ok()) return done(ss);
+    cudaError_t e = cuda::launch_quantize_x(x, cols, scratch, st);
+    if (e == cudaSuccess) e = cuda::launch_gemv_q4_0(w, w2, scratch, nullptr, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st);
+    return launch_result(e, what);
 }
 
 // Scratch of dooms_cuda_argmax_noalloc: the per-block partial results (8 bytes each) for up to DOOMS_CUDA_ARGMAX_NOALLOC_MAX logits. It is part of the
@@ -362,7 +369,8 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
     }
     if (rows == 0) return DOOMS_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, st, "matvec");
+    if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, false, st, "matvec");
+    if (dtype == DOOMS_Q4_K && cuda::gemv_q4_k_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, true, st, "matvec");
     return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, st), "matvec");
 }
 
@@ -375,7 +383,10 @@ DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, cons
     if (rows == 0) return DOOMS_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_wg, rows, cols) && cuda::gemv_q4_0_supported(d_wu, rows, cols)) {
-        return fast_q4_0(d_wg, d_wu, d_x, d_h, nullptr, rows, cols, 0u, st, "gate_up");
+        return fast_q4_0(d_wg, d_wu, d_x, d_h, nullptr, rows, cols, 0u, false, st, "gate_up");
+    }
+    if (dtype == DOOMS_Q4_K && cuda::gemv_q4_k_supported(d_wg, rows, cols) && cuda::gemv_q4_k_supported(d_wu, rows, cols)) {
+        return fast_q4_0(d_wg, d_wu, d_x, d_h, nullptr, rows, cols, 0u, true, st, "gate_up");
     }
     return launch_result(cuda::launch_gate_up(dtype, d_wg, d_wu, d_x, d_h, rows, cols, st), "gate_up");
 }

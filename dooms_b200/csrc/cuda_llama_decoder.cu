@@ -168,7 +168,10 @@ struct CudaLlamaDecoder::Impl {
         run("all_reduce", [&] { return nccl.AllReduce(buf, buf, count, NcclApi::kFloat32, NcclApi::kSum, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown; });
     }
 
-    bool fast(const MatDev & w) const { return w.dt == DType::Q4_0 && cuda::gemv_q4_0_supported(w.ptr, w.rows, w.cols); }
+    // the integer tensor-core GEMV takes q4_0 and q4_K rows
+    bool fast(const MatDev & w) const {
+        return (w.dt == DType::Q4_0 && cuda::gemv_q4_0_supported(w.ptr, w.rows, w.cols)) || (w.dt == DType::Q4_K && cuda::gemv_q4_k_supported(w.ptr, w.rows, w.cols));
+    }
     // One-token projection of `in`, RMS-normalized with gamma first when gamma is given. The streaming kernels do the norm (and the q4_0 kernel the split of
     // its input into int8 limbs) in their prologue; only shapes they do not take go through a norm launch and the row-per-warp kernel. A producer that
     // already wrote the split of `in` (the attention merge) leaves it in xq and says so in xq_of.
@@ -185,7 +188,7 @@ struct CudaLlamaDecoder::Impl {
         if (fast(w)) {
             prepare_fast_input(in, gamma, w.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
-            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
+            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream); });
             return;
         }
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
@@ -208,7 +211,7 @@ struct CudaLlamaDecoder::Impl {
         if (fast(wg) && fast(wu)) {
             prepare_fast_input(in, gamma, wg.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
-            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream); });
+            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream); });
             return;
         }
         if (cuda::gemv_blocks_supported(int(wg.dt), wg.ptr, in, wg.rows, wg.cols) && cuda::gemv_blocks_supported(int(wu.dt), wu.ptr, in, wu.rows, wu.cols)) {

@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -153,7 +154,7 @@ __device__ __forceinline__ void dequant_q4_K_group(const uint32_t (&w)[36], uint
         const int c = 2 * J + s;
         uint32_t sc, mn;
         if (c < 4) { sc = qb(c) & 63u; mn = qb(c + 4) & 63u; }
-        else { sc = (qb(c + 4) & 15u) | ((qb(c - 4) >> 6) << 4); mn = (qb(c + 4) >> 4) | ((qb(c) >> 6) << 4); }
+        else { sc = (qb(c + 4) & 15u) | ((qb(c < 4 ? 0 : c - 4) >> 6) << 4); mn = (qb(c + 4) >> 4) | ((qb(c) >> 6) << 4); }
         ds[s] = __fmul_rn(d, float(sc));
         mm[s] = __fmul_rn(dmin, float(mn));
     }
@@ -222,7 +223,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     bool ok = true;
 
     if (warp < kProducerWarps && (DT == kQ4_0 || DT == kQ4_K) && p.wide) {
-        // ---- weight producers, q4_0 / q4_K rows of whole 256-element groups (144 bytes in both formats): the two threads of a row take the groups (four k steps each) in turn. A group is
+        // ---- weight producers, q4_0 / q4_K rows of whole 256-element groups (144 bytes in both formats): the two threads of a row take the groups (four
+        // k steps each) in turn (both threads on every step, half a tile row each, measured 22 % slower on q4_0). A group is
         // 144 consecutive bytes, fetched with nine 16-byte loads per matrix before anything is computed, so that the other thread's stores overlap this
         // thread's loads; the thread then fills its four stages, a whole 128-byte row of the tile per step. ----
         const int r = (warp & 3) * 32 + lane, half = warp >> 2;

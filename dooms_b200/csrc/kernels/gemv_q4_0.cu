@@ -85,6 +85,48 @@ __device__ __forceinline__ void pair_step(uint32_t a0, uint32_t a1, uint32_t d0a
     acc1 = fmaf(float(c[2] + 128 * c[3]), d1 * sx, acc1);
 }
 
+// q4_K: a 256-element super-block is 144 bytes as well (d, dmin, 12 packed 6-bit scales / mins, 128 quant bytes), so rows, chunks and stages have the
+// geometry of eight q4_0 blocks and only the unpacking differs. "Pair" J of a super-block = sub-blocks 2J (low nibbles of quant bytes 32J .. 32J+31) and
+// 2J+1 (their high nibbles); value = d sc q - dmin m (Q4_K::elem, llama_kernels.h:1085-1110), so per sub-block the lane adds (d sc) (q . x) from the MMA
+// and, once per row and sub-block, subtracts (dmin m) sum(x) with the sums of the input's 32-element blocks precomputed in shared memory.
+// h0 / h1: the super-block's four header words of the lane's two rows. s = t >> 1: which sub-block of the pair this lane scales.
+template <int J>
+__device__ __forceinline__ void pair_step_k4(uint32_t a0, uint32_t a1, const uint4 & h0, const uint4 & h1, uint32_t ba, uint32_t sa, uint32_t suma, bool first,
+                                             uint32_t s, bool low_pair, float & acc0, float & acc1) {
+    const uint2 bv = lds64<J * 256>(ba);
+    const float sx = ldsf<J * 16>(sa) * 16.f;                     // the split's factor assumes weights scaled by 16 (the q4_0 path); these are plain 0..15
+    const uint32_t w00 = lds32<16 + 32 * J>(a0), w10 = lds32<32 + 32 * J>(a0), w01 = lds32<16 + 32 * J>(a1), w11 = lds32<32 + 32 * J>(a1);
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+    int c[4] = {0, 0, 0, 0};
+    mma_u8s8_16832(c, w00 & M, w01 & M, w10 & M, w11 & M, first ? bv.x : 0u, first ? bv.y : 0u);
+    mma_u8s8_16832(c, (w00 >> 4) & M, (w01 >> 4) & M, (w10 >> 4) & M, (w11 >> 4) & M, first ? 0u : bv.x, first ? 0u : bv.y);
+    // 6-bit scale and min of sub-block 2J + s (ggml's get_scale_min_k4): bytes 2J+s of the first two scale words for the first four sub-blocks, split
+    // between the third word's nibbles and the top two bits of the first two words' bytes for the last four
+    const uint32_t sh = 16u * (J & 1) + 8u * s;
+    uint32_t sc0, mn0, sc1, mn1;
+    if (J < 2) {
+        sc0 = (h0.y >> sh) & 63u; mn0 = (h0.z >> sh) & 63u;
+        sc1 = (h1.y >> sh) & 63u; mn1 = (h1.z >> sh) & 63u;
+    } else {
+        sc0 = ((h0.w >> sh) & 15u) | ((((h0.y >> sh) >> 6) & 3u) << 4); mn0 = (((h0.w >> sh) >> 4) & 15u) | ((((h0.z >> sh) >> 6) & 3u) << 4);
+        sc1 = ((h1.w >> sh) & 15u) | ((((h1.y >> sh) >> 6) & 3u) << 4); mn1 = (((h1.w >> sh) >> 4) & 15u) | ((((h1.z >> sh) >> 6) & 3u) << 4);
+    }
+    const float d0 = half_bits_to_float(h0.x & 0xFFFFu), d1 = half_bits_to_float(h1.x & 0xFFFFu);
+    acc0 = fmaf(float(c[0] + 128 * c[1]), d0 * float(sc0) * sx, acc0);
+    acc1 = fmaf(float(c[2] + 128 * c[3]), d1 * float(sc1) * sx, acc1);
+    if (low_pair) {      // one lane of the two that share the sub-block
+        const float sum = ldsf<J * 8>(suma);
+        acc0 = fmaf(-(half_bits_to_float(h0.x >> 16) * float(mn0)), sum, acc0);
+        acc1 = fmaf(-(half_bits_to_float(h1.x >> 16) * float(mn1)), sum, acc1);
+    }
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -96,7 +138,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // of stages with 16-byte asynchronous copies (commit / wait groups: a waiting warp sleeps in hardware, there is no polling and nothing that can hang).
 // A warp adds what it computed for a (tile, matrix) into its own slot of a small shared table; after one block-wide barrier the table's slots are summed
 // in a fixed order, so the result does not depend on timing.
-template <int WARPS, int STAGES>
+template <int WARPS, int STAGES, bool K4>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
@@ -117,7 +159,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     const uint32_t sxp = xl + uint32_t(nb) * 128u;
     const uint32_t stride = uint32_t(p.stride);
     const uint32_t stage_bytes = uint32_t(kTileRows) * stride;
-    const uint32_t stages_base = xl + ((uint32_t(nb) * 136u + 127u) & ~127u);
+    const uint32_t sumx = sxp + uint32_t(nb) * 8u;                                   // q4_K: the sum of each 32-element block of the input
+    const uint32_t stages_base = xl + ((uint32_t(nb) * 140u + 127u) & ~127u);
     const uint32_t my_stages = stages_base + uint32_t(warp) * STAGES * stage_bytes;
     float * partial = reinterpret_cast<float *>(smem + (stages_base - smem_base) + size_t(WARPS) * STAGES * stage_bytes);   // [tile][mat][warp][16]
 
@@ -220,6 +263,22 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         cp_async_wait<0>();
     }
     __syncthreads();
+    if (K4) {
+        // sum of each input block from its digits: lane l holds four bytes of digit l / 8; X = S0 + 128 S1 + 128^2 S2 + 128^3 S3, times the block's factor
+        for (int blk = warp; blk < nb; blk += WARPS) {
+            const uint32_t w = lds32<0>(xl + uint32_t(blk) * 128u + uint32_t(lane) * 4u);
+            int sd = __dp4a(int(w), 0x01010101, 0);
+            sd += __shfl_xor_sync(0xffffffffu, sd, 1); sd += __shfl_xor_sync(0xffffffffu, sd, 2); sd += __shfl_xor_sync(0xffffffffu, sd, 4);
+            const float s0 = float(__shfl_sync(0xffffffffu, sd, 0)), s1 = float(__shfl_sync(0xffffffffu, sd, 8));
+            const float s2 = float(__shfl_sync(0xffffffffu, sd, 16)), s3 = float(__shfl_sync(0xffffffffu, sd, 24));
+            if (lane == 0) {
+                const float f = ldsf<0>(sxp + uint32_t(blk) * 8u) * 16.f;        // s 2^-26
+                const float total = ((s3 * 128.f + s2) * 128.f + s1) * 128.f + s0;
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(sumx + uint32_t(blk) * 4u), "f"(total * f) : "memory");
+            }
+        }
+        __syncthreads();
+    }
 
     const bool first = g < 4;
     const uint32_t b_lane = xl + uint32_t(g >> 2) * 128u + uint32_t(g & 3) * 32u + uint32_t(t) * 8u;
@@ -258,18 +317,32 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         uint32_t a0 = row0 + 4u * t, a1 = row1 + 4u * t, d0a = row0 + 18u * (t >> 1), d1a = row1 + 18u * (t >> 1);
         uint32_t ba = b_lane + uint32_t(u_chunk * p.cbk) * 128u, sa = s_lane + uint32_t(u_chunk * p.cbk) * 8u;
         int pr = 0;
-        #pragma unroll 1
-        for (; pr + 4 <= npairs; pr += 4) {
-            pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-            pair_step<1>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-            pair_step<2>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-            pair_step<3>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-            a0 += 144; a1 += 144; d0a += 144; d1a += 144; ba += 1024; sa += 64;
-        }
-        #pragma unroll 1
-        for (; pr < npairs; pr++) {
-            pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-            a0 += 36; a1 += 36; d0a += 36; d1a += 36; ba += 256; sa += 16;
+        if constexpr (K4) {
+            // one super-block (four pairs) per round; its header words are read once per row
+            uint32_t suma = sumx + uint32_t(u_chunk * p.cbk) * 4u + uint32_t(t >> 1) * 4u, h0a = row0, h1a = row1;
+            #pragma unroll 1
+            for (; pr + 4 <= npairs; pr += 4) {
+                const uint4 h0 = lds128(h0a), h1 = lds128(h1a);
+                pair_step_k4<0>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
+                pair_step_k4<1>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
+                pair_step_k4<2>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
+                pair_step_k4<3>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
+                a0 += 144; a1 += 144; h0a += 144; h1a += 144; ba += 1024; sa += 64; suma += 32;
+            }
+        } else {
+            #pragma unroll 1
+            for (; pr + 4 <= npairs; pr += 4) {
+                pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+                pair_step<1>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+                pair_step<2>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+                pair_step<3>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+                a0 += 144; a1 += 144; d0a += 144; d1a += 144; ba += 1024; sa += 64;
+            }
+            #pragma unroll 1
+            for (; pr < npairs; pr++) {
+                pair_step<0>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
+                a0 += 36; a1 += 36; d0a += 36; d1a += 36; ba += 256; sa += 16;
+            }
         }
         u_chunk += step_chunk;
         u_tm += step_tm;
@@ -305,18 +378,18 @@ struct Plan { int cbk, nchunks, stride, stages, warps; size_t smem; bool ok; };
 // Chunks of an even number of blocks that divides the row; the row stride in a stage is an odd multiple of 16 bytes so that the 8 rows of a fragment fall
 // on different banks.
 constexpr int kMaxStages = 6;
-Plan plan_for(int64_t cols, int nmat) {
+Plan plan_for(int64_t cols, int nmat, bool k4) {      // k4: q4_K rows, chunks of whole 256-element super-blocks (8 or 16 blocks)
     Plan best{};
     const int nb = int(cols / 32);
-    if (cols % 64 != 0 || nb < 2) return best;
-    const size_t fixed = (size_t(nb) * 136 + 127) & ~size_t(127);
+    if (cols % (k4 ? 256 : 64) != 0 || nb < 2) return best;
+    const size_t fixed = (size_t(nb) * 140 + 127) & ~size_t(127);
     int64_t best_score = -1;
     int fw = 0, fc = 0, fs = 0;
     if (const char * f = getenv("DOOMS_GEMV_FORCE")) sscanf(f, "%d:%d:%d", &fw, &fc, &fs);
     for (int warps : {16, 8}) {
         if (fw && warps != fw) continue;
         for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
-            if (nb % cbk) continue;
+            if (nb % cbk || (k4 && cbk % 8)) continue;
             if (fc && cbk != fc && nb % fc == 0) continue;
             int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
             if (stride % 32 != 16) stride += 16;
@@ -337,38 +410,41 @@ Plan plan_for(int64_t cols, int nmat) {
     return best;
 }
 
-template <int WARPS, int STAGES>
+template <int WARPS, int STAGES, bool K4>
 cudaError_t launch_with(const GemvQ40Params & p, size_t smem, unsigned grid, cudaStream_t stream) {
     static int configured_device = -1;      // the attribute is per function and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_device != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
+        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES, K4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
     static const bool early = [] { const char * e = getenv("DOOMS_PDL_GEMV"); return !(e && *e == '0'); }();
-    return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
+    return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES, K4>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
 }
 
-template <int WARPS>
+template <int WARPS, bool K4>
 cudaError_t launch_stages(const GemvQ40Params & p, const Plan & pl, unsigned grid, cudaStream_t stream) {
     switch (pl.stages) {
-        case 6: return launch_with<WARPS, 6>(p, pl.smem, grid, stream);
-        case 5: return launch_with<WARPS, 5>(p, pl.smem, grid, stream);
-        case 4: return launch_with<WARPS, 4>(p, pl.smem, grid, stream);
-        case 3: return launch_with<WARPS, 3>(p, pl.smem, grid, stream);
-        default: return launch_with<WARPS, 2>(p, pl.smem, grid, stream);
+        case 6: return launch_with<WARPS, 6, K4>(p, pl.smem, grid, stream);
+        case 5: return launch_with<WARPS, 5, K4>(p, pl.smem, grid, stream);
+        case 4: return launch_with<WARPS, 4, K4>(p, pl.smem, grid, stream);
+        case 3: return launch_with<WARPS, 3, K4>(p, pl.smem, grid, stream);
+        default: return launch_with<WARPS, 2, K4>(p, pl.smem, grid, stream);
     }
 }
 
 }  // namespace
 
 bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols) {
-    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 1).ok;
+    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 1, false).ok;
+}
+bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols) {
+    return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 2, true).ok;
 }
 
-size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }
+size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }      // the kernel adds 4 bytes per block of its own in shared memory
 
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
     const int nb = int(cols / 32);
@@ -376,8 +452,8 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
-    const Plan pl = plan_for(cols, W2 ? 2 : 1);
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream) {
+    const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k);
     if (!pl.ok) return cudaErrorInvalidValue;
     GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, y, bias, rows, int(cols), flags,
                     pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 0u, 0u};
@@ -394,7 +470,8 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     p.rows_r = int(rows % grid);
     p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
     p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
-    return pl.warps == 16 ? launch_stages<16>(p, pl, grid, stream) : launch_stages<8>(p, pl, grid, stream);
+    if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, pl, grid, stream) : launch_stages<8, true>(p, pl, grid, stream);
+    return pl.warps == 16 ? launch_stages<16, false>(p, pl, grid, stream) : launch_stages<8, false>(p, pl, grid, stream);
 }
 
 }  // namespace cuda

@@ -103,8 +103,10 @@ bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
 // y[r] (+)= W[r] . x (+ bias[r]); with W2: y[r] = silu(W[r] . x) * (W2[r] . x). The input comes either split (xq, from launch_quantize_x or from a kernel
 // that writes the split itself) or as f32 (xq == nullptr, x != nullptr): then every block splits it in its prologue, after RMS-normalizing it when gamma is
 // given (x[i] * rsqrt(mean(x^2) + eps) * gamma[i]), which saves the norm's and the split's own launches in a decode step.
+// q4_k: the rows are q4_K super-blocks (same bytes per 256 elements, other unpacking); gemv_q4_k_supported says whether the kernel takes the matrix.
+bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols);
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream);
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;
