@@ -84,6 +84,7 @@ struct CudaLlamaDecoder::Impl {
     int gqa_splits = 1;
     double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
     int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
+    int * split_counters = nullptr; // one per 32 rows of h: rows written by the gate/up GEMV's blocks (zero between launches)
     int32_t pos = 0;
     bool has_pending = false;
     // decode graph
@@ -114,7 +115,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters, (void *)split_counters,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -207,11 +208,18 @@ struct CudaLlamaDecoder::Impl {
         });
         xq_of = do_split ? xn : nullptr;
     }
-    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out) {
+    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split) {
         if (fast(wg) && fast(wu)) {
             prepare_fast_input(in, gamma, wg.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
-            run("gate_up", [&] { return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream); });
+            // a result that the integer GEMV reads next (ffn_down) is left split by the blocks that complete its 32-row groups: no split launch, and no
+            // split in the next kernel's prologue
+            const bool split_out = down_takes_split && wg.rows % 32 == 0 && split_counters;
+            run("gate_up", [&] {
+                return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
+                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr);
+            });
+            xq_of = split_out ? out : nullptr;
             return;
         }
         if (cuda::gemv_blocks_supported(int(wg.dt), wg.ptr, in, wg.rows, wg.cols) && cuda::gemv_blocks_supported(int(wu.dt), wu.ptr, in, wu.rows, wu.cols)) {
@@ -341,7 +349,7 @@ struct CudaLlamaDecoder::Impl {
                 matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags);
                 xq_of = nullptr;
                 reduce_into_x(1);
-                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h);
+                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down));
                 matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
             } else if (use_tc) {
@@ -725,6 +733,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     }
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn_counters), size_t(std::max(1, m.nkv)) * sizeof(int), "the attention counters"));
     cudaMemset(m.attn_counters, 0, size_t(std::max(1, m.nkv)) * sizeof(int));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.split_counters), (size_t(m.ff) / 32 + 1) * sizeof(int), "the split counters"));
+    cudaMemset(m.split_counters, 0, (size_t(m.ff) / 32 + 1) * sizeof(int));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
                                     "the split projection input"));
     if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {

@@ -17,7 +17,6 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdio>
 #include <cstdlib>
 
 #include "kernels.h"
@@ -43,6 +42,10 @@ struct GemvQ40Params {
     const float * x;        // the input as f32 (xq == nullptr)
     const float * gamma;    // with x: RMS-normalize it first, x[i] * rsqrt(mean(x^2) + eps) * gamma[i] (norm_vec, llama_kernels.h:1272-1286); nullptr: as it is
     float eps;
+    // Optional (rows a multiple of 32): the output row is also left split for the next projection (xq layout for `rows` elements). The blocks count the rows
+    // they have written per 32-row group in out_counters (rows / 32 zeroed ints, left zeroed); whoever completes a group splits it.
+    uint8_t * xq_out;
+    int * out_counters;
     float * y;
     const float * bias;
     int64_t rows;
@@ -367,6 +370,23 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         if (p.flags & kFlagBias) s += p.bias[row];
         p.y[row] = (p.flags & kFlagAccumulate) ? p.y[row] + s : s;
     }
+    if (p.xq_out) {
+        __threadfence();              // this block's rows are visible before they are counted
+        __syncthreads();
+        const int64_t R1 = R0 + nrows;
+        for (int64_t grp = R0 / 32 + warp; grp * 32 < R1; grp += WARPS) {
+            const int mine = int(min(R1, grp * 32 + 32) - max(R0, grp * 32));
+            int done = 0;
+            if (lane == 0) {
+                done = atomicAdd(p.out_counters + grp, mine) + mine == 32;
+                if (done) p.out_counters[grp] = 0;      // complete: nobody adds to it again in this launch
+            }
+            if (__shfl_sync(0xffffffffu, done, 0)) {
+                __threadfence();
+                split_block(__ldcg(p.y + grp * 32 + lane), lane, int(grp), int(p.rows / 32), p.xq_out);
+            }
+        }
+    }
 }
 
 constexpr size_t kSmemLimit = 224 * 1024;
@@ -384,20 +404,15 @@ Plan plan_for(int64_t cols, int nmat, bool k4) {      // k4: q4_K rows, chunks o
     if (cols % (k4 ? 256 : 64) != 0 || nb < 2) return best;
     const size_t fixed = (size_t(nb) * 140 + 127) & ~size_t(127);
     int64_t best_score = -1;
-    int fw = 0, fc = 0, fs = 0;
-    if (const char * f = getenv("DOOMS_GEMV_FORCE")) sscanf(f, "%d:%d:%d", &fw, &fc, &fs);
     for (int warps : {16, 8}) {
-        if (fw && warps != fw) continue;
         for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
             if (nb % cbk || (k4 && cbk % 8)) continue;
-            if (fc && cbk != fc && nb % fc == 0) continue;
             int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
             if (stride % 32 != 16) stride += 16;
             if ((cbk * kBlockBytes + 30) / 16 * kTileRows > kMaxPieces * 32 || kTileRows * stride >= (1 << 13)) continue;
             int stages = 0;
             for (int st = kMaxStages; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps, nmat) <= kSmemLimit) { stages = st; break; }
             if (!stages) continue;
-            if (fs && fs <= stages) stages = fs;
             // Measured on B200 (8B shapes, back-to-back launches over distinct matrices): the kernel is bound by instruction issue and shared-memory
             // bandwidth more than by the bytes in flight, so the longest chunk (fewest per-unit fixed costs) wins, then 16 warps over 8, then stages.
             const int64_t score = int64_t(cbk) * 1000 + (warps == 16 ? 100 : 0) + stages;
@@ -452,10 +467,11 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream) {
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters) {
+    if (xq_out && (!out_counters || rows % 32 != 0)) return cudaErrorInvalidValue;
     const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k);
     if (!pl.ok) return cudaErrorInvalidValue;
-    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, y, bias, rows, int(cols), flags,
+    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, y, bias, rows, int(cols), flags,
                     pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 0u, 0u};
     if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover

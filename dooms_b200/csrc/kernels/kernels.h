@@ -105,8 +105,10 @@ bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
 // given (x[i] * rsqrt(mean(x^2) + eps) * gamma[i]), which saves the norm's and the split's own launches in a decode step.
 // q4_k: the rows are q4_K super-blocks (same bytes per 256 elements, other unpacking); gemv_q4_k_supported says whether the kernel takes the matrix.
 bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols);
+// xq_out (optional, rows a multiple of 32, with out_counters = rows / 32 zeroed ints that are left zeroed): the output row is also written split, for a
+// following projection that takes it as xq; the block that completes a 32-row group of y splits it.
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream);
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr);
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;
