@@ -189,7 +189,8 @@ struct CudaLlamaDecoder::Impl {
         if (fast(w)) {
             prepare_fast_input(in, gamma, w.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
-            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream); });
+            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream, nullptr, nullptr,
+                                                               host_error); });
             return;
         }
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
@@ -217,7 +218,7 @@ struct CudaLlamaDecoder::Impl {
             const bool split_out = down_takes_split && wg.rows % 32 == 0 && split_counters;
             run("gate_up", [&] {
                 return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
-                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr);
+                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error);
             });
             xq_of = split_out ? out : nullptr;
             return;

@@ -439,6 +439,19 @@ cudaError_t make_activation_map(TensorMap * out, const void * base, int64_t rows
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+cudaError_t make_rows_map(TensorMap * out, const void * base, int64_t rows, int64_t row_bytes, int box_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return cudaErrorNotSupported;
+    if (row_bytes % 16 != 0 || box_bytes % 16 != 0 || box_bytes > 512 || box_rows < 1 || box_rows > 256 || (reinterpret_cast<uintptr_t>(base) & 15u) != 0) return cudaErrorInvalidValue;
+    const cuuint64_t dims[2] = {cuuint64_t(row_bytes / 2), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+    const cuuint32_t box[2] = {cuuint32_t(box_bytes / 2), cuuint32_t(box_rows)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
     (void)W;
     const bool type_ok = dt == kF16 || dt == kQ4_0 || dt == kQ5_0 || dt == kQ8_0 || dt == kQ4_K || dt == kQ6_K;

@@ -14,6 +14,7 @@
 //     that keeps the 8 rows of a fragment on different banks. One block-wide barrier after the prologue, one before the epilogue.
 // The block formulas are the reference's (src/backend/metal/llama_kernels.h:1012-1040: value = d (q - 8)); matvec1q / gate_up1q there are the kernels this
 // replaces (llama_kernels.h:1197-1269).
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -32,6 +33,7 @@ using namespace dooms::dev;
 namespace {
 
 constexpr int kTileRows = 16;
+constexpr int kMaxTilesPerBlockDev = 8;     // the table of per-warp sums holds this many 16-row tiles
 constexpr int kBlockBytes = 18;
 constexpr int kMaxPieces = 10;      // 16-byte pieces of a stage one lane copies: 16 rows x at most 20 pieces per row / 32 lanes
 
@@ -46,6 +48,7 @@ struct GemvQ40Params {
     // they have written per 32-row group in out_counters (rows / 32 zeroed ints, left zeroed); whoever completes a group splits it.
     uint8_t * xq_out;
     int * out_counters;
+    int32_t * error;        // optional mapped host word: set to 4 when a bounded wait for a tensor copy ran out (TMA variant)
     float * y;
     const float * bias;
     int64_t rows;
@@ -55,7 +58,8 @@ struct GemvQ40Params {
     int nchunks;            // chunks per row
     int stride;             // bytes between the rows of a stage (multiple of 16, = 16 mod 128)
     int upr;                // 16-byte pieces copied per row of a stage (the aligned cover of a chunk)
-    int rows_q, rows_r;     // rows / grid and rows % grid: block b has rows_q + (b < rows_r) rows starting at b rows_q + min(b, rows_r)
+    int rows_q, rows_r;     // units / grid and units % grid: block b has rows_q + (b < rows_r) units of row_unit rows starting at unit b rows_q + min(b, rows_r)
+    int row_unit;
     uint32_t inv_upr, inv_nchunks;   // 65536 / d + 1: (j * inv) >> 16 = j / d for the small j divided here
 };
 
@@ -141,8 +145,14 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // of stages with 16-byte asynchronous copies (commit / wait groups: a waiting warp sleeps in hardware, there is no polling and nothing that can hang).
 // A warp adds what it computed for a (tile, matrix) into its own slot of a small shared table; after one block-wide barrier the table's slots are summed
 // in a fixed order, so the result does not depend on timing.
-template <int WARPS, int STAGES, bool K4>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params p) {
+// TMA: the stages are filled by tensor copies (cp.async.bulk.tensor.2d over the matrix seen as rows of 16-bit words) instead of per-lane 16-byte copies.
+// A copy's shared-memory destination has to be 128-byte aligned and its rows land densely, so the stage is cut into sub-stages of 16 rows x 144 bytes (one
+// round of four pairs = eight blocks = one q4_K super-block): 144 bytes = 36 words = 4 banks more per row, which puts the 8 rows of a fragment on
+// different banks, and 8 rows x 144 bytes = 1152 bytes keeps every copy's destination aligned. One elected lane issues two 8-row copies per sub-stage (one
+// when the block's last tile has at most 8 rows) and the warp waits on its own mbarrier per stage (bounded). Blocks own multiples of 8 rows, so nothing
+// outside a block's range is fetched; rows past the end of the matrix are zero-filled by the copy.
+template <int WARPS, int STAGES, bool K4, bool TMA>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_constant__ CUtensorMap mw, const __grid_constant__ CUtensorMap mw2, const GemvQ40Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const int nb = p.cols / 32;
@@ -151,8 +161,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     const uint32_t CB = uint32_t(p.cbk) * kBlockBytes;
 
     // this block's rows
-    const int nrows = p.rows_q + (int(blockIdx.x) < p.rows_r ? 1 : 0);
-    const int64_t R0 = int64_t(blockIdx.x) * p.rows_q + min(int(blockIdx.x), p.rows_r);
+    // rows are dealt in units of p.row_unit rows (1, or 8 with tensor copies): block b gets rows_q + (b < rows_r) units
+    const int64_t R0 = (int64_t(blockIdx.x) * p.rows_q + min(int(blockIdx.x), p.rows_r)) * p.row_unit;
+    const int nrows = int(min(int64_t(p.rows_q + (int(blockIdx.x) < p.rows_r ? 1 : 0)) * p.row_unit, p.rows - R0));
     const int ntiles = (nrows + kTileRows - 1) / kTileRows;
     const int total_units = ntiles * nmat * p.nchunks;
     const int my_units = warp < total_units ? (total_units - warp - 1) / WARPS + 1 : 0;
@@ -161,11 +172,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     const uint32_t xl = smem_base;                                                  // limbs: nb x 128, then the block scales: nb x 2 floats
     const uint32_t sxp = xl + uint32_t(nb) * 128u;
     const uint32_t stride = uint32_t(p.stride);
-    const uint32_t stage_bytes = uint32_t(kTileRows) * stride;
+    constexpr uint32_t kSub = 16u * 144u;                                           // TMA: a sub-stage, 16 rows of eight blocks
+    const uint32_t rounds = uint32_t(p.cbk) / 8u;
+    const uint32_t stage_bytes = TMA ? rounds * kSub : uint32_t(kTileRows) * stride;
     const uint32_t sumx = sxp + uint32_t(nb) * 8u;                                   // q4_K: the sum of each 32-element block of the input
     const uint32_t stages_base = xl + ((uint32_t(nb) * 140u + 127u) & ~127u);
     const uint32_t my_stages = stages_base + uint32_t(warp) * STAGES * stage_bytes;
     float * partial = reinterpret_cast<float *>(smem + (stages_base - smem_base) + size_t(WARPS) * STAGES * stage_bytes);   // [tile][mat][warp][16]
+    // TMA: this warp's mbarriers, one per stage, after the table (kMaxTilesPerBlock tiles of nmat matrices)
+    const uint32_t bars = stages_base + uint32_t(WARPS) * STAGES * stage_bytes + uint32_t(kMaxTilesPerBlockDev * nmat * WARPS * kTileRows * 4) + uint32_t(warp) * STAGES * 8u;
 
     // Unit u of this warp is unit warp + u WARPS of the block: (tile * nmat + mat) = that / nchunks, chunk = that % nchunks. Going to the next unit adds
     // WARPS: a fixed step in the chunk index plus a carry.
@@ -179,7 +194,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     // rows, and the pieces of the missing ones are not copied (what those rows of the stage hold is computed on and dropped).
     uint32_t tab[kMaxPieces], piece_rows[2] = {0u, 0u};
     #pragma unroll
-    for (int k = 0; k < kMaxPieces; k++) {
+    for (int k = 0; k < (TMA ? 0 : kMaxPieces); k++) {
         const uint32_t j = uint32_t(lane) + 32u * k;
         const uint32_t row = (j * p.inv_upr) >> 16, col = j - row * uint32_t(p.upr);
         tab[k] = row < uint32_t(kTileRows) ? ((row * RB + col * 16u) << 13) | (row * stride + col * 16u) : 0xFFFFFFFFu;
@@ -191,7 +206,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         const uint8_t * base = (mat ? p.W2 : p.W) + (R0 + tile * kTileRows) * int64_t(RB) + uint32_t(f_chunk) * CB;      // the tile's first row, this chunk
         const uint32_t lo = uint32_t(reinterpret_cast<uintptr_t>(base));
         const uint32_t dst0 = my_stages + uint32_t(f_slot) * stage_bytes;
-        if (tile != ntiles - 1) {
+        if constexpr (TMA) {
+            if (lane == 0) {
+                const uint32_t halves = tile != ntiles - 1 ? 2u : uint32_t(last_rows + 8) / 8u;      // 8-row copies that hold rows of this block
+                const uint32_t bar = bars + 8u * uint32_t(f_slot);
+                mbar_arrive_expect_tx(bar, rounds * halves * (kSub / 2u));
+                const CUtensorMap * m = mat ? &mw2 : &mw;
+                const int x = f_chunk * int(CB / 2u), y = int(R0) + tile * kTileRows;
+                for (uint32_t r = 0; r < rounds; r++) {
+                    for (uint32_t hb = 0; hb < halves; hb++) {
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(dst0 + r * kSub + hb * (kSub / 2u)), "l"(m), "r"(x + int(r) * 72), "r"(y + int(hb) * 8), "r"(bar) : "memory");
+                    }
+                }
+            }
+        } else if (tile != ntiles - 1) {
             #pragma unroll
             for (int k = 0; k < kMaxPieces; k++) {
                 const uint32_t e = tab[k];
@@ -217,6 +246,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
     };
 
     int fetched = 0;
+    bool arrived = true;
+    if constexpr (TMA) {
+        if (lane == 0) {
+            for (int s2 = 0; s2 < STAGES; s2++) mbar_init(bars + 8u * s2, 1);
+            mbar_init_fence();
+        }
+        __syncwarp();
+    }
     // The first STAGES - 1 stages of weights are asked for at once: they do not depend on the kernel before this one, which may still be running (this
     // kernel is launched early, see launch.cuh). Only then wait for that kernel, and fetch the split input it (or one before it) wrote, as one more group.
     pdl_trigger();
@@ -305,7 +342,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         acc1 = 0.f;
     };
     for (int u = 0; u < my_units; u++) {
-        cp_async_wait<STAGES - 2>();      // stage u has landed (this lane's pieces) ...
+        if constexpr (TMA) {
+            if (arrived) arrived = mbar_wait(bars + 8u * uint32_t(u_slot), uint32_t(u / STAGES) & 1u);      // bounded; after a failure the rest runs on without waiting
+        } else {
+            cp_async_wait<STAGES - 2>();  // stage u has landed (this lane's pieces) ...
+        }
         __syncwarp();                     // ... and every lane's; also: every lane is done reading the slot refilled next
         if (fetched < my_units) { fetch(); fetched++; }
         cp_async_commit();
@@ -315,8 +356,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         const int last = nrows - 1 - tile * kTileRows;
         const uint32_t lo = ((nmat == 2 && (u_tm & 1)) ? w2_lo : w_lo) + uint32_t(tile * kTileRows) * RB + uint32_t(u_chunk) * CB;
         const uint32_t st = my_stages + uint32_t(u_slot) * stage_bytes;
-        const uint32_t row0 = st + row_lane0 + ((lo + uint32_t(min(g, last)) * RB) & 15u);
-        const uint32_t row1 = st + row_lane1 + ((lo + uint32_t(min(g + 8, last)) * RB) & 15u);
+        const uint32_t row0 = TMA ? st + uint32_t(g) * 144u : st + row_lane0 + ((lo + uint32_t(min(g, last)) * RB) & 15u);
+        const uint32_t row1 = TMA ? row0 + 8u * 144u : st + row_lane1 + ((lo + uint32_t(min(g + 8, last)) * RB) & 15u);
+        constexpr uint32_t kRound = TMA ? kSub : 144u;      // from one round's bytes of a row to the next round's
         uint32_t a0 = row0 + 4u * t, a1 = row1 + 4u * t, d0a = row0 + 18u * (t >> 1), d1a = row1 + 18u * (t >> 1);
         uint32_t ba = b_lane + uint32_t(u_chunk * p.cbk) * 128u, sa = s_lane + uint32_t(u_chunk * p.cbk) * 8u;
         int pr = 0;
@@ -330,7 +372,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
                 pair_step_k4<1>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
                 pair_step_k4<2>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
                 pair_step_k4<3>(a0, a1, h0, h1, ba, sa, suma, first, uint32_t(t >> 1), (t & 1) == 0, acc0, acc1);
-                a0 += 144; a1 += 144; h0a += 144; h1a += 144; ba += 1024; sa += 64; suma += 32;
+                a0 += kRound; a1 += kRound; h0a += kRound; h1a += kRound; ba += 1024; sa += 64; suma += 32;
             }
         } else {
             #pragma unroll 1
@@ -339,7 +381,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
                 pair_step<1>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
                 pair_step<2>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
                 pair_step<3>(a0, a1, d0a, d1a, ba, sa, first, acc0, acc1);
-                a0 += 144; a1 += 144; d0a += 144; d1a += 144; ba += 1024; sa += 64;
+                a0 += kRound; a1 += kRound; d0a += kRound; d1a += kRound; ba += 1024; sa += 64;
             }
             #pragma unroll 1
             for (; pr < npairs; pr++) {
@@ -353,6 +395,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
         if (++u_slot == STAGES) u_slot = 0;
     }
     cp_async_wait<0>();
+    if (TMA && !arrived && lane == 0 && p.error) *p.error = 4;
     if (my_units > 0) flush();
     __syncthreads();
     // the rows of this block: the warps' shares summed in warp order, then the epilogue
@@ -390,7 +433,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const GemvQ40Params
 }
 
 constexpr size_t kSmemLimit = 224 * 1024;
-constexpr int kMaxTilesPerBlock = 8;        // the table of per-warp sums holds this many 16-row tiles of two matrices
+constexpr int kMaxTilesPerBlock = kMaxTilesPerBlockDev;        // the table of per-warp sums holds this many 16-row tiles of two matrices
 constexpr size_t partial_bytes(int warps, int nmat) { return size_t(kMaxTilesPerBlock) * nmat * warps * kTileRows * sizeof(float); }
 
 struct Plan { int cbk, nchunks, stride, stages, warps; size_t smem; bool ok; };
@@ -398,7 +441,8 @@ struct Plan { int cbk, nchunks, stride, stages, warps; size_t smem; bool ok; };
 // Chunks of an even number of blocks that divides the row; the row stride in a stage is an odd multiple of 16 bytes so that the 8 rows of a fragment fall
 // on different banks.
 constexpr int kMaxStages = 6;
-Plan plan_for(int64_t cols, int nmat, bool k4) {      // k4: q4_K rows, chunks of whole 256-element super-blocks (8 or 16 blocks)
+// tma: stages of 16 rows x chunk with one mbarrier per stage and warp; chunks of 8 or 16 blocks, at most 4 stages.
+Plan plan_for(int64_t cols, int nmat, bool k4, bool tma = false) {      // k4: q4_K rows, chunks of whole 256-element super-blocks (8 or 16 blocks)
     Plan best{};
     const int nb = int(cols / 32);
     if (cols % (k4 ? 256 : 64) != 0 || nb < 2) return best;
@@ -406,47 +450,59 @@ Plan plan_for(int64_t cols, int nmat, bool k4) {      // k4: q4_K rows, chunks o
     int64_t best_score = -1;
     for (int warps : {16, 8}) {
         for (int cbk = 2; cbk <= std::min(nb, 16); cbk += 2) {
-            if (nb % cbk || (k4 && cbk % 8)) continue;
+            if (nb % cbk || ((k4 || tma) && cbk % 8)) continue;
             int stride = (cbk * kBlockBytes + 32 + 15) / 16 * 16;
             if (stride % 32 != 16) stride += 16;
             if ((cbk * kBlockBytes + 30) / 16 * kTileRows > kMaxPieces * 32 || kTileRows * stride >= (1 << 13)) continue;
             int stages = 0;
-            for (int st = kMaxStages; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps, nmat) <= kSmemLimit) { stages = st; break; }
+            const size_t stage = tma ? size_t(kTileRows) * cbk * kBlockBytes : size_t(kTileRows) * stride;
+            for (int st = tma ? 4 : kMaxStages; st >= 2; st--) {
+                if (fixed + size_t(warps) * st * stage + partial_bytes(warps, nmat) + (tma ? size_t(warps) * st * 8 : 0) <= kSmemLimit) { stages = st; break; }
+            }
             if (!stages) continue;
             // Measured on B200 (8B shapes, back-to-back launches over distinct matrices): the kernel is bound by instruction issue and shared-memory
             // bandwidth more than by the bytes in flight, so the longest chunk (fewest per-unit fixed costs) wins, then 16 warps over 8, then stages.
             const int64_t score = int64_t(cbk) * 1000 + (warps == 16 ? 100 : 0) + stages;
             if (score > best_score) {
                 best_score = score;
-                best = Plan{cbk, nb / cbk, stride, stages, warps, fixed + size_t(warps) * stages * kTileRows * stride + partial_bytes(warps, nmat), true};
+                best = Plan{cbk, nb / cbk, stride, stages, warps, fixed + size_t(warps) * stages * stage + partial_bytes(warps, nmat) + (tma ? size_t(warps) * stages * 8 : 0), true};
             }
         }
     }
     return best;
 }
 
-template <int WARPS, int STAGES, bool K4>
-cudaError_t launch_with(const GemvQ40Params & p, size_t smem, unsigned grid, cudaStream_t stream) {
+struct Maps { CUtensorMap w, w2; };
+
+template <int WARPS, int STAGES, bool K4, bool TMA>
+cudaError_t launch_with(const GemvQ40Params & p, const Maps & maps, size_t smem, unsigned grid, cudaStream_t stream) {
     static int configured_device = -1;      // the attribute is per function and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_device != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES, K4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
+        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES, K4, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
         if (e != cudaSuccess) return e;
         configured_device = dev;
     }
     static const bool early = [] { const char * e = getenv("DOOMS_PDL_GEMV"); return !(e && *e == '0'); }();
-    return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES, K4>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
+    return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES, K4, TMA>, dim3(grid), dim3(WARPS * 32), smem, stream, maps.w, maps.w2, p);
 }
 
 template <int WARPS, bool K4>
-cudaError_t launch_stages(const GemvQ40Params & p, const Plan & pl, unsigned grid, cudaStream_t stream) {
+cudaError_t launch_stages(const GemvQ40Params & p, const Maps & maps, bool tma, const Plan & pl, unsigned grid, cudaStream_t stream) {
+    if (tma) {
+        switch (pl.stages) {
+            case 4: return launch_with<WARPS, 4, K4, true>(p, maps, pl.smem, grid, stream);
+            case 3: return launch_with<WARPS, 3, K4, true>(p, maps, pl.smem, grid, stream);
+            default: return launch_with<WARPS, 2, K4, true>(p, maps, pl.smem, grid, stream);
+        }
+    }
     switch (pl.stages) {
-        case 6: return launch_with<WARPS, 6, K4>(p, pl.smem, grid, stream);
-        case 5: return launch_with<WARPS, 5, K4>(p, pl.smem, grid, stream);
-        case 4: return launch_with<WARPS, 4, K4>(p, pl.smem, grid, stream);
-        case 3: return launch_with<WARPS, 3, K4>(p, pl.smem, grid, stream);
-        default: return launch_with<WARPS, 2, K4>(p, pl.smem, grid, stream);
+        case 6: return launch_with<WARPS, 6, K4, false>(p, maps, pl.smem, grid, stream);
+        case 5: return launch_with<WARPS, 5, K4, false>(p, maps, pl.smem, grid, stream);
+        case 4: return launch_with<WARPS, 4, K4, false>(p, maps, pl.smem, grid, stream);
+        case 3: return launch_with<WARPS, 3, K4, false>(p, maps, pl.smem, grid, stream);
+        default: return launch_with<WARPS, 2, K4, false>(p, maps, pl.smem, grid, stream);
     }
 }
 
@@ -467,12 +523,23 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters) {
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error) {
     if (xq_out && (!out_counters || rows % 32 != 0)) return cudaErrorInvalidValue;
-    const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k);
+    // tensor copies when rows and chunks are whole 16-byte units (cols a multiple of 256) and the driver hands out the encoder; per-lane copies otherwise
+    static const bool tma_off = [] { const char * e = getenv("DOOMS_GEMV_TMA"); return e && *e == '0'; }();
+    Maps maps{};
+    bool tma = !tma_off && cols % 256 == 0 && rows < (int64_t(1) << 31) && plan_for(cols, W2 ? 2 : 1, q4_k, true).ok;
+    if (tma) {
+        const Plan tp = plan_for(cols, W2 ? 2 : 1, q4_k, true);
+        const int64_t rb = cols / 32 * kBlockBytes;
+        (void)tp;
+        tma = make_rows_map(reinterpret_cast<TensorMap *>(&maps.w), W, rows, rb, 8 * kBlockBytes, 8) == cudaSuccess &&
+              (!W2 || make_rows_map(reinterpret_cast<TensorMap *>(&maps.w2), W2, rows, rb, 8 * kBlockBytes, 8) == cudaSuccess);
+    }
+    const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k, tma);
     if (!pl.ok) return cudaErrorInvalidValue;
-    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, y, bias, rows, int(cols), flags,
-                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 0u, 0u};
+    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, error, y, bias, rows, int(cols), flags,
+                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u};
     if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
@@ -481,13 +548,15 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     // one block per SM; more (whole multiples) only when a block's share would exceed the table of kMaxTilesPerBlock tiles
     const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
     const int64_t waves = (rows + 148 * max_rows - 1) / (148 * max_rows);
-    const unsigned grid = unsigned(std::min<int64_t>(148 * waves, rows));
-    p.rows_q = int(rows / grid);
-    p.rows_r = int(rows % grid);
+    p.row_unit = tma ? 8 : 1;
+    const int64_t units = (rows + p.row_unit - 1) / p.row_unit;
+    const unsigned grid = unsigned(std::min<int64_t>(148 * waves, units));
+    p.rows_q = int(units / grid);
+    p.rows_r = int(units % grid);
     p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
     p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
-    if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, pl, grid, stream) : launch_stages<8, true>(p, pl, grid, stream);
-    return pl.warps == 16 ? launch_stages<16, false>(p, pl, grid, stream) : launch_stages<8, false>(p, pl, grid, stream);
+    if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, maps, tma, pl, grid, stream) : launch_stages<8, true>(p, maps, tma, pl, grid, stream);
+    return pl.warps == 16 ? launch_stages<16, false>(p, maps, tma, pl, grid, stream) : launch_stages<8, false>(p, maps, tma, pl, grid, stream);
 }
 
 }  // namespace cuda

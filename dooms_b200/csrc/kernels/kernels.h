@@ -108,7 +108,8 @@ bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols);
 // xq_out (optional, rows a multiple of 32, with out_counters = rows / 32 zeroed ints that are left zeroed): the output row is also written split, for a
 // following projection that takes it as xq; the block that completes a 32-row group of y splits it.
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr);
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr,
+                             int32_t * error = nullptr);   // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;
@@ -131,6 +132,9 @@ cudaError_t launch_allreduce_add(const PeerAllReduce & p, const float * partial,
 // A TMA descriptor of an f16 activation buffer [rows][cols] (cols a multiple of 64), opaque here so that this header needs no driver types.
 struct alignas(64) TensorMap { unsigned char bytes[128]; };
 cudaError_t make_activation_map(TensorMap * out, const void * base, int64_t rows, int64_t cols);
+// A matrix of `rows` rows of row_bytes bytes (a multiple of 16, 16-byte aligned base) as a 2-D tensor of 16-bit words, copied in boxes of box_rows rows x
+// box_bytes bytes (a multiple of 16, at most 512), no swizzle, rows past the end read as zeros.
+cudaError_t make_rows_map(TensorMap * out, const void * base, int64_t rows, int64_t row_bytes, int box_bytes, int box_rows);
 bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K);
 // Y[m][n] (+)= X[m] . W[n] (+ bias[n]) for M tokens; X is the f16 buffer behind xmap. With W2: silu(X . W[n]) * (X . W2[n]). Y (f32) and / or Y16 (f16)
 // receive the result. *error is set to 2 if a pipeline wait ran out.
