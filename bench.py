@@ -193,8 +193,8 @@ def gemv_roofline(spec, torch, lib, L, hbm_gbs: float, source: str) -> dict:
     achieved = per_launch / (us * 1e-6) / 1e9
     return {"bound": "hbm", "kernel": "gate_up GEMV " + L.DTYPE_NAMES[dt] + f" {F}x{E} x2", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
             "frac": achieved / hbm_gbs, "peak_source": source, "frac_of_nominal_8000": achieved / 8000.0,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape (ncu capture summarised under profiles/): 66 116 352 + 945 920
-            "traffic": 67062272 if (F, E, dt) == (14336, 4096, L.Q4_0) else None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape (ncu capture summarised under profiles/): 66 129 920 + 897 792
+            "traffic": 67027712 if (F, E, dt) == (14336, 4096, L.Q4_0) else None,
             "bytes_per_launch": per_launch, "us_per_launch": us, "launches_timed": reps * n_mats}
 
 
