@@ -398,8 +398,10 @@ DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const 
         ((flags & cuda::kFlagBias) && !d_bias) || (flags & ~(cuda::kFlagAccumulate | cuda::kFlagBias)) || (d_w2 && flags)) {
         return fail(DOOMS_INVALID_ARGUMENT, "matmul: NULL pointer, unknown flag, or rows that are not whole blocks and a multiple of 64 elements");
     }
+    // 512 tokens or more: room for the matrix (both, for gate/up) as f16 rows, so that it is dequantized once and both operands arrive by TMA
+    const size_t w16_bytes = tokens >= 512 && dtype != DOOMS_F16 ? size_t(rows) * size_t(cols) * 2 * (d_w2 ? 2 : 1) : 0;
     void * scratch = nullptr;
-    const Status ss = scratch_for(256, &scratch);
+    const Status ss = scratch_for(256 + w16_bytes, &scratch);
     if (!ss.is_ok()) return done(ss);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cuda::TensorMap map;
@@ -407,7 +409,8 @@ DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const 
     if (e != cudaSuccess) return launch_result(e, "matmul (tensor map)");
     e = cudaMemsetAsync(scratch, 0, 4, st);
     if (e == cudaSuccess) {
-        e = cuda::launch_gemm_tc(dtype, d_w, d_w2, &map, d_y, nullptr, d_bias, tokens, rows, cols, rows, 0, flags, static_cast<int32_t *>(scratch), st);
+        e = cuda::launch_gemm_tc(dtype, d_w, d_w2, &map, d_y, nullptr, d_bias, tokens, rows, cols, rows, 0, flags, static_cast<int32_t *>(scratch), st,
+                                 w16_bytes ? static_cast<uint8_t *>(scratch) + 256 : nullptr, w16_bytes);
     }
     return launch_result(e, "matmul");
 }

@@ -84,6 +84,8 @@ struct CudaLlamaDecoder::Impl {
     int gqa_splits = 1;
     double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
     int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
+    void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 512 tokens or more dequantize a matrix once per call
+    size_t w16_bytes = 0;
     int * split_counters = nullptr; // one per 32 rows of h: rows written by the gate/up GEMV's blocks (zero between launches)
     int32_t pos = 0;
     bool has_pending = false;
@@ -115,7 +117,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters, (void *)split_counters,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters, (void *)split_counters, w16,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -248,7 +250,7 @@ struct CudaLlamaDecoder::Impl {
                  int64_t out_stride, int64_t out16_stride, uint32_t flags) {
         run(kind, [&] {
             return cuda::launch_gemm_tc(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, &map, out, out16, bias, M, w.rows, w.cols, out_stride, out16_stride, flags,
-                                        host_error, stream);
+                                        host_error, stream, w16, w16_bytes);
         });
     }
     // x += partial sums of the other ranks' shares: with one GPU the projection accumulated into x directly.
@@ -745,6 +747,14 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         m.tc_capable = cuda::make_activation_map(&m.map_xn, m.xn16, int64_t(B), E) == cudaSuccess &&
                        cuda::make_activation_map(&m.map_attn, m.attn16, int64_t(B), m.q_width) == cudaSuccess &&
                        cuda::make_activation_map(&m.map_h, m.h16, int64_t(B), m.ff) == cudaSuccess;
+        size_t largest = 0;
+        for (const LayerDev & L : m.layers) {
+            for (const QkvPart & q : L.qkv) largest = std::max(largest, size_t(q.w.rows) * size_t(q.w.cols) * 2);
+            largest = std::max({largest, size_t(L.attn_output.rows) * size_t(L.attn_output.cols) * 2, size_t(L.ffn_down.rows) * size_t(L.ffn_down.cols) * 2,
+                                size_t(L.ffn_gate.rows) * size_t(L.ffn_gate.cols) * 4});
+        }
+        if (B >= 512 && largest > 0 && cudaMalloc(&m.w16, largest) == cudaSuccess) m.w16_bytes = largest;      // optional: without it the GEMM dequantizes per tile
+        else { (void)cudaGetLastError(); m.w16 = nullptr; }
         for (const LayerDev & L : m.layers) {
             for (const QkvPart & q : L.qkv) m.tc_capable = m.tc_capable && cuda::gemm_tc_supported(int(q.w.dt), q.w.ptr, q.w.rows, q.w.cols);
             for (const MatDev * w : {&L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down}) {

@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -172,6 +173,21 @@ __device__ __forceinline__ void dequant_q4_K_group(const uint32_t (&w)[36], uint
     }
 }
 
+// Whole rows to f16, the value every tile of the fused kernel would hold (half(Q::elem)): one thread per 32 elements.
+template <int DT>
+__global__ void __launch_bounds__(256) k_dequant_f16(const uint8_t * W, __half * out, int64_t rows, int cols) {
+    const int64_t units = rows * (cols / 32);
+    const int64_t RB = row_bytes_of(DT, cols);
+    for (int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += int64_t(gridDim.x) * blockDim.x) {
+        const int64_t r = u / (cols / 32);
+        const uint32_t k0 = uint32_t(u - r * (cols / 32)) * 32u;
+        uint4 v[4];
+        dequant32<DT>(W + r * RB, k0, v);
+        uint4 * dst = reinterpret_cast<uint4 *>(out + r * cols + k0);
+        dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; dst[3] = v[3];
+    }
+}
+
 struct GemmTcParams {
     const uint8_t * W;
     const uint8_t * W2;        // gate/up: the up matrix
@@ -188,8 +204,12 @@ struct GemmTcParams {
 };
 
 // Shared memory: [stage][W tile | W2 tile | X tile], then the mbarriers and the TMEM base address.
-template <int DT, bool GATE>
-__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const GemmTcParams p) {
+// PRE: the weights were dequantized to f16 rows beforehand (k_dequant_f16; the reference's dequant_half + matmul_big pair for large M,
+// llama_kernels.h:1474-1480, metal_llama_decoder.mm:31): their tiles arrive by TMA like the token tile (wmap / w2map), the producer warps only run the
+// epilogue, and the stage's single "full" barrier counts the bytes of all its tiles.
+template <int DT, bool GATE, bool PRE>
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                                                         const __grid_constant__ CUtensorMap w2map, const GemmTcParams p) {
     constexpr int NMAT = GATE ? 2 : 1;
     constexpr int STAGES = GATE ? 3 : 4;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -222,7 +242,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
     bool ok = true;
 
-    if (warp < kProducerWarps && (DT == kQ4_0 || DT == kQ4_K) && p.wide) {
+    if (PRE && warp < kProducerWarps) {
+        // nothing to produce: the weight tiles come by TMA
+    } else if (warp < kProducerWarps && (DT == kQ4_0 || DT == kQ4_K) && p.wide) {
         // ---- weight producers, q4_0 / q4_K rows of whole 256-element groups (144 bytes in both formats): the two threads of a row take the groups (four
         // k steps each) in turn (both threads on every step, half a tile row each, measured 22 % slower on q4_0). A group is
         // 144 consecutive bytes, fetched with nine 16-byte loads per matrix before anything is computed, so that the other thread's stores overlap this
@@ -311,8 +333,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 if (ks >= STAGES) ok = mbar_wait(empty + 8 * s, uint32_t(ks / STAGES - 1) & 1u);
                 if (!ok) break;
                 const uint32_t dst = smem0 + s * stage_bytes + NMAT * kTileWBytes;
-                mbar_arrive_expect_tx(full_x + 8 * s, tile_x_bytes);
+                mbar_arrive_expect_tx(full_x + 8 * s, tile_x_bytes + (PRE ? NMAT * kTileWBytes : 0u));
                 for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, ks * kStepK, m0 + part * 128, full_x + 8 * s);
+                if (PRE) {
+                    tma_load_2d(smem0 + s * stage_bytes, &wmap, ks * kStepK, int(n0), full_x + 8 * s);
+                    if (GATE) tma_load_2d(smem0 + s * stage_bytes + kTileWBytes, &w2map, ks * kStepK, int(n0), full_x + 8 * s);
+                }
             }
         } else if (lane == 1 && p.wide) {
             // ---- tracker: passes through every phase of the stages' "empty" barriers in order and publishes the number of steps consumed ----
@@ -328,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             for (int ks = 0; ks < ksteps && ok; ks++) {
                 const int s = ks % STAGES;
                 const uint32_t ph = uint32_t(ks / STAGES) & 1u;
-                ok = mbar_wait(full_x + 8 * s, ph) && mbar_wait(full_w + 8 * s, ph);
+                ok = mbar_wait(full_x + 8 * s, ph) && (PRE || mbar_wait(full_w + 8 * s, ph));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t wt = smem0 + s * stage_bytes, xt = wt + NMAT * kTileWBytes;
@@ -404,8 +430,8 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int DT>
-cudaError_t launch_dt(const CUtensorMap & map, const GemmTcParams & p, bool gate, cudaStream_t stream) {
+template <int DT, bool PRE>
+cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const CUtensorMap & w2map, const GemmTcParams & p, bool gate, cudaStream_t stream) {
     const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
     const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
     const dim3 grid(unsigned((p.N + kRowsW - 1) / kRowsW), unsigned((p.M + p.T - 1) / p.T));
@@ -413,14 +439,32 @@ cudaError_t launch_dt(const CUtensorMap & map, const GemmTcParams & p, bool gate
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured[gate] != dev) {
-        const cudaError_t e = gate ? cudaFuncSetAttribute(k_gemm_tc<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
-                                   : cudaFuncSetAttribute(k_gemm_tc<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        const cudaError_t e = gate ? cudaFuncSetAttribute(k_gemm_tc<DT, true, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
+                                   : cudaFuncSetAttribute(k_gemm_tc<DT, false, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return e;
         configured[gate] = dev;
     }
-    if (gate) k_gemm_tc<DT, true><<<grid, kThreads, smem, stream>>>(map, p);
-    else k_gemm_tc<DT, false><<<grid, kThreads, smem, stream>>>(map, p);
+    if (gate) k_gemm_tc<DT, true, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
+    else k_gemm_tc<DT, false, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
     return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t dequant_rows(const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream) {
+    const int64_t units = rows * (cols / 32);
+    k_dequant_f16<DT><<<unsigned(std::min<int64_t>((units + 255) / 256, 148 * 16)), 256, 0, stream>>>(static_cast<const uint8_t *>(W), static_cast<__half *>(out), rows, int(cols));
+    return cudaGetLastError();
+}
+cudaError_t dequant_rows_dt(int dt, const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream) {
+    switch (dt) {
+        case kF16: return dequant_rows<kF16>(W, out, rows, cols, stream);
+        case kQ4_0: return dequant_rows<kQ4_0>(W, out, rows, cols, stream);
+        case kQ5_0: return dequant_rows<kQ5_0>(W, out, rows, cols, stream);
+        case kQ8_0: return dequant_rows<kQ8_0>(W, out, rows, cols, stream);
+        case kQ4_K: return dequant_rows<kQ4_K>(W, out, rows, cols, stream);
+        case kQ6_K: return dequant_rows<kQ6_K>(W, out, rows, cols, stream);
+    }
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace
@@ -459,20 +503,38 @@ bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
 }
 
 cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
-                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream) {
+                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, void * w16_scratch, size_t w16_bytes) {
     if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
                    flags, M > 128 ? 256 : 128, 0, error};
     p.wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
+    // Many tokens: dequantize the matrix once to f16 rows and let TMA feed both operands (the reference does the same from 320 tokens on,
+    // metal_llama_decoder.mm:31); otherwise every token tile would redo the dequantization in its producer warps.
+    const size_t need = size_t(N) * size_t(K) * 2 * (gate ? 2 : 1);
+    static const int pre_from = [] { const char * e = getenv("DOOMS_GEMM_PRE_FROM"); return e ? atoi(e) : 512; }();
+    // Measured on the 8B shapes: q4_0 / q4_K gate/up is faster fused (875 against 836 TFLOP/s: no f16 copy to write and read), everything else is faster
+    // or much faster from f16 rows (ffn_down 961 against 925; q6_K 754 against 83).
+    if (w16_scratch && need <= w16_bytes && M >= pre_from && dt != kF16 && !(p.wide && gate)) {
+        __half * w16 = static_cast<__half *>(w16_scratch);
+        cudaError_t e = dequant_rows_dt(dt, W, w16, N, K, stream);
+        if (e == cudaSuccess && gate) e = dequant_rows_dt(dt, W2, w16 + size_t(N) * size_t(K), N, K, stream);
+        if (e != cudaSuccess) return e;
+        TensorMap wmap, w2map;
+        e = make_activation_map(&wmap, w16, N, K);
+        if (e == cudaSuccess) e = make_activation_map(&w2map, gate ? w16 + size_t(N) * size_t(K) : w16, N, K);
+        if (e != cudaSuccess) return e;
+        p.wide = 0;
+        return launch_dt<kF16, true>(map, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate, stream);
+    }
     switch (dt) {
-        case kF16: return launch_dt<kF16>(map, p, gate, stream);
-        case kQ4_0: return launch_dt<kQ4_0>(map, p, gate, stream);
-        case kQ5_0: return launch_dt<kQ5_0>(map, p, gate, stream);
-        case kQ8_0: return launch_dt<kQ8_0>(map, p, gate, stream);
-        case kQ4_K: return launch_dt<kQ4_K>(map, p, gate, stream);
-        case kQ6_K: return launch_dt<kQ6_K>(map, p, gate, stream);
+        case kF16: return launch_dt<kF16, false>(map, map, map, p, gate, stream);
+        case kQ4_0: return launch_dt<kQ4_0, false>(map, map, map, p, gate, stream);
+        case kQ5_0: return launch_dt<kQ5_0, false>(map, map, map, p, gate, stream);
+        case kQ8_0: return launch_dt<kQ8_0, false>(map, map, map, p, gate, stream);
+        case kQ4_K: return launch_dt<kQ4_K, false>(map, map, map, p, gate, stream);
+        case kQ6_K: return launch_dt<kQ6_K, false>(map, map, map, p, gate, stream);
     }
     return cudaErrorInvalidValue;
 }

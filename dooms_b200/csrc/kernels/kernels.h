@@ -138,8 +138,11 @@ cudaError_t make_rows_map(TensorMap * out, const void * base, int64_t rows, int6
 bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K);
 // Y[m][n] (+)= X[m] . W[n] (+ bias[n]) for M tokens; X is the f16 buffer behind xmap. With W2: silu(X . W[n]) * (X . W2[n]). Y (f32) and / or Y16 (f16)
 // receive the result. *error is set to 2 if a pipeline wait ran out.
+// w16_scratch (optional, w16_bytes): room for the matrix (both, for gate/up) as f16 rows; with it and 512 or more tokens the weights are dequantized once
+// per call and both operands arrive by TMA.
 cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
-                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream);
+                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream,
+                           void * w16_scratch = nullptr, size_t w16_bytes = 0);
 
 }  // namespace cuda
 }  // namespace dooms

@@ -228,3 +228,25 @@ def test_head_dim_128_prefill_and_decode(model_dir, qwen):
         assert rel_l2(dec.logits(), want) < BATCHED_TOL
         assert collect(dec, 8, 2) == want_tokens
         dec.close()
+
+
+@pytest.mark.parametrize("plan", ["q4_0", "Q4_K_M-like mix"])
+def test_chunks_of_512_tokens_and_more_take_the_pre_dequantized_gemm(model_dir, plan):
+    """A 700-token prompt in one chunk: from 512 tokens on the decoder dequantizes each matrix once per call and the GEMM reads both operands by TMA. Same
+    bounds as the other long prompts: within 3e-3 of the checker with the reference's operand rounding, tokens equal, then a decode step."""
+    path = write(model_dir, "exact_" + plan.replace(" ", "_"), synth.tiny_spec(QUANT_PLANS[plan], random_blocks=True), 11)
+    dec = CudaLlamaDecoder.load(path, 720, 704)
+    prompt = [(i * 7 + 3) % 50 for i in range(700)]
+    o = ob.OracleDecoder(path, 720)
+    want = o.eval_tokens(prompt)
+    rounded = ob.OracleDecoder(path, 720, round_operands=True).eval_tokens(prompt)
+    dec.eval_tokens(prompt)
+    got = dec.logits()
+    assert rel_l2(got, rounded) < BATCHED_TOL
+    assert rel_l2(got, want) < 2 * BATCHED_TOL
+    assert dec.pending_token() == ob.argmax(want)
+    nxt = ob.argmax(want)
+    want = o.eval_tokens([nxt])
+    dec.eval_tokens([nxt])
+    assert rel_l2(dec.logits(), want) < 2 * BATCHED_TOL
+    dec.close()
