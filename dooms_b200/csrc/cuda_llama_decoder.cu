@@ -571,6 +571,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.vocab_row0 = int32_t(share.value().vocab_row0);
     m.vocab_rows = int32_t(share.value().vocab_rows);
 
+    if (opt.operand_bf16) return unsupported("bf16 prefill operands are not built: the tensor-core tiles hold f16 operands, the reference's rounding");
     if (cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking) != cudaSuccess) return internal_error(cuda_msg("cudaStreamCreate", cudaGetLastError()));
     cudaEventCreate(&m.ev_a);
     cudaEventCreate(&m.ev_b);

@@ -50,7 +50,7 @@ struct CudaOptions {
     int32_t tp_rank = 0, tp_size = 1;        // tensor parallelism: q/k/v/gate/up split by output rows, attn_output/ffn_down by input columns
     const void * nccl_unique_id = nullptr;   // 128 bytes shared by the ranks of the group (tp_size > 1)
     const char * nccl_library = nullptr;
-    bool operand_bf16 = false;               // tensor-core prefill operands: f16 (the reference's rounding) or bf16
+    bool operand_bf16 = false;               // reserved: bf16 tensor-core operands; true is refused with Unsupported (the tiles hold f16, the reference's rounding)
     bool use_graphs = true;                  // decode steps replay a captured CUDA graph
 };
 

@@ -86,7 +86,7 @@ typedef struct dooms_cuda_options {
     int32_t tp_size;
     const void * nccl_unique_id;   /* tp_size > 1: the 128-byte ncclUniqueId every rank of the group passes (rank 0 makes it with dooms_cuda_nccl_unique_id) */
     const char * nccl_library;     /* path of libnccl.so.2 to load; NULL: the dynamic loader's search path */
-    int32_t operand_bf16;    /* prefill tensor-core operands: 0 = f16 (the reference's rounding, llama_kernels.h:197), 1 = bf16 */
+    int32_t operand_bf16;    /* prefill tensor-core operands: 0 = f16 (the reference's rounding, llama_kernels.h:197); 1 (bf16) is refused: DOOMS_UNSUPPORTED */
     int32_t use_graphs;      /* 1: decode steps replay a CUDA graph; 0: plain launches */
 } dooms_cuda_options;
 

@@ -250,3 +250,12 @@ def test_chunks_of_512_tokens_and_more_take_the_pre_dequantized_gemm(model_dir, 
     dec.eval_tokens([nxt])
     assert rel_l2(dec.logits(), want) < 2 * BATCHED_TOL
     dec.close()
+
+
+def test_bf16_operands_are_refused(model_dir):
+    """The option exists in the options struct; the tiles hold f16 operands only, so asking for bf16 is Unsupported rather than silently ignored."""
+    path = write(model_dir, "tiny_f16", tiny_f16(), 1)
+    with pytest.raises(DoomsError) as e:
+        CudaLlamaDecoder.load(path, 64, 32, operand_bf16=True)
+    assert e.value.code == L.UNSUPPORTED
+
