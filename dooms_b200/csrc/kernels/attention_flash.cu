@@ -16,7 +16,7 @@ using namespace dooms::dev;
 
 namespace {
 
-constexpr int kQ = 64, kK = 64, kWarps = 4;
+constexpr int kQ = 128, kK = 64, kWarps = 8;      // 16 queries per warp
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -41,7 +41,8 @@ __global__ void __launch_bounds__(kWarps * 32) k_attention_flash(const float * q
     __half * Qs = reinterpret_cast<__half *>(smem);                    // [kQ][LD]
     __half * KVs = Qs + kQ * LD;                                       // [2 stages][K | V][kK][LD]
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
-    const int h = blockIdx.x, t0 = blockIdx.y * kQ, p0 = st->pos;
+    // the last query tiles see the most keys: they go first, so that the short ones fill the tail
+    const int h = blockIdx.x, t0 = int(gridDim.y - 1 - blockIdx.y) * kQ, p0 = st->pos;
     const int kvh = h / (p.n_head / p.n_head_kv);
     const int last_key = p0 + min(t0 + kQ, M) - 1;
     const int ntiles = last_key / kK + 1;
