@@ -261,6 +261,10 @@ struct CudaLlamaDecoder::Impl {
             run("all_reduce", [&] { return cuda::launch_allreduce_add(par, red, x, int(n), stream); });
             return;
         }
+        if (M == 1 && (tp & (tp - 1)) == 0) {      // the projection already wrote x / tp + its share into x
+            all_reduce(x, n);
+            return;
+        }
         all_reduce(red, n);
         run("residual", [&] { return cuda::launch_add(x, red, int64_t(n), stream); });
     }
@@ -331,8 +335,13 @@ struct CudaLlamaDecoder::Impl {
         for (size_t l = 0; l < layers.size(); l++) {
             const LayerDev & L = layers[l];
             __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
-            float * o_dst = single ? x : red;
-            const uint32_t o_flags = single ? kFlagAccumulate : 0u;
+            // Tensor-parallel decode steps with a power-of-two group: the projection leaves x / tp + its share of the product in x, and the in-place all-reduce
+            // of x is the residual add (no buffer for the partial sums, no add kernel). Chunks and other group sizes reduce a separate buffer and add it.
+            const bool share = !single && M == 1 && !use_par && (tp & (tp - 1)) == 0;
+            uint32_t log2_tp = 0;
+            while ((1 << log2_tp) < tp) log2_tp++;
+            float * o_dst = (single || share) ? x : red;
+            const uint32_t o_flags = single ? kFlagAccumulate : share ? (kFlagAccumulate | (log2_tp << cuda::kFlagShareShift)) : 0u;
             const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
             if (M > 1) norm(x, L.attn_norm, M, false, use_tc);
             if (M == 1) {

@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
         }
         const int64_t rr = R0 + r;
         if (p.flags & kFlagBias) s += p.bias[rr];
-        p.y[rr] = (p.flags & kFlagAccumulate) ? p.y[rr] + s : s;
+        p.y[rr] = (p.flags & kFlagAccumulate) ? accumulate_base(p.y[rr], p.flags) + s : s;
     }
 }
 

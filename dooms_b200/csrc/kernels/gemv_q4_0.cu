@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
         }
         const int64_t row = R0 + r;
         if (p.flags & kFlagBias) s += p.bias[row];
-        p.y[row] = (p.flags & kFlagAccumulate) ? p.y[row] + s : s;
+        p.y[row] = (p.flags & kFlagAccumulate) ? accumulate_base(p.y[row], p.flags) + s : s;
     }
     if (p.xq_out) {
         __threadfence();              // this block's rows are visible before they are counted

@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kMvWarps * 32) k_matvec(const uint8_t * W, con
     acc = warp_sum(acc);
     if (lane == 0) {
         if (flags & kFlagBias) acc += bias[r];
-        y[r] = (flags & kFlagAccumulate) ? y[r] + acc : acc;
+        y[r] = (flags & kFlagAccumulate) ? accumulate_base(y[r], flags) + acc : acc;
     }
 }
 

@@ -17,6 +17,17 @@ struct DevState {
 };
 
 enum : uint32_t { kFlagAccumulate = 2, kFlagBias = 4 };   // the reference's MatvecParams / GemmParams flags (metal_llama_decoder.mm:51)
+// One-token projections only, with kFlagAccumulate: bits 8..11 = k > 0 scale the old value by 2^-k first, y = y 2^-k + W x. With 2^k tensor-parallel ranks
+// an in-place all-reduce of y then gives y + the sum of the ranks' products on every rank (the scaling by a power of two is exact), without an add kernel.
+constexpr uint32_t kFlagShareShift = 8;
+__host__ __device__ inline float accumulate_base(float y, uint32_t flags) {
+    const uint32_t k = (flags >> kFlagShareShift) & 15u;
+#ifdef __CUDA_ARCH__
+    return k ? y * __uint_as_float((127u - k) << 23) : y;
+#else
+    return k ? y / float(1u << k) : y;
+#endif
+}
 
 cudaError_t launch_set_state(DevState * st, int32_t pos, int32_t tok_in, int32_t tok_out, cudaStream_t stream);
 
