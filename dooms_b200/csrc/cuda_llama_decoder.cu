@@ -187,16 +187,28 @@ struct CudaLlamaDecoder::Impl {
             xq_of = in;
         }
     }
-    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags) {
+    // What the streaming GEMV of a matrix (pair) reads first, for the kernel launched before it to bring into L2 (kernels/l2_prefetch.cuh): the decode
+    // step is a chain of short dependent kernels, and without this device memory idles across every kernel boundary.
+    int64_t pf_budget = 16 << 20, pf_attn_budget = 32 << 20;      // bytes asked for ahead of a projection / ahead of gate/up during the attention kernel
+    cuda::L2Prefetch hint_for(const MatDev & w, const MatDev * w2, int64_t budget) const {
+        if (budget <= 0 || !w.ptr) return cuda::L2Prefetch{};
+        if (fast(w) && (!w2 || fast(*w2))) return cuda::gemv_q4_0_prefetch(w.ptr, w2 ? w2->ptr : nullptr, w.rows, w.cols, w.dt == DType::Q4_K, budget);
+        if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, x, w.rows, w.cols) && (!w2 || cuda::gemv_blocks_supported(int(w2->dt), w2->ptr, x, w2->rows, w2->cols))) {
+            return cuda::gemv_blocks_prefetch(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, w.rows, w.cols, budget);
+        }
+        return cuda::L2Prefetch{};
+    }
+    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags,
+                const cuda::L2Prefetch * next = nullptr) {
         if (fast(w)) {
             prepare_fast_input(in, gamma, w.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
             run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream, nullptr, nullptr,
-                                                               host_error); });
+                                                               host_error, next); });
             return;
         }
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
-            run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
+            run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream, next); });
             return;
         }
         if (gamma) { norm(in, gamma, 1, false); in = xn; }
@@ -211,7 +223,8 @@ struct CudaLlamaDecoder::Impl {
         });
         xq_of = do_split ? xn : nullptr;
     }
-    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split) {
+    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split,
+                 const cuda::L2Prefetch * next = nullptr) {
         if (fast(wg) && fast(wu)) {
             prepare_fast_input(in, gamma, wg.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
@@ -220,13 +233,13 @@ struct CudaLlamaDecoder::Impl {
             const bool split_out = down_takes_split && wg.rows % 32 == 0 && split_counters;
             run("gate_up", [&] {
                 return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
-                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error);
+                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error, next);
             });
             xq_of = split_out ? out : nullptr;
             return;
         }
         if (cuda::gemv_blocks_supported(int(wg.dt), wg.ptr, in, wg.rows, wg.cols) && cuda::gemv_blocks_supported(int(wu.dt), wu.ptr, in, wu.rows, wu.cols)) {
-            run("gate_up", [&] { return cuda::launch_gemv_blocks(int(wg.dt), wg.ptr, wu.ptr, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream); });
+            run("gate_up", [&] { return cuda::launch_gemv_blocks(int(wg.dt), wg.ptr, wu.ptr, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream, next); });
             return;
         }
         if (gamma) { norm(in, gamma, 1, false); in = xn; }
@@ -345,13 +358,26 @@ struct CudaLlamaDecoder::Impl {
             const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
             if (M > 1) norm(x, L.attn_norm, M, false, use_tc);
             if (M == 1) {
+                // every kernel of the step brings the head of what the next one streams into L2: the layer's key / value rows and attn_output while qkv
+                // runs, gate / up while the attention kernel runs (it moves few bytes itself), ffn_down during gate / up, the next layer's qkv during ffn_down
+                cuda::L2Prefetch after_qkv = hint_for(L.attn_output, nullptr, pf_budget);
+                if (pf_budget > 0 && gqa) {
+                    after_qkv.lin[0] = reinterpret_cast<const uint8_t *>(kcl);
+                    after_qkv.lin[1] = reinterpret_cast<const uint8_t *>(vcl);
+                    after_qkv.lin_bytes_per_pos = uint32_t(kv_width) * 2u;
+                    after_qkv.pos = &state->pos;
+                }
+                const cuda::L2Prefetch after_attn = hint_for(L.ffn_gate, &L.ffn_up, pf_attn_budget);
+                const cuda::L2Prefetch after_gate_up = hint_for(L.ffn_down, nullptr, pf_budget);
+                const cuda::L2Prefetch after_down = l + 1 < layers.size() ? hint_for(layers[l + 1].qkv[0].w, nullptr, pf_budget) : hint_for(output, nullptr, pf_budget);
                 for (const QkvPart & q : L.qkv) {
-                    matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
+                    matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u,
+                           &q == &L.qkv.back() ? &after_qkv : nullptr);
                 }
                 const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
                 if (gqa) {
                     run("attention", [&] {
-                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream);
+                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream, &after_attn);
                     });
                 } else {
                     run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, 1, as, stream); });
@@ -361,8 +387,8 @@ struct CudaLlamaDecoder::Impl {
                 matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags);
                 xq_of = nullptr;
                 reduce_into_x(1);
-                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down));
-                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags);
+                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down), &after_gate_up);
+                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags, &after_down);
                 reduce_into_x(1);
             } else if (use_tc) {
                 // (the chunk's norm above wrote xn16)
@@ -579,6 +605,9 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.vocab_stride = int32_t((V + tp - 1) / tp);
     m.vocab_row0 = int32_t(share.value().vocab_row0);
     m.vocab_rows = int32_t(share.value().vocab_rows);
+    // tuning knobs for measurements: megabytes brought into L2 ahead of a projection / ahead of gate / up (0: off)
+    if (const char * e = getenv("DOOMS_L2_PREFETCH_MB")) m.pf_budget = int64_t(std::max(0, atoi(e))) << 20;
+    if (const char * e = getenv("DOOMS_L2_PREFETCH_ATTN_MB")) m.pf_attn_budget = int64_t(std::max(0, atoi(e))) << 20;
 
     if (opt.operand_bf16) return unsupported("bf16 prefill operands are not built: the tensor-core tiles hold f16 operands, the reference's rounding");
     if (cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking) != cudaSuccess) return internal_error(cuda_msg("cudaStreamCreate", cudaGetLastError()));

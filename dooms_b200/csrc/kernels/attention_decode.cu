@@ -10,6 +10,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "l2_prefetch.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "xsplit.cuh"
@@ -39,6 +40,7 @@ struct AttnDecodeParams {
     int * counters;
     float * out;
     uint8_t * xq;
+    L2Prefetch next;          // what the kernels after this one read first (l2_prefetch.cuh); all null: nothing
 };
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
@@ -64,6 +66,7 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
 
     pdl_trigger();
     pdl_wait();
+    if (threadIdx.x == kThreads - 1) l2_prefetch_issue(p.next, int(blockIdx.y * gridDim.x + blockIdx.x), int(gridDim.x * gridDim.y));
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int G = p.s.n_head / p.s.n_head_kv;
@@ -308,14 +311,8 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
 template <int D, int GP>
 cudaError_t launch_one(const AttnDecodeParams & p, cudaStream_t stream) {
     constexpr size_t smem = ((GP * D + GP * kTileKeys + GP) * 4 + 127) / 128 * 128 + size_t(kStages) * kTileKeys * (D * 4 + 16);
-    static int configured_device = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_device != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_attention_decode<D, GP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
-        configured_device = dev;
-    }
+    static std::atomic<uint64_t> configured{0};
+    if (const cudaError_t e = allow_dynamic_smem(k_attention_decode<D, GP>, int(smem), configured); e != cudaSuccess) return e;
     return launch_pdl(k_attention_decode<D, GP>, dim3(p.s.n_head_kv, p.splits), dim3(kThreads), smem, stream, p);
 }
 
@@ -335,15 +332,15 @@ bool attention_gqa_supported(const AttnShape & s) {
 
 int attention_gqa_splits(int n_head_kv, int n_ctx) {
     // about one block per SM, and no more ranges than the context has tiles
-    const int want = std::max(1, (148 + n_head_kv - 1) / n_head_kv);
+    const int want = std::max(1, (sm_count() + n_head_kv - 1) / n_head_kv);
     return std::max(1, std::min(want, (n_ctx + kTileKeys - 1) / kTileKeys));
 }
 
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
-                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream) {
+                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream, const L2Prefetch * next) {
     if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1) || (counters && !out) || (xq && !counters)) return cudaErrorInvalidValue;
     const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
-                             static_cast<uint8_t *>(xq)};
+                             static_cast<uint8_t *>(xq), next ? *next : L2Prefetch{}};
     return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
 }
 

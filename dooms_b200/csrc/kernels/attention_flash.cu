@@ -7,6 +7,7 @@
 #include <math_constants.h>
 
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace dooms {
@@ -181,14 +182,8 @@ template <int D>
 cudaError_t launch_d(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M, const AttnShape & s,
                      cudaStream_t stream) {
     const size_t smem = size_t(kQ + 4 * kK) * (D + 8) * 2;
-    static int configured = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_attention_flash<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
-        configured = dev;
-    }
+    static std::atomic<uint64_t> configured{0};
+    if (const cudaError_t e = allow_dynamic_smem(k_attention_flash<D>, int(smem), configured); e != cudaSuccess) return e;
     const dim3 grid(s.n_head, (M + kQ - 1) / kQ);
     k_attention_flash<D><<<grid, kWarps * 32, smem, stream>>>(qkv, static_cast<const __half *>(kc), static_cast<const __half *>(vc), out,
                                                               static_cast<__half *>(out16), st, M, s);

@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 #include "quant.cuh"
 
@@ -435,15 +436,9 @@ cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const C
     const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
     const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
     const dim3 grid(unsigned((p.N + kRowsW - 1) / kRowsW), unsigned((p.M + p.T - 1) / p.T));
-    static int configured[2] = {-1, -1};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured[gate] != dev) {
-        const cudaError_t e = gate ? cudaFuncSetAttribute(k_gemm_tc<DT, true, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
-                                   : cudaFuncSetAttribute(k_gemm_tc<DT, false, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        if (e != cudaSuccess) return e;
-        configured[gate] = dev;
-    }
+    static std::atomic<uint64_t> configured[2];
+    if (const cudaError_t e = gate ? allow_dynamic_smem(k_gemm_tc<DT, true, PRE>, 220 * 1024, configured[1])
+                                   : allow_dynamic_smem(k_gemm_tc<DT, false, PRE>, 220 * 1024, configured[0]); e != cudaSuccess) return e;
     if (gate) k_gemm_tc<DT, true, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
     else k_gemm_tc<DT, false, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
     return cudaGetLastError();
@@ -452,7 +447,7 @@ cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const C
 template <int DT>
 cudaError_t dequant_rows(const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream) {
     const int64_t units = rows * (cols / 32);
-    k_dequant_f16<DT><<<unsigned(std::min<int64_t>((units + 255) / 256, 148 * 16)), 256, 0, stream>>>(static_cast<const uint8_t *>(W), static_cast<__half *>(out), rows, int(cols));
+    k_dequant_f16<DT><<<unsigned(std::min<int64_t>((units + 255) / 256, sm_count() * 16)), 256, 0, stream>>>(static_cast<const uint8_t *>(W), static_cast<__half *>(out), rows, int(cols));
     return cudaGetLastError();
 }
 cudaError_t dequant_rows_dt(int dt, const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream) {

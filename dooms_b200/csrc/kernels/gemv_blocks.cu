@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "l2_prefetch.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "quant.cuh"
@@ -51,6 +52,7 @@ struct GemvBlocksParams {
     int stride, upr;        // bytes between the rows of a stage; 16-byte pieces copied per row
     int rows_q, rows_r;     // block b has rows_q + (b < rows_r) rows starting at b rows_q + min(b, rows_r)
     uint32_t inv_upr, inv_nchunks;
+    L2Prefetch next;        // what the kernel after this one reads first (l2_prefetch.cuh); all null: nothing
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
@@ -140,6 +142,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
+    if (threadIdx.x == WARPS * 32 - 1) l2_prefetch_issue(p.next, int(blockIdx.x), int(gridDim.x));
     for (uint32_t i = threadIdx.x; i < uint32_t(p.cols) / 4u; i += WARPS * 32) cp_async16(smem_base + i * 16u, p.x + size_t(i) * 4);
     cp_async_commit();
     cp_async_wait<0>();
@@ -248,15 +251,17 @@ Plan plan_for(int BE, int BB, int64_t cols, int nmat) {
 
 template <int DT, int WARPS, int STAGES>
 cudaError_t launch_with(const GemvBlocksParams & p, size_t smem, unsigned grid, cudaStream_t stream) {
-    static int configured_device = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_device != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_gemv_blocks<DT, WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
-        if (e != cudaSuccess) return e;
-        configured_device = dev;
-    }
+    static std::atomic<uint64_t> configured{0};
+    if (const cudaError_t e = allow_dynamic_smem(k_gemv_blocks<DT, WARPS, STAGES>, int(kSmemLimit), configured); e != cudaSuccess) return e;
     return launch_pdl(k_gemv_blocks<DT, WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, stream, p);
+}
+
+// One block per SM; more (whole multiples) only when a block's share would exceed the table of kMaxTilesPerBlock tiles.
+unsigned grid_for(int64_t rows) {
+    const int sms = sm_count();
+    const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
+    const int64_t waves = (rows + sms * max_rows - 1) / (sms * max_rows);
+    return unsigned(std::min<int64_t>(sms * waves, rows));
 }
 
 template <int DT>
@@ -264,9 +269,7 @@ cudaError_t launch_dt(GemvBlocksParams p, int64_t rows, cudaStream_t stream) {
     const Plan pl = plan_for(Fmt<DT>::BE, Fmt<DT>::BB, p.cols, p.W2 ? 2 : 1);
     if (!pl.ok) return cudaErrorInvalidValue;
     p.cbk = pl.cbk; p.nchunks = pl.nchunks; p.stride = pl.stride; p.upr = pl.upr;
-    const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
-    const int64_t waves = (rows + 148 * max_rows - 1) / (148 * max_rows);
-    const unsigned grid = unsigned(std::min<int64_t>(148 * waves, rows));
+    const unsigned grid = grid_for(rows);
     p.rows_q = int(rows / grid);
     p.rows_r = int(rows % grid);
     p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
@@ -302,9 +305,25 @@ bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows,
     return plan_for(fmt_be(dt), fmt_bb(dt), cols, 2).ok;
 }
 
+L2Prefetch gemv_blocks_prefetch(int dt, const void * W, const void * W2, int64_t rows, int64_t cols, int64_t budget_bytes) {
+    L2Prefetch h{};
+    if (budget_bytes <= 0 || !W || fmt_bb(dt) == 0) return h;
+    const int grid = int(grid_for(rows));
+    const int64_t row_bytes = cols / fmt_be(dt) * fmt_bb(dt);
+    const int64_t per_block = budget_bytes / (int64_t(grid) * (W2 ? 2 : 1));
+    h.mat[0] = static_cast<const uint8_t *>(W);
+    h.mat[1] = static_cast<const uint8_t *>(W2);
+    h.row_bytes = uint32_t(row_bytes);
+    h.rows_q = int(rows / grid); h.rows_r = int(rows % grid); h.row_unit = 1; h.grid = grid;
+    h.head_rows = int32_t(std::min<int64_t>(std::max<int64_t>(per_block / row_bytes, 1), int64_t(h.rows_q) + 1));
+    h.rows = rows;
+    return h;
+}
+
 cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
-    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, gamma, eps, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u};
+                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream, const L2Prefetch * next) {
+    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, gamma, eps, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u,
+                       next ? *next : L2Prefetch{}};
     switch (dt) {
         case kF16: return launch_dt<kF16>(p, rows, stream);
         case kQ4_0: return launch_dt<kQ4_0>(p, rows, stream);

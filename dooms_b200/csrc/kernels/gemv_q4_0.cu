@@ -24,6 +24,7 @@
 #include "ptx.cuh"
 #include "launch.cuh"
 #include "xsplit.cuh"
+#include "l2_prefetch.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -61,6 +62,7 @@ struct GemvQ40Params {
     int rows_q, rows_r;     // units / grid and units % grid: block b has rows_q + (b < rows_r) units of row_unit rows starting at unit b rows_q + min(b, rows_r)
     int row_unit;
     uint32_t inv_upr, inv_nchunks;   // 65536 / d + 1: (j * inv) >> 16 = j / d for the small j divided here
+    L2Prefetch next;        // what the kernel after this one reads first (l2_prefetch.cuh); all null: nothing
 };
 
 // x[K] (f32) -> xq. One warp per 32-element block.
@@ -264,6 +266,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
+    if (threadIdx.x == WARPS * 32 - 1) l2_prefetch_issue(p.next, int(blockIdx.x), int(gridDim.x));
     if (p.xq) {
         for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
         cp_async_commit();
@@ -474,16 +477,28 @@ Plan plan_for(int64_t cols, int nmat, bool k4, bool tma = false) {      // k4: q
 
 struct Maps { CUtensorMap w, w2; };
 
+// How a launch deals the rows to its blocks: one block per SM; more (whole multiples) only when a block's share would exceed the table of
+// kMaxTilesPerBlock tiles. Rows go in units of 8 with tensor copies, else singly.
+struct RowSplit { int grid, rows_q, rows_r, row_unit; };
+RowSplit row_split(int64_t rows, bool tma) {
+    const int sms = sm_count();
+    const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
+    const int64_t waves = (rows + sms * max_rows - 1) / (sms * max_rows);
+    const int row_unit = tma ? 8 : 1;
+    const int64_t units = (rows + row_unit - 1) / row_unit;
+    const int grid = int(std::min<int64_t>(sms * waves, units));
+    return RowSplit{grid, int(units / grid), int(units % grid), row_unit};
+}
+
+bool takes_tma(int64_t rows, int64_t cols, int nmat, bool q4_k) {
+    static const bool tma_off = [] { const char * e = getenv("DOOMS_GEMV_TMA"); return e && *e == '0'; }();
+    return !tma_off && cols % 256 == 0 && rows < (int64_t(1) << 31) && plan_for(cols, nmat, q4_k, true).ok;
+}
+
 template <int WARPS, int STAGES, bool K4, bool TMA>
 cudaError_t launch_with(const GemvQ40Params & p, const Maps & maps, size_t smem, unsigned grid, cudaStream_t stream) {
-    static int configured_device = -1;      // the attribute is per function and device
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_device != dev) {
-        const cudaError_t e = cudaFuncSetAttribute(k_gemv_q4_0<WARPS, STAGES, K4, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit));
-        if (e != cudaSuccess) return e;
-        configured_device = dev;
-    }
+    static std::atomic<uint64_t> configured{0};
+    if (const cudaError_t e = allow_dynamic_smem(k_gemv_q4_0<WARPS, STAGES, K4, TMA>, int(kSmemLimit), configured); e != cudaSuccess) return e;
     static const bool early = [] { const char * e = getenv("DOOMS_PDL_GEMV"); return !(e && *e == '0'); }();
     return launch_pdl_if(early, k_gemv_q4_0<WARPS, STAGES, K4, TMA>, dim3(grid), dim3(WARPS * 32), smem, stream, maps.w, maps.w2, p);
 }
@@ -515,6 +530,21 @@ bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols) {
     return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 2, true).ok;
 }
 
+L2Prefetch gemv_q4_0_prefetch(const void * W, const void * W2, int64_t rows, int64_t cols, bool q4_k, int64_t budget_bytes) {
+    L2Prefetch h{};
+    if (budget_bytes <= 0 || !W) return h;
+    const RowSplit rs = row_split(rows, takes_tma(rows, cols, W2 ? 2 : 1, q4_k));
+    const int64_t row_bytes = cols / 32 * kBlockBytes;
+    const int64_t per_block = budget_bytes / (int64_t(rs.grid) * (W2 ? 2 : 1));
+    h.mat[0] = static_cast<const uint8_t *>(W);
+    h.mat[1] = static_cast<const uint8_t *>(W2);
+    h.row_bytes = uint32_t(row_bytes);
+    h.rows_q = rs.rows_q; h.rows_r = rs.rows_r; h.row_unit = rs.row_unit; h.grid = rs.grid;
+    h.head_rows = int32_t(std::min<int64_t>(std::max<int64_t>(per_block / row_bytes, 1), int64_t(rs.rows_q + 1) * rs.row_unit));
+    h.rows = rows;
+    return h;
+}
+
 size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }      // the kernel adds 4 bytes per block of its own in shared memory
 
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
@@ -523,12 +553,12 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error) {
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error,
+                             const L2Prefetch * next) {
     if (xq_out && (!out_counters || rows % 32 != 0)) return cudaErrorInvalidValue;
     // tensor copies when rows and chunks are whole 16-byte units (cols a multiple of 256) and the driver hands out the encoder; per-lane copies otherwise
-    static const bool tma_off = [] { const char * e = getenv("DOOMS_GEMV_TMA"); return e && *e == '0'; }();
     Maps maps{};
-    bool tma = !tma_off && cols % 256 == 0 && rows < (int64_t(1) << 31) && plan_for(cols, W2 ? 2 : 1, q4_k, true).ok;
+    bool tma = takes_tma(rows, cols, W2 ? 2 : 1, q4_k);
     if (tma) {
         const Plan tp = plan_for(cols, W2 ? 2 : 1, q4_k, true);
         const int64_t rb = cols / 32 * kBlockBytes;
@@ -539,20 +569,18 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k, tma);
     if (!pl.ok) return cudaErrorInvalidValue;
     GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, error, y, bias, rows, int(cols), flags,
-                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u};
+                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u, L2Prefetch{}};
     if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
     const int chunk_bytes = pl.cbk * kBlockBytes;
     p.upr = (row_bytes % 16 == 0 && chunk_bytes % 16 == 0) ? chunk_bytes / 16 : (chunk_bytes + 30) / 16;
-    // one block per SM; more (whole multiples) only when a block's share would exceed the table of kMaxTilesPerBlock tiles
-    const int64_t max_rows = int64_t(kMaxTilesPerBlock) * kTileRows;
-    const int64_t waves = (rows + 148 * max_rows - 1) / (148 * max_rows);
-    p.row_unit = tma ? 8 : 1;
-    const int64_t units = (rows + p.row_unit - 1) / p.row_unit;
-    const unsigned grid = unsigned(std::min<int64_t>(148 * waves, units));
-    p.rows_q = int(units / grid);
-    p.rows_r = int(units % grid);
+    const RowSplit rs = row_split(rows, tma);
+    const unsigned grid = unsigned(rs.grid);
+    p.row_unit = rs.row_unit;
+    p.rows_q = rs.rows_q;
+    p.rows_r = rs.rows_r;
+    if (next) p.next = *next;
     p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
     p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
     if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, maps, tma, pl, grid, stream) : launch_stages<8, true>(p, maps, tma, pl, grid, stream);

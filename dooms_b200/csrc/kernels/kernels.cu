@@ -489,13 +489,13 @@ cudaError_t launch_matmul_tile(int dt, const void * W, const void * W2, const fl
 
 cudaError_t launch_dequantize(int dt, const void * blocks, int64_t rows, int64_t cols, float * out, cudaStream_t stream) {
     const int64_t total = rows * cols;
-    const unsigned grid = unsigned(std::min<int64_t>((total + 255) / 256, 148 * 16));
+    const unsigned grid = unsigned(std::min<int64_t>((total + 255) / 256, sm_count() * 16));
     const bool ok = dispatch_mat(dt, [&]<int DT>() { k_dequantize<DT><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(blocks), out, rows, int(cols)); });
     return ok ? cudaGetLastError() : cudaErrorInvalidValue;
 }
 
 cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream) {
-    k_add<<<unsigned(std::min<int64_t>((n + 255) / 256, 148 * 8)), 256, 0, stream>>>(x, y, n);
+    k_add<<<unsigned(std::min<int64_t>((n + 255) / 256, sm_count() * 8)), 256, 0, stream>>>(x, y, n);
     return cudaGetLastError();
 }
 
@@ -506,8 +506,8 @@ cudaError_t launch_rope_store(float * qkv, void * kc, void * vc, const DevState 
 }
 
 int attention_splits(int n_head, int n_ctx) {
-    // enough blocks to fill 148 SMs a few times over, ranges of at least 64 positions once the context is long
-    const int want = std::max(1, (148 * 2 + n_head - 1) / n_head);
+    // enough blocks to fill the SMs a few times over, ranges of at least 64 positions once the context is long
+    const int want = std::max(1, (sm_count() * 2 + n_head - 1) / n_head);
     return std::max(1, std::min(want, (n_ctx + 63) / 64));
 }
 

@@ -5,6 +5,8 @@
 // before it can finish itself, waiting for the immediate predecessor orders a kernel after everything earlier in the stream.
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <cstdint>
 #include <cstdlib>
 
 namespace dooms {
@@ -14,6 +16,33 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 }  // namespace dev
 
 namespace cuda {
+
+// Multiprocessors of the current device, asked once per device (the launchers size their grids by it).
+inline int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int slot = dev & 63;
+    int n = cached[slot].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) { cudaGetLastError(); n = 148; }
+        cached[slot].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device. The attribute belongs to (function, device); `done` is one word per kernel instantiation
+// (a function-local static at the call site) with a bit per device, so threads that drive different devices never undo each other's work.
+template <class K>
+cudaError_t allow_dynamic_smem(K kernel, int bytes, std::atomic<uint64_t> & done) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = uint64_t(1) << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
+}
 
 // Early launches are OFF unless DOOMS_PDL=1 is in the environment: measured on B200 they slow an 8B-shape decode step down (5.8 ms against 4.0 ms per
 // token; the waiting blocks of the next kernels sit on the SMs the 200 KB GEMV blocks need). Without the launch attribute the kernels' waits return at

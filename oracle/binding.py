@@ -21,7 +21,21 @@ REF_SO = HERE / "_ref" / "libref_gguf.so"
 _GGML_TO_DTYPE = {v: k for k, v in L.GGML_TYPE_ID.items()}
 
 
-def build(ref_root: str = "/root/reference") -> None:
+REF_DECODER_SO = HERE / "_ref" / "libref_decoder.so"
+
+
+def reference_checkout() -> str:
+    """Where the reference's sources lie: $DOOMS_REFERENCE_DIR, else a `reference` directory beside this repository; "" when neither exists."""
+    import os
+    for cand in (os.environ.get("DOOMS_REFERENCE_DIR"), str(HERE.parent.parent / "reference")):
+        if cand and (Path(cand) / "src" / "format").is_dir():
+            return cand
+    return ""
+
+
+def build(ref_root: str | None = None) -> None:
+    """Builds the checker; with the reference's sources at hand also oracle/_ref (the reference's own reader and its own CPU decoder class)."""
+    ref_root = reference_checkout() if ref_root is None else ref_root
     subprocess.run(["make", "-C", str(HERE), "all", f"REF={ref_root}"], check=True, capture_output=True)
 
 
@@ -178,6 +192,110 @@ class OracleDecoder:
     def embedding(self, token: int) -> np.ndarray:
         out = np.empty(self.cfg.n_embd, dtype=np.float32)
         oracle().oracle_embedding(self._h, token, out.ctypes.data)
+        return out
+
+
+# ---- the reference's own CPU decoder class (oracle/_ref/libref_decoder.so), when it was built ----
+_ref_decoder = None
+
+
+def reference_decoder_lib():
+    global _ref_decoder
+    if _ref_decoder is None and REF_DECODER_SO.exists():
+        r = C.CDLL(str(REF_DECODER_SO))
+        r.ref_decoder_new.restype = C.c_void_p
+        r.ref_decoder_new.argtypes = [C.c_int32] * 7 + [C.c_float, C.c_int32, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]
+        r.ref_decoder_add_layer.argtypes = [C.c_void_p] * 9
+        for name in ("ref_decoder_seal", "ref_decoder_reset", "ref_decoder_free"):
+            getattr(r, name).argtypes = [C.c_void_p]
+        r.ref_decoder_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        r.ref_decoder_embedding.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
+        _ref_decoder = r
+    return _ref_decoder
+
+
+class ReferenceDecoder:
+    """The reference test's own `Reference` class (tests/unit/test_metal_llama_decoder.cpp:110-192, compiled from the reference's file) over a GGUF model.
+    The class takes f16 matrices: quantized tensors are handed over as the f16 values of their dequantization (by this checker's block formulas, which are
+    pinned against gguf-py), exactly what the reference's quantized tests do with ggml's to_float (:226-254); `exact` says whether that conversion lost
+    nothing (true for f16 files and for blocks with power-of-two scales)."""
+
+    def __init__(self, path: str):
+        lib = reference_decoder_lib()
+        if lib is None:
+            raise RuntimeError("oracle/_ref/libref_decoder.so is not built (needs the reference's sources: make -C oracle ref REF=...)")
+        self._lib = lib
+        cfg, w, keep = model_structs(path, 8)
+        self.cfg = cfg
+        self.exact = True
+        self._keep = []
+
+        def matrix(ref) -> np.ndarray:
+            n = ref.rows * ref.cols
+            nbytes = n // L.BLOCK_ELEMS[ref.dtype] * L.BLOCK_BYTES[ref.dtype]
+            raw = np.ctypeslib.as_array(C.cast(ref.data, C.POINTER(C.c_uint8)), shape=(nbytes,))
+            f32 = dequantize(ref.dtype, raw, n)
+            f16 = f32.astype(np.float16)
+            if not np.array_equal(f16.astype(np.float32), f32):
+                self.exact = False
+            self._keep.append(f16)
+            return f16
+
+        def vector(ref) -> np.ndarray:
+            raw = np.ctypeslib.as_array(C.cast(ref.data, C.POINTER(C.c_uint8)), shape=(ref.cols * (4 if ref.dtype == L.F32 else 2),))
+            v = np.ascontiguousarray(dequantize(ref.dtype, raw, ref.cols), dtype=np.float32)
+            self._keep.append(v)
+            return v
+
+        embd, out, on = matrix(w.token_embd), matrix(w.output), vector(w.output_norm)
+        self._h = lib.ref_decoder_new(cfg.n_layer, cfg.n_embd, cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.n_ff, cfg.n_vocab, cfg.rope_base, cfg.rope_neox, cfg.rms_eps,
+                                      embd.ctypes.data, out.ctypes.data, on.ctypes.data)
+        for l in range(cfg.n_layer):
+            lw = w.layers[l]
+            qkv = matrix(lw.attn_qkv) if lw.attn_qkv.data else np.concatenate([matrix(lw.attn_q), matrix(lw.attn_k), matrix(lw.attn_v)])
+            bias = None
+            if lw.attn_qkv_bias.data:
+                bias = vector(lw.attn_qkv_bias)
+            elif lw.attn_q_bias.data:
+                bias = np.concatenate([vector(lw.attn_q_bias), vector(lw.attn_k_bias), vector(lw.attn_v_bias)])
+            self._keep += [qkv, bias]
+            an, fn = vector(lw.attn_norm), vector(lw.ffn_norm)
+            wo, gate, up, down = matrix(lw.attn_output), matrix(lw.ffn_gate), matrix(lw.ffn_up), matrix(lw.ffn_down)
+            lib.ref_decoder_add_layer(self._h, an.ctypes.data, fn.ctypes.data, bias.ctypes.data if bias is not None else None, qkv.ctypes.data, wo.ctypes.data,
+                                      gate.ctypes.data, up.ctypes.data, down.ctypes.data)
+        lib.ref_decoder_seal(self._h)
+        del keep
+
+    def close(self):
+        if self._h:
+            self._lib.ref_decoder_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def reset(self):
+        self._lib.ref_decoder_reset(self._h)
+
+    def embedding(self, token: int) -> np.ndarray:
+        out = np.empty(self.cfg.n_embd, dtype=np.float64)
+        self._lib.ref_decoder_embedding(self._h, int(token), out.ctypes.data)
+        return out
+
+    def step(self, x: np.ndarray) -> np.ndarray:
+        """One position given as n_embd input values; the logits (Reference::step)."""
+        x = np.ascontiguousarray(x, dtype=np.float64)
+        out = np.empty(self.cfg.n_vocab, dtype=np.float64)
+        self._lib.ref_decoder_step(self._h, x.ctypes.data, out.ctypes.data)
+        return out
+
+    def eval_tokens(self, tokens) -> np.ndarray:
+        out = None
+        for t in tokens:
+            out = self.step(self.embedding(int(t)))
         return out
 
 

@@ -9,10 +9,15 @@
  *     rotary pairs, keys and values rounded to f16 into the cache, grouped-query softmax attention, SwiGLU, residuals, final norm, lm_head);
  *   - the first-index argmax of llama_kernels.h:949-975 / src/core/argmax.h:15-53 (NaN never wins).
  *
- * Pinning: the reference checks in no golden files for this path (its tests compute the expectation live). The dequantization here is pinned against
- * gguf-py's dequantize (the file format's own Python package) and against byte patterns worked out by hand from the formulas; the decoder math is pinned
- * against an independent numpy restatement on the reference's tiny test shapes (tests/golden). At the boundary to llama.cpp, which the reference links
- * but does not vendor, parity is unpinned.
+ * Pinning: the reference checks in no golden files for this path (its tests compute the expectation live), so the checker is held to the reference's own
+ * code and to independent implementations instead:
+ *   - the decoder math against the reference's `Reference` class itself, compiled from the reference's test file (oracle/Makefile target `ref`,
+ *     oracle/ref_decoder_shim.cpp): logits position by position to 1e-12 and the greedy tokens, on the reference test's f16 shapes and on quantized
+ *     models whose values are exact in f16 (tests/test_oracle.py);
+ *   - the dequantization bit for bit against gguf-py's dequantize (the file format's own Python package), against byte patterns worked out by hand from
+ *     the formulas, and against committed vectors (tests/golden);
+ *   - the argmax and the block tables against the reference's own functions compiled from its sources (oracle/_ref/libref_gguf.so).
+ * At the boundary to llama.cpp, which the reference links but does not vendor, parity stays unpinned.
  *
  * Build: see oracle/Makefile (gcc, -ffp-contract=off so that the f32 block formulas round exactly as written).
  */

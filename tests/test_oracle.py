@@ -145,3 +145,42 @@ def test_oracle_refuses_overflow_and_bad_tokens(model_dir):
         o.eval_tokens([50])
     o.eval_tokens([1] * 8)
     assert o.position() == 8
+
+
+# ---- the reference's own CPU decoder class, compiled from the reference's test file (oracle/_ref/libref_decoder.so) ----
+REFERENCE_CASES = {
+    # make_tiny's variants (tests/unit/test_metal_llama_decoder.cpp:57-82): llama and qwen2 blocks, head_dim 16 and 64
+    "llama_f16": lambda: tiny_f16(), "qwen_f16": lambda: tiny_f16(qwen=True), "llama_f16_hd64": lambda: tiny_f16(head_dim=64), "qwen_f16_hd64": lambda: tiny_f16(qwen=True, head_dim=64),
+    # random blocks with power-of-two scales, every value exact in f16 (random_quant, :226-254), each format alone and the Q4_K_M-like plan (:390)
+    **{name: (lambda plan=plan: synth.tiny_spec(plan, random_blocks=True)) for name, plan in QUANT_PLANS.items()},
+}
+
+
+@pytest.mark.parametrize("name", sorted(REFERENCE_CASES))
+def test_checker_matches_the_reference_class(model_dir, name):
+    """oracle.c against `Reference` (tests/unit/test_metal_llama_decoder.cpp:110-192) itself, built from the reference's source: the prompt's logits position by
+    position and eight free-running greedy tokens, as the reference's own tests drive it (:322-350). Both compute in double; they differ only in the order
+    of the sums."""
+    if ob.reference_decoder_lib() is None:
+        pytest.skip("oracle/_ref/libref_decoder.so is not built (the reference's sources are needed to build it)")
+    path = write(model_dir, "refclass_" + name.replace(" ", "_"), REFERENCE_CASES[name](), 23)
+    ref = ob.ReferenceDecoder(path)
+    assert ref.exact, "the model's weights are not exactly representable in f16: Reference would see other weights than the checker"
+    o = ob.OracleDecoder(path, 64)
+    for t in K_PROMPT:
+        want = ref.eval_tokens([t])
+        got = o.eval_tokens([t])
+        assert rel_l2(got, want) < 1e-12
+    tok_ref, tok_o = [], []
+    for _ in range(8):
+        t = int(np.argmax(want))          # the reference test's argmax (std::max_element: first maximum)
+        assert ob.argmax(got) == t
+        tok_ref.append(t)
+        want, got = ref.eval_tokens([t]), o.eval_tokens([t])
+        assert rel_l2(got, want) < 1e-12
+    # the whole prompt in one call is the same computation in the checker
+    o2 = ob.OracleDecoder(path, 64)
+    ref.reset()
+    assert rel_l2(o2.eval_tokens(K_PROMPT), ref.eval_tokens(K_PROMPT)) < 1e-12
+    # embeddings: Reference::embedding and the checker's row lookup agree exactly
+    assert np.array_equal(ref.embedding(7), o.embedding(7).astype(np.float64))
