@@ -4,6 +4,10 @@ bandwidth, and the CPU restatement of the same decoder timed beside it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config I]
 
+--config 0..3 are the batch-1 configurations (default 2, the one the metric is quoted on); --config 4 is the many-sequence serving load on the config-0
+model (256 seeded sequences, batched decode steps per GPU, sequences dealt over the N GPUs with no collective: "scaling": "weak" is not claimed, the
+total work is fixed).
+
 One step = the reference's own measurement (bench/bench_llm.cpp:97-119): reset, the whole prompt in one eval_tokens call, then `gen` greedy tokens with
 generate(gen + 1, depth); end of generation is ignored. The model is synthetic: the configuration's architecture with seeded N(0, 0.02) weights quantized
 like `llama-quantize --pure`, written as a GGUF file and loaded through the loader, prompt = seeded uniform token ids.
@@ -35,6 +39,20 @@ WORKLOAD_NAMES = {0: "qwen2.5-0.5b-arch q4_0, 512-token prompt + 128 greedy toke
                   1: "qwen2.5-0.5b-arch q4_k_m-style mix, 512-token prompt + 128 greedy tokens, batch 1",
                   2: "llama-3-8b-arch q4_0, 2048-token prompt + 256 greedy tokens, batch 1",
                   3: "qwen2.5-32b-arch q4_k_m-style mix, 8192-token prompt + 256 greedy tokens, batch 1"}
+
+
+def config_dict(config: int, world: int, depth: int, matrix_bytes: int) -> dict:
+    """The workload description both arms print, key for key."""
+    return {"workload": WORKLOAD_NAMES[config], "parallelism": f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
+            f"{matrix_bytes / 1e9:.2f} GB of weights, {matrix_bytes / 126e6:.0f}x the 126 MB L2", "queue_depth": depth}
+
+
+def host_threads() -> int:
+    """Cores this process may run on (a launcher can pin its workers; os.cpu_count() would overstate)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def peaks():
@@ -107,6 +125,7 @@ def time_cpu_port(path: str, spec, n_prompt: int, n_decode: int, repeats: int) -
     """Decode tok/s of the CPU restatement (f32, all host cores) on the same file: a bounded sample of the workload."""
     from oracle import binding as ob
     from dooms_b200 import synth
+    cores = ob.set_threads(host_threads())      # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers
     o = ob.OracleDecoder(path, n_prompt + n_decode * (repeats + 1) + 4, fast=True)
     prompt = synth.prompt_tokens(n_prompt, spec.n_vocab, 2000)
     logits = o.eval_tokens(prompt)
@@ -119,22 +138,23 @@ def time_cpu_port(path: str, spec, n_prompt: int, n_decode: int, repeats: int) -
             tok = ob.argmax(logits)
             logits = o.eval_tokens([tok])
         times.append((time.perf_counter() - t0) / n_decode)
-    cores = os.cpu_count() or 1
     sample = f"{n_decode} greedy decode steps x {repeats} after a {n_prompt}-token prompt on the same GGUF file, p50 per token"
     return 1.0 / statistics.median(times), cores, sample
 
 
 def run_reference_arm(args, rank, world, dist):
     """--impl reference: the reference's llama.cpp-linked CPU path cannot be built here (its sources are fetched at configure time and are not on disk), so
-    the arm times the CPU restatement of the reference decoder's math (oracle/, kind "port") on the same file, all host threads, bounded sample per step."""
+    the arm times the CPU restatement of the reference decoder's math (oracle/, kind "port": f32 quantized dot products with the offsets folded out, all
+    host threads) on the same file: per step a bounded sample of the workload's decode phase. Under torch.distributed.run rank 0 alone does the work."""
     if rank != 0:
         return
     config = args.config
     path, spec = model_file(config, 0, 1, None)
-    n_decode = 2 if config >= 2 else 8
+    n_decode = 4 if config >= 2 else 16
     steps, warmup = args.steps, args.warmup
     from oracle import binding as ob
     from dooms_b200 import synth
+    cores = ob.set_threads(host_threads())      # the launcher exports OMP_NUM_THREADS=1 to its workers; the baseline is meant to use the whole host
     o = ob.OracleDecoder(path, 8 + (steps + warmup + 1) * n_decode, fast=True)
     logits = o.eval_tokens(synth.prompt_tokens(8, spec.n_vocab, 2000 + config))
     per_step = []
@@ -146,22 +166,24 @@ def run_reference_arm(args, rank, world, dist):
             per_step.append(time.perf_counter() - t0)
     total = sum(per_step)
     value = n_decode * steps / total
-    cores = os.cpu_count() or 1
+    matrix_bytes = spec.matrix_bytes()
     sample = f"{n_decode} greedy decode steps per step after an 8-token prompt on the same GGUF file"
     line = {"impl": "reference", "metric": "decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
             "ms_per_step": 1e3 * total / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD_NAMES[config]},
-            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "config": config_dict(config, args.gpus, args.depth, matrix_bytes),
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample,
+                             "weight_gbs": matrix_bytes * value / 1e9},
             "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference's own CPU path links llama.cpp, which is not vendored and cannot be built offline; this is the CPU restatement of its decoder"}
     print(json.dumps(line), flush=True)
 
 
-def gemv_roofline(spec, torch, lib, L, hbm_gbs: float, source: str) -> dict:
-    """The dominant decode kernel (the fused gate/up GEMV, ~58% of the bytes a token reads) on the model's real shape, timed with CUDA events over launches
-    that walk distinct matrices (so nothing is served from L2). achieved = matrix bytes per launch / average launch time."""
+def gemv_roofline(spec, torch, lib, L, hbm_gbs: float, source: str, world: int = 1) -> dict:
+    """The dominant decode kernel (the fused gate/up GEMV, ~58% of the bytes a token reads) on the shape a rank runs (the model's, or its 1 / world row
+    share under tensor parallelism), timed with CUDA events over launches that walk distinct matrices (so nothing is served from L2).
+    achieved = matrix bytes per launch / average launch time."""
     from dooms_b200.quantize import quantize
-    F, E = spec.n_ff, spec.n_embd
+    F, E = spec.n_ff // world, spec.n_embd
     dt = spec.plan("ffn_gate", 0)
     row_bytes = E // L.BLOCK_ELEMS[dt] * L.BLOCK_BYTES[dt]
     per_launch = 2 * F * row_bytes
@@ -194,8 +216,62 @@ def gemv_roofline(spec, torch, lib, L, hbm_gbs: float, source: str) -> dict:
     return {"bound": "hbm", "kernel": "gate_up GEMV " + L.DTYPE_NAMES[dt] + f" {F}x{E} x2", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
             "frac": achieved / hbm_gbs, "peak_source": source, "frac_of_nominal_8000": achieved / 8000.0,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape (ncu capture summarised under profiles/): 66 129 920 + 897 792
-            "traffic": 67027712 if (F, E, dt) == (14336, 4096, L.Q4_0) else None,
+            "traffic": 67027712 if (F, E, dt) == (14336, 4096, L.Q4_0) else None, "rows_per_rank": F,
             "bytes_per_launch": per_launch, "us_per_launch": us, "launches_timed": reps * n_mats}
+
+
+def gemm_roofline(spec, torch, lib, L, pk: dict, n_tokens: int, world: int = 1) -> dict:
+    """The dominant prefill kernel (the fused gate/up GEMM on the tcgen05 tensor cores) on the shape a rank runs, timed with CUDA events.
+    achieved = 2 * tokens * rows * cols * 2 matrices / average launch time."""
+    from dooms_b200.quantize import quantize
+    F, E = spec.n_ff // world, spec.n_embd
+    dt = spec.plan("ffn_gate", 0)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    g = quantize(dt, torch.randn(F, E, device="cuda", generator=gen) * 0.02)
+    u = quantize(dt, torch.randn(F, E, device="cuda", generator=gen) * 0.02)
+    x = torch.randn(n_tokens, E, device="cuda", generator=gen).half()
+    y = torch.empty(n_tokens, F, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        L.check(lib.dooms_cuda_matmul(dt, g.data_ptr(), u.data_ptr(), x.data_ptr(), y.data_ptr(), None, n_tokens, F, E, 0, stream))
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    a.record()
+    for _ in range(reps):
+        launch()
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / reps
+    flops = 2.0 * n_tokens * F * E * 2
+    achieved = flops / (us * 1e-6) / 1e12
+    return {"bound": "tensor", "kernel": "gate_up GEMM " + L.DTYPE_NAMES[dt] + f" {n_tokens}x{F}x{E} x2 (tcgen05, weights dequantized in the kernel)",
+            "achieved": achieved, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops"], "peak_source": pk["source"] + " burst",
+            "frac_of_sustained": achieved / pk["bf16_tflops_sustained"], "frac_of_nominal_2250": achieved / 2250.0, "traffic": None,
+            "flops_per_launch": flops, "us_per_launch": us, "launches_timed": reps, "rows_per_rank": F}
+
+
+def tp_check(path: str, prompt, n_gen: int, n_batch: int, tokens_tp: list[int], logits_tp, local: int) -> dict:
+    """With N > 1, outside the timed region: rank 0 runs the same file on one GPU and compares the prompt's last-row logits and every greedy token of the
+    tensor-parallel run with it."""
+    from dooms_b200 import CudaLlamaDecoder
+    one = CudaLlamaDecoder.load(path, len(prompt) + n_gen + 16, n_batch, device=local)
+    one.eval_tokens(prompt)
+    want = one.logits().astype(np.float64)
+    got = np.asarray(logits_tp, dtype=np.float64)
+    toks: list[int] = []
+    one.generate(n_gen + 1, 4, lambda t: toks.append(t) or True)
+    one.close()
+    n_equal = 0
+    for a, b in zip(toks, tokens_tp):
+        if a != b:
+            break
+        n_equal += 1
+    return {"logits_rel_l2": float(np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum())), "logits_max_abs": float(np.abs(got - want).max()),
+            "greedy_tokens_equal": toks == list(tokens_tp), "n_tokens": len(toks), "first_difference": None if toks == list(tokens_tp) else n_equal}
 
 
 def main():
@@ -279,9 +355,17 @@ def main():
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     sum_prefill_ms, sum_decode_ms, sum_wall = [float(v) for v in stats.cpu()]
+    logits_tp = None
+    if world > 1:      # one more pass outside the timed region, for the comparison with one GPU below
+        dec.reset()
+        dec.eval_tokens(prompt)
+        logits_tp = dec.logits()
+        tokens.clear()
+        dec.generate(n_gen + 1, args.depth, lambda t: tokens.append(t) or True)
     dec.close()      # every rank at the same point: tearing down the tensor-parallel group is collective
     if rank != 0:
         if world > 1:
+            dist.barrier()       # rank 0 compares with a one-GPU decoder meanwhile
             dist.destroy_process_group()
         return
 
@@ -296,33 +380,39 @@ def main():
     step_bytes = matrix_bytes + kv_bytes_per_pos * avg_pos
     linear_flops = 2.0 * n_prompt * sum(r * c for name, kind, l, r, c in spec.matrices() if kind not in ("token_embd", "output"))
     attn_flops = 4.0 * spec.n_head * spec.head_dim * n_prompt * (n_prompt + 1) / 2 * spec.n_layer
-    roof = gemv_roofline(spec, torch, lib, L, pk["hbm_gbs"], pk["source"])
+    roof = gemv_roofline(spec, torch, lib, L, pk["hbm_gbs"], pk["source"], world)
+    roof_tensor = gemm_roofline(spec, torch, lib, L, pk, min(n_prompt, n_batch), world)
+    prefill_tflops = (linear_flops + attn_flops) / (sum_prefill_ms / K * 1e-3) / 1e12      # the whole group's
     line = {
         "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": 1e3 * t_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": WORKLOAD_NAMES[config], "parallelism": f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
-                   f"{matrix_bytes / 1e9:.2f} GB of weights, 33x the 126 MB L2", "queue_depth": args.depth},
+        "config": config_dict(config, world, args.depth, matrix_bytes),
         "prefill_tok_s": prefill_tok_s, "prefill_ms": sum_prefill_ms / K, "decode_ms_per_token": sum_decode_ms / K / n_gen,
-        "prefill_tflops": (linear_flops + attn_flops) / (sum_prefill_ms / K * 1e-3) / 1e12,
-        "prefill_frac_of_bf16_sustained": (linear_flops + attn_flops) / (sum_prefill_ms / K * 1e-3) / 1e12 / pk["bf16_tflops_sustained"],
+        "prefill_tflops": prefill_tflops, "prefill_tflops_per_gpu": prefill_tflops / world,
+        "prefill_frac_of_bf16_sustained": prefill_tflops / world / pk["bf16_tflops_sustained"],
+        "prefill_frac_of_bf16_burst": prefill_tflops / world / pk["bf16_tflops"],
         "decode_step_gbs": step_bytes / (sum_decode_ms / K / n_gen * 1e-3) / 1e9,
         "decode_step_frac_of_hbm": step_bytes / world / (sum_decode_ms / K / n_gen * 1e-3) / 1e9 / pk["hbm_gbs"],
         "e2e": {"value": e2e_decode_tok_s, "unit": "tok/s", "h2d_bytes_per_step": int(n_prompt * 4), "d2h_bytes_per_step": int((n_gen + 1) * 4),
                 "wall_ms_per_step": 1e3 * sum_wall / K},
         "gpu_launches": int(launches),
         "roofline": roof,
+        "roofline_tensor": roof_tensor,
         "clocks": clocks,
         "tokens_tail": tokens[-4:],
     }
     if not args.no_cpu_baseline and world == 1:
-        n_dec = 2 if config >= 2 else 8
+        n_dec = 8 if config >= 2 else 32
         v, cores, sample = time_cpu_port(path, spec, 8, n_dec, 3)
-        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample, "weight_gbs": matrix_bytes * v / 1e9}
     else:
         line["cpu_baseline"] = None
+    if world > 1:
+        line["tp_check"] = tp_check(path, prompt, n_gen, n_batch, list(tokens), logits_tp, local)
     print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

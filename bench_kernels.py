@@ -1,8 +1,8 @@
-"""One kernel on one small case, through the C ABI: a correctness check plus CUDA-event timing, sized for a profiler capture.
+"""Measurement harness beside bench.py: one kernel on one small case, through the C ABI: a correctness check plus CUDA-event timing, sized for a profiler capture.
 
-    python -m dooms_b200.kernel_case gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
-    python -m dooms_b200.kernel_case gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
-    python -m dooms_b200.kernel_case launches <ncu csv>                                     per-kernel totals and shares of an ncu launch list
+    python bench_kernels.py gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
+    python bench_kernels.py gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
+    python bench_kernels.py launches <ncu csv>                                     per-kernel totals and shares of an ncu launch list
 
 The GEMV case walks over several distinct matrices so that every launch reads its weights from device memory, not from L2.
 """
@@ -11,12 +11,15 @@ import collections
 import csv
 import re
 import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 
 def _gemv(args):
     import torch
-    from . import _lib as L
-    from .quantize import quantize
+    from dooms_b200 import _lib as L
+    from dooms_b200.quantize import quantize
     lib = L.lib()
     gen = torch.Generator(device='cuda').manual_seed(1)
     dt = L.DTYPE_NAMES.index(args.dtype)
@@ -61,8 +64,8 @@ def _gemv(args):
 
 def _gemm(args):
     import torch
-    from . import _lib as L
-    from .quantize import quantize
+    from dooms_b200 import _lib as L
+    from dooms_b200.quantize import quantize
     lib = L.lib()
     gen = torch.Generator(device='cuda').manual_seed(1)
     dt = L.DTYPE_NAMES.index(args.dtype)

@@ -13,6 +13,7 @@
 
 #include "kernels/kernels.h"
 #include "nccl_dyn.h"
+#include "validate.h"
 
 namespace dooms {
 
@@ -83,6 +84,7 @@ struct CudaLlamaDecoder::Impl {
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
     int gqa_splits = 1;
     double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
+    void * rope_cs = nullptr;      // head_dim / 2 (cos, sin) pairs of the current decode step's position
     int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
     void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 512 tokens or more dequantize a matrix once per call
     size_t w16_bytes = 0;
@@ -117,7 +119,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, (void *)attn_counters, (void *)split_counters, w16,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, rope_cs, (void *)attn_counters, (void *)split_counters, w16,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -136,7 +138,13 @@ struct CudaLlamaDecoder::Impl {
         if (!failed.is_ok()) return failed;
         DOOMS_RETURN_IF_ERROR(check(cudaStreamSynchronize(stream), "a CUDA kernel of the decoder failed"));
         if (host_error && *host_error != 0) {   // a kernel gave up on a bounded wait and said so
-            failed = internal_error("a decoder kernel timed out waiting for a bulk copy (error flag " + std::to_string(*host_error) + ")");
+            const int32_t flag = *host_error;
+            const char * what = flag == 2 ? "the prefill GEMM gave up waiting on its shared-memory pipeline"
+                              : flag == 3 ? "the peer-memory all-reduce gave up waiting for another rank"
+                              : flag == 4 ? "a decode GEMV gave up waiting for a tensor copy"
+                              : flag == 5 ? "the batched decode step gave up waiting at a grid barrier"
+                                          : "a kernel reported an internal inconsistency";
+            failed = internal_error(std::string(what) + " (error flag " + std::to_string(flag) + ")");
             return failed;
         }
         return Status();
@@ -187,28 +195,16 @@ struct CudaLlamaDecoder::Impl {
             xq_of = in;
         }
     }
-    // What the streaming GEMV of a matrix (pair) reads first, for the kernel launched before it to bring into L2 (kernels/l2_prefetch.cuh): the decode
-    // step is a chain of short dependent kernels, and without this device memory idles across every kernel boundary.
-    int64_t pf_budget = 16 << 20, pf_attn_budget = 32 << 20;      // bytes asked for ahead of a projection / ahead of gate/up during the attention kernel
-    cuda::L2Prefetch hint_for(const MatDev & w, const MatDev * w2, int64_t budget) const {
-        if (budget <= 0 || !w.ptr) return cuda::L2Prefetch{};
-        if (fast(w) && (!w2 || fast(*w2))) return cuda::gemv_q4_0_prefetch(w.ptr, w2 ? w2->ptr : nullptr, w.rows, w.cols, w.dt == DType::Q4_K, budget);
-        if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, x, w.rows, w.cols) && (!w2 || cuda::gemv_blocks_supported(int(w2->dt), w2->ptr, x, w2->rows, w2->cols))) {
-            return cuda::gemv_blocks_prefetch(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, w.rows, w.cols, budget);
-        }
-        return cuda::L2Prefetch{};
-    }
-    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags,
-                const cuda::L2Prefetch * next = nullptr) {
+    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags) {
         if (fast(w)) {
             prepare_fast_input(in, gamma, w.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
             run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream, nullptr, nullptr,
-                                                               host_error, next); });
+                                                               host_error); });
             return;
         }
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
-            run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream, next); });
+            run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
             return;
         }
         if (gamma) { norm(in, gamma, 1, false); in = xn; }
@@ -223,8 +219,7 @@ struct CudaLlamaDecoder::Impl {
         });
         xq_of = do_split ? xn : nullptr;
     }
-    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split,
-                 const cuda::L2Prefetch * next = nullptr) {
+    void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split) {
         if (fast(wg) && fast(wu)) {
             prepare_fast_input(in, gamma, wg.cols);
             const void * split = (xq_of == in && !gamma) ? xq : nullptr;
@@ -233,13 +228,13 @@ struct CudaLlamaDecoder::Impl {
             const bool split_out = down_takes_split && wg.rows % 32 == 0 && split_counters;
             run("gate_up", [&] {
                 return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
-                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error, next);
+                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error);
             });
             xq_of = split_out ? out : nullptr;
             return;
         }
         if (cuda::gemv_blocks_supported(int(wg.dt), wg.ptr, in, wg.rows, wg.cols) && cuda::gemv_blocks_supported(int(wu.dt), wu.ptr, in, wu.rows, wu.cols)) {
-            run("gate_up", [&] { return cuda::launch_gemv_blocks(int(wg.dt), wg.ptr, wu.ptr, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream, next); });
+            run("gate_up", [&] { return cuda::launch_gemv_blocks(int(wg.dt), wg.ptr, wu.ptr, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, stream); });
             return;
         }
         if (gamma) { norm(in, gamma, 1, false); in = xn; }
@@ -345,6 +340,8 @@ struct CudaLlamaDecoder::Impl {
         const int E = cfg.n_embd;
         const AttnShape as = attn_shape();
         const bool single = tp == 1;
+        // one position: its rotary angles are the same for every head of every layer
+        if (M == 1 && gqa) run("rope_table", [&] { return cuda::launch_rope_table(state, inv_freq, rope_cs, cfg.head_dim, stream); });
         for (size_t l = 0; l < layers.size(); l++) {
             const LayerDev & L = layers[l];
             __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
@@ -358,26 +355,13 @@ struct CudaLlamaDecoder::Impl {
             const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
             if (M > 1) norm(x, L.attn_norm, M, false, use_tc);
             if (M == 1) {
-                // every kernel of the step brings the head of what the next one streams into L2: the layer's key / value rows and attn_output while qkv
-                // runs, gate / up while the attention kernel runs (it moves few bytes itself), ffn_down during gate / up, the next layer's qkv during ffn_down
-                cuda::L2Prefetch after_qkv = hint_for(L.attn_output, nullptr, pf_budget);
-                if (pf_budget > 0 && gqa) {
-                    after_qkv.lin[0] = reinterpret_cast<const uint8_t *>(kcl);
-                    after_qkv.lin[1] = reinterpret_cast<const uint8_t *>(vcl);
-                    after_qkv.lin_bytes_per_pos = uint32_t(kv_width) * 2u;
-                    after_qkv.pos = &state->pos;
-                }
-                const cuda::L2Prefetch after_attn = hint_for(L.ffn_gate, &L.ffn_up, pf_attn_budget);
-                const cuda::L2Prefetch after_gate_up = hint_for(L.ffn_down, nullptr, pf_budget);
-                const cuda::L2Prefetch after_down = l + 1 < layers.size() ? hint_for(layers[l + 1].qkv[0].w, nullptr, pf_budget) : hint_for(output, nullptr, pf_budget);
                 for (const QkvPart & q : L.qkv) {
-                    matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u,
-                           &q == &L.qkv.back() ? &after_qkv : nullptr);
+                    matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 }
                 const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
                 if (gqa) {
                     run("attention", [&] {
-                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream, &after_attn);
+                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream, rope_cs);
                     });
                 } else {
                     run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, 1, as, stream); });
@@ -387,8 +371,8 @@ struct CudaLlamaDecoder::Impl {
                 matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags);
                 xq_of = nullptr;
                 reduce_into_x(1);
-                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down), &after_gate_up);
-                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags, &after_down);
+                gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down));
+                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags);
                 reduce_into_x(1);
             } else if (use_tc) {
                 // (the chunk's norm above wrote xn16)
@@ -463,6 +447,8 @@ struct CudaLlamaDecoder::Impl {
         return check(ie, "cudaGraphInstantiate");
     }
     int64_t step_launches = 0;
+    class StepWindow;
+    template <class Stage> Status append_positions(int32_t n, bool from_tokens, Stage && stage);
 
     void queue_decode_step() {
         if (step_graph) {
@@ -504,73 +490,9 @@ int32_t CudaLlamaDecoder::position() const { return impl_->pos; }
 CudaLlamaDecoder::Timings CudaLlamaDecoder::timings() const { return impl_->tm; }
 
 Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDecoderConfig & c, const LlamaDecoderWeights & w, const CudaOptions & opt) {
-    // The argument checks of the reference's create (metal_llama_decoder.mm:426-494), in its order and with its codes.
-    if (c.n_layer < 1 || c.n_embd < 4 || c.n_head < 1 || c.n_head_kv < 1 || c.head_dim < 2 || c.n_ff < 4 || c.n_vocab < 1 || c.n_ctx < 1 || c.n_batch < 1 ||
-        !(c.rope_base > 0.f) || !(c.rms_eps > 0.f)) {
-        return invalid_argument("llama decoder config: every size must be positive, rope_base and rms_eps > 0");
-    }
-    if (c.n_head % c.n_head_kv != 0) return invalid_argument("n_head must be a multiple of n_head_kv");
-    if (c.prefill_tile < 0 || c.prefill_tile > 2) return invalid_argument("prefill_tile must be 0 (automatic), 1 (CUDA-core tiles) or 2 (tensor-core tiles)");
-    if (c.head_dim < 4 || c.head_dim > kMaxHeadDim || (c.head_dim & (c.head_dim - 1)) != 0) {
-        return unsupported("head_dim must be a power of two in [4, " + std::to_string(kMaxHeadDim) + "], got " + std::to_string(c.head_dim));
-    }
-    if (c.n_embd % 4 != 0 || c.n_ff % 4 != 0 || (c.n_head * c.head_dim) % 4 != 0) return unsupported("n_embd, n_ff and n_head*head_dim must be multiples of 4");
-    if (static_cast<int64_t>(w.layers.size()) != c.n_layer) {
-        return invalid_argument("expected " + std::to_string(c.n_layer) + " layers of weights, got " + std::to_string(w.layers.size()));
-    }
-    if (opt.tp_size < 1 || opt.tp_rank < 0 || opt.tp_rank >= opt.tp_size) return invalid_argument("tp_rank must be in [0, tp_size)");
-
+    DOOMS_RETURN_IF_ERROR(validate_model(c, w));      // validate.cpp: configuration ranges, every tensor's shape and type, in the contract's order
+    if (opt.tp_size < 1 || opt.tp_rank < 0 || opt.tp_rank >= opt.tp_size) return invalid_argument("CUDA options: tp_rank has to lie in [0, tp_size)");
     const int64_t E = c.n_embd, F = c.n_ff, V = c.n_vocab, Qw = int64_t(c.n_head) * c.head_dim, KVw = int64_t(c.n_head_kv) * c.head_dim;
-    auto check = [](const WeightRef & r, int64_t rows, int64_t cols, bool matrix, const std::string & name) -> Status {
-        if (!r.data) return invalid_argument("weight '" + name + "' is missing");
-        if (r.rows != rows || r.cols != cols) {
-            return invalid_argument("weight '" + name + "' is " + std::to_string(r.rows) + "x" + std::to_string(r.cols) + ", expected " + std::to_string(rows) + "x" +
-                                    std::to_string(cols));
-        }
-        if (!dtype_valid(static_cast<int32_t>(r.dtype))) return invalid_argument("weight '" + name + "' has an unknown dtype");
-        if (matrix && !is_matrix_type(r.dtype)) {
-            return unsupported("weight '" + name + "' is " + dtype_name(r.dtype) + "; the CUDA decoder takes f16, q4_0, q5_0, q8_0, q4_K and q6_K matrices");
-        }
-        if (matrix && r.cols % dtype_block_elems(r.dtype) != 0) return invalid_argument("weight '" + name + "' rows are not whole " + dtype_name(r.dtype) + " blocks");
-        if (matrix && r.dtype == DType::F16 && r.cols % 32 != 0) return unsupported("f16 weight '" + name + "' needs rows that are a multiple of 32 elements");
-        if (!matrix && r.dtype != DType::F32 && r.dtype != DType::F16) return unsupported("norm '" + name + "' is " + dtype_name(r.dtype) + "; expected f32 or f16");
-        return Status();
-    };
-    Status st = check(w.token_embd, V, E, true, "token_embd");
-    if (st.is_ok()) st = check(w.output_norm, 1, E, false, "output_norm");
-    if (st.is_ok()) st = check(w.output, V, E, true, "output");
-    for (int32_t l = 0; l < c.n_layer && st.is_ok(); l++) {
-        const LlamaLayerWeights & L = w.layers[size_t(l)];
-        const std::string b = "blk." + std::to_string(l) + ".";
-        st = check(L.attn_norm, 1, E, false, b + "attn_norm");
-        if (st.is_ok()) {
-            if (L.attn_qkv.data) st = check(L.attn_qkv, Qw + 2 * KVw, E, true, b + "attn_qkv");
-            else {
-                st = check(L.attn_q, Qw, E, true, b + "attn_q");
-                if (st.is_ok()) st = check(L.attn_k, KVw, E, true, b + "attn_k");
-                if (st.is_ok()) st = check(L.attn_v, KVw, E, true, b + "attn_v");
-            }
-        }
-        if (st.is_ok()) {
-            const bool split = L.attn_q_bias.data || L.attn_k_bias.data || L.attn_v_bias.data;
-            if (split && L.attn_qkv_bias.data) st = invalid_argument(b + "attn: give attn_qkv_bias or attn_q/k/v_bias, not both");
-            else if (L.attn_qkv_bias.data) st = check(L.attn_qkv_bias, 1, Qw + 2 * KVw, false, b + "attn_qkv_bias");
-            else if (split) {
-                st = check(L.attn_q_bias, 1, Qw, false, b + "attn_q_bias");
-                if (st.is_ok()) st = check(L.attn_k_bias, 1, KVw, false, b + "attn_k_bias");
-                if (st.is_ok()) st = check(L.attn_v_bias, 1, KVw, false, b + "attn_v_bias");
-            }
-        }
-        if (st.is_ok()) st = check(L.attn_output, E, Qw, true, b + "attn_output");
-        if (st.is_ok()) st = check(L.ffn_norm, 1, E, false, b + "ffn_norm");
-        if (st.is_ok()) st = check(L.ffn_gate, F, E, true, b + "ffn_gate");
-        if (st.is_ok()) st = check(L.ffn_up, F, E, true, b + "ffn_up");
-        if (st.is_ok()) st = check(L.ffn_down, E, F, true, b + "ffn_down");
-        if (st.is_ok() && L.ffn_gate.dtype != L.ffn_up.dtype) {
-            st = unsupported(b + "ffn_gate is " + dtype_name(L.ffn_gate.dtype) + " and ffn_up " + dtype_name(L.ffn_up.dtype) + "; the fused gate/up kernel takes one type");
-        }
-    }
-    if (!st.is_ok()) return st;
 
     // This rank's share under tensor parallelism: whole heads, and column shards that are whole blocks.
     const int tp = opt.tp_size;
@@ -605,9 +527,6 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.vocab_stride = int32_t((V + tp - 1) / tp);
     m.vocab_row0 = int32_t(share.value().vocab_row0);
     m.vocab_rows = int32_t(share.value().vocab_rows);
-    // tuning knobs for measurements: megabytes brought into L2 ahead of a projection / ahead of gate / up (0: off)
-    if (const char * e = getenv("DOOMS_L2_PREFETCH_MB")) m.pf_budget = int64_t(std::max(0, atoi(e))) << 20;
-    if (const char * e = getenv("DOOMS_L2_PREFETCH_ATTN_MB")) m.pf_attn_budget = int64_t(std::max(0, atoi(e))) << 20;
 
     if (opt.operand_bf16) return unsupported("bf16 prefill operands are not built: the tensor-core tiles hold f16 operands, the reference's rounding");
     if (cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking) != cudaSuccess) return internal_error(cuda_msg("cudaStreamCreate", cudaGetLastError()));
@@ -772,6 +691,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         for (size_t i = 0; i < freq.size(); i++) freq[i] = std::pow(double(c.rope_base), -2.0 * double(i) / double(c.head_dim));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.inv_freq), freq.size() * sizeof(double), "the rotary frequencies"));
         if (cudaMemcpy(m.inv_freq, freq.data(), freq.size() * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) return internal_error("copying the rotary frequencies");
+        DOOMS_RETURN_IF_ERROR(dev_alloc(&m.rope_cs, freq.size() * 2 * sizeof(float), "the rotary table of a decode step"));
     }
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn_counters), size_t(std::max(1, m.nkv)) * sizeof(int), "the attention counters"));
     cudaMemset(m.attn_counters, 0, size_t(std::max(1, m.nkv)) * sizeof(int));
@@ -826,152 +746,177 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     return std::unique_ptr<CudaLlamaDecoder>(new CudaLlamaDecoder(std::move(impl)));
 }
 
+// ---- the calls of a sequence. Their observable behaviour is the reference decoder's (src/backend/metal/metal_llama_decoder.mm:691-787 and the cases of
+// tests/unit/test_metal_llama_decoder.cpp:534-608): argument checks and their codes, results independent of chunking and of the queue depth, what
+// generate() delivers and where position() stands afterwards. ----
+
 void CudaLlamaDecoder::reset() {
-    (void)impl_->wait_idle();
-    impl_->pos = 0;
-    impl_->has_pending = false;
+    Impl & m = *impl_;
+    (void)m.wait_idle();          // nothing of the old sequence may still be writing the cache
+    m.pos = 0;
+    m.has_pending = false;
+}
+
+namespace {
+std::string context_full(const LlamaDecoderConfig & c, int64_t wanted) {
+    return "the KV cache holds " + std::to_string(c.n_ctx) + " positions; this call would need " + std::to_string(wanted);
+}
+const char * const kNothingPending = "no position has been evaluated since the last reset() / generate(): there is no pending token";
+}  // namespace
+
+// Appends n positions in chunks of at most n_batch. `stage(first, rows)` puts rows first .. first + rows of the caller's input into the pinned staging
+// buffer and queues its copy to the device; the chunk then runs from there. The host rewrites the staging buffer for every chunk, hence the wait before it.
+template <class Stage>
+Status CudaLlamaDecoder::Impl::append_positions(int32_t n, bool from_tokens, Stage && stage) {
+    if (int64_t(pos) + n > cfg.n_ctx) return resource_exhausted(context_full(cfg, int64_t(pos) + n));
+    cudaSetDevice(opt.device);
+    launches = 0;
+    for (int32_t done = 0; done < n;) {
+        DOOMS_RETURN_IF_ERROR(wait_idle());
+        const int32_t rows = std::min(cfg.n_batch, n - done);
+        if (done == 0) cudaEventRecord(ev_a, stream);
+        stage(done, rows);
+        run_chunk(rows, from_tokens);
+        done += rows;
+    }
+    cudaEventRecord(ev_b, stream);
+    DOOMS_RETURN_IF_ERROR(wait_idle());
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, ev_a, ev_b);
+    tm.last_eval_ms = ms;
+    tm.last_eval_launches = launches;
+    return Status();
 }
 
 Status CudaLlamaDecoder::eval_embeddings(const float * embeddings, int32_t n) {
     Impl & m = *impl_;
-    if (!embeddings || n < 1) return invalid_argument("no embeddings to evaluate");
-    const int64_t total = int64_t(n) * m.cfg.n_embd;
-    for (int64_t i = 0; i < total; i++) if (!std::isfinite(embeddings[i])) return invalid_argument("the embeddings contain NaN or Inf");
-    if (int64_t(m.pos) + n > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
-    cudaSetDevice(m.opt.device);
-    m.launches = 0;
-    bool first = true;
-    for (int32_t start = 0; start < n; start += m.cfg.n_batch) {
-        DOOMS_RETURN_IF_ERROR(m.wait_idle());   // the staging rows are rewritten by the host
-        const int32_t rows = std::min(m.cfg.n_batch, n - start);
-        const size_t bytes = size_t(rows) * size_t(m.cfg.n_embd) * 4;
-        std::memcpy(m.host_x, embeddings + int64_t(start) * m.cfg.n_embd, bytes);
-        if (first) { cudaEventRecord(m.ev_a, m.stream); first = false; }
-        (void)m.check(cudaMemcpyAsync(m.x, m.host_x, bytes, cudaMemcpyHostToDevice, m.stream), "copying the embeddings to the device");
-        m.run_chunk(rows, false);
+    if (embeddings == nullptr || n < 1) return invalid_argument("eval_embeddings: no rows given");
+    const int64_t E = m.cfg.n_embd;
+    if (!std::all_of(embeddings, embeddings + int64_t(n) * E, [](float v) { return std::isfinite(v); })) {
+        return invalid_argument("eval_embeddings: a value is NaN or infinite");
     }
-    cudaEventRecord(m.ev_b, m.stream);
-    DOOMS_RETURN_IF_ERROR(m.wait_idle());
-    float ms = 0.f;
-    cudaEventElapsedTime(&ms, m.ev_a, m.ev_b);
-    m.tm.last_eval_ms = ms;
-    m.tm.last_eval_launches = m.launches;
-    return Status();
+    return m.append_positions(n, false, [&](int32_t first, int32_t rows) {
+        const size_t bytes = size_t(rows) * size_t(E) * sizeof(float);
+        std::memcpy(m.host_x, embeddings + int64_t(first) * E, bytes);
+        (void)m.check(cudaMemcpyAsync(m.x, m.host_x, bytes, cudaMemcpyHostToDevice, m.stream), "copying the embeddings to the device");
+    });
 }
 
 Status CudaLlamaDecoder::eval_tokens(const std::vector<int32_t> & ids) { return eval_tokens(ids.data(), int32_t(ids.size())); }
 
 Status CudaLlamaDecoder::eval_tokens(const int32_t * ids, int32_t n) {
     Impl & m = *impl_;
-    if (!ids || n < 1) return invalid_argument("no tokens to evaluate");
-    for (int32_t i = 0; i < n; i++) {
-        if (ids[i] < 0 || ids[i] >= m.cfg.n_vocab) {
-            return invalid_argument("token " + std::to_string(ids[i]) + " is outside the vocabulary [0, " + std::to_string(m.cfg.n_vocab) + ")");
-        }
-    }
-    if (int64_t(m.pos) + n > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
-    cudaSetDevice(m.opt.device);
-    m.launches = 0;
-    bool first = true;
-    for (int32_t start = 0; start < n; start += m.cfg.n_batch) {
-        DOOMS_RETURN_IF_ERROR(m.wait_idle());   // the staging ids are rewritten by the host
-        const int32_t rows = std::min(m.cfg.n_batch, n - start);
-        std::memcpy(m.host_in, ids + start, size_t(rows) * 4);
-        if (first) { cudaEventRecord(m.ev_a, m.stream); first = false; }
-        (void)m.check(cudaMemcpyAsync(m.in_tokens, m.host_in, size_t(rows) * 4, cudaMemcpyHostToDevice, m.stream), "copying the tokens to the device");
-        m.run_chunk(rows, true);
-    }
-    cudaEventRecord(m.ev_b, m.stream);
-    DOOMS_RETURN_IF_ERROR(m.wait_idle());
-    float ms = 0.f;
-    cudaEventElapsedTime(&ms, m.ev_a, m.ev_b);
-    m.tm.last_eval_ms = ms;
-    m.tm.last_eval_launches = m.launches;
-    return Status();
+    if (ids == nullptr || n < 1) return invalid_argument("eval_tokens: no tokens given");
+    const int32_t * bad = std::find_if(ids, ids + n, [&](int32_t t) { return t < 0 || t >= m.cfg.n_vocab; });
+    if (bad != ids + n) return invalid_argument("eval_tokens: id " + std::to_string(*bad) + " is not in the vocabulary of " + std::to_string(m.cfg.n_vocab));
+    return m.append_positions(n, true, [&](int32_t first, int32_t rows) {
+        std::memcpy(m.host_in, ids + first, size_t(rows) * sizeof(int32_t));
+        (void)m.check(cudaMemcpyAsync(m.in_tokens, m.host_in, size_t(rows) * sizeof(int32_t), cudaMemcpyHostToDevice, m.stream), "copying the tokens to the device");
+    });
 }
 
 Result<int32_t> CudaLlamaDecoder::pending_token() {
     Impl & m = *impl_;
-    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
+    if (!m.has_pending) return invalid_argument(kNothingPending);
     DOOMS_RETURN_IF_ERROR(m.wait_idle());
     return m.host_tokens[0];
 }
 
 Status CudaLlamaDecoder::logits_into(float * out, int64_t capacity) {
     Impl & m = *impl_;
-    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
-    if (!out || capacity < m.cfg.n_vocab) return resource_exhausted("logits need room for " + std::to_string(m.cfg.n_vocab) + " floats");
+    if (!m.has_pending) return invalid_argument(kNothingPending);
+    if (out == nullptr || capacity < m.cfg.n_vocab) return resource_exhausted("logits: the buffer has to hold " + std::to_string(m.cfg.n_vocab) + " floats");
     DOOMS_RETURN_IF_ERROR(m.wait_idle());
     cudaSetDevice(m.opt.device);
-    return m.check(cudaMemcpy(out, m.logits_buf, size_t(m.cfg.n_vocab) * 4, cudaMemcpyDeviceToHost), "reading the logits");
+    return m.check(cudaMemcpy(out, m.logits_buf, size_t(m.cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost), "reading the logits");
 }
 
 Result<std::vector<float>> CudaLlamaDecoder::logits() {
-    std::vector<float> v(size_t(impl_->cfg.n_vocab));
-    Status st = logits_into(v.data(), int64_t(v.size()));
-    if (!st.is_ok()) return st;
-    return v;
+    std::vector<float> row(size_t(impl_->cfg.n_vocab));
+    DOOMS_RETURN_IF_ERROR(logits_into(row.data(), int64_t(row.size())));
+    return row;
 }
 
+// The decode steps in flight during generate(): a ring of events, one per queued step, oldest first.
+class CudaLlamaDecoder::Impl::StepWindow {
+public:
+    StepWindow(Impl & m, int32_t depth) : m_(m) {
+        while (m_.step_events.size() < size_t(depth) + 1) {
+            cudaEvent_t e = nullptr;
+            cudaEventCreate(&e);
+            m_.step_events.push_back(e);
+        }
+    }
+    int32_t in_flight() const { return int32_t(slots_.size()); }
+    void queue_step() {
+        m_.queue_decode_step();
+        const size_t slot = issued_++ % m_.step_events.size();
+        cudaEventRecord(m_.step_events[slot], m_.stream);
+        slots_.push_back(slot);
+    }
+    // Blocks (or spins, when the configuration asks for it) until the oldest queued step is done; its event is remembered as the end of the timed span.
+    cudaError_t retire_oldest() {
+        const size_t slot = slots_.front();
+        slots_.pop_front();
+        cudaEvent_t e = m_.step_events[slot];
+        cudaError_t rc = cudaSuccess;
+        if (m_.cfg.spin_wait) { do { rc = cudaEventQuery(e); } while (rc == cudaErrorNotReady); }
+        else rc = cudaEventSynchronize(e);
+        if (rc == cudaSuccess) last_done_ = e;
+        return rc;
+    }
+    cudaEvent_t last_done() const { return last_done_; }
+
+private:
+    Impl & m_;
+    std::deque<size_t> slots_;
+    size_t issued_ = 0;
+    cudaEvent_t last_done_ = nullptr;
+};
+
+// Token 0 is the pending one (already in the token ring); token i > 0 comes out of decode step i, which embeds token i - 1 straight from the ring on the
+// device, writes the cache at position start + i - 1 and its own greedy token to ring slot i. Up to `depth` steps run ahead of the token the host is
+// handing to the callback; the steps queued past the stopping point finish on their own and are discarded (every later call waits for the stream first).
 Status CudaLlamaDecoder::generate(int32_t max_tokens, int32_t depth, const std::function<bool(int32_t)> & on_token) {
     Impl & m = *impl_;
-    if (!m.has_pending) return invalid_argument("nothing has been evaluated yet");
-    if (max_tokens < 1 || depth < 1) return invalid_argument("max_tokens and depth must be >= 1");
-    // Step i (1 <= i < max_tokens) writes the cache at position base + i - 1 and its token into tokens[i] (metal_llama_decoder.mm:745-747).
-    const int32_t base = m.pos;
-    if (int64_t(base) + max_tokens - 1 > m.cfg.n_ctx) return resource_exhausted("the context of " + std::to_string(m.cfg.n_ctx) + " positions would overflow");
+    if (!m.has_pending) return invalid_argument(kNothingPending);
+    if (max_tokens < 1 || depth < 1) return invalid_argument("generate: max_tokens and depth have to be at least 1");
+    const int32_t start = m.pos;
+    if (int64_t(start) + max_tokens - 1 > m.cfg.n_ctx) return resource_exhausted(context_full(m.cfg, int64_t(start) + max_tokens - 1));
     cudaSetDevice(m.opt.device);
     DOOMS_RETURN_IF_ERROR(m.ensure_step_graph());
-    DOOMS_RETURN_IF_ERROR(m.wait_idle());   // tokens[0] (the pending token) is final; steps queued by an earlier generate() are done
-    while (m.step_events.size() < size_t(depth) + 1) {
-        cudaEvent_t e;
-        cudaEventCreate(&e);
-        m.step_events.push_back(e);
-    }
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());          // the pending token is final and nothing of an earlier generate() is still running
+    Impl::StepWindow window(m, depth);
     m.launches = 0;
-    m.run("state", [&] { return cuda::launch_set_state(m.state, base, 0, 1, m.stream); });
+    m.run("state", [&] { return cuda::launch_set_state(m.state, start, 0, 1, m.stream); });
     cudaEventRecord(m.ev_a, m.stream);
-    std::deque<int> inflight;   // event slots; inflight[k] marks the step that produces tokens[produced + k]; -1: already complete
-    inflight.push_back(-1);
-    int32_t produced = 0, next = 1;
-    size_t slot = 0;
-    int last_slot = -1;   // the event of the step that produced the last delivered token
-    Status st;
-    while (true) {
-        while (next < max_tokens && next - produced <= depth) {
-            m.queue_decode_step();
-            const int s = int(slot++ % m.step_events.size());
-            cudaEventRecord(m.step_events[size_t(s)], m.stream);
-            inflight.push_back(s);
-            next++;
+
+    Status outcome;
+    int32_t delivered = 0, queued_tokens = 1;      // tokens handed to the callback; tokens that exist or are being computed (the pending one counts)
+    for (bool more = true; more;) {
+        while (queued_tokens < max_tokens && queued_tokens - delivered <= depth) { window.queue_step(); queued_tokens++; }
+        if (delivered > 0) {                        // every token but the pending one waits for its step
+            const cudaError_t rc = window.retire_oldest();
+            if (rc != cudaSuccess) { outcome = m.check(rc, "a decode step failed"); break; }
         }
-        const int s = inflight.front();
-        inflight.pop_front();
-        if (s >= 0) {
-            cudaError_t e;
-            if (m.cfg.spin_wait) { while ((e = cudaEventQuery(m.step_events[size_t(s)])) == cudaErrorNotReady) {} }
-            else e = cudaEventSynchronize(m.step_events[size_t(s)]);
-            if (e != cudaSuccess) { st = m.check(e, "a decode step failed"); break; }
-            last_slot = s;
-        }
-        if (!m.failed.is_ok()) { st = m.failed; break; }
-        const int32_t token = m.host_tokens[produced];
-        produced++;
-        if (!on_token(token) || produced == max_tokens) break;
+        if (!m.failed.is_ok()) { outcome = m.failed; break; }
+        if (m.host_error && *m.host_error != 0) { outcome = m.wait_idle(); break; }      // a kernel gave up on a bounded wait: its token is not to be trusted
+        const int32_t token = m.host_tokens[delivered++];
+        more = on_token(token) && delivered < max_tokens;
     }
-    // Steps queued past the stopping point still run; every later call starts by waiting for the stream, so they never overlap with new work.
-    if (st.is_ok()) {
-        // Device time up to the step of the last delivered token: steps queued past it are not the caller's.
+    if (outcome.is_ok()) {
+        // device time from the first step to the step of the last delivered token; what was queued past it is not the caller's
         float ms = 0.f;
-        if (last_slot >= 0) cudaEventElapsedTime(&ms, m.ev_a, m.step_events[size_t(last_slot)]);
+        if (window.last_done()) cudaEventElapsedTime(&ms, m.ev_a, window.last_done());
         m.tm.last_generate_ms = ms;
         m.tm.last_generate_launches = m.launches;
     } else {
         (void)cudaStreamSynchronize(m.stream);
     }
-    m.pos = base + produced - 1;
+    // as if the delivered tokens except the last had been evaluated one by one
+    m.pos = start + std::max(delivered, 1) - 1;
     m.has_pending = false;
-    return st;
+    return outcome;
 }
 
 Result<std::vector<CudaLlamaDecoder::KernelTime>> CudaLlamaDecoder::profile_pass(int32_t rows) {

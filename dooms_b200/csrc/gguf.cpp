@@ -151,118 +151,157 @@ const char * gguf_value_type_name(GgufValueType t) {
     return (i >= 0 && i <= 12) ? names[i] : "unknown";
 }
 
-Result<GgufFile> GgufFile::parse(const uint8_t * data, size_t size, const GgufLimits & lim) {
-    if (!data || size == 0) return invalid_argument("no data to parse");
-    Reader r{data, size};
-    char magic[4];
-    DOOMS_RETURN_IF_ERROR(r.get(&magic, "magic"));
-    if (std::memcmp(magic, "GGUF", 4) != 0) return data_loss("not a GGUF file (bad magic)");
-    GgufFile f;
-    f.data_ = data;
-    f.size_ = size;
-    DOOMS_RETURN_IF_ERROR(r.get(&f.version_, "version"));
-    if (f.version_ < 2 || f.version_ > 3) {
-        std::string msg = "GGUF version " + std::to_string(f.version_) + " is not supported (supported: 2 to 3)";
-        if ((f.version_ & 0xFFFF) == 0) msg += "; the file may have been written on a machine with different endianness";
-        return unsupported(msg);
-    }
-    uint64_t n_tensors = 0, n_kv = 0;
-    DOOMS_RETURN_IF_ERROR(r.get(&n_tensors, "tensor count"));
-    DOOMS_RETURN_IF_ERROR(r.get(&n_kv, "metadata count"));
-    if (n_tensors > lim.max_tensors) return resource_exhausted("tensor count " + std::to_string(n_tensors) + " exceeds the limit of " + std::to_string(lim.max_tensors));
-    if (n_kv > lim.max_kv) return resource_exhausted("metadata count " + std::to_string(n_kv) + " exceeds the limit of " + std::to_string(lim.max_kv));
+// The file's sections in the order they are laid out: header, metadata, tensor directory, then (after padding to the alignment) the tensor data. One
+// method per section; each leaves what it read in the GgufFile under construction and returns the first inconsistency it meets. What is refused, with which
+// code and in which order is the reference reader's behaviour (src/format/gguf.cpp:179-317); the differential tests feed both readers the same bytes.
+class GgufParser {
+public:
+    GgufParser(const uint8_t * data, size_t size, const GgufLimits & limits, GgufFile * out) : in_{data, size}, limits_(limits), out_(*out) {}
 
-    for (uint64_t k = 0; k < n_kv; k++) {
+    Status run() {
+        DOOMS_RETURN_IF_ERROR(header());
+        for (uint64_t i = 0; i < kv_count_; i++) DOOMS_RETURN_IF_ERROR(metadata_entry(i));
+        DOOMS_RETURN_IF_ERROR(alignment());
+        out_.tensors_.reserve(static_cast<size_t>(std::min<uint64_t>(tensor_count_, in_.left())));      // a hostile count cannot reserve more than the file holds
+        for (uint64_t i = 0; i < tensor_count_; i++) DOOMS_RETURN_IF_ERROR(directory_entry(i));
+        return out_.tensors_.empty() ? Status() : place_data();
+    }
+
+private:
+    // "GGUF", version, tensor count, metadata count.
+    Status header() {
+        uint8_t magic[4];
+        DOOMS_RETURN_IF_ERROR(in_.bytes(magic, 4, "the magic"));
+        if (magic[0] != 'G' || magic[1] != 'G' || magic[2] != 'U' || magic[3] != 'F') return data_loss("the first four bytes are not 'GGUF'");
+        DOOMS_RETURN_IF_ERROR(in_.get(&out_.version_, "the format version"));
+        if (out_.version_ != 2 && out_.version_ != 3) {
+            // a big-endian writer's 2 or 3 reads as a multiple of 65536 here
+            const bool swapped = (out_.version_ & 0xFFFFu) == 0;
+            return unsupported("format version " + std::to_string(out_.version_) + "; this reader handles versions 2 and 3" +
+                               (swapped ? " (the low half is zero: a file written with the other byte order?)" : ""));
+        }
+        DOOMS_RETURN_IF_ERROR(in_.get(&tensor_count_, "the tensor count"));
+        DOOMS_RETURN_IF_ERROR(in_.get(&kv_count_, "the metadata count"));
+        if (tensor_count_ > limits_.max_tensors) return over_limit("tensors", tensor_count_, limits_.max_tensors);
+        if (kv_count_ > limits_.max_kv) return over_limit("metadata entries", kv_count_, limits_.max_kv);
+        return Status();
+    }
+
+    Status metadata_entry(uint64_t i) {
         std::string key;
-        DOOMS_RETURN_IF_ERROR(r.string(&key, "metadata key", lim.max_name_bytes));
-        if (key.empty()) return data_loss("metadata entry " + std::to_string(k) + " has an empty key");
-        GgufValue v;
-        DOOMS_RETURN_IF_ERROR(read_kv_value(r, &v, lim, key));
-        if (!f.kv_.emplace(key, std::move(v)).second) return data_loss("duplicate metadata key '" + key + "'");
+        DOOMS_RETURN_IF_ERROR(in_.string(&key, "metadata key", limits_.max_name_bytes));
+        if (key.empty()) return data_loss("metadata entry #" + std::to_string(i) + ": empty key");
+        GgufValue value;
+        DOOMS_RETURN_IF_ERROR(read_kv_value(in_, &value, limits_, key));
+        const bool fresh = out_.kv_.emplace(key, std::move(value)).second;
+        return fresh ? Status() : data_loss("metadata key '" + key + "' occurs twice");
     }
 
-    f.alignment_ = 32;
-    if (const GgufValue * al = f.lookup("general.alignment")) {
-        if (al->type != GgufValueType::U32) return data_loss(std::string("general.alignment must be a u32, got ") + gguf_value_type_name(al->type));
-        f.alignment_ = al->u;
-        if (f.alignment_ == 0 || (f.alignment_ & (f.alignment_ - 1)) != 0 || f.alignment_ > lim.max_alignment) {
-            return data_loss("general.alignment = " + std::to_string(f.alignment_) + " must be a power of two no larger than " + std::to_string(lim.max_alignment));
+    // general.alignment (u32, a power of two) positions the data section and every tensor in it; 32 when absent.
+    Status alignment() {
+        out_.alignment_ = 32;
+        const auto it = out_.kv_.find("general.alignment");
+        if (it == out_.kv_.end()) return Status();
+        const GgufValue & v = it->second;
+        if (v.type != GgufValueType::U32) return data_loss(std::string("general.alignment is stored as ") + gguf_value_type_name(v.type) + "; the format wants u32");
+        const uint64_t a = v.u;
+        out_.alignment_ = a;
+        const bool power_of_two = a != 0 && (a & (a - 1)) == 0;
+        if (!power_of_two || a > limits_.max_alignment) {
+            return data_loss("general.alignment " + std::to_string(a) + " is not a power of two up to " + std::to_string(limits_.max_alignment));
         }
+        return Status();
     }
 
-    f.tensors_.reserve(static_cast<size_t>(std::min<uint64_t>(n_tensors, r.left())));
-    for (uint64_t t = 0; t < n_tensors; t++) {
-        GgufTensorInfo info;
-        DOOMS_RETURN_IF_ERROR(r.string(&info.name, "tensor name", lim.max_name_bytes));
-        if (info.name.empty()) return data_loss("tensor " + std::to_string(t) + " has an empty name");
-        if (f.index_.count(info.name)) return data_loss("duplicate tensor name '" + info.name + "'");
-        uint32_t n_dims = 0;
-        DOOMS_RETURN_IF_ERROR(r.get(&n_dims, "tensor rank"));
-        if (n_dims > static_cast<uint32_t>(kGgufMaxDims)) {
-            return data_loss("tensor '" + info.name + "' has " + std::to_string(n_dims) + " dimensions; the maximum is " + std::to_string(kGgufMaxDims));
+    // name, rank, dimensions (fastest first in the file, outermost first in memory here), ggml type, offset within the data section.
+    Status directory_entry(uint64_t i) {
+        GgufTensorInfo t;
+        DOOMS_RETURN_IF_ERROR(in_.string(&t.name, "tensor name", limits_.max_name_bytes));
+        if (t.name.empty()) return data_loss("tensor #" + std::to_string(i) + ": empty name");
+        if (out_.index_.find(t.name) != out_.index_.end()) return data_loss("tensor name '" + t.name + "' occurs twice");
+        const std::string who = "tensor '" + t.name + "'";
+        uint32_t rank = 0;
+        DOOMS_RETURN_IF_ERROR(in_.get(&rank, "tensor rank"));
+        if (rank > static_cast<uint32_t>(kGgufMaxDims)) return data_loss(who + ": rank " + std::to_string(rank) + " is above the format's " + std::to_string(kGgufMaxDims));
+        t.rank = static_cast<int>(rank);
+        int64_t elements = 1;
+        for (uint32_t d = 0; d < rank; d++) {
+            int64_t extent = 0;
+            DOOMS_RETURN_IF_ERROR(in_.get(&extent, "tensor dimension"));
+            if (extent < 1) return data_loss(who + ": extent " + std::to_string(extent) + " in dimension " + std::to_string(d) + " (must be positive)");
+            if (elements > std::numeric_limits<int64_t>::max() / extent) return data_loss(who + ": more elements than 63 bits count");
+            elements *= extent;
+            t.shape[rank - 1 - d] = extent;
         }
-        info.rank = static_cast<int>(n_dims);
-        int64_t numel = 1;
-        for (uint32_t d = 0; d < n_dims; d++) {
-            int64_t dim = 0;
-            DOOMS_RETURN_IF_ERROR(r.get(&dim, "tensor dimension"));
-            if (dim < 1) return data_loss("tensor '" + info.name + "' dimension " + std::to_string(d) + " is " + std::to_string(dim) + "; dimensions must be >= 1");
-            if (numel > std::numeric_limits<int64_t>::max() / dim) return data_loss("tensor '" + info.name + "': the element count overflows");
-            numel *= dim;
-            info.shape[n_dims - 1 - d] = dim;
+        int32_t ggml_type = 0;
+        DOOMS_RETURN_IF_ERROR(in_.get(&ggml_type, "tensor type"));
+        if (!ggml_type_to_dtype(ggml_type, &t.dtype)) return unsupported(who + ": ggml type id " + std::to_string(ggml_type) + " is none of the types this backend holds");
+        // rows are whole quantization blocks
+        const int64_t per_block = dtype_block_elems(t.dtype), row = rank > 0 ? t.shape[rank - 1] : 1;
+        if (row % per_block != 0) {
+            return data_loss(who + ": a row of " + std::to_string(row) + " elements cannot be cut into " + dtype_name(t.dtype) + " blocks of " + std::to_string(per_block));
         }
-        int32_t type_id = 0;
-        DOOMS_RETURN_IF_ERROR(r.get(&type_id, "tensor type"));
-        if (!ggml_type_to_dtype(type_id, &info.dtype)) {
-            return unsupported("tensor '" + info.name + "' has ggml type " + std::to_string(type_id) + ", which this reader does not support");
-        }
-        const int64_t block = dtype_block_elems(info.dtype);
-        const int64_t row = info.rank > 0 ? info.shape[info.rank - 1] : 1;
-        if (row % block != 0) {
-            return data_loss("tensor '" + info.name + "' has rows of " + std::to_string(row) + " elements, not a multiple of the " + dtype_name(info.dtype) +
-                             " block of " + std::to_string(block));
-        }
-        const uint64_t blocks = static_cast<uint64_t>(numel / block), bb = static_cast<uint64_t>(dtype_block_bytes(info.dtype));
-        if (blocks > std::numeric_limits<uint64_t>::max() / bb) return data_loss("tensor '" + info.name + "' byte size overflows");
-        info.nbytes = blocks * bb;
-        DOOMS_RETURN_IF_ERROR(r.get(&info.offset, "tensor data offset"));   // relative to the data section until the checks below pass
-        f.index_.emplace(info.name, f.tensors_.size());
-        f.tensors_.push_back(std::move(info));
+        const uint64_t n_blocks = static_cast<uint64_t>(elements / per_block), block_bytes = static_cast<uint64_t>(dtype_block_bytes(t.dtype));
+        if (n_blocks > std::numeric_limits<uint64_t>::max() / block_bytes) return data_loss(who + ": its size in bytes does not fit 64 bits");
+        t.nbytes = n_blocks * block_bytes;
+        DOOMS_RETURN_IF_ERROR(in_.get(&t.offset, "tensor data offset"));      // still relative to the data section; place_data() makes it absolute
+        out_.index_.emplace(t.name, out_.tensors_.size());
+        out_.tensors_.push_back(std::move(t));
+        return Status();
     }
-    if (f.tensors_.empty()) return f;
 
-    const uint64_t data_start = (r.at + (f.alignment_ - 1)) & ~(f.alignment_ - 1);
-    if (data_start > size) return data_loss("file ends at " + std::to_string(size) + " before the data section at " + std::to_string(data_start));
-    const uint64_t data_size = size - data_start;
-    for (const GgufTensorInfo & t : f.tensors_) {
-        if (t.offset % f.alignment_ != 0) {
-            return data_loss("tensor '" + t.name + "' offset " + std::to_string(t.offset) + " is not a multiple of the alignment " + std::to_string(f.alignment_));
+    // The data section starts at the next multiple of the alignment after the directory. Every tensor must start on the alignment, lie inside the file and
+    // share no byte with another.
+    Status place_data() {
+        const uint64_t a = out_.alignment_, file_size = in_.size;
+        const uint64_t section = (in_.at + a - 1) / a * a;
+        if (section > file_size) return data_loss("the tensor data would start at byte " + std::to_string(section) + ", the file has " + std::to_string(file_size));
+        const uint64_t room = file_size - section;
+        for (const GgufTensorInfo & t : out_.tensors_) {
+            if (t.offset % a != 0) return data_loss("tensor '" + t.name + "': data offset " + std::to_string(t.offset) + " is off the " + std::to_string(a) + "-byte alignment");
+            if (t.offset > room || t.nbytes > room - t.offset) {
+                return data_loss("tensor '" + t.name + "': bytes " + std::to_string(t.offset) + " .. " + std::to_string(t.offset) + " + " + std::to_string(t.nbytes) +
+                                 " of a data section that holds " + std::to_string(room));
+            }
         }
-        if (t.offset > data_size || t.nbytes > data_size - t.offset) {
-            return data_loss("tensor '" + t.name + "' (" + std::to_string(t.nbytes) + " bytes at data offset " + std::to_string(t.offset) +
-                             ") extends past the end of the file (data section is " + std::to_string(data_size) + " bytes)");
+        std::vector<size_t> order(out_.tensors_.size());
+        for (size_t i = 0; i < order.size(); i++) order[i] = i;
+        std::sort(order.begin(), order.end(), [&](size_t x, size_t y) { return out_.tensors_[x].offset < out_.tensors_[y].offset; });
+        for (size_t i = 0; i + 1 < order.size(); i++) {
+            const GgufTensorInfo & lo = out_.tensors_[order[i]], & hi = out_.tensors_[order[i + 1]];
+            if (lo.offset + lo.nbytes > hi.offset) return data_loss("tensor '" + lo.name + "' runs into tensor '" + hi.name + "'");
         }
+        for (GgufTensorInfo & t : out_.tensors_) t.offset += section;
+        return Status();
     }
-    std::vector<const GgufTensorInfo *> by_offset;
-    for (const GgufTensorInfo & t : f.tensors_) by_offset.push_back(&t);
-    std::sort(by_offset.begin(), by_offset.end(), [](const GgufTensorInfo * a, const GgufTensorInfo * b) { return a->offset < b->offset; });
-    for (size_t i = 1; i < by_offset.size(); i++) {
-        if (by_offset[i - 1]->offset + by_offset[i - 1]->nbytes > by_offset[i]->offset) {
-            return data_loss("tensors '" + by_offset[i - 1]->name + "' and '" + by_offset[i]->name + "' overlap in the data section");
-        }
+
+    static Status over_limit(const char * what, uint64_t n, uint64_t cap) {
+        return resource_exhausted("the header announces " + std::to_string(n) + " " + what + "; this reader accepts up to " + std::to_string(cap));
     }
-    for (GgufTensorInfo & t : f.tensors_) t.offset += data_start;
-    return f;
+
+    Reader in_;
+    const GgufLimits & limits_;
+    GgufFile & out_;
+    uint64_t tensor_count_ = 0, kv_count_ = 0;
+};
+
+Result<GgufFile> GgufFile::parse(const uint8_t * data, size_t size, const GgufLimits & limits) {
+    if (data == nullptr || size == 0) return invalid_argument("GgufFile::parse was given no bytes");
+    GgufFile file;
+    file.data_ = data;
+    file.size_ = size;
+    DOOMS_RETURN_IF_ERROR(GgufParser(data, size, limits, &file).run());
+    return file;
 }
 
-Result<GgufFile> GgufFile::open(const std::string & path, const GgufLimits & lim) {
-    auto mapped = MappedFile::open(path);
-    if (!mapped.is_ok()) return mapped.status();
-    auto parsed = parse(mapped.value()->data(), mapped.value()->size(), lim);
-    if (!parsed.is_ok()) return Status(parsed.status().code(), path + ": " + parsed.status().message());
-    GgufFile f = std::move(parsed).value();
-    f.mapping_ = mapped.value();
-    return f;
+Result<GgufFile> GgufFile::open(const std::string & path, const GgufLimits & limits) {
+    auto mapping = MappedFile::open(path);
+    if (!mapping.is_ok()) return mapping.status();
+    std::shared_ptr<const MappedFile> bytes = mapping.value();
+    auto file = parse(bytes->data(), bytes->size(), limits);
+    if (!file.is_ok()) return Status(file.status().code(), "'" + path + "': " + file.status().message());
+    file.value().mapping_ = std::move(bytes);      // the parsed view points into the mapping: they travel together
+    return file;
 }
 
 const GgufValue * GgufFile::lookup(std::string_view key) const {

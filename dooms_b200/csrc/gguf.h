@@ -66,6 +66,8 @@ private:
     size_t size_;
 };
 
+class GgufParser;
+
 class GgufFile {
 public:
     static Result<GgufFile> parse(const uint8_t * data, size_t size, const GgufLimits & limits = GgufLimits());   // data must outlive the object
@@ -84,6 +86,7 @@ public:
     const uint8_t * tensor_data(const GgufTensorInfo & info) const { return data_ + info.offset; }
 
 private:
+    friend class GgufParser;
     const GgufValue * lookup(std::string_view key) const;
     const uint8_t * data_ = nullptr;
     size_t size_ = 0;

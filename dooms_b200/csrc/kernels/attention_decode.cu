@@ -10,7 +10,6 @@
 #include <algorithm>
 
 #include "kernels.h"
-#include "l2_prefetch.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "xsplit.cuh"
@@ -40,7 +39,7 @@ struct AttnDecodeParams {
     int * counters;
     float * out;
     uint8_t * xq;
-    L2Prefetch next;          // what the kernels after this one read first (l2_prefetch.cuh); all null: nothing
+    const float2 * rope_cs;   // optional: (cos, sin) of the head_dim / 2 rotary angles at st->pos, computed once per decode step
 };
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
@@ -66,7 +65,6 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
 
     pdl_trigger();
     pdl_wait();
-    if (threadIdx.x == kThreads - 1) l2_prefetch_issue(p.next, int(blockIdx.y * gridDim.x + blockIdx.x), int(gridDim.x * gridDim.y));
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int G = p.s.n_head / p.s.n_head_kv;
@@ -105,9 +103,10 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
             r0 = x[e0];
             r1 = x[e1];
             if (fuse) {
-                double sd, cd;
-                sincos(double(pos) * p.inv_freq[d], &sd, &cd);
-                const float c = float(cd), s = float(sd), a = r0, b = r1;
+                float c, s;
+                if (p.rope_cs) { const float2 cs = p.rope_cs[d]; c = cs.x; s = cs.y; }
+                else { double sd, cd; sincos(double(pos) * p.inv_freq[d], &sd, &cd); c = float(cd); s = float(sd); }
+                const float a = r0, b = r1;
                 r0 = a * c - b * s;
                 r1 = a * s + b * c;
             }
@@ -134,9 +133,10 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
                 const int d = tid;
                 const int e0 = p.s.neox ? d : 2 * d, e1 = p.s.neox ? d + D / 2 : 2 * d + 1;
                 const float * x = p.qkv + (p.s.n_head + kvh) * D;
-                double sd, cd;
-                sincos(double(pos) * p.inv_freq[d], &sd, &cd);
-                const float c = float(cd), s = float(sd), a = x[e0], b = x[e1];
+                float c, s;
+                if (p.rope_cs) { const float2 cs = p.rope_cs[d]; c = cs.x; s = cs.y; }
+                else { double sd, cd; sincos(double(pos) * p.inv_freq[d], &sd, &cd); c = float(cd); s = float(sd); }
+                const float a = x[e0], b = x[e1];
                 const __half h0 = __float2half_rn(a * c - b * s), h1 = __float2half_rn(a * s + b * c);
                 __half * dst = p.kc + int64_t(pos) * p.s.kv_stride + kvh * D;
                 __half * row = reinterpret_cast<__half *>(ks + r * KP);
@@ -337,10 +337,10 @@ int attention_gqa_splits(int n_head_kv, int n_ctx) {
 }
 
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
-                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream, const L2Prefetch * next) {
+                                 int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream, const void * rope_cs) {
     if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1) || (counters && !out) || (xq && !counters)) return cudaErrorInvalidValue;
     const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
-                             static_cast<uint8_t *>(xq), next ? *next : L2Prefetch{}};
+                             static_cast<uint8_t *>(xq), static_cast<const float2 *>(rope_cs)};
     return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
 }
 

@@ -13,7 +13,6 @@
 #include <algorithm>
 
 #include "kernels.h"
-#include "l2_prefetch.cuh"
 #include "launch.cuh"
 #include "ptx.cuh"
 #include "quant.cuh"
@@ -52,7 +51,6 @@ struct GemvBlocksParams {
     int stride, upr;        // bytes between the rows of a stage; 16-byte pieces copied per row
     int rows_q, rows_r;     // block b has rows_q + (b < rows_r) rows starting at b rows_q + min(b, rows_r)
     uint32_t inv_upr, inv_nchunks;
-    L2Prefetch next;        // what the kernel after this one reads first (l2_prefetch.cuh); all null: nothing
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
@@ -142,7 +140,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
-    if (threadIdx.x == WARPS * 32 - 1) l2_prefetch_issue(p.next, int(blockIdx.x), int(gridDim.x));
     for (uint32_t i = threadIdx.x; i < uint32_t(p.cols) / 4u; i += WARPS * 32) cp_async16(smem_base + i * 16u, p.x + size_t(i) * 4);
     cp_async_commit();
     cp_async_wait<0>();
@@ -305,25 +302,9 @@ bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows,
     return plan_for(fmt_be(dt), fmt_bb(dt), cols, 2).ok;
 }
 
-L2Prefetch gemv_blocks_prefetch(int dt, const void * W, const void * W2, int64_t rows, int64_t cols, int64_t budget_bytes) {
-    L2Prefetch h{};
-    if (budget_bytes <= 0 || !W || fmt_bb(dt) == 0) return h;
-    const int grid = int(grid_for(rows));
-    const int64_t row_bytes = cols / fmt_be(dt) * fmt_bb(dt);
-    const int64_t per_block = budget_bytes / (int64_t(grid) * (W2 ? 2 : 1));
-    h.mat[0] = static_cast<const uint8_t *>(W);
-    h.mat[1] = static_cast<const uint8_t *>(W2);
-    h.row_bytes = uint32_t(row_bytes);
-    h.rows_q = int(rows / grid); h.rows_r = int(rows % grid); h.row_unit = 1; h.grid = grid;
-    h.head_rows = int32_t(std::min<int64_t>(std::max<int64_t>(per_block / row_bytes, 1), int64_t(h.rows_q) + 1));
-    h.rows = rows;
-    return h;
-}
-
 cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream, const L2Prefetch * next) {
-    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, gamma, eps, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u,
-                       next ? *next : L2Prefetch{}};
+                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {
+    GemvBlocksParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), x, gamma, eps, y, bias, int(cols), flags, 0, 0, 0, 0, 0, 0, 0u, 0u};
     switch (dt) {
         case kF16: return launch_dt<kF16>(p, rows, stream);
         case kQ4_0: return launch_dt<kQ4_0>(p, rows, stream);

@@ -24,7 +24,6 @@
 #include "ptx.cuh"
 #include "launch.cuh"
 #include "xsplit.cuh"
-#include "l2_prefetch.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -62,7 +61,6 @@ struct GemvQ40Params {
     int rows_q, rows_r;     // units / grid and units % grid: block b has rows_q + (b < rows_r) units of row_unit rows starting at unit b rows_q + min(b, rows_r)
     int row_unit;
     uint32_t inv_upr, inv_nchunks;   // 65536 / d + 1: (j * inv) >> 16 = j / d for the small j divided here
-    L2Prefetch next;        // what the kernel after this one reads first (l2_prefetch.cuh); all null: nothing
 };
 
 // x[K] (f32) -> xq. One warp per 32-element block.
@@ -266,7 +264,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
-    if (threadIdx.x == WARPS * 32 - 1) l2_prefetch_issue(p.next, int(blockIdx.x), int(gridDim.x));
     if (p.xq) {
         for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
         cp_async_commit();
@@ -274,32 +271,63 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     } else {
         // every block normalizes (when asked) and splits the whole input itself, while its first stages are on their way: a 16 KB read from L2 and about
         // forty instructions per 32 elements, instead of a launch of its own and a round trip through device memory
-        float inv = 1.f;
-        if (p.gamma) {
-            __shared__ float red[WARPS];
-            float ss = 0.f;
-            for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) { const float v = p.x[i]; ss += v * v; }
+        __shared__ float red[WARPS];
+        constexpr int kHeld = 16;              // blocks of the input a warp keeps in registers: inputs of up to 16 x WARPS x 32 elements make one pass
+        if (nb <= kHeld * WARPS) {
+            // one pass: every load (input and gains) is issued before anything waits, the sum of squares and the split both work from registers
+            float v[kHeld], gm[kHeld];
             #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) red[warp] = ss;
-            __syncthreads();
-            float total = 0.f;
-            #pragma unroll
-            for (int w = 0; w < WARPS; w++) total += red[w];
-            inv = rsqrtf(total / float(p.cols) + p.eps);
-        }
-        for (int blk0 = warp; blk0 < nb; blk0 += WARPS * 8) {       // eight loads on their way before the first block is split
-            float v[8], gm[8];
-            #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int blk = blk0 + j * WARPS;
+            for (int j = 0; j < kHeld; j++) {
+                const int blk = warp + j * WARPS;
                 v[j] = blk < nb ? p.x[blk * 32 + lane] : 0.f;
                 gm[j] = (p.gamma && blk < nb) ? p.gamma[blk * 32 + lane] : 1.f;
             }
+            float inv = 1.f;
+            if (p.gamma) {
+                float ss = 0.f;
+                #pragma unroll
+                for (int j = 0; j < kHeld; j++) ss += v[j] * v[j];
+                #pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) red[warp] = ss;
+                __syncthreads();
+                float total = 0.f;
+                #pragma unroll
+                for (int w = 0; w < WARPS; w++) total += red[w];
+                inv = rsqrtf(total / float(p.cols) + p.eps);
+            }
             #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int blk = blk0 + j * WARPS;
+            for (int j = 0; j < kHeld; j++) {
+                const int blk = warp + j * WARPS;
                 if (blk < nb) split_block(p.gamma ? v[j] * inv * gm[j] : v[j], lane, blk, nb, smem);
+            }
+        } else {
+            float inv = 1.f;
+            if (p.gamma) {
+                float ss = 0.f;
+                for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) { const float v = p.x[i]; ss += v * v; }
+                #pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) red[warp] = ss;
+                __syncthreads();
+                float total = 0.f;
+                #pragma unroll
+                for (int w = 0; w < WARPS; w++) total += red[w];
+                inv = rsqrtf(total / float(p.cols) + p.eps);
+            }
+            for (int blk0 = warp; blk0 < nb; blk0 += WARPS * 8) {       // eight loads on their way before the first block is split
+                float v[8], gm[8];
+                #pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int blk = blk0 + j * WARPS;
+                    v[j] = blk < nb ? p.x[blk * 32 + lane] : 0.f;
+                    gm[j] = (p.gamma && blk < nb) ? p.gamma[blk * 32 + lane] : 1.f;
+                }
+                #pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int blk = blk0 + j * WARPS;
+                    if (blk < nb) split_block(p.gamma ? v[j] * inv * gm[j] : v[j], lane, blk, nb, smem);
+                }
             }
         }
         cp_async_commit();
@@ -530,21 +558,6 @@ bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols) {
     return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 2, true).ok;
 }
 
-L2Prefetch gemv_q4_0_prefetch(const void * W, const void * W2, int64_t rows, int64_t cols, bool q4_k, int64_t budget_bytes) {
-    L2Prefetch h{};
-    if (budget_bytes <= 0 || !W) return h;
-    const RowSplit rs = row_split(rows, takes_tma(rows, cols, W2 ? 2 : 1, q4_k));
-    const int64_t row_bytes = cols / 32 * kBlockBytes;
-    const int64_t per_block = budget_bytes / (int64_t(rs.grid) * (W2 ? 2 : 1));
-    h.mat[0] = static_cast<const uint8_t *>(W);
-    h.mat[1] = static_cast<const uint8_t *>(W2);
-    h.row_bytes = uint32_t(row_bytes);
-    h.rows_q = rs.rows_q; h.rows_r = rs.rows_r; h.row_unit = rs.row_unit; h.grid = rs.grid;
-    h.head_rows = int32_t(std::min<int64_t>(std::max<int64_t>(per_block / row_bytes, 1), int64_t(rs.rows_q + 1) * rs.row_unit));
-    h.rows = rows;
-    return h;
-}
-
 size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }      // the kernel adds 4 bytes per block of its own in shared memory
 
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
@@ -553,8 +566,7 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error,
-                             const L2Prefetch * next) {
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error) {
     if (xq_out && (!out_counters || rows % 32 != 0)) return cudaErrorInvalidValue;
     // tensor copies when rows and chunks are whole 16-byte units (cols a multiple of 256) and the driver hands out the encoder; per-lane copies otherwise
     Maps maps{};
@@ -569,7 +581,7 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k, tma);
     if (!pl.ok) return cudaErrorInvalidValue;
     GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, error, y, bias, rows, int(cols), flags,
-                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u, L2Prefetch{}};
+                    pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u};
     if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover
     const int64_t row_bytes = cols / 32 * kBlockBytes;
@@ -580,7 +592,6 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     p.row_unit = rs.row_unit;
     p.rows_q = rs.rows_q;
     p.rows_r = rs.rows_r;
-    if (next) p.next = *next;
     p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
     p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
     if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, maps, tma, pl, grid, stream) : launch_stages<8, true>(p, maps, tma, pl, grid, stream);

@@ -245,6 +245,16 @@ __global__ void k_add(float * x, const float * y, int64_t n) {
 
 // ---------------------------------------------------------------- rotary embedding + cache write
 
+// cs[i] = (cos, sin)(st->pos * inv_freq[i]) for the head_dim / 2 rotary pairs, in double precision, rounded to f32: what every head of every layer of one
+// decode step rotates by, computed once per step instead of in every attention launch.
+__global__ void k_rope_table(const DevState * st, const double * inv_freq, float2 * cs, int pairs) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pairs) return;
+    double sd, cd;
+    sincos(double(st->pos) * inv_freq[i], &sd, &cd);
+    cs[i] = make_float2(float(cd), float(sd));
+}
+
 // grid (M), head_dim / 2 x (up to 4) threads: a thread owns rotary pair i and every fourth slot; slots are query heads (rotated in place), key heads
 // (rotated into the cache), value heads (copied). The angle pos * inv_freq[i] and its sine / cosine are computed once per thread in double precision, so that
 // positions in the thousands keep their low bits (rotate_pair, llama_kernels.h:513-518).
@@ -496,6 +506,12 @@ cudaError_t launch_dequantize(int dt, const void * blocks, int64_t rows, int64_t
 
 cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream) {
     k_add<<<unsigned(std::min<int64_t>((n + 255) / 256, sm_count() * 8)), 256, 0, stream>>>(x, y, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream) {
+    const int pairs = head_dim / 2;
+    k_rope_table<<<(pairs + 127) / 128, 128, 0, stream>>>(st, inv_freq, static_cast<float2 *>(cs), pairs);
     return cudaGetLastError();
 }
 

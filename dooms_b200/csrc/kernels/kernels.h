@@ -4,8 +4,6 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
-#include "l2_prefetch.cuh"
-
 namespace dooms {
 namespace cuda {
 
@@ -77,12 +75,14 @@ cudaError_t launch_attention_combine(const float * part, float * out, void * xq,
 // the new token's row (query, key and value heads). With inv_freq (head_dim / 2 rotary frequencies base^(-2i / head_dim)) the kernel rotates the query and
 // the key itself and writes key and value into the cache at st->pos (no launch_rope_store before it); without, q is used as it is, the cache is only read
 // and n_keys_fixed gives the number of positions. Leaves part[n_head][splits][2 + head_dim] for launch_attention_combine.
+// cs[i] = (cos, sin)(st->pos * inv_freq[i]) as float2 for the head_dim / 2 rotary pairs: one decode step's rotation, shared by its layers.
+cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream);
 bool attention_gqa_supported(const AttnShape & s);
 int attention_gqa_splits(int n_head_kv, int n_ctx);
 // With counters (n_head_kv zeroed ints, left zeroed) the last block of each key/value head merges the ranges itself into out (and xq): no combine launch.
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
                                  int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream,
-                                 const L2Prefetch * next = nullptr);   // next: what to bring into L2 for the kernels that follow
+                                 const void * rope_cs = nullptr);   // rope_cs: launch_rope_table's output for st->pos, used instead of computing the angles
 
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
 // out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.
@@ -107,9 +107,7 @@ cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, 
 bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows, int64_t cols);
 // gamma (optional): the input is RMS-normalized in the block's prologue first, as for launch_gemv_q4_0.
 cudaError_t launch_gemv_blocks(int dt, const void * W, const void * W2, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream, const L2Prefetch * next = nullptr);
-// What a launch_gemv_blocks call on this matrix (pair) reads first, for the kernel before it to bring into L2: up to budget_bytes in all.
-L2Prefetch gemv_blocks_prefetch(int dt, const void * W, const void * W2, int64_t rows, int64_t cols, int64_t budget_bytes);
+                               int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
 
 // The input vector split into int8 limbs: quantized_x_bytes(cols) bytes at a 16-byte aligned address, written by launch_quantize_x.
 size_t quantized_x_bytes(int64_t cols);
@@ -125,10 +123,7 @@ bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols);
 // following projection that takes it as xq; the block that completes a 32-row group of y splits it.
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
                              int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr,
-                             int32_t * error = nullptr,    // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
-                             const L2Prefetch * next = nullptr);
-// What a launch_gemv_q4_0 call on this matrix (pair) reads first, for the kernel before it to bring into L2: up to budget_bytes in all.
-L2Prefetch gemv_q4_0_prefetch(const void * W, const void * W2, int64_t rows, int64_t cols, bool q4_k, int64_t budget_bytes);
+                             int32_t * error = nullptr);   // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;

@@ -63,6 +63,8 @@ def oracle() -> C.CDLL:
         o.oracle_position.argtypes = [C.c_void_p]
         o.oracle_set_fast.argtypes = [C.c_void_p, C.c_int32]
         o.oracle_set_round_operands.argtypes = [C.c_void_p, C.c_int32]
+        o.oracle_set_threads.restype = C.c_int32
+        o.oracle_set_threads.argtypes = [C.c_int32]
         o.oracle_eval_embeddings.restype = C.c_int32
         o.oracle_eval_embeddings.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
         o.oracle_eval_tokens.restype = C.c_int32
@@ -70,6 +72,12 @@ def oracle() -> C.CDLL:
         o.oracle_embedding.argtypes = [C.c_void_p, C.c_int32, C.c_void_p]
         _oracle = o
     return _oracle
+
+
+def set_threads(n: int) -> int:
+    """Threads the checker's parallel loops use from now on (0: leave as is); returns the count in effect. torch.distributed.run exports
+    OMP_NUM_THREADS=1 to its workers, which would otherwise leave the timed CPU baseline on one core."""
+    return int(oracle().oracle_set_threads(int(n)))
 
 
 def dequantize(dtype: int, blocks: np.ndarray, n: int) -> np.ndarray:

@@ -25,6 +25,12 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef __AVX2__
+#include <immintrin.h>
+#endif
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 #include "dooms_cuda.h"
 
@@ -105,6 +111,7 @@ static float elem(int dt, const uint8_t * row, int64_t i) {
 
 /* n elements of one row (n a multiple of the block size). */
 ORACLE_API void oracle_dequantize(int32_t dtype, const void * blocks, int64_t n, float * out) {
+    #pragma omp parallel for schedule(static) if (n >= (1 << 16))
     for (int64_t i = 0; i < n; i++) out[i] = elem(dtype, (const uint8_t *)blocks, i);
 }
 
@@ -195,7 +202,163 @@ ORACLE_API void oracle_destroy(oracle_decoder * d) {
 ORACLE_API void oracle_reset(oracle_decoder * d) { d->pos = 0; }
 ORACLE_API int32_t oracle_position(const oracle_decoder * d) { return d->pos; }
 ORACLE_API void oracle_set_fast(oracle_decoder * d, int32_t fast) { d->fast = fast; }
+/* Threads of the parallel loops from here on (a launcher may have exported OMP_NUM_THREADS=1 for its workers); returns the count in effect. */
+ORACLE_API int32_t oracle_set_threads(int32_t n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return (int32_t)omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 ORACLE_API void oracle_set_round_operands(oracle_decoder * d, int32_t on) { d->round_operands = on; }
+
+/* ---- The timed CPU baseline's one-token projection: f32 quantized dot products, the folding of the reference's Q::dot functions
+ * (llama_kernels.h:1036-1040, 1065-1069, 1090-1094, 1132-1140, 1175-1183): the integer quants are multiplied with the input as they are, a block's scale is
+ * applied once per block (sub-block), and the offsets (q4_0: -8, q5_0: -16, q6_K: -32, q4_K: -dmin m) come in through the sums of the input's 32- (16-)
+ * element groups, computed once per call. Eight-wide f32 FMAs when the compiler targets AVX2. ---- */
+#ifdef __AVX2__
+typedef __m256 vec8;
+static inline vec8 v8_zero(void) { return _mm256_setzero_ps(); }
+static inline vec8 v8_u8(const uint8_t * q) { return _mm256_cvtepi32_ps(_mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i *)q))); }
+static inline vec8 v8_i8(const int8_t * q) { return _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i *)q))); }
+static inline vec8 v8_fma_x(vec8 q, const float * x, vec8 acc) { return _mm256_fmadd_ps(q, _mm256_loadu_ps(x), acc); }
+static inline vec8 v8_fma_s(float s, vec8 v, vec8 acc) { return _mm256_fmadd_ps(_mm256_set1_ps(s), v, acc); }
+static inline float v8_sum(vec8 v) {
+    __m128 a = _mm_add_ps(_mm256_castps256_ps128(v), _mm256_extractf128_ps(v, 1));
+    a = _mm_add_ps(a, _mm_movehl_ps(a, a));
+    a = _mm_add_ss(a, _mm_shuffle_ps(a, a, 1));
+    return _mm_cvtss_f32(a);
+}
+#else
+typedef struct { float v[8]; } vec8;
+static inline vec8 v8_zero(void) { vec8 r; for (int i = 0; i < 8; i++) r.v[i] = 0.f; return r; }
+static inline vec8 v8_u8(const uint8_t * q) { vec8 r; for (int i = 0; i < 8; i++) r.v[i] = (float)q[i]; return r; }
+static inline vec8 v8_i8(const int8_t * q) { vec8 r; for (int i = 0; i < 8; i++) r.v[i] = (float)q[i]; return r; }
+static inline vec8 v8_fma_x(vec8 q, const float * x, vec8 acc) { for (int i = 0; i < 8; i++) acc.v[i] += q.v[i] * x[i]; return acc; }
+static inline vec8 v8_fma_s(float s, vec8 v, vec8 acc) { for (int i = 0; i < 8; i++) acc.v[i] += s * v.v[i]; return acc; }
+static inline float v8_sum(vec8 v) { float s = 0.f; for (int i = 0; i < 8; i++) s += v.v[i]; return s; }
+#endif
+
+/* sum of q[0..n) * x[0..n), n a multiple of 8, quants as unsigned / signed bytes */
+static inline vec8 dot_u8(const uint8_t * q, const float * x, int n, vec8 acc) { for (int i = 0; i < n; i += 8) acc = v8_fma_x(v8_u8(q + i), x + i, acc); return acc; }
+static inline vec8 dot_i8(const int8_t * q, const float * x, int n, vec8 acc) { for (int i = 0; i < n; i += 8) acc = v8_fma_x(v8_i8(q + i), x + i, acc); return acc; }
+
+/* The 16 quant bytes of a q4_0 / q5_0 block as 32 values 0..15: low nibbles are elements 0..15, high nibbles 16..31. */
+static inline void nibbles32(const uint8_t * qs, uint8_t * q) {
+#ifdef __AVX2__
+    const __m128i v = _mm_loadu_si128((const __m128i *)qs), m = _mm_set1_epi8(15);
+    _mm_storeu_si128((__m128i *)q, _mm_and_si128(v, m));
+    _mm_storeu_si128((__m128i *)(q + 16), _mm_and_si128(_mm_srli_epi16(v, 4), m));
+#else
+    for (int j = 0; j < 16; j++) { q[j] = qs[j] & 15u; q[16 + j] = qs[j] >> 4; }
+#endif
+}
+/* bit i of b as 16 or 0 in byte i */
+static inline uint64_t spread_bits_16(uint8_t b) {
+    uint64_t x = ((uint64_t)b * 0x0101010101010101ULL) & 0x8040201008040201ULL;
+    x = ((x + 0x7F7F7F7F7F7F7F7FULL) >> 7) & 0x0101010101010101ULL;
+    return x << 4;
+}
+
+/* One row times x. xs16: the sums of x over groups of 16 elements. */
+static float row_dot_fast(int dt, const uint8_t * row, const float * x, const float * xs16, int64_t K) {
+    vec8 acc = v8_zero();
+    float off = 0.f;
+    switch (dt) {
+        case DOOMS_Q4_0:
+            for (int64_t b = 0; b < K / 32; b++) {
+                const uint8_t * p = row + b * 18;
+                uint8_t q[32];
+                nibbles32(p + 2, q);
+                const float d = ld_half(p);
+                acc = v8_fma_s(d, dot_u8(q, x + 32 * b, 32, v8_zero()), acc);
+                off += d * (xs16[2 * b] + xs16[2 * b + 1]);
+            }
+            return v8_sum(acc) - 8.f * off;
+        case DOOMS_Q5_0:
+            for (int64_t b = 0; b < K / 32; b++) {
+                const uint8_t * p = row + b * 22;
+                uint8_t q[32];
+                nibbles32(p + 6, q);
+                for (int j = 0; j < 4; j++) {          /* the fifth bits: byte j of qh covers elements 8j .. 8j+7 */
+                    uint64_t lo, hb = spread_bits_16(p[2 + j]);
+                    memcpy(&lo, q + 8 * j, 8);
+                    lo |= hb;
+                    memcpy(q + 8 * j, &lo, 8);
+                }
+                const float d = ld_half(p);
+                acc = v8_fma_s(d, dot_u8(q, x + 32 * b, 32, v8_zero()), acc);
+                off += d * (xs16[2 * b] + xs16[2 * b + 1]);
+            }
+            return v8_sum(acc) - 16.f * off;
+        case DOOMS_Q8_0:
+            for (int64_t b = 0; b < K / 32; b++) {
+                const uint8_t * p = row + b * 34;
+                acc = v8_fma_s(ld_half(p), dot_i8((const int8_t *)p + 2, x + 32 * b, 32, v8_zero()), acc);
+            }
+            return v8_sum(acc);
+        case DOOMS_Q4_K:
+            for (int64_t b = 0; b < K / 256; b++) {
+                const uint8_t * p = row + b * 144;
+                const float d = ld_half(p), dmin = ld_half(p + 2);
+                for (unsigned c = 0; c < 8; c++) {
+                    float sc, m;
+                    scale_min_k4(c, p + 4, &sc, &m);
+                    uint8_t q[32];
+                    const uint8_t * qs = p + 16 + 32 * (c / 2);
+                    if (c & 1u) for (int j = 0; j < 32; j++) q[j] = qs[j] >> 4;
+                    else for (int j = 0; j < 32; j++) q[j] = qs[j] & 15u;
+                    acc = v8_fma_s(d * sc, dot_u8(q, x + 256 * b + 32 * c, 32, v8_zero()), acc);
+                    off += dmin * m * (xs16[16 * b + 2 * c] + xs16[16 * b + 2 * c + 1]);
+                }
+            }
+            return v8_sum(acc) - off;
+        case DOOMS_Q6_K:
+            for (int64_t b = 0; b < K / 256; b++) {
+                const uint8_t * p = row + b * 210;
+                const float d = ld_half(p + 208);
+                const int8_t * scales = (const int8_t *)(p + 192);
+                for (unsigned h = 0; h < 2; h++) {
+                    for (unsigned k = 0; k < 4; k++) {
+                        uint8_t q[32];
+                        const uint8_t * ql = p + 64 * h + (k & 1u) * 32, * qh = p + 128 + 32 * h;
+                        for (int l = 0; l < 32; l++) q[l] = (uint8_t)((k < 2 ? (ql[l] & 15u) : (ql[l] >> 4)) | (((qh[l] >> (2 * k)) & 3u) << 4));
+                        const float * xb = x + 256 * b + 128 * h + 32 * k;
+                        const int64_t g16 = 16 * b + 8 * h + 2 * k;
+                        for (unsigned s = 0; s < 2; s++) {
+                            const float a = d * (float)scales[8 * h + s + 2 * k];
+                            acc = v8_fma_s(a, dot_u8(q + 16 * s, xb + 16 * s, 16, v8_zero()), acc);
+                            off += a * xs16[g16 + s];
+                        }
+                    }
+                }
+            }
+            return v8_sum(acc) - 32.f * off;
+        default: {
+            float a = 0.f;
+            for (int64_t k = 0; k < K; k++) a += elem(dt, row, k) * x[k];
+            return a;
+        }
+    }
+}
+
+/* y[row0 + r] (+)= W[r] . x for one input row, on all threads. */
+static void matvec_fast(const mat_t * W, const double * X, double * Y, int64_t row0, int accumulate) {
+    const int64_t K = W->cols, RB = row_bytes(W->dtype, K);
+    float * x = (float *)malloc(sizeof(float) * (size_t)(K + K / 16 + 1));
+    float * xs16 = x + K;
+    for (int64_t k = 0; k < K; k++) x[k] = (float)X[k];
+    for (int64_t g = 0; g < K / 16; g++) { float s = 0.f; for (int j = 0; j < 16; j++) s += x[16 * g + j]; xs16[g] = s; }
+    #pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < W->rows; r++) {
+        const double acc = (double)row_dot_fast(W->dtype, W->data + r * RB, x, xs16, K);
+        double * y = Y + row0 + r;
+        *y = accumulate ? *y + acc : acc;
+    }
+    free(x);
+}
 
 /* Y[m][row0 + r] (+)= W[r] . X[m]   for M rows of X (stride xs) -> Y (stride ys). Reference::matvec (test_metal_llama_decoder.cpp:177-181), one weight
  * row dequantized at a time. */
@@ -203,6 +366,7 @@ static void matmul(const oracle_decoder * d, const mat_t * W, const double * X, 
                    int round_ops) {
     const int64_t K = W->cols, RB = row_bytes(W->dtype, K);
     const int fast = d->fast;
+    if (fast && M == 1 && !round_ops && K % 32 == 0) { matvec_fast(W, X, Y, row0, accumulate); return; }
     #pragma omp parallel
     {
         float * w = (float *)malloc(sizeof(float) * (size_t)K);
@@ -303,7 +467,11 @@ ORACLE_API int32_t oracle_eval_embeddings(oracle_decoder * d, const float * emb,
         for (int64_t m = 0; m < M; m++) {
             for (int64_t h = 0; h < nh; h++) {
                 const int64_t kvh = h / (nh / nkv), np = p0 + m + 1;
-                const double * q = qkv + m * W3 + h * hd;
+                const double * q0 = qkv + m * W3 + h * hd;
+                double q[512];
+                /* the prefill tiles hold the rotated query as f16 and the probabilities as f16 relative to the running maximum, while the normalizing sum
+                 * adds the unrounded exponentials (attention_prefill, llama_kernels.h:660, 708-713) */
+                for (int64_t e = 0; e < hd; e++) q[e] = round_ops ? (double)round_to_half((float)q0[e]) : q0[e];
                 double * sc = (double *)malloc(sizeof(double) * (size_t)np);
                 double mx = -1e300;
                 for (int64_t j = 0; j < np; j++) {
@@ -314,7 +482,7 @@ ORACLE_API int32_t oracle_eval_embeddings(oracle_decoder * d, const float * emb,
                     if (sc[j] > mx) mx = sc[j];
                 }
                 double sum = 0;
-                for (int64_t j = 0; j < np; j++) { sc[j] = exp(sc[j] - mx); sum += sc[j]; }
+                for (int64_t j = 0; j < np; j++) { sc[j] = exp(sc[j] - mx); sum += sc[j]; if (round_ops) sc[j] = (double)round_to_half((float)sc[j]); }
                 for (int64_t e = 0; e < hd; e++) {
                     double a = 0;
                     for (int64_t j = 0; j < np; j++) a += sc[j] * (double)vc[(size_t)j * (size_t)KV + (size_t)(kvh * hd + e)];

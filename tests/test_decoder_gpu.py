@@ -37,6 +37,24 @@ def check_prompt_and_generation(path, n_ctx, n_batch, n_gen, depth, batched_tol=
     dec.close()
 
 
+def check_long_prompt(dec, path, n_ctx, prompt, want):
+    """dec has just evaluated `prompt` in one call; `want`: the exact checker's logits. The reference's bound for a prompt in one call (rel-L2 < 3e-3), taken
+    once: against the checker that rounds the operands where the reference's prefill tiles do, and against the exact checker as well unless that
+    rounding alone already puts the checker's own rounded variant past the bound (on prompts of hundreds of tokens it reaches ~2.5e-3 on the mixed model;
+    the reference's 3e-3 held for its seeds) - then the product may not be further out than the rounding itself, by more than a fifth. The decode step
+    after it is held to the rounded checker continuing on the cache that prefill left."""
+    orr = ob.OracleDecoder(path, n_ctx, round_operands=True)
+    rounded = orr.eval_tokens(prompt)
+    got = dec.logits()
+    assert rel_l2(got, rounded) < BATCHED_TOL
+    assert rel_l2(got, want) < max(BATCHED_TOL, 1.2 * rel_l2(rounded, want)), (rel_l2(got, want), rel_l2(rounded, want))
+    assert dec.pending_token() == ob.argmax(want)
+    nxt = ob.argmax(want)
+    want_next = orr.eval_tokens([nxt])
+    dec.eval_tokens([nxt])
+    assert rel_l2(dec.logits(), want_next) < BATCHED_TOL
+
+
 def test_prompt_logits_and_greedy_generation_match_the_oracle(model_dir):
     path = write(model_dir, "tiny_llama", tiny_f16(), 1)
     check_prompt_and_generation(path, 128, 64, 24, 3)
@@ -74,20 +92,9 @@ def test_longer_prompts_in_one_call(model_dir, plan):
         prompt = [(i * 13 + 5) % 50 for i in range(n)]
         o = ob.OracleDecoder(path, 400)
         want = o.eval_tokens(prompt)
-        # On prompts this long the half-rounded operand tiles alone put the checker's own rounded variant ~2.5e-3 from the exact one on the mixed model
-        # (the reference's 3e-3 held for its seeds). So: within 3e-3 of the checker WITH the reference's operand rounding, and within twice that of the
-        # exact one.
-        rounded = ob.OracleDecoder(path, 400, round_operands=True).eval_tokens(prompt)
         dec.reset()
         dec.eval_tokens(prompt)
-        got = dec.logits()
-        assert rel_l2(got, rounded) < BATCHED_TOL
-        assert rel_l2(got, want) < 2 * BATCHED_TOL
-        assert dec.pending_token() == ob.argmax(want)
-        nxt = ob.argmax(want)
-        want = o.eval_tokens([nxt])
-        dec.eval_tokens([nxt])
-        assert rel_l2(dec.logits(), want) < 2 * BATCHED_TOL
+        check_long_prompt(dec, path, 400, prompt, want)
 
 
 @pytest.mark.parametrize("qwen", [False, True])
@@ -239,16 +246,8 @@ def test_chunks_of_512_tokens_and_more_take_the_pre_dequantized_gemm(model_dir, 
     prompt = [(i * 7 + 3) % 50 for i in range(700)]
     o = ob.OracleDecoder(path, 720)
     want = o.eval_tokens(prompt)
-    rounded = ob.OracleDecoder(path, 720, round_operands=True).eval_tokens(prompt)
     dec.eval_tokens(prompt)
-    got = dec.logits()
-    assert rel_l2(got, rounded) < BATCHED_TOL
-    assert rel_l2(got, want) < 2 * BATCHED_TOL
-    assert dec.pending_token() == ob.argmax(want)
-    nxt = ob.argmax(want)
-    want = o.eval_tokens([nxt])
-    dec.eval_tokens([nxt])
-    assert rel_l2(dec.logits(), want) < 2 * BATCHED_TOL
+    check_long_prompt(dec, path, 720, prompt, want)
     dec.close()
 
 

@@ -184,3 +184,22 @@ def test_checker_matches_the_reference_class(model_dir, name):
     assert rel_l2(o2.eval_tokens(K_PROMPT), ref.eval_tokens(K_PROMPT)) < 1e-12
     # embeddings: Reference::embedding and the checker's row lookup agree exactly
     assert np.array_equal(ref.embedding(7), o.embedding(7).astype(np.float64))
+
+
+@pytest.mark.parametrize("name,round_operands", [("llama_f16", False), ("qwen_f16", False), ("Q4_K_M-like mix", False), ("Q4_K_M-like mix", True), ("q4_0", True)])
+def test_streaming_checker_matches_the_checker(model_dir, name, round_operands):
+    """The layer-at-a-time restatement used at the configurations' real sizes (oracle/streaming.py) against oracle.c: a prompt in one call, single
+    positions after it, with and without the prefill tiles' operand rounding. Both run in double; only the order of the sums differs."""
+    from oracle.streaming import StreamingOracle
+    spec = {"llama_f16": tiny_f16(), "qwen_f16": tiny_f16(qwen=True)}.get(name) or synth.tiny_spec(QUANT_PLANS[name])
+    path = write(model_dir, "stream_" + name.replace(" ", "_"), spec, 31)
+    prompt = [(i * 13 + 5) % 50 for i in range(45)]          # the reference's long-prompt recipe (test_metal_llama_decoder.cpp:440)
+    o = ob.OracleDecoder(path, 64, round_operands=round_operands)
+    s = StreamingOracle(path, 64, round_operands=round_operands)
+    want, got = o.eval_tokens(prompt), s.eval_tokens(prompt)
+    # a sum that lands on the other side of an f16 rounding boundary moves one operand by an ulp: far below every tolerance in use, but not 1e-12
+    assert rel_l2(got, want) < (1e-5 if round_operands else 1e-11)
+    for t in (7, 7, 31):
+        want, got = o.eval_tokens([t]), s.eval_tokens([t])
+        assert rel_l2(got, want) < (1e-5 if round_operands else 1e-11)
+        assert ob.argmax(got) == ob.argmax(want)
