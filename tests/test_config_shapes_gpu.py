@@ -12,8 +12,8 @@ Bounds are the benchmark's own for logits, 2e-2 absolute + 1e-2 relative, taken 
   * greedy tokens are equal, except where the checker's two best logits are closer than the bound.
 The exception: the 2048-token prompt through all 32 layers of the 8B shape. Two implementations of the same f16-operand arithmetic do not stay bit-close:
 after a few layers their activations differ by more than a fraction of an f16 ulp, from then on they round independently, and their difference grows to
-about 0.7 of what the rounding itself does to the exact result (measured: 0.025 max-abs between product and rounding checker, 0.030 between rounding and
-exact checker, on 128 256 logits). There the element-wise bound is asserted for all but one logit in ten thousand, none further out than 1.5 times the
+about 0.7 of what the rounding itself does to the exact result (measured: 0.025 max-abs between product and rounding checker, 0.040 between rounding and
+exact checker, on 128 256 logits). There the element-wise bound is asserted for all but one logit in ten thousand, none further out than 1.25 times the
 bound, together with rel-L2 < 1e-2; everywhere else it is asserted for every logit.
 With DOOMS_PARITY_FIGURES=<file> the measured maxima are appended to that file, one JSON line per case."""
 import dataclasses
@@ -70,7 +70,7 @@ def assert_close(got, want, every_logit, context):
         assert within(got, want), context
     else:
         worst, outside = excess(got, want)
-        assert rel_l2(got, want) < REL_TOL and outside <= 1e-4 and worst <= 1.5, (worst, outside, context)
+        assert rel_l2(got, want) < REL_TOL and outside <= 1e-4 and worst <= 1.25, (worst, outside, context)
 
 
 def record(case, **figures):
