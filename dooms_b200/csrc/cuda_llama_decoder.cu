@@ -89,6 +89,14 @@ struct CudaLlamaDecoder::Impl {
     void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 512 tokens or more dequantize a matrix once per call
     size_t w16_bytes = 0;
     int * split_counters = nullptr; // one per 32 rows of h: rows written by the gate/up GEMV's blocks (zero between launches)
+    // The norm between two projections of a decode step, folded into the producer (kernels.h, GemvNormLink): the projection that finishes the residual row
+    // x leaves x * (the next norm's gains) split in xq2 and its blocks' sums of squares in norm_ss; the next projection takes both instead of reading,
+    // normalizing and splitting x in every one of its blocks.
+    uint8_t * xq2 = nullptr;
+    float * norm_ss = nullptr;
+    int * norm_counters = nullptr;  // one per 32 rows of x
+    bool link_ready = false;        // xq2 / norm_ss describe the current x
+    int link_blocks = 0;
     int32_t pos = 0;
     bool has_pending = false;
     // decode graph
@@ -119,7 +127,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, rope_cs, (void *)attn_counters, (void *)split_counters, w16,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, rope_cs, (void *)attn_counters, (void *)split_counters, (void *)xq2, (void *)norm_ss, (void *)norm_counters, w16,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -195,14 +203,24 @@ struct CudaLlamaDecoder::Impl {
             xq_of = in;
         }
     }
-    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags) {
+    // next_gamma: the gains of the norm that the next projection applies to `out` (= x); given when that projection can take the norm from here.
+    void matvec(const char * kind, const MatDev & w, const float * in, const float * gamma, float * out, const float * bias, uint32_t flags,
+                const float * next_gamma = nullptr) {
+        const bool writes_x = out == x;
         if (fast(w)) {
-            prepare_fast_input(in, gamma, w.cols);
-            const void * split = (xq_of == in && !gamma) ? xq : nullptr;
-            run(kind, [&] { return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream, nullptr, nullptr,
-                                                               host_error); });
+            const bool consume = gamma && in == x && link_ready;
+            const bool produce = next_gamma && writes_x && tp == 1 && w.rows % 32 == 0 && norm_counters;
+            if (!consume) prepare_fast_input(in, gamma, w.cols);
+            const void * split = consume ? xq2 : (xq_of == in && !gamma) ? xq : nullptr;
+            const cuda::GemvNormLink link{produce ? next_gamma : nullptr, produce ? norm_ss : nullptr, consume ? norm_ss : nullptr, consume ? link_blocks : 0};
+            run(kind, [&] {
+                return cuda::launch_gemv_q4_0(w.ptr, nullptr, split, in, consume ? nullptr : gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, w.dt == DType::Q4_K, stream,
+                                              produce ? xq2 : nullptr, produce ? norm_counters : nullptr, host_error, &link);
+            });
+            if (writes_x) { link_ready = produce; link_blocks = cuda::gemv_q4_0_blocks(w.rows, w.cols, false, w.dt == DType::Q4_K); }
             return;
         }
+        if (writes_x) link_ready = false;
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
             run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
             return;
@@ -221,14 +239,16 @@ struct CudaLlamaDecoder::Impl {
     }
     void gate_up(const MatDev & wg, const MatDev & wu, const float * in, const float * gamma, float * out, bool down_takes_split) {
         if (fast(wg) && fast(wu)) {
-            prepare_fast_input(in, gamma, wg.cols);
-            const void * split = (xq_of == in && !gamma) ? xq : nullptr;
+            const bool consume = gamma && in == x && link_ready;
+            if (!consume) prepare_fast_input(in, gamma, wg.cols);
+            const void * split = consume ? xq2 : (xq_of == in && !gamma) ? xq : nullptr;
+            const cuda::GemvNormLink link{nullptr, nullptr, consume ? norm_ss : nullptr, consume ? link_blocks : 0};
             // a result that the integer GEMV reads next (ffn_down) is left split by the blocks that complete its 32-row groups: no split launch, and no
             // split in the next kernel's prologue
             const bool split_out = down_takes_split && wg.rows % 32 == 0 && split_counters;
             run("gate_up", [&] {
-                return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
-                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error);
+                return cuda::launch_gemv_q4_0(wg.ptr, wu.ptr, split, in, consume ? nullptr : gamma, cfg.rms_eps, out, nullptr, wg.rows, wg.cols, 0u, wg.dt == DType::Q4_K, stream,
+                                              split_out ? xq : nullptr, split_out ? split_counters : nullptr, host_error, &link);
             });
             xq_of = split_out ? out : nullptr;
             return;
@@ -340,6 +360,7 @@ struct CudaLlamaDecoder::Impl {
         const int E = cfg.n_embd;
         const AttnShape as = attn_shape();
         const bool single = tp == 1;
+        link_ready = false;      // x was just written by the embedding (or by the caller)
         // one position: its rotary angles are the same for every head of every layer
         if (M == 1 && gqa) run("rope_table", [&] { return cuda::launch_rope_table(state, inv_freq, rope_cs, cfg.head_dim, stream); });
         for (size_t l = 0; l < layers.size(); l++) {
@@ -368,11 +389,20 @@ struct CudaLlamaDecoder::Impl {
                     run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
                 }
                 xq_of = split_attn ? attn : nullptr;
-                matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags);
+                // the projections that finish x also prepare the norm of the projection after them, when that one is a kernel that can take it
+                const bool gate_up_takes = fast(L.ffn_gate) && fast(L.ffn_up);
+                matvec("attn_output", L.attn_output, attn, nullptr, o_dst, nullptr, o_flags, gate_up_takes ? L.ffn_norm : nullptr);
                 xq_of = nullptr;
                 reduce_into_x(1);
                 gate_up(L.ffn_gate, L.ffn_up, x, L.ffn_norm, h, fast(L.ffn_down));
-                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags);
+                const float * after_gamma = nullptr;
+                if (l + 1 < layers.size()) {
+                    const LayerDev & N = layers[l + 1];
+                    if (std::all_of(N.qkv.begin(), N.qkv.end(), [&](const QkvPart & q) { return fast(q.w); })) after_gamma = N.attn_norm;
+                } else if (output.rows > 0 && fast(output)) {
+                    after_gamma = output_norm;
+                }
+                matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags, after_gamma);
                 reduce_into_x(1);
             } else if (use_tc) {
                 // (the chunk's norm above wrote xn16)
@@ -697,6 +727,10 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     cudaMemset(m.attn_counters, 0, size_t(std::max(1, m.nkv)) * sizeof(int));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.split_counters), (size_t(m.ff) / 32 + 1) * sizeof(int), "the split counters"));
     cudaMemset(m.split_counters, 0, (size_t(m.ff) / 32 + 1) * sizeof(int));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq2), cuda::quantized_x_bytes(E) + 64, "the split residual row"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.norm_ss), 4096 * sizeof(float), "the sums of squares of the residual row"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.norm_counters), (size_t(E) / 32 + 1) * sizeof(int), "the residual split counters"));
+    cudaMemset(m.norm_counters, 0, (size_t(E) / 32 + 1) * sizeof(int));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
                                     "the split projection input"));
     if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {

@@ -267,41 +267,69 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
     // weights of the ranges, per head: warp w takes head w (the stage buffers are free now and hold them)
     float * wts = reinterpret_cast<float *>(stages);            // [GP][splits]
     float * tot = wts + GP * p.splits;                          // [GP]
+    // Every load of the merge is issued before anything waits on one: the partial results sit in L2, a round trip there costs more than all the
+    // arithmetic of the merge, and loops that load and add split by split would pay it once per split.
     if (warp < G) {
         const float * base = p.part + int64_t(kvh * G + warp) * p.splits * (2 + D);
+        constexpr int kPerLane = 8;                                   // ranges per lane held in registers: up to 256 ranges
+        float2 ml[kPerLane];
+        #pragma unroll
+        for (int k = 0; k < kPerLane; k++) {
+            const int sp = lane + 32 * k;
+            ml[k] = sp < p.splits ? __ldcg(reinterpret_cast<const float2 *>(base + sp * (2 + D))) : make_float2(-CUDART_INF_F, 0.f);
+        }
         float mx = -CUDART_INF_F;
-        for (int sp = lane; sp < p.splits; sp += 32) if (__ldcg(base + sp * (2 + D) + 1) > 0.f) mx = fmaxf(mx, __ldcg(base + sp * (2 + D)));
+        #pragma unroll
+        for (int k = 0; k < kPerLane; k++) if (ml[k].y > 0.f) mx = fmaxf(mx, ml[k].x);
         #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float total = 0.f;
-        for (int sp = lane; sp < p.splits; sp += 32) {
-            const float l = __ldcg(base + sp * (2 + D) + 1);
-            const float w = l > 0.f ? expf(__ldcg(base + sp * (2 + D)) - mx) : 0.f;      // an empty range weighs nothing
-            wts[warp * p.splits + sp] = w;
-            total += l * w;
+        #pragma unroll
+        for (int k = 0; k < kPerLane; k++) {
+            const int sp = lane + 32 * k;
+            if (sp < p.splits) {
+                const float w = ml[k].y > 0.f ? expf(ml[k].x - mx) : 0.f;      // an empty range weighs nothing
+                wts[warp * p.splits + sp] = w;
+                total += ml[k].y * w;
+            }
         }
         #pragma unroll
         for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         if (lane == 0) tot[warp] = total;
     }
-    __syncthreads();
+    constexpr int kChunk = 16;                                        // ranges whose values are in flight together, per output
+    float v[MERGE_IT][kChunk];
+    float merged[MERGE_IT];
+    #pragma unroll
+    for (int it = 0; it < MERGE_IT; it++) merged[it] = 0.f;
+    for (int sp0 = 0; sp0 < p.splits; sp0 += kChunk) {
+        #pragma unroll
+        for (int it = 0; it < MERGE_IT; it++) {
+            const int idx = tid + it * kThreads;            // (head, element): a warp holds 32 consecutive elements of one head
+            const int hq = idx / D, d = idx % D;
+            const bool mine = idx < GP * D && hq < G;
+            const float * col = p.part + int64_t(kvh * G + (mine ? hq : 0)) * p.splits * (2 + D) + 2 + d;
+            #pragma unroll
+            for (int k = 0; k < kChunk; k++) v[it][k] = (mine && sp0 + k < p.splits) ? __ldcg(col + (sp0 + k) * (2 + D)) : 0.f;
+        }
+        if (sp0 == 0) __syncthreads();                                // the weights are in shared memory (the first chunk's loads are already on their way)
+        #pragma unroll
+        for (int it = 0; it < MERGE_IT; it++) {
+            const int idx = tid + it * kThreads;
+            const int hq = idx / D;
+            if (idx < GP * D && hq < G) {
+                const float * w = wts + hq * p.splits + sp0;
+                #pragma unroll
+                for (int k = 0; k < kChunk; k++) if (sp0 + k < p.splits) merged[it] += v[it][k] * w[k];      // an empty range's values are finite (zeros), its weight 0
+            }
+        }
+    }
     #pragma unroll
     for (int it = 0; it < MERGE_IT; it++) {
-        const int idx = tid + it * kThreads;            // (head, element): a warp holds 32 consecutive elements of one head
+        const int idx = tid + it * kThreads;
         const int hq = idx / D, d = idx % D;
         if (idx < GP * D && hq < G) {
-            const float * col = p.part + int64_t(kvh * G + hq) * p.splits * (2 + D) + 2 + d;
-            const float * w = wts + hq * p.splits;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            int sp = 0;
-            for (; sp + 4 <= p.splits; sp += 4) {       // independent loads: an empty range's values are finite (zeros) and its weight is 0
-                a0 += __ldcg(col + (sp + 0) * (2 + D)) * w[sp + 0];
-                a1 += __ldcg(col + (sp + 1) * (2 + D)) * w[sp + 1];
-                a2 += __ldcg(col + (sp + 2) * (2 + D)) * w[sp + 2];
-                a3 += __ldcg(col + (sp + 3) * (2 + D)) * w[sp + 3];
-            }
-            for (; sp < p.splits; sp++) a0 += __ldcg(col + sp * (2 + D)) * w[sp];
-            const float r = ((a0 + a1) + (a2 + a3)) / tot[hq];
+            const float r = merged[it] / tot[hq];
             p.out[(kvh * G + hq) * D + d] = r;
             if (p.xq) split_block(r, lane, ((kvh * G + hq) * D + d) / 32, p.s.n_head * D / 32, p.xq);
         }

@@ -48,6 +48,14 @@ struct GemvQ40Params {
     // they have written per 32-row group in out_counters (rows / 32 zeroed ints, left zeroed); whoever completes a group splits it.
     uint8_t * xq_out;
     int * out_counters;
+    // The RMS norm of the NEXT projection, moved to where its input is produced (both optional, with xq_out): the split that goes to xq_out is of
+    // y[i] * gamma_out[i], and block b leaves the sum of its rows' y^2 in ss_out[b]. The consumer then takes xq as its input and ss_in (the producer's
+    // ss_out, ss_n entries) and multiplies its own results by rsqrt(sum(ss_in) / cols + eps): W (s u) = s (W u), so the scale factor of the norm can wait
+    // until after the product, and no block has to read, normalize and split the whole input for itself again.
+    const float * gamma_out;
+    float * ss_out;
+    const float * ss_in;
+    int ss_n;
     int32_t * error;        // optional mapped host word: set to 4 when a bounded wait for a tensor copy ran out (TMA variant)
     float * y;
     const float * bias;
@@ -264,9 +272,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
+    __shared__ float norm_scale;
     if (p.xq) {
         for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
         cp_async_commit();
+        if (warp == 0) {
+            // the producer's per-block sums of squares, added in a fixed order (lane l takes entries l, l + 32, ...; then the shuffle tree)
+            float ss = 0.f;
+            for (int i = lane; i < p.ss_n; i += 32) ss += __ldcg(p.ss_in + i);
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) norm_scale = p.ss_in ? rsqrtf(ss / float(p.cols) + p.eps) : 1.f;
+        }
         cp_async_wait<0>();               // the split input has landed (this thread's part), and with it the first stages
     } else {
         // every block normalizes (when asked) and splits the whole input itself, while its first stages are on their way: a 16 KB read from L2 and about
@@ -430,19 +447,38 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     if (my_units > 0) flush();
     __syncthreads();
     // the rows of this block: the warps' shares summed in warp order, then the epilogue
+    const float in_scale = (p.xq && p.ss_in) ? norm_scale : 1.f;      // written before the barrier above
+    float sq = 0.f;
     for (int r = threadIdx.x; r < nrows; r += WARPS * 32) {
         const float * src = partial + size_t(r / kTileRows) * nmat * WARPS * kTileRows + (r % kTileRows);
         float s = 0.f, s2 = 0.f;
         #pragma unroll
         for (int w = 0; w < WARPS; w++) s += src[w * kTileRows];
+        s *= in_scale;
         if (nmat == 2) {
             #pragma unroll
             for (int w = 0; w < WARPS; w++) s2 += src[(WARPS + w) * kTileRows];
-            s = s / (1.f + expf(-s)) * s2;
+            s = s / (1.f + expf(-s)) * (s2 * in_scale);
         }
         const int64_t row = R0 + r;
         if (p.flags & kFlagBias) s += p.bias[row];
-        p.y[row] = (p.flags & kFlagAccumulate) ? accumulate_base(p.y[row], p.flags) + s : s;
+        const float out = (p.flags & kFlagAccumulate) ? accumulate_base(p.y[row], p.flags) + s : s;
+        p.y[row] = out;
+        sq += out * out;
+    }
+    if (p.ss_out) {
+        // this block's sum of squares: lanes, then warps, in a fixed order
+        __shared__ float sq_warp[WARPS];
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) sq_warp[warp] = sq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.f;
+            #pragma unroll
+            for (int w = 0; w < WARPS; w++) total += sq_warp[w];
+            p.ss_out[blockIdx.x] = total;
+        }
     }
     if (p.xq_out) {
         __threadfence();              // this block's rows are visible before they are counted
@@ -457,7 +493,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
             }
             if (__shfl_sync(0xffffffffu, done, 0)) {
                 __threadfence();
-                split_block(__ldcg(p.y + grp * 32 + lane), lane, int(grp), int(p.rows / 32), p.xq_out);
+                const float v = __ldcg(p.y + grp * 32 + lane);
+                split_block(p.gamma_out ? v * p.gamma_out[grp * 32 + lane] : v, lane, int(grp), int(p.rows / 32), p.xq_out);
             }
         }
     }
@@ -558,6 +595,10 @@ bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols) {
     return rows >= 1 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && plan_for(cols, 2, true).ok;
 }
 
+int gemv_q4_0_blocks(int64_t rows, int64_t cols, bool gate_up, bool q4_k) {
+    return row_split(rows, takes_tma(rows, cols, gate_up ? 2 : 1, q4_k)).grid;
+}
+
 size_t quantized_x_bytes(int64_t cols) { return size_t(cols / 32) * 136; }      // the kernel adds 4 bytes per block of its own in shared memory
 
 cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStream_t stream) {
@@ -566,8 +607,11 @@ cudaError_t launch_quantize_x(const float * x, int64_t cols, void * xq, cudaStre
 }
 
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
-                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error) {
+                             int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out, int * out_counters, int32_t * error,
+                             const GemvNormLink * link) {
     if (xq_out && (!out_counters || rows % 32 != 0)) return cudaErrorInvalidValue;
+    if (link && ((link->gamma_out || link->ss_out) && !xq_out)) return cudaErrorInvalidValue;
+    if (link && link->ss_in && !xq) return cudaErrorInvalidValue;
     // tensor copies when rows and chunks are whole 16-byte units (cols a multiple of 256) and the driver hands out the encoder; per-lane copies otherwise
     Maps maps{};
     bool tma = takes_tma(rows, cols, W2 ? 2 : 1, q4_k);
@@ -580,7 +624,8 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     }
     const Plan pl = plan_for(cols, W2 ? 2 : 1, q4_k, tma);
     if (!pl.ok) return cudaErrorInvalidValue;
-    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters, error, y, bias, rows, int(cols), flags,
+    GemvQ40Params p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), static_cast<const uint8_t *>(xq), x, gamma, eps, static_cast<uint8_t *>(xq_out), out_counters,
+                    link ? link->gamma_out : nullptr, link ? link->ss_out : nullptr, link ? link->ss_in : nullptr, link ? link->ss_n : 0, error, y, bias, rows, int(cols), flags,
                     pl.cbk, pl.nchunks, pl.stride, 0, 0, 0, 1, 0u, 0u};
     if (!xq && !x) return cudaErrorInvalidValue;
     // pieces per row: exactly the chunk when rows and chunks start on 16-byte boundaries, otherwise the widest aligned cover

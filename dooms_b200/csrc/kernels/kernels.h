@@ -121,9 +121,16 @@ bool gemv_q4_0_supported(const void * W, int64_t rows, int64_t cols);
 bool gemv_q4_k_supported(const void * W, int64_t rows, int64_t cols);
 // xq_out (optional, rows a multiple of 32, with out_counters = rows / 32 zeroed ints that are left zeroed): the output row is also written split, for a
 // following projection that takes it as xq; the block that completes a 32-row group of y splits it.
+// link (optional): the RMS norm between two projections, moved to the producer. As producer (with xq_out): the split left in xq_out is of
+// y[i] * gamma_out[i] and block b writes the sum of its rows' y^2 to ss_out[b] (gemv_q4_0_blocks(...) entries). As consumer (with xq): ss_in / ss_n are
+// the producer's ss_out and its block count; the results are multiplied by rsqrt(sum(ss_in) / cols + eps), which is the norm's scale factor applied
+// after the product instead of before it.
+struct GemvNormLink { const float * gamma_out; float * ss_out; const float * ss_in; int ss_n; };
+int gemv_q4_0_blocks(int64_t rows, int64_t cols, bool gate_up, bool q4_k);      // blocks a launch on this shape uses
 cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, const float * x, const float * gamma, float eps, float * y, const float * bias,
                              int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr,
-                             int32_t * error = nullptr);   // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
+                             int32_t * error = nullptr,    // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
+                             const GemvNormLink * link = nullptr);
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;
