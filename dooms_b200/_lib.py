@@ -49,7 +49,7 @@ class LlamaWeights(C.Structure):
 
 class CudaOptions(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("device", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("nccl_unique_id", C.c_void_p),
-                ("nccl_library", C.c_char_p), ("operand_bf16", C.c_int32), ("use_graphs", C.c_int32)]
+                ("nccl_library", C.c_char_p), ("operand_bf16", C.c_int32), ("use_graphs", C.c_int32), ("max_sequences", C.c_int32)]
 
 
 class NativeOptions(C.Structure):
@@ -62,7 +62,8 @@ class KernelTime(C.Structure):
 
 class Timings(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("last_eval_ms", C.c_double), ("last_generate_ms", C.c_double), ("last_eval_launches", C.c_int64),
-                ("last_generate_launches", C.c_int64), ("weight_bytes", C.c_int64), ("kv_bytes", C.c_int64)]
+                ("last_generate_launches", C.c_int64), ("weight_bytes", C.c_int64), ("kv_bytes", C.c_int64), ("last_batch_ms", C.c_double),
+                ("last_batch_launches", C.c_int64)]
 
 
 class GgufTensor(C.Structure):
@@ -111,6 +112,10 @@ SIGNATURES = {
     "dooms_cuda_llama_generate": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, TOKEN_CALLBACK, C.c_void_p]),
     "dooms_cuda_llama_profile_pass": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(KernelTime), C.c_int32, C.POINTER(C.c_int32)]),
     "dooms_cuda_llama_timings": (C.c_int32, [C.c_void_p, C.POINTER(Timings)]),
+    "dooms_cuda_llama_max_sequences": (C.c_int32, [C.c_void_p]),
+    "dooms_cuda_llama_max_batch_rows": (C.c_int32, [C.c_void_p]),
+    "dooms_cuda_llama_select_sequence": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dooms_cuda_llama_decode_batch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "dooms_cuda_dequantize": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "dooms_cuda_matvec": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
     "dooms_cuda_gate_up": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),

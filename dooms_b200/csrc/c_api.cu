@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -69,6 +70,7 @@ CudaOptions options_of(const dooms_cuda_options * o) {
     c.nccl_library = o->nccl_library;
     c.operand_bf16 = o->operand_bf16 != 0;
     c.use_graphs = o->use_graphs != 0;
+    if (o->struct_size >= offsetof(dooms_cuda_options, max_sequences) + sizeof(int32_t)) c.max_sequences = o->max_sequences < 1 ? 1 : o->max_sequences;
     return c;
 }
 
@@ -346,7 +348,22 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, doom
     const CudaLlamaDecoder::Timings t = d->dec->timings();
     out->last_eval_ms = t.last_eval_ms; out->last_generate_ms = t.last_generate_ms; out->last_eval_launches = t.last_eval_launches;
     out->last_generate_launches = t.last_generate_launches; out->weight_bytes = t.weight_bytes; out->kv_bytes = t.kv_bytes;
+    if (out->struct_size >= offsetof(dooms_cuda_timings, last_batch_launches) + sizeof(int64_t)) {
+        out->last_batch_ms = t.last_batch_ms;
+        out->last_batch_launches = t.last_batch_launches;
+    }
     return DOOMS_OK;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_llama_max_sequences(const dooms_cuda_llama * d) { return d ? d->dec->max_sequences() : 0; }
+DOOMS_CUDA_API int32_t dooms_cuda_llama_max_batch_rows(const dooms_cuda_llama * d) { return d ? d->dec->max_batch_rows() : 0; }
+DOOMS_CUDA_API int32_t dooms_cuda_llama_select_sequence(dooms_cuda_llama * d, int32_t slot) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->select_sequence(slot));
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llama_decode_batch(dooms_cuda_llama * d, const int32_t * slots, int32_t n, int32_t steps, int32_t * out_tokens) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->decode_batch(slots, n, steps, out_tokens));
 }
 
 // ---------------------------------------------------------------- single kernels

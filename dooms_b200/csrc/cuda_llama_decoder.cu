@@ -69,6 +69,24 @@ struct CudaLlamaDecoder::Impl {
     std::vector<LayerDev> layers;
     __half * kc = nullptr, * vc = nullptr;
     size_t cache_layer_elems = 0, kv_bytes = 0;
+    // Several sequences (CudaOptions::max_sequences): each layer's cache holds one slot of n_ctx positions per sequence. The calls of the single-sequence
+    // interface act on the selected slot; its position and pending-token flag live in pos / has_pending, the other slots' in seqs.
+    struct Sequence { int32_t pos = 0; bool has_pending = false; int32_t pending = 0; };
+    std::vector<Sequence> seqs;
+    int32_t cur = 0, graph_slot = 0, logits_slot = 0;
+    size_t slot_elems = 0;          // f16 elements of one slot within a layer: n_ctx * kv_width
+    // one decode step over several slots at once (decode_batch)
+    int32_t max_rows = 0;           // rows such a step can hold
+    int32_t * b_rows = nullptr;     // device: slot[max_rows], pos[max_rows], tok[max_rows]
+    int32_t * b_out = nullptr;      // device: [kMaxBatchSteps][max_rows] tokens
+    int32_t * b_step = nullptr;     // device: steps done in the current call
+    int32_t * h_rows = nullptr, * h_out = nullptr;   // pinned staging of the same
+    float * b_logits = nullptr, * b_part = nullptr;
+    void * b_argmax_part = nullptr;
+    int * b_counters = nullptr;
+    int b_splits = 1;
+    std::vector<std::pair<int32_t, cudaGraphExec_t>> batch_graphs;   // per number of rows
+    int64_t batch_step_launches_count = 0;
     float * x = nullptr, * xn = nullptr, * qkv = nullptr, * attn = nullptr, * h = nullptr, * red = nullptr, * logits_buf = nullptr, * part = nullptr;
     void * argmax_part = nullptr;
     __half * xn16 = nullptr, * attn16 = nullptr, * h16 = nullptr;   // f16 activations of a prefill chunk, the tensor-core GEMM's token operands
@@ -121,6 +139,9 @@ struct CudaLlamaDecoder::Impl {
     ~Impl() {
         if (stream) cudaStreamSynchronize(stream);
         if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
+        for (auto & g : batch_graphs) cudaGraphExecDestroy(g.second);
+        for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters}) if (p) cudaFree(p);
+        for (void * p : {(void *)h_rows, (void *)h_out}) if (p) cudaFreeHost(p);
         for (void * p : par_opened) cudaIpcCloseMemHandle(p);
         for (void * p : {par_inbox, par_flags, par_words}) if (p) cudaFree(p);
         if (comm) nccl.CommDestroy(comm);
@@ -365,7 +386,7 @@ struct CudaLlamaDecoder::Impl {
         if (M == 1 && gqa) run("rope_table", [&] { return cuda::launch_rope_table(state, inv_freq, rope_cs, cfg.head_dim, stream); });
         for (size_t l = 0; l < layers.size(); l++) {
             const LayerDev & L = layers[l];
-            __half * kcl = kc + l * cache_layer_elems, * vcl = vc + l * cache_layer_elems;
+            __half * kcl = kc + l * cache_layer_elems + size_t(cur) * slot_elems, * vcl = vc + l * cache_layer_elems + size_t(cur) * slot_elems;
             // Tensor-parallel decode steps with a power-of-two group: the projection leaves x / tp + its share of the product in x, and the in-place all-reduce
             // of x is the residual add (no buffer for the partial sums, no add kernel). Chunks and other group sizes reduce a separate buffer and add it.
             const bool share = !single && M == 1 && !use_par && (tp & (tp - 1)) == 0;
@@ -461,7 +482,13 @@ struct CudaLlamaDecoder::Impl {
     }
 
     Status ensure_step_graph() {
+        if (step_graph && graph_slot != cur) {      // the captured launches point into another slot's cache
+            DOOMS_RETURN_IF_ERROR(wait_idle());
+            cudaGraphExecDestroy(step_graph);
+            step_graph = nullptr;
+        }
         if (step_graph || !opt.use_graphs) return Status();
+        graph_slot = cur;
         DOOMS_RETURN_IF_ERROR(wait_idle());
         const int64_t before = launches;
         cudaGraph_t graph = nullptr;
@@ -477,6 +504,65 @@ struct CudaLlamaDecoder::Impl {
         return check(ie, "cudaGraphInstantiate");
     }
     int64_t step_launches = 0;
+
+    // ---- one decode step for several slots (rows) at once: the chunk path's kernels with one row per sequence. Every row's token comes from and goes
+    // to device memory (b_rows), so the same captured launches serve any set of slots. ----
+    static constexpr int32_t kMaxBatchSteps = 256;
+    cuda::BatchRows batch_rows() const { return cuda::BatchRows{b_rows, b_rows + max_rows, b_rows + 2 * max_rows, int64_t(slot_elems)}; }
+    void batch_step_launches(int32_t n) {
+        const cuda::BatchRows rows = batch_rows();
+        const int E = cfg.n_embd;
+        const AttnShape as = attn_shape();
+        embed(rows.tok, nullptr, n);
+        for (size_t l = 0; l < layers.size(); l++) {
+            const LayerDev & L = layers[l];
+            norm(x, L.attn_norm, n, false, true);
+            for (const QkvPart & q : L.qkv) {
+                gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, n, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
+            }
+            run("attention", [&] {
+                return cuda::launch_attention_gqa_rows(qkv, kc + l * cache_layer_elems, vc + l * cache_layer_elems, b_part, inv_freq, b_splits, as, b_counters, attn, attn16,
+                                                       rows, n, stream);
+            });
+            gemm_tc("attn_output", L.attn_output, nullptr, map_attn, x, nullptr, nullptr, n, E, 0, kFlagAccumulate);
+            norm(x, L.ffn_norm, n, false, true);
+            gemm_tc("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, n, 0, ff, 0u);
+            gemm_tc("ffn_down", L.ffn_down, nullptr, map_h, x, nullptr, nullptr, n, E, 0, kFlagAccumulate);
+        }
+        norm(x, output_norm, n, false, true);
+        gemm_tc("output", output, nullptr, map_xn, b_logits, nullptr, nullptr, n, cfg.n_vocab, 0, 0u);
+        run("argmax", [&] { return cuda::launch_argmax_rows(b_logits, cfg.n_vocab, cfg.n_vocab, rows, n, b_out, b_step, b_argmax_part, stream); });
+    }
+    Result<cudaGraphExec_t> batch_graph(int32_t n) {
+        for (auto & g : batch_graphs) if (g.first == n) return g.second;
+        DOOMS_RETURN_IF_ERROR(wait_idle());
+        const int64_t before = launches;
+        cudaGraph_t graph = nullptr;
+        DOOMS_RETURN_IF_ERROR(check(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture"));
+        batch_step_launches(n);
+        const cudaError_t e = cudaStreamEndCapture(stream, &graph);
+        batch_step_launches_count = launches - before;
+        launches = before;
+        if (!failed.is_ok()) { if (graph) cudaGraphDestroy(graph); return failed; }
+        DOOMS_RETURN_IF_ERROR(check(e, "cudaStreamEndCapture"));
+        cudaGraphExec_t exec = nullptr;
+        const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        DOOMS_RETURN_IF_ERROR(check(ie, "cudaGraphInstantiate"));
+        batch_graphs.emplace_back(n, exec);
+        return exec;
+    }
+    // The selected slot's state to and from its entry in seqs (the stream is idle).
+    void stash_selected() { seqs[size_t(cur)] = Sequence{pos, has_pending, has_pending ? host_tokens[0] : 0}; }
+    void restore_selected() {
+        const Sequence & q = seqs[size_t(cur)];
+        pos = q.pos;
+        has_pending = q.has_pending;
+        if (has_pending) {
+            host_tokens[0] = q.pending;
+            (void)check(cudaMemcpy(tokens, &q.pending, sizeof(int32_t), cudaMemcpyHostToDevice), "restoring the pending token");
+        }
+    }
     class StepWindow;
     template <class Stage> Status append_positions(int32_t n, bool from_tokens, Stage && stage);
 
@@ -699,7 +785,10 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
 
     // ---- activations for the largest chunk, the KV cache, the logits and the token ring ----
     const size_t B = size_t(c.n_batch);
-    m.cache_layer_elems = size_t(c.n_ctx) * size_t(m.kv_width);
+    const int32_t n_seq = std::max(1, opt.max_sequences);
+    m.seqs.assign(size_t(n_seq), Impl::Sequence{});
+    m.slot_elems = size_t(c.n_ctx) * size_t(m.kv_width);
+    m.cache_layer_elems = size_t(n_seq) * m.slot_elems;
     m.kv_bytes = 2 * size_t(c.n_layer) * m.cache_layer_elems * sizeof(__half);
     m.splits = cuda::attention_splits(m.nh, c.n_ctx);
     m.gqa = cuda::attention_gqa_supported(m.attn_shape());
@@ -773,6 +862,27 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         return resource_exhausted("could not allocate pinned host memory for the decoder");
     }
     *m.host_error = 0;
+    // a decode step over several slots needs the tensor-core chunk path, the grouped-query attention kernel and the whole model on this GPU
+    m.max_rows = (n_seq > 1 && tp == 1 && m.tc_capable && m.gqa && cuda::gemm_tc_supported(int(m.output.dt), m.output.ptr, m.output.rows, m.output.cols))
+                     ? std::min<int32_t>({n_seq, c.n_batch, 1024}) : 0;
+    if (m.max_rows > 0) {
+        const size_t R = size_t(m.max_rows);
+        // about two blocks per SM over (rows x key/value heads x ranges), and no more ranges than the context has tiles of 64 positions
+        m.b_splits = std::max(1, std::min({cuda::attention_gqa_splits(m.nkv, c.n_ctx), (2 * prop.multiProcessorCount + m.max_rows * m.nkv - 1) / (m.max_rows * m.nkv)}));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_rows), 3 * R * sizeof(int32_t), "the rows of a batched decode step"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_out), size_t(Impl::kMaxBatchSteps) * R * sizeof(int32_t), "the tokens of a batched decode call"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_step), sizeof(int32_t), "the step counter"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_logits), R * size_t(c.n_vocab) * sizeof(float), "the logits of a batched decode step"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_part), R * size_t(m.b_splits) * size_t(m.nh) * size_t(2 + c.head_dim) * sizeof(float), "the batched attention partial results"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(&m.b_argmax_part, R * size_t(cuda::argmax_blocks(c.n_vocab)) * 8, "the batched argmax partial results"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_counters), R * size_t(m.nkv) * sizeof(int), "the batched attention counters"));
+        cudaMemset(m.b_counters, 0, R * size_t(m.nkv) * sizeof(int));
+        if (cudaHostAlloc(reinterpret_cast<void **>(&m.h_rows), 3 * R * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess ||
+            cudaHostAlloc(reinterpret_cast<void **>(&m.h_out), size_t(Impl::kMaxBatchSteps) * R * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return resource_exhausted("could not allocate pinned host memory for the batched decode step");
+        }
+    }
     if (tp > 1) m.setup_peer_allreduce();
     if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
     m.tm.weight_bytes = int64_t(m.matrix_bytes);
@@ -811,6 +921,7 @@ Status CudaLlamaDecoder::Impl::append_positions(int32_t n, bool from_tokens, Sta
         if (done == 0) cudaEventRecord(ev_a, stream);
         stage(done, rows);
         run_chunk(rows, from_tokens);
+        logits_slot = cur;
         done += rows;
     }
     cudaEventRecord(ev_b, stream);
@@ -860,6 +971,7 @@ Status CudaLlamaDecoder::logits_into(float * out, int64_t capacity) {
     Impl & m = *impl_;
     if (!m.has_pending) return invalid_argument(kNothingPending);
     if (out == nullptr || capacity < m.cfg.n_vocab) return resource_exhausted("logits: the buffer has to hold " + std::to_string(m.cfg.n_vocab) + " floats");
+    if (m.logits_slot != m.cur) return invalid_argument("logits: another sequence (or a batched step) was evaluated since this one; only the last evaluation's logits are kept");
     DOOMS_RETURN_IF_ERROR(m.wait_idle());
     cudaSetDevice(m.opt.device);
     return m.check(cudaMemcpy(out, m.logits_buf, size_t(m.cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost), "reading the logits");
@@ -951,6 +1063,85 @@ Status CudaLlamaDecoder::generate(int32_t max_tokens, int32_t depth, const std::
     m.pos = start + std::max(delivered, 1) - 1;
     m.has_pending = false;
     return outcome;
+}
+
+// ---- several sequences ----
+
+int32_t CudaLlamaDecoder::max_sequences() const { return int32_t(impl_->seqs.size()); }
+int32_t CudaLlamaDecoder::selected_sequence() const { return impl_->cur; }
+int32_t CudaLlamaDecoder::max_batch_rows() const { return impl_->max_rows; }
+
+Status CudaLlamaDecoder::select_sequence(int32_t slot) {
+    Impl & m = *impl_;
+    if (slot < 0 || slot >= int32_t(m.seqs.size())) return invalid_argument("select_sequence: slot " + std::to_string(slot) + " of " + std::to_string(m.seqs.size()));
+    if (slot == m.cur) return Status();
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    cudaSetDevice(m.opt.device);
+    m.stash_selected();
+    m.cur = slot;
+    m.restore_selected();
+    return m.failed;
+}
+
+Status CudaLlamaDecoder::decode_batch(const int32_t * slots, int32_t n, int32_t steps, int32_t * out_tokens) {
+    Impl & m = *impl_;
+    if (m.max_rows == 0) {
+        return unsupported("decode_batch needs max_sequences > 1, one GPU, head_dim 64 or 128 and widths that are multiples of 64 (the tensor-core chunk path)");
+    }
+    if (slots == nullptr || out_tokens == nullptr || n < 1 || steps < 1) return invalid_argument("decode_batch: no slots, no room for the tokens, or no steps");
+    if (n > m.max_rows) return resource_exhausted("decode_batch: " + std::to_string(n) + " rows; one step holds " + std::to_string(m.max_rows));
+    if (steps > Impl::kMaxBatchSteps) return invalid_argument("decode_batch: at most " + std::to_string(Impl::kMaxBatchSteps) + " steps per call");
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    cudaSetDevice(m.opt.device);
+    m.stash_selected();
+    std::vector<bool> taken(m.seqs.size(), false);
+    for (int32_t i = 0; i < n; i++) {
+        const int32_t s = slots[i];
+        if (s < 0) continue;                        // an idle row
+        if (s >= int32_t(m.seqs.size())) return invalid_argument("decode_batch: slot " + std::to_string(s) + " of " + std::to_string(m.seqs.size()));
+        if (taken[size_t(s)]) return invalid_argument("decode_batch: slot " + std::to_string(s) + " is listed twice");
+        taken[size_t(s)] = true;
+        const Impl::Sequence & q = m.seqs[size_t(s)];
+        if (!q.has_pending) return invalid_argument("decode_batch: slot " + std::to_string(s) + " has no pending token (evaluate its prompt first)");
+        if (int64_t(q.pos) + steps > m.cfg.n_ctx) return resource_exhausted(context_full(m.cfg, int64_t(q.pos) + steps));
+    }
+    const size_t R = size_t(m.max_rows);
+    for (int32_t i = 0; i < n; i++) {
+        const int32_t s = slots[i];
+        m.h_rows[i] = s;
+        m.h_rows[R + size_t(i)] = s < 0 ? 0 : m.seqs[size_t(s)].pos;
+        m.h_rows[2 * R + size_t(i)] = s < 0 ? 0 : m.seqs[size_t(s)].pending;
+    }
+    auto graph = m.opt.use_graphs ? m.batch_graph(n) : Result<cudaGraphExec_t>(cudaGraphExec_t(nullptr));
+    if (!graph.is_ok()) return graph.status();
+    m.launches = 0;
+    for (int part = 0; part < 3; part++) {
+        (void)m.check(cudaMemcpyAsync(m.b_rows + size_t(part) * R, m.h_rows + size_t(part) * R, size_t(n) * sizeof(int32_t), cudaMemcpyHostToDevice, m.stream), "copying the rows to the device");
+    }
+    (void)m.check(cudaMemsetAsync(m.b_step, 0, sizeof(int32_t), m.stream), "clearing the step counter");
+    cudaEventRecord(m.ev_a, m.stream);
+    for (int32_t t = 0; t < steps; t++) {
+        if (graph.value()) { m.launches += m.batch_step_launches_count; (void)m.check(cudaGraphLaunch(graph.value(), m.stream), "cudaGraphLaunch"); }
+        else m.batch_step_launches(n);
+    }
+    cudaEventRecord(m.ev_b, m.stream);
+    (void)m.check(cudaMemcpyAsync(m.h_out, m.b_out, size_t(steps) * size_t(n) * sizeof(int32_t), cudaMemcpyDeviceToHost, m.stream), "reading the tokens");
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, m.ev_a, m.ev_b);
+    m.tm.last_batch_ms = ms;
+    m.tm.last_batch_launches = m.launches;
+    std::memcpy(out_tokens, m.h_out, size_t(steps) * size_t(n) * sizeof(int32_t));
+    for (int32_t i = 0; i < n; i++) {
+        const int32_t s = slots[i];
+        if (s < 0) continue;
+        Impl::Sequence & q = m.seqs[size_t(s)];
+        q.pos += steps;
+        q.pending = m.h_out[size_t(steps - 1) * size_t(n) + size_t(i)];
+    }
+    m.logits_slot = -1;              // the single-sequence logits buffer no longer belongs to any slot's last position
+    m.restore_selected();
+    return m.failed;
 }
 
 Result<std::vector<CudaLlamaDecoder::KernelTime>> CudaLlamaDecoder::profile_pass(int32_t rows) {

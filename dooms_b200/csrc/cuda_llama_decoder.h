@@ -52,6 +52,7 @@ struct CudaOptions {
     const char * nccl_library = nullptr;
     bool operand_bf16 = false;               // reserved: bf16 tensor-core operands; true is refused with Unsupported (the tiles hold f16, the reference's rounding)
     bool use_graphs = true;                  // decode steps replay a captured CUDA graph
+    int32_t max_sequences = 1;               // independent KV caches ("slots") of n_ctx positions each; see select_sequence / decode_batch
 };
 
 // A rank's share of the model under tensor parallelism: whole heads, a slice of the feed-forward width, a slice of the vocabulary.
@@ -81,11 +82,31 @@ public:
     Status logits_into(float * out, int64_t capacity);
     Status generate(int32_t max_tokens, int32_t depth, const std::function<bool(int32_t)> & on_token);
 
+    // ---- several sequences on one decoder (no counterpart in the reference, which serves one request at a time: python/dooms/server.py:262-269) ----
+    // The decoder holds max_sequences KV-cache slots. Every call above acts on the selected slot (0 at creation); select_sequence switches. logits() is
+    // kept for the last evaluation only.   InvalidArgument  slot outside [0, max_sequences)
+    int32_t max_sequences() const;
+    int32_t selected_sequence() const;
+    Status select_sequence(int32_t slot);
+    // `steps` greedy decode steps for n slots at once, one pass over the weights per step for all of them (the chunk path's tensor-core kernels with one
+    // row per sequence, each attending over its own slot). slots[i] < 0 marks an idle row. Every listed slot needs a pending token, as for generate();
+    // out_tokens[t * n + i] receives the token step t produced for slots[i] (-1 for idle rows). Afterwards each slot's position has advanced by `steps` and
+    // its pending token is the last one produced: as after `steps` calls of eval_tokens({pending}).
+    //   Unsupported  built with max_sequences = 1, tensor parallelism, or shapes the tensor-core chunk path does not take (max_batch_rows() == 0)
+    //   InvalidArgument  a slot out of range or listed twice, a slot without pending token, steps outside [1, 256]     ResourceExhausted  context, rows
+    int32_t max_batch_rows() const;
+    Status decode_batch(const int32_t * slots, int32_t n, int32_t steps, int32_t * out_tokens);
+
     struct KernelTime { const char * kind; int32_t dispatches; double gpu_ms; };
     Result<std::vector<KernelTime>> profile_pass(int32_t rows = 1);
 
     // Device-side measurements of the last calls (CUDA events on the decoder's stream).
-    struct Timings { double last_eval_ms = 0, last_generate_ms = 0; int64_t last_eval_launches = 0, last_generate_launches = 0, weight_bytes = 0, kv_bytes = 0; };
+    struct Timings {
+        double last_eval_ms = 0, last_generate_ms = 0;
+        int64_t last_eval_launches = 0, last_generate_launches = 0, weight_bytes = 0, kv_bytes = 0;
+        double last_batch_ms = 0;            // device time of the last decode_batch call's steps
+        int64_t last_batch_launches = 0;
+    };
     Timings timings() const;
 
 private:

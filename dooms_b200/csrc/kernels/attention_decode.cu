@@ -40,6 +40,14 @@ struct AttnDecodeParams {
     float * out;
     uint8_t * xq;
     const float2 * rope_cs;   // optional: (cos, sin) of the head_dim / 2 rotary angles at st->pos, computed once per decode step
+    // One step over several sequences (grid z = row of the step): row r reads its position from b_pos[r] and works on the cache of slot b_slot[r] (a
+    // negative slot: the row is idle and its blocks leave at once). qkv, part, counters, out and out16 are then indexed by row.
+    const int32_t * b_slot;
+    const int32_t * b_pos;
+    int b_rows;
+    int64_t slot_elems;       // f16 elements between the caches of consecutive slots
+    int64_t part_row_floats;  // floats of `part` per row
+    __half * out16;           // optional: the merged rows as f16 as well ([row][n_head * head_dim]), the tensor-core GEMM's operand
 };
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
@@ -48,7 +56,7 @@ template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.as
 
 // D: head_dim (64 or 128). GP: query heads per key/value head, rounded up to 1, 2, 4 or 8.
 template <int D, int GP>
-__global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeParams p) {
+__global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeParams pp) {
     constexpr int KP = D * 2 + 16;                      // bytes between key rows in a stage: 16-byte loads of 8 consecutive rows fall on different banks
     constexpr int VP = D * 2;
     constexpr int STAGE = kTileKeys * (KP + VP);
@@ -65,11 +73,27 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
 
     pdl_trigger();
     pdl_wait();
+    // the row's view of the arguments
+    AttnDecodeParams p = pp;
+    const int row = blockIdx.z;
+    int row_pos = 0;
+    if (pp.b_slot) {
+        const int slot = pp.b_slot[row];
+        if (slot < 0) return;
+        row_pos = pp.b_pos[row];
+        p.kc = pp.kc + int64_t(slot) * pp.slot_elems;
+        p.vc = pp.vc + int64_t(slot) * pp.slot_elems;
+        p.qkv = pp.qkv + int64_t(row) * pp.s.qkv_stride;
+        p.part = pp.part + int64_t(row) * pp.part_row_floats;
+        p.counters = pp.counters + row * pp.s.n_head_kv;
+        p.out = pp.out + int64_t(row) * pp.s.out_stride;
+        if (pp.out16) p.out16 = pp.out16 + int64_t(row) * pp.s.n_head * D;
+    }
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int G = p.s.n_head / p.s.n_head_kv;
     const bool fuse = p.inv_freq != nullptr;
-    const int pos = fuse ? p.st->pos : 0;
+    const int pos = !fuse ? 0 : pp.b_slot ? row_pos : p.st->pos;
     const int n_keys = p.n_keys_fixed > 0 ? p.n_keys_fixed : pos + 1;
     // ranges of whole tiles, the same for every head: at least one tile per range, so short contexts leave the later ranges empty
     const int tiles_total = (n_keys + kTileKeys - 1) / kTileKeys;
@@ -331,6 +355,7 @@ __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeP
         if (idx < GP * D && hq < G) {
             const float r = merged[it] / tot[hq];
             p.out[(kvh * G + hq) * D + d] = r;
+            if (p.out16) p.out16[(kvh * G + hq) * D + d] = __float2half_rn(r);
             if (p.xq) split_block(r, lane, ((kvh * G + hq) * D + d) / 32, p.s.n_head * D / 32, p.xq);
         }
     }
@@ -341,7 +366,7 @@ cudaError_t launch_one(const AttnDecodeParams & p, cudaStream_t stream) {
     constexpr size_t smem = ((GP * D + GP * kTileKeys + GP) * 4 + 127) / 128 * 128 + size_t(kStages) * kTileKeys * (D * 4 + 16);
     static std::atomic<uint64_t> configured{0};
     if (const cudaError_t e = allow_dynamic_smem(k_attention_decode<D, GP>, int(smem), configured); e != cudaSuccess) return e;
-    return launch_pdl(k_attention_decode<D, GP>, dim3(p.s.n_head_kv, p.splits), dim3(kThreads), smem, stream, p);
+    return launch_pdl(k_attention_decode<D, GP>, dim3(p.s.n_head_kv, p.splits, p.b_slot ? unsigned(p.b_rows) : 1u), dim3(kThreads), smem, stream, p);
 }
 
 template <int D>
@@ -368,7 +393,15 @@ cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float 
                                  int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream, const void * rope_cs) {
     if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1) || (counters && !out) || (xq && !counters)) return cudaErrorInvalidValue;
     const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
-                             static_cast<uint8_t *>(xq), static_cast<const float2 *>(rope_cs)};
+                             static_cast<uint8_t *>(xq), static_cast<const float2 *>(rope_cs), nullptr, nullptr, 0, 0, 0, nullptr};
+    return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
+}
+
+cudaError_t launch_attention_gqa_rows(const float * qkv, void * kc, void * vc, float * part, const double * inv_freq, int splits, const AttnShape & s, int * counters,
+                                      float * out, void * out16, const BatchRows & rows, int n_rows, cudaStream_t stream) {
+    if (!attention_gqa_supported(s) || !inv_freq || !counters || !out || n_rows < 1 || splits < 1) return cudaErrorInvalidValue;
+    const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, nullptr, inv_freq, 0, splits, s, counters, out, nullptr, nullptr,
+                             rows.slot, rows.pos, n_rows, rows.slot_elems, int64_t(splits) * s.n_head * (2 + s.head_dim), static_cast<__half *>(out16)};
     return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
 }
 

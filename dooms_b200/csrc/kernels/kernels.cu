@@ -444,6 +444,43 @@ __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_final(const Best * pa
     }
 }
 
+// The same reduction for every row of a batched decode step: grid (blocks per row, rows), then one block per row.
+__global__ void __launch_bounds__(kArgmaxThreads) k_argmax_rows_part(const float * logits, int64_t n, int64_t stride, const int32_t * slot, Best * part) {
+    const int row = blockIdx.y;
+    if (slot[row] < 0) return;
+    const float * v0 = logits + int64_t(row) * stride;
+    const int64_t begin = int64_t(blockIdx.x) * kArgmaxPerBlock, end = min(n, begin + kArgmaxPerBlock);
+    Best b{0.f, -1};
+    for (int64_t i = begin + threadIdx.x; i < end; i += kArgmaxThreads) {
+        const float v = v0[i];
+        if (better(v, int32_t(i), b.v, b.i)) { b.v = v; b.i = int32_t(i); }
+    }
+    b = block_best(b);
+    if (threadIdx.x == 0) part[int64_t(row) * gridDim.x + blockIdx.x] = b;
+}
+
+__global__ void __launch_bounds__(kArgmaxThreads) k_argmax_rows_final(const Best * part, int nparts, const int32_t * slot, int32_t * pos, int32_t * tok, int32_t * out,
+                                                                      int32_t * step) {
+    const int row = blockIdx.x, rows = gridDim.x;
+    const int32_t at = *step;      // read by every block before the last block to finish bumps it: the bump happens in a kernel of its own, below
+    if (slot[row] < 0) {
+        if (threadIdx.x == 0) out[int64_t(at) * rows + row] = -1;
+        return;
+    }
+    const Best * mine = part + int64_t(row) * nparts;
+    Best b{0.f, -1};
+    for (int i = threadIdx.x; i < nparts; i += kArgmaxThreads) if (better(mine[i].v, mine[i].i, b.v, b.i)) b = mine[i];
+    b = block_best(b);
+    if (threadIdx.x == 0) {
+        const int32_t t = b.i < 0 ? 0 : b.i;
+        tok[row] = t;
+        pos[row] += 1;
+        out[int64_t(at) * rows + row] = t;
+    }
+}
+
+__global__ void k_bump(int32_t * counter) { *counter += 1; }
+
 }  // namespace
 
 // ---------------------------------------------------------------- launchers
@@ -557,6 +594,15 @@ cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int
     if (e != cudaSuccess) return e;
     return launch_pdl(k_argmax_final, dim3(1), dim3(kArgmaxThreads), 0, stream, static_cast<const Best *>(part), blocks, tokens, host_tokens, st,
                       static_cast<int32_t *>(nullptr), advance);
+}
+
+cudaError_t launch_argmax_rows(const float * logits, int64_t n, int64_t stride, const BatchRows & rows, int n_rows, int32_t * out, int32_t * step, void * part,
+                               cudaStream_t stream) {
+    const int blocks = argmax_blocks(n);
+    k_argmax_rows_part<<<dim3(blocks, n_rows), kArgmaxThreads, 0, stream>>>(logits, n, stride, rows.slot, static_cast<Best *>(part));
+    k_argmax_rows_final<<<n_rows, kArgmaxThreads, 0, stream>>>(static_cast<const Best *>(part), blocks, rows.slot, rows.pos, rows.tok, out, step);
+    k_bump<<<1, 1, 0, stream>>>(step);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream) {

@@ -84,6 +84,20 @@ cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float 
                                  int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream,
                                  const void * rope_cs = nullptr);   // rope_cs: launch_rope_table's output for st->pos, used instead of computing the angles
 
+// ---- one decode step over several sequences at once ----
+// Row r of the step belongs to the KV-cache slot slot[r] (negative: the row is idle, every kernel skips it) and sits at position pos[r] of that
+// sequence; tok[r] is the token the row embeds and, after the step, the row's greedy token. Slots are slot_elems f16 elements apart within a layer's cache.
+struct BatchRows { const int32_t * slot; int32_t * pos; int32_t * tok; int64_t slot_elems; };
+// launch_attention_gqa for n_rows rows: qkv [n_rows][qkv_stride], out [n_rows][out_stride] (+ out16 [n_rows][n_head * head_dim] as f16, optional);
+// part: n_rows x splits x n_head x (2 + head_dim) floats; counters: n_rows x n_head_kv zeroed ints (left zeroed). Each row rotates its query and key by
+// its own position and appends key and value to its own slot's cache.
+cudaError_t launch_attention_gqa_rows(const float * qkv, void * kc, void * vc, float * part, const double * inv_freq, int splits, const AttnShape & s, int * counters,
+                                      float * out, void * out16, const BatchRows & rows, int n_rows, cudaStream_t stream);
+// Greedy token of every row: logits [n_rows][stride], first n of each row. Active rows (slot >= 0): tok[r] = argmax, pos[r] += 1, and the token also goes
+// to out[(*step) * n_rows + r]; idle rows write -1 there. *step is incremented once per launch. part: n_rows x argmax_blocks(n) x 2 words.
+cudaError_t launch_argmax_rows(const float * logits, int64_t n, int64_t stride, const BatchRows & rows, int n_rows, int32_t * out, int32_t * step, void * part,
+                               cudaStream_t stream);
+
 // Causal attention of M query rows at positions st->pos + t over the cache (attention_prefill, llama_kernels.h:640-769; this version runs on CUDA cores).
 // out16 (optional): the same rows as f16, for the tensor-core GEMM that follows.
 cudaError_t launch_attention_prefill(const float * qkv, const void * kc, const void * vc, float * out, void * out16, const DevState * st, int M,

@@ -58,7 +58,7 @@ LAYER_FIELDS = [n for n, _ in L.LayerWeights._fields_]
 
 
 def cuda_options(device: int = 0, tp_rank: int = 0, tp_size: int = 1, nccl_unique_id: bytes | None = None, operand_bf16: bool = False,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_sequences: int = 1):
     o = L.CudaOptions()
     o.struct_size = C.sizeof(L.CudaOptions)
     o.device, o.tp_rank, o.tp_size = device, tp_rank, tp_size
@@ -70,6 +70,7 @@ def cuda_options(device: int = 0, tp_rank: int = 0, tp_size: int = 1, nccl_uniqu
     o.nccl_library = path.encode() if path else None
     o.operand_bf16 = int(operand_bf16)
     o.use_graphs = int(use_graphs)
+    o.max_sequences = int(max_sequences)
     return o, keep
 
 
@@ -172,6 +173,23 @@ class CudaLlamaDecoder:
         L.check(L.lib().dooms_cuda_llama_generate(self._h, max_tokens, depth, L.TOKEN_CALLBACK(cb), None))
         if err:
             raise err[0]
+
+    # ---- several sequences on one decoder (include/dooms_cuda.h: dooms_cuda_llama_select_sequence / _decode_batch) ----
+    def max_sequences(self) -> int:
+        return L.lib().dooms_cuda_llama_max_sequences(self._h)
+
+    def max_batch_rows(self) -> int:
+        return L.lib().dooms_cuda_llama_max_batch_rows(self._h)
+
+    def select_sequence(self, slot: int) -> None:
+        L.check(L.lib().dooms_cuda_llama_select_sequence(self._h, slot))
+
+    def decode_batch(self, slots: Sequence[int], steps: int = 1) -> np.ndarray:
+        """`steps` greedy steps for the listed KV-cache slots at once (-1: an idle row); the tokens as int32 [steps][len(slots)]."""
+        a = np.ascontiguousarray(np.asarray(slots, dtype=np.int32))
+        out = np.empty((steps, a.size), dtype=np.int32)
+        L.check(L.lib().dooms_cuda_llama_decode_batch(self._h, a.ctypes.data, a.size, steps, out.ctypes.data))
+        return out
 
     def profile_pass(self, rows: int = 1) -> list[dict]:
         arr = (L.KernelTime * 32)()

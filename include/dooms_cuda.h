@@ -88,6 +88,8 @@ typedef struct dooms_cuda_options {
     const char * nccl_library;     /* path of libnccl.so.2 to load; NULL: the dynamic loader's search path */
     int32_t operand_bf16;    /* prefill tensor-core operands: 0 = f16 (the reference's rounding, llama_kernels.h:197); 1 (bf16) is refused: DOOMS_UNSUPPORTED */
     int32_t use_graphs;      /* 1: decode steps replay a CUDA graph; 0: plain launches */
+    int32_t max_sequences;   /* independent KV caches ("slots") of n_ctx positions each; 0 or 1: one sequence, as the reference's class. Read only when
+                              * struct_size covers it. */
 } dooms_cuda_options;
 
 /* dooms::NativeLlamaOptions (src/pipeline/native_llama.h:15-20). */
@@ -172,8 +174,23 @@ typedef struct dooms_cuda_timings {
     int64_t last_generate_launches;
     int64_t weight_bytes;        /* bytes of weight matrices resident on this GPU */
     int64_t kv_bytes;            /* bytes of the KV cache on this GPU */
+    double last_batch_ms;        /* device time of the steps of the last dooms_cuda_llama_decode_batch call (written only when struct_size covers it) */
+    int64_t last_batch_launches;
 } dooms_cuda_timings;
 DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, dooms_cuda_timings * out);
+
+/* ---- Several sequences on one decoder. No counterpart in the reference, which serves one request at a time (python/dooms/server.py:262-269); this is
+ * the batched decode step the many-sequence serving load needs: one pass over the weights per step for all sequences of the batch. ----
+ * A decoder created with max_sequences = S holds S KV-cache slots. Every call above acts on the selected slot (0 at creation); logits are kept for the
+ * last evaluation only. */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_max_sequences(const dooms_cuda_llama * d);
+DOOMS_CUDA_API int32_t dooms_cuda_llama_max_batch_rows(const dooms_cuda_llama * d);   /* rows one batched step can hold; 0: decode_batch is unsupported here */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_select_sequence(dooms_cuda_llama * d, int32_t slot);
+/* `steps` greedy decode steps for the n listed slots at once (slots[i] < 0: an idle row). Every listed slot needs a pending token, as for generate.
+ * out_tokens[t * n + i] = the token step t produced for slots[i] (-1 for idle rows). Afterwards each slot's position has advanced by `steps` and its pending
+ * token is the last one produced. DOOMS_UNSUPPORTED when max_batch_rows is 0; DOOMS_INVALID_ARGUMENT for a bad / repeated slot, a slot without pending
+ * token or steps outside [1, 256]; DOOMS_RESOURCE_EXHAUSTED when a slot's context or the step's rows would overflow. */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_decode_batch(dooms_cuda_llama * d, const int32_t * slots, int32_t n, int32_t steps, int32_t * out_tokens);
 
 /* ---- Single kernels on DEVICE pointers, for parity tests and roofline measurement. `stream` is a cudaStream_t (NULL: the default stream). ---- */
 /* dequant_half<Q> / Q::elem (llama_kernels.h:1012-1154, 1474-1480): rows x cols blocks -> f32 values, bit for bit the block formulas. */

@@ -178,6 +178,11 @@ class OracleDecoder:
     def reset(self):
         oracle().oracle_reset(self._h)
 
+    def set_round_operands(self, mode: int) -> None:
+        """0: exact; 1: calls of several positions round the projections' operands to f16 like the prefill tiles; 2: every call does, the output projection
+        included (a decode step that runs several sequences as the rows of one chunk)."""
+        oracle().oracle_set_round_operands(self._h, int(mode))
+
     def position(self) -> int:
         return oracle().oracle_position(self._h)
 

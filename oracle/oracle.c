@@ -147,7 +147,9 @@ typedef struct oracle_decoder {
     float * kc, * vc;          /* [n_layer][n_ctx][KV], values rounded to f16 */
     int32_t pos;
     int fast;                  /* 1: f32 accumulation (the timed CPU baseline); 0: double (the checker) */
-    int round_operands;        /* 1: multi-token calls round the projections' operands to f16 like the reference's prefill tiles (llama_kernels.h:186-199) */
+    int round_operands;        /* 1: multi-token calls round the projections' operands to f16 like the reference's prefill tiles (llama_kernels.h:186-199);
+                                * 2: every call does, single positions and the output projection included: the arithmetic of a decode step that runs
+                                * several sequences as the rows of one chunk through the same tiles */
 } oracle_decoder;
 
 static mat_t mat_of(const dooms_weight_ref * r) { mat_t m = {(const uint8_t *)r->data, r->dtype, r->rows, r->cols}; return m; }
@@ -434,7 +436,8 @@ ORACLE_API int32_t oracle_eval_embeddings(oracle_decoder * d, const float * emb,
     const dooms_llama_config * c = &d->cfg;
     const int64_t E = c->n_embd, F = c->n_ff, hd = c->head_dim, nh = c->n_head, nkv = c->n_head_kv, Q = nh * hd, KV = nkv * hd, W3 = Q + 2 * KV, M = n;
     if (n < 1 || (int64_t)d->pos + n > c->n_ctx) return 1;
-    const int round_ops = d->round_operands && M > 1;
+    const int round_all = d->round_operands == 2;
+    const int round_ops = round_all || (d->round_operands && M > 1);
     double * x = (double *)malloc(sizeof(double) * (size_t)(M * E));
     double * xn = (double *)malloc(sizeof(double) * (size_t)(M * (E > F ? E : F)));
     double * qkv = (double *)malloc(sizeof(double) * (size_t)(M * W3));
@@ -504,8 +507,8 @@ ORACLE_API int32_t oracle_eval_embeddings(oracle_decoder * d, const float * emb,
         matmul(d, &L->down, g, F, x, E, 0, M, 1, round_ops);
     }
     /* the logits of the last position only: never operand-rounded (the reference runs its one-token kernel there, metal_llama_decoder.mm:375) */
-    rms_rows(d, x + (M - 1) * E, d->output_norm, xn, 1, E, 0);
-    matmul(d, &d->output, xn, E, logits, c->n_vocab, 0, 1, 0, 0);
+    rms_rows(d, x + (M - 1) * E, d->output_norm, xn, 1, E, round_all);
+    matmul(d, &d->output, xn, E, logits, c->n_vocab, 0, 1, 0, round_all);
     d->pos += n;
     free(x); free(xn); free(qkv); free(att); free(g); free(u);
     return 0;
