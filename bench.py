@@ -38,12 +38,13 @@ WORKLOADS = {0: (512, 128, 512), 1: (512, 128, 512), 2: (2048, 256, 2048), 3: (8
 WORKLOAD_NAMES = {0: "qwen2.5-0.5b-arch q4_0, 512-token prompt + 128 greedy tokens, batch 1",
                   1: "qwen2.5-0.5b-arch q4_k_m-style mix, 512-token prompt + 128 greedy tokens, batch 1",
                   2: "llama-3-8b-arch q4_0, 2048-token prompt + 256 greedy tokens, batch 1",
-                  3: "qwen2.5-32b-arch q4_k_m-style mix, 8192-token prompt + 256 greedy tokens, batch 1"}
+                  3: "qwen2.5-32b-arch q4_k_m-style mix, 8192-token prompt + 256 greedy tokens, batch 1",
+                  4: "qwen2.5-0.5b-arch q4_0, 256 sequences, prompts U[32,4096] + U[16,512] greedy tokens, batched per GPU, data parallel"}
 
 
 def config_dict(config: int, world: int, depth: int, matrix_bytes: int) -> dict:
     """The workload description both arms print, key for key."""
-    return {"workload": WORKLOAD_NAMES[config], "parallelism": f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
+    return {"workload": WORKLOAD_NAMES[config], "parallelism": f"dp{world}" if config == 4 else f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
             f"{matrix_bytes / 1e9:.2f} GB of weights, {matrix_bytes / 126e6:.0f}x the 126 MB L2", "queue_depth": depth}
 
 
@@ -149,8 +150,8 @@ def run_reference_arm(args, rank, world, dist):
     if rank != 0:
         return
     config = args.config
-    path, spec = model_file(config, 0, 1, None)
-    n_decode = 4 if config >= 2 else 16
+    path, spec = model_file(0 if config == 4 else config, 0, 1, None)
+    n_decode = 4 if config in (2, 3) else 16
     steps, warmup = args.steps, args.warmup
     from oracle import binding as ob
     from dooms_b200 import synth
@@ -274,13 +275,113 @@ def tp_check(path: str, prompt, n_gen: int, n_batch: int, tokens_tp: list[int], 
             "greedy_tokens_equal": toks == list(tokens_tp), "n_tokens": len(toks), "first_difference": None if toks == list(tokens_tp) else n_equal}
 
 
+def run_serving_config(args, rank, world, local):
+    """--config 4: the many-sequence load on the config-0 model. The 256 seeded sequences are dealt over the ranks (longest first, round-robin; no
+    collective on the data path), each rank evaluates its prompts into KV-cache slots and then decodes all of its sequences together, one pass over the
+    weights per step. One bench step = the whole job. value = generated tokens of all ranks / the slowest rank's device time in the decode steps."""
+    import torch
+    import torch.distributed as dist
+    from dooms_b200 import CudaLlamaDecoder, serving
+    from dooms_b200 import _lib as L
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decoder has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))      # barriers and the max over ranks of the timings only
+    path, spec = model_file(0, rank, world, dist)
+    seqs = serving.workload(256, spec.n_vocab, 3000)
+    order = sorted(range(len(seqs)), key=lambda i: -(seqs[i][1] * 8 + len(seqs[i][0])))
+    mine = order[rank::world]
+    n_ctx = max(len(p) + d for p, d in seqs) + 8
+    dec = CudaLlamaDecoder.load(path, n_ctx, 2048, device=local, max_sequences=len(mine))
+    share = [seqs[i] for i in mine]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    tokens = None
+    for _ in range(max(args.warmup, 3)):
+        tokens, _ = serving.run_batched(dec, share)
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    t_begin = time.perf_counter()
+    tot = {"prefill_ms": 0.0, "decode_ms": 0.0, "prefill_wall_s": 0.0, "decode_wall_s": 0.0}
+    steps_run = 0
+    for _ in range(args.steps):
+        tokens, st = serving.run_batched(dec, share)
+        for k in tot:
+            tot[k] += st[k]
+        steps_run = st["steps"]
+    launches = dec.timings()["last_batch_launches"]
+    barrier()
+    t_total = time.perf_counter() - t_begin
+    clocks = sampler.stop() if rank == 0 else None
+    stats = torch.tensor([tot["prefill_ms"], tot["decode_ms"], tot["prefill_wall_s"], tot["decode_wall_s"]], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    prefill_ms, decode_ms, prefill_wall, decode_wall = [float(v) for v in stats.cpu()]
+    check = None
+    if rank == 0:
+        # outside the timed region: a sample of this rank's sequences run alone (one position per call), compared token by token
+        dec.close()
+        one = CudaLlamaDecoder.load(path, n_ctx, 2048, device=local)
+        sample = list(range(0, len(share), max(1, len(share) // 8)))[:8]
+        agree = total = identical = 0
+        for j in sample:
+            alone = serving.run_sequence(one, share[j][0], share[j][1])[0]
+            prefix = next((i for i, (a, b) in enumerate(zip(alone, tokens[j])) if a != b), len(alone))
+            agree += prefix
+            total += len(alone)
+            identical += prefix == len(alone)
+        one.close()
+        check = {"sequences_checked": len(sample), "identical_sequences": identical, "tokens": total, "tokens_before_first_difference": agree,
+                 "note": "a batched step rounds operands to f16 in its tensor-core tiles, a single run does not: a sequence may part from its single run at a near tie"}
+    else:
+        dec.close()
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    pk = peaks()
+    K = args.steps
+    n_gen = sum(d for _, d in seqs)
+    n_prompt = sum(len(p) for p, _ in seqs)
+    decode_tokens = n_gen - len(seqs)                  # a sequence's first token comes out of its prompt
+    matrix_bytes = spec.matrix_bytes()
+    step_us = decode_ms / K / max(steps_run, 1) * 1e3
+    line = {
+        "metric": "decode_tok_s", "value": decode_tokens * K / (decode_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": 1e3 * t_total / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "ours",
+        "config": config_dict(4, world, args.depth, matrix_bytes), "sequences_per_gpu": len(mine),
+        "prefill_tok_s": n_prompt * K / (prefill_ms * 1e-3), "prefill_ms": prefill_ms / K, "decode_ms": decode_ms / K, "decode_steps": steps_run,
+        "decode_step_us": step_us,
+        "e2e": {"value": decode_tokens * K / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": int(n_prompt * 4 + steps_run * 0 + 3 * 4 * len(mine)),
+                "d2h_bytes_per_step": int(n_gen * 4), "wall_ms_per_step": 1e3 * (prefill_wall + decode_wall) / K,
+                "total_tok_s_wall": (n_prompt + n_gen) * K / (prefill_wall + decode_wall)},
+        "gpu_launches": int(launches * steps_run * K),
+        "roofline": {"bound": "hbm", "kernel": f"one batched decode step ({len(mine)} rows): every weight matrix read once", "achieved": matrix_bytes / (step_us * 1e-6) / 1e9,
+                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": matrix_bytes / (step_us * 1e-6) / 1e9 / pk["hbm_gbs"], "peak_source": pk["source"],
+                     "traffic": None, "bytes_per_launch": matrix_bytes, "us_per_launch": step_us},
+        "clocks": clocks, "dp_check": check, "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[0, 1, 2, 3])
+    ap.add_argument("--config", type=int, default=2, choices=[0, 1, 2, 3, 4])
     ap.add_argument("--depth", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -291,6 +392,9 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, rank, world, None)
+        return
+    if args.config == 4:
+        run_serving_config(args, rank, world, local)
         return
 
     import torch

@@ -867,8 +867,9 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
                      ? std::min<int32_t>({n_seq, c.n_batch, 1024}) : 0;
     if (m.max_rows > 0) {
         const size_t R = size_t(m.max_rows);
-        // about two blocks per SM over (rows x key/value heads x ranges), and no more ranges than the context has tiles of 64 positions
-        m.b_splits = std::max(1, std::min({cuda::attention_gqa_splits(m.nkv, c.n_ctx), (2 * prop.multiProcessorCount + m.max_rows * m.nkv - 1) / (m.max_rows * m.nkv)}));
+        // Rows attend over very different lengths (a fresh sequence beside one at the end of its context), so the ranges are short: about eight tiles of 64
+        // positions each, which bounds what one block does and lets the long rows spread over many SMs; a short row's later ranges are empty and leave at once.
+        m.b_splits = std::max(1, std::min(64, (c.n_ctx + 511) / 512));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_rows), 3 * R * sizeof(int32_t), "the rows of a batched decode step"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_out), size_t(Impl::kMaxBatchSteps) * R * sizeof(int32_t), "the tokens of a batched decode call"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_step), sizeof(int32_t), "the step counter"));

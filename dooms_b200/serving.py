@@ -1,7 +1,10 @@
 """Many independent sequences over one or more GPUs, data parallel: one worker process per GPU, each with its own decoder (weights replicated, its own KV
-cache), pulling sequences from a shared queue and running them one after another: prompt in chunks, then greedy decode. No collective on the data path.
-This is the replicas form of the reference's serving loop, which handles one request at a time (docs/USING.md:103, python/dooms/server.py:262-269);
-batching several sequences into one decode step is not built.
+cache). No collective on the data path. Two ways to run a GPU's share:
+  * batched (serve_batched, the default of the command below): the decoder holds one KV-cache slot per sequence, every prompt is evaluated into its slot,
+    and then all sequences decode together, one pass over the weights per step for all of them (CudaLlamaDecoder.decode_batch); a sequence that has all
+    its tokens leaves its row idle;
+  * one at a time (serve): sequences pulled from a shared queue and run one after another, the reference's serving loop (docs/USING.md:103,
+    python/dooms/server.py:262-269), optionally several decoders per GPU on their own streams.
 
     python -m dooms_b200.serving --model m.gguf --gpus 2 --sequences 256 [--check 4]
 
@@ -37,6 +40,86 @@ def run_sequence(dec, prompt, n_decode: int, depth: int = 4):
     tokens: list[int] = []
     dec.generate(n_decode, depth, lambda t: tokens.append(t) or True)
     return tokens, prefill_ms, dec.timings()["last_generate_ms"]
+
+
+def run_batched(dec, sequences, max_steps_per_call: int = 256):
+    """Every (prompt, n_decode) of `sequences` on one decoder with at least len(sequences) slots: prompts one after another into their slots, then batched
+    decode steps until the longest is done. Returns (tokens per sequence, {device ms and wall seconds of the prompts and of the decode steps, steps run})."""
+    n = len(sequences)
+    tokens: list[list[int]] = []
+    prefill_ms = 0.0
+    t_start = time.perf_counter()
+    for s, (prompt, _) in enumerate(sequences):
+        dec.select_sequence(s)
+        dec.reset()
+        dec.eval_tokens(prompt)
+        prefill_ms += dec.timings()["last_eval_ms"]
+        tokens.append([dec.pending_token()])          # the first token comes from the prompt
+    need = [d - 1 for _, d in sequences]               # decode steps each sequence still wants
+    decode_ms, steps_run = 0.0, 0
+    t_decode = time.perf_counter()
+    while any(k > 0 for k in need):
+        k = min(min(k for k in need if k > 0), max_steps_per_call)
+        slots = [s if need[s] > 0 else -1 for s in range(n)]      # always n rows: one captured graph serves every call
+        out = dec.decode_batch(slots, k)
+        decode_ms += dec.timings()["last_batch_ms"]
+        steps_run += k
+        for s in range(n):
+            if need[s] > 0:
+                tokens[s].extend(int(t) for t in out[:, s])
+                need[s] -= k
+    t_end = time.perf_counter()
+    return tokens, {"prefill_ms": prefill_ms, "decode_ms": decode_ms, "steps": steps_run, "prefill_wall_s": t_decode - t_start, "decode_wall_s": t_end - t_decode}
+
+
+def _batched_worker(device: int, path: str, n_ctx: int, n_batch: int, sequences, mine, done):
+    from . import CudaLlamaDecoder
+    dec = CudaLlamaDecoder.load(path, n_ctx, n_batch, device=device, max_sequences=max(2, len(mine)))
+    done.put(("ready", device))
+    tokens, st = run_batched(dec, [sequences[i] for i in mine])
+    done.put(("batch", device, mine, tokens, st["prefill_ms"], st["decode_ms"], st["steps"]))
+    dec.close()
+    done.put(("closed", device))
+
+
+def serve_batched(path: str, sequences, devices, n_ctx: int, n_batch: int = 2048):
+    """The sequences dealt over the devices (longest first, round-robin, so that every device's longest sequences are alike), each device's share run as
+    one batch. Returns (tokens per sequence, stats); decode_tok_s = generated tokens of all devices / the slowest device's decode time."""
+    ctx = mp.get_context("spawn")
+    done = ctx.Queue()
+    order = sorted(range(len(sequences)), key=lambda i: -(sequences[i][1] * 8 + len(sequences[i][0])))
+    shares = [order[k::len(devices)] for k in range(len(devices))]
+    workers = [ctx.Process(target=_batched_worker, args=(d, path, n_ctx, n_batch, sequences, mine, done), daemon=True) for d, mine in zip(devices, shares)]
+    for w in workers:
+        w.start()
+    tokens = [None] * len(sequences)
+    pre, dec_ms, steps = {}, {}, {}
+    ready = closed = 0
+    t0 = None
+    while closed < len(workers):
+        msg = done.get()
+        if msg[0] == "ready":
+            ready += 1
+            if ready == len(workers):
+                t0 = time.perf_counter()          # (the workers start on their own; this wall clock is a lower bound of the job's)
+        elif msg[0] == "batch":
+            _, dev, mine, toks, p_ms, d_ms, st = msg
+            for i, t in zip(mine, toks):
+                tokens[i] = t
+            pre[dev], dec_ms[dev], steps[dev] = p_ms, d_ms, st
+        elif msg[0] == "closed":
+            closed += 1
+    wall = time.perf_counter() - (t0 or time.perf_counter())
+    for w in workers:
+        w.join()
+    n_gen = sum(len(t) for t in tokens)
+    n_prompt = sum(len(s[0]) for s in sequences)
+    slowest = max(dec_ms.values()) / 1e3
+    stats = {"sequences": len(sequences), "prompt_tokens": n_prompt, "generated_tokens": n_gen, "wall_s": wall, "mode": "batched",
+             "decode_tok_s": (n_gen - len(sequences)) / slowest if slowest > 0 else 0.0,
+             "prefill_tok_s": n_prompt / (max(pre.values()) / 1e3) if max(pre.values()) > 0 else 0.0,
+             "decode_steps": max(steps.values()), "workers": len(devices)}
+    return tokens, stats
 
 
 def _worker(device: int, path: str, n_ctx: int, n_batch: int, sequences, todo, done, streams: int = 1):
@@ -113,7 +196,7 @@ def main(argv=None):
     ap.add_argument("--sequences", type=int, default=256)
     ap.add_argument("--check", type=int, default=0, help="re-run this many sequences alone on GPU 0 and compare their tokens")
     ap.add_argument("--seed", type=int, default=3000)
-    ap.add_argument("--streams", type=int, default=1, help="decoders per GPU, each on its own stream and thread")
+    ap.add_argument("--streams", type=int, default=0, help="0: each GPU's share as one batch; K > 0: one sequence at a time on K decoders per GPU")
     args = ap.parse_args(argv)
     from . import CudaLlamaDecoder
     from .gguf_io import GgufFile
@@ -122,12 +205,16 @@ def main(argv=None):
     f.close()
     seqs = workload(args.sequences, n_vocab, args.seed)
     n_ctx = max(len(p) + d for p, d in seqs) + 8
-    tokens, stats = serve(args.model, seqs, list(range(args.gpus)), n_ctx, streams=args.streams)
+    if args.streams > 0:
+        tokens, stats = serve(args.model, seqs, list(range(args.gpus)), n_ctx, streams=args.streams)
+    else:
+        tokens, stats = serve_batched(args.model, seqs, list(range(args.gpus)), n_ctx)
     if args.check:
         dec = CudaLlamaDecoder.load(args.model, n_ctx, 2048, device=0)
         same = 0
         for i in range(0, len(seqs), max(1, len(seqs) // args.check))[:args.check]:
-            same += run_sequence(dec, seqs[i][0], seqs[i][1])[0] == tokens[i]
+            alone = run_sequence(dec, seqs[i][0], seqs[i][1])[0]
+            same += alone == tokens[i]
         dec.close()
         stats["checked"] = args.check
         stats["identical"] = int(same)
