@@ -115,6 +115,10 @@ struct CudaLlamaDecoder::Impl {
     int * norm_counters = nullptr;  // one per 32 rows of x
     bool link_ready = false;        // xq2 / norm_ss describe the current x
     int link_blocks = 0;
+    // All layers of a one-sequence decode step as one cooperative launch (kernels.h, "the fused decode step"), when the model's shapes allow it.
+    cuda::DecodeLayersPlan * fused = nullptr;
+    int32_t fused_slot = -1;        // the plan holds the cache pointers of this slot
+    bool fused_refused = false;     // the shapes do not fit: do not ask again
     int32_t pos = 0;
     bool has_pending = false;
     // decode graph
@@ -139,6 +143,7 @@ struct CudaLlamaDecoder::Impl {
     ~Impl() {
         if (stream) cudaStreamSynchronize(stream);
         if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
+        cuda::decode_layers_destroy(fused);
         for (auto & g : batch_graphs) cudaGraphExecDestroy(g.second);
         for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters}) if (p) cudaFree(p);
         for (void * p : {(void *)h_rows, (void *)h_out}) if (p) cudaFreeHost(p);
@@ -375,6 +380,40 @@ struct CudaLlamaDecoder::Impl {
         use_par = sum == 0.f;
     }
 
+    // The plan of the fused decode step for the selected slot, or nullptr when this model / option set runs kernel by kernel.
+    cuda::DecodeLayersPlan * fused_plan() {
+        // Opt-in (DOOMS_FUSED_STEP=1). Measured on B200 with the 8B shape it is the slower way today: 2.13 ms per token against 1.84 ms for the chain of
+        // early-launched kernels. Stamps inside the kernel show where a layer's 64 us go: not into launches (there are none) but into what every phase
+        // boundary costs however it is implemented: waiting at the barrier for the slowest block of the phase before (1.5 - 4 us of spread per phase),
+        // 2.5 - 3 us of epilogue where a projection also splits its output and leaves the norm's sums, and the attention merge (4 us on eight blocks).
+        static const bool on = [] { const char * e = getenv("DOOMS_FUSED_STEP"); return e && *e == '1'; }();
+        if (!on || fused_refused || tp != 1 || !gqa || profile) return nullptr;
+        if (fused && fused_slot == cur) return fused;
+        cuda::decode_layers_destroy(fused);
+        fused = nullptr;
+        std::vector<cuda::FusedLayer> fl;
+        for (size_t l = 0; l < layers.size(); l++) {
+            const LayerDev & L = layers[l];
+            bool ok = L.qkv.size() == 1 && fast(L.qkv[0].w);
+            for (const MatDev * w : {&L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down}) ok = ok && fast(*w);
+            if (!ok) { fused_refused = true; return nullptr; }
+            auto mat = [](const MatDev & w) { return cuda::FusedMatrix{w.ptr, w.rows, w.cols, w.dt == DType::Q4_K}; };
+            const float * next = l + 1 < layers.size() ? layers[l + 1].attn_norm : output_norm;
+            fl.push_back(cuda::FusedLayer{mat(L.qkv[0].w), mat(L.attn_output), mat(L.ffn_gate), mat(L.ffn_up), mat(L.ffn_down), L.attn_norm, L.ffn_norm, L.qkv_bias, next,
+                                          kc + l * cache_layer_elems + size_t(cur) * slot_elems, vc + l * cache_layer_elems + size_t(cur) * slot_elems});
+        }
+        const cuda::FusedBuffers fb{x, qkv, attn, h, xq, xq2, norm_ss, norm_counters, split_counters, attn_counters, part, state, inv_freq, rope_cs, host_error, cfg.rms_eps,
+                                    attn_shape(), gqa_splits};
+        if (cuda::decode_layers_create(fl.data(), int(fl.size()), fb, &fused) != cudaSuccess) {
+            (void)cudaGetLastError();
+            fused = nullptr;
+            fused_refused = true;
+            return nullptr;
+        }
+        fused_slot = cur;
+        return fused;
+    }
+
     // All layers for M positions starting at state->pos whose input rows are in x; then the logits and the greedy token of the last row
     // (encode_forward, metal_llama_decoder.mm:311-385).
     void forward(int M, bool advance) {
@@ -383,8 +422,17 @@ struct CudaLlamaDecoder::Impl {
         const bool single = tp == 1;
         link_ready = false;      // x was just written by the embedding (or by the caller)
         // one position: its rotary angles are the same for every head of every layer
-        if (M == 1 && gqa) run("rope_table", [&] { return cuda::launch_rope_table(state, inv_freq, rope_cs, cfg.head_dim, stream); });
-        for (size_t l = 0; l < layers.size(); l++) {
+        cuda::DecodeLayersPlan * const one_launch = M == 1 ? fused_plan() : nullptr;
+        if (M == 1 && gqa) {
+            run("rope_table", [&] { return cuda::launch_rope_table(state, inv_freq, rope_cs, cfg.head_dim, stream, one_launch ? cuda::decode_layers_barrier(one_launch) : nullptr); });
+        }
+        if (one_launch) {
+            run("layers", [&] { return cuda::launch_decode_layers(one_launch, stream); });
+            link_ready = true;          // its last ffn_down prepared the output norm
+            link_blocks = cuda::decode_layers_blocks(one_launch);
+            xq_of = nullptr;
+        }
+        for (size_t l = 0; l < (one_launch ? 0 : layers.size()); l++) {
             const LayerDev & L = layers[l];
             __half * kcl = kc + l * cache_layer_elems + size_t(cur) * slot_elems, * vcl = vc + l * cache_layer_elems + size_t(cur) * slot_elems;
             // Tensor-parallel decode steps with a power-of-two group: the projection leaves x / tp + its share of the product in x, and the in-place all-reduce
@@ -489,6 +537,7 @@ struct CudaLlamaDecoder::Impl {
         }
         if (step_graph || !opt.use_graphs) return Status();
         graph_slot = cur;
+        (void)fused_plan();      // built (device allocations, copies) before the capture starts
         DOOMS_RETURN_IF_ERROR(wait_idle());
         const int64_t before = launches;
         cudaGraph_t graph = nullptr;

@@ -19,11 +19,14 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <memory>
+#include <vector>
 
 #include "kernels.h"
 #include "ptx.cuh"
 #include "launch.cuh"
 #include "xsplit.cuh"
+#include "attention_decode_body.cuh"
 
 namespace dooms {
 namespace cuda {
@@ -159,9 +162,51 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // different banks, and 8 rows x 144 bytes = 1152 bytes keeps every copy's destination aligned. One elected lane issues two 8-row copies per sub-stage (one
 // when the block's last tile has at most 8 rows) and the warp waits on its own mbarrier per stage (bounded). Blocks own multiples of 8 rows, so nothing
 // outside a block's range is fetched; rows past the end of the matrix are zero-filled by the copy.
-template <int WARPS, int STAGES, bool K4, bool TMA>
-__global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_constant__ CUtensorMap mw, const __grid_constant__ CUtensorMap mw2, const GemvQ40Params p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+//
+// The kernel's work is a device function so that two kernels run it: k_gemv_q4_0 (one projection per launch) and the fused decode step further down, which
+// walks through all projections of all layers in one launch. FUSED: `block_index` / `n_blocks` stand for blockIdx.x / gridDim.x, the wait for the
+// producer of the input is a grid-wide barrier (grid) instead of the launch dependency, the mbarriers are invalidated at the end so that the next phase
+// can set them up again, and a block may own no rows at all.
+// A barrier over all blocks of a cooperative launch. Arrivals are counted in one device word (zeroed by the launch's first kernel); the block whose
+// arrival completes a round publishes the round's number in a second word, on a cache line of its own, and that is the word the others poll: the
+// counter's line only ever sees the atomics. Waits are bounded: after one that ran out the block stops waiting at later barriers, reports through
+// `error` (5) and runs to the end on whatever data it finds; the host discards the step.
+struct GridBarrier {
+    unsigned * words;          // [0]: arrivals; [32]: rounds completed
+    int32_t * error;
+    unsigned n_blocks;
+    unsigned round = 0;
+    bool broken = false;
+};
+constexpr uint32_t kGridPolls = 1u << 22;
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned * p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void grid_barrier(GridBarrier & g) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        g.round += 1;
+        unsigned seen;
+        // release: this block's writes (ordered before by the barrier above) are visible before its arrival is; acquire: the last arriver sees everyone's
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(g.words) : "memory");
+        if (seen + 1 == g.round * g.n_blocks) {
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.words + 32), "r"(g.round) : "memory");
+        } else if (!g.broken) {
+            uint32_t polls = 0;
+            while (ld_acquire_gpu(g.words + 32) < g.round) {
+                if (++polls > kGridPolls) { g.broken = true; if (g.error) *g.error = 5; break; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+template <int WARPS, int STAGES, bool K4, bool TMA, bool FUSED>
+__device__ __forceinline__ void gemv_q4_0_body(const CUtensorMap * mwp, const CUtensorMap * mw2p, const GemvQ40Params & p, uint8_t * smem, const int block_index,
+                                               const int n_blocks, GridBarrier * grid) {
+    (void)n_blocks;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const int nb = p.cols / 32;
     const int nmat = p.W2 ? 2 : 1;
@@ -170,8 +215,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
 
     // this block's rows
     // rows are dealt in units of p.row_unit rows (1, or 8 with tensor copies): block b gets rows_q + (b < rows_r) units
-    const int64_t R0 = (int64_t(blockIdx.x) * p.rows_q + min(int(blockIdx.x), p.rows_r)) * p.row_unit;
-    const int nrows = int(min(int64_t(p.rows_q + (int(blockIdx.x) < p.rows_r ? 1 : 0)) * p.row_unit, p.rows - R0));
+    const int64_t R0 = (int64_t(block_index) * p.rows_q + min(block_index, p.rows_r)) * p.row_unit;
+    const int nrows = int(max(int64_t(0), min(int64_t(p.rows_q + (block_index < p.rows_r ? 1 : 0)) * p.row_unit, p.rows - R0)));
     const int ntiles = (nrows + kTileRows - 1) / kTileRows;
     const int total_units = ntiles * nmat * p.nchunks;
     const int my_units = warp < total_units ? (total_units - warp - 1) / WARPS + 1 : 0;
@@ -219,7 +264,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
                 const uint32_t halves = tile != ntiles - 1 ? 2u : uint32_t(last_rows + 8) / 8u;      // 8-row copies that hold rows of this block
                 const uint32_t bar = bars + 8u * uint32_t(f_slot);
                 mbar_arrive_expect_tx(bar, rounds * halves * (kSub / 2u));
-                const CUtensorMap * m = mat ? &mw2 : &mw;
+                const CUtensorMap * m = mat ? mw2p : mwp;
                 const int x = f_chunk * int(CB / 2u), y = int(R0) + tile * kTileRows;
                 for (uint32_t r = 0; r < rounds; r++) {
                     for (uint32_t hb = 0; hb < halves; hb++) {
@@ -264,14 +309,15 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
     }
     // The first STAGES - 1 stages of weights are asked for at once: they do not depend on the kernel before this one, which may still be running (this
     // kernel is launched early, see launch.cuh). Only then wait for that kernel, and fetch the split input it (or one before it) wrote, as one more group.
-    pdl_trigger();
+    if constexpr (!FUSED) pdl_trigger();
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (fetched < my_units) { fetch(); fetched++; }
         cp_async_commit();
     }
     for (int i = threadIdx.x; i < ntiles * nmat * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
-    pdl_wait();
+    if constexpr (FUSED) grid_barrier(*grid);      // the phase before this one has written its results, everywhere
+    else pdl_wait();
     __shared__ float norm_scale;
     if (p.xq) {
         for (uint32_t i = threadIdx.x; i < uint32_t(nb) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
@@ -296,7 +342,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
             #pragma unroll
             for (int j = 0; j < kHeld; j++) {
                 const int blk = warp + j * WARPS;
-                v[j] = blk < nb ? p.x[blk * 32 + lane] : 0.f;
+                v[j] = blk < nb ? __ldcg(p.x + blk * 32 + lane) : 0.f;
                 gm[j] = (p.gamma && blk < nb) ? p.gamma[blk * 32 + lane] : 1.f;
             }
             float inv = 1.f;
@@ -322,7 +368,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
             float inv = 1.f;
             if (p.gamma) {
                 float ss = 0.f;
-                for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) { const float v = p.x[i]; ss += v * v; }
+                for (int i = threadIdx.x; i < p.cols; i += WARPS * 32) { const float v = __ldcg(p.x + i); ss += v * v; }
                 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 if (lane == 0) red[warp] = ss;
@@ -337,7 +383,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
                 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int blk = blk0 + j * WARPS;
-                    v[j] = blk < nb ? p.x[blk * 32 + lane] : 0.f;
+                    v[j] = blk < nb ? __ldcg(p.x + blk * 32 + lane) : 0.f;
                     gm[j] = (p.gamma && blk < nb) ? p.gamma[blk * 32 + lane] : 1.f;
                 }
                 #pragma unroll
@@ -462,7 +508,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
         }
         const int64_t row = R0 + r;
         if (p.flags & kFlagBias) s += p.bias[row];
-        const float out = (p.flags & kFlagAccumulate) ? accumulate_base(p.y[row], p.flags) + s : s;
+        const float out = (p.flags & kFlagAccumulate) ? accumulate_base(__ldcg(p.y + row), p.flags) + s : s;
         p.y[row] = out;
         sq += out * out;
     }
@@ -477,10 +523,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
             float total = 0.f;
             #pragma unroll
             for (int w = 0; w < WARPS; w++) total += sq_warp[w];
-            p.ss_out[blockIdx.x] = total;
+            p.ss_out[block_index] = total;
         }
     }
-    if (p.xq_out) {
+    if constexpr (FUSED) {
+        __syncwarp();
+        if (TMA && lane == 0) for (int s2 = 0; s2 < STAGES; s2++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bars + 8u * s2) : "memory");
+    }
+    if (p.xq_out && nrows > 0) {
         __threadfence();              // this block's rows are visible before they are counted
         __syncthreads();
         const int64_t R1 = R0 + nrows;
@@ -497,6 +547,67 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_consta
                 split_block(p.gamma_out ? v * p.gamma_out[grp * 32 + lane] : v, lane, int(grp), int(p.rows / 32), p.xq_out);
             }
         }
+    }
+}
+
+template <int WARPS, int STAGES, bool K4, bool TMA>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q4_0(const __grid_constant__ CUtensorMap mw, const __grid_constant__ CUtensorMap mw2, const GemvQ40Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    gemv_q4_0_body<WARPS, STAGES, K4, TMA, false>(&mw, &mw2, p, smem, int(blockIdx.x), int(gridDim.x), nullptr);
+}
+
+// ---- the fused decode step: every projection and every attention of all layers in ONE cooperative launch ----
+// A decode step of one sequence is a chain of ~5 dependent kernels per layer, each a few microseconds long; between two of them the GPU drains, launches,
+// warms up and refills its copy pipelines, which costs about as much as the kernels' own streaming. Here one block per SM stays resident for the whole
+// step and walks through the phases (qkv projection, attention, attn_output, gate / up, ffn_down of every layer); where a launch boundary stood there is
+// a grid-wide barrier, and every projection asks for its first weight stages BEFORE it waits at that barrier, so the weights keep arriving while the
+// previous phase's last blocks finish. The phases run the same device code as the kernels of their own (gemv_q4_0_body, attention_decode_body).
+constexpr int kFusedWarps = 16, kFusedStages = 2, kFusedThreads = kFusedWarps * 32;
+
+struct FusedPhase {
+    int32_t kind;              // 0: projection, 1: attention
+    int32_t k4;                // projection: q4_K rows
+    int32_t map_w, map_w2;     // projection: indices into the tensor map array
+    GemvQ40Params g;
+    attn_decode::AttnDecodeParams a;
+};
+struct FusedArgs {
+    const FusedPhase * phases;
+    const CUtensorMap * maps;
+    int32_t n_phases;
+    unsigned * barrier;        // two words 128 bytes apart, zeroed by the step's first kernel
+    int32_t * error;
+};
+
+template <int D, int GP>
+__global__ void __launch_bounds__(kFusedThreads, 1) k_decode_layers(const FusedArgs fa) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(16) FusedPhase ph[2];
+    static_assert(sizeof(FusedPhase) % 4 == 0, "phases are copied word by word");
+    constexpr int kWords = int(sizeof(FusedPhase) / 4);
+    GridBarrier gb{fa.barrier, fa.error, gridDim.x};
+    const int block = int(blockIdx.x), n_blocks = int(gridDim.x);
+    auto stage_phase = [&](int i) {      // phase i's description into its shared-memory slot (a handful of words per thread)
+        const uint32_t * src = reinterpret_cast<const uint32_t *>(fa.phases + i);
+        uint32_t * dst = reinterpret_cast<uint32_t *>(&ph[i & 1]);
+        for (int w = threadIdx.x; w < kWords; w += kFusedThreads) dst[w] = __ldg(src + w);
+    };
+    stage_phase(0);
+    __syncthreads();
+    for (int i = 0; i < fa.n_phases; i++) {
+        if (i + 1 < fa.n_phases) stage_phase(i + 1);      // nobody reads that slot during this phase; the barrier at the phase's end publishes it
+        const FusedPhase & cur = ph[i & 1];
+        if (cur.kind == 0) {
+            if (cur.k4) gemv_q4_0_body<kFusedWarps, kFusedStages, true, true, true>(fa.maps + cur.map_w, fa.maps + cur.map_w2, cur.g, smem, block, n_blocks, &gb);
+            else gemv_q4_0_body<kFusedWarps, kFusedStages, false, true, true>(fa.maps + cur.map_w, fa.maps + cur.map_w2, cur.g, smem, block, n_blocks, &gb);
+        } else {
+            grid_barrier(gb);                              // q, k and v of this layer are complete
+            const int nkv = cur.a.s.n_head_kv;
+            if (threadIdx.x < attn_decode::kThreads && block < nkv * cur.a.splits) {
+                attn_decode::attention_decode_body<D, GP, false>(cur.a, block % nkv, block / nkv, cur.a.splits, 0, smem);
+            }
+        }
+        __syncthreads();                                   // the phase's shared memory is free, the next phase's description is in place
     }
 }
 
@@ -641,6 +752,169 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
     p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
     if (q4_k) return pl.warps == 16 ? launch_stages<16, true>(p, maps, tma, pl, grid, stream) : launch_stages<8, true>(p, maps, tma, pl, grid, stream);
     return pl.warps == 16 ? launch_stages<16, false>(p, maps, tma, pl, grid, stream) : launch_stages<8, false>(p, maps, tma, pl, grid, stream);
+}
+
+// ---- host side of the fused decode step ----
+struct DecodeLayersPlan {
+    FusedPhase * phases = nullptr;
+    CUtensorMap * maps = nullptr;
+    unsigned * barrier = nullptr;
+    int n_phases = 0, blocks = 0, head_dim = 0, gp = 0;
+    size_t smem = 0;
+    int32_t * error = nullptr;
+};
+
+namespace {
+
+// One projection's kernel arguments as the fused kernel runs it: tensor copies, kFusedWarps warps, kFusedStages stages, the rows dealt over `blocks`.
+bool fused_projection(const FusedMatrix & m, const void * w2, int blocks, GemvQ40Params * out, size_t * smem) {
+    const int nmat = w2 ? 2 : 1;
+    if (!m.w || (reinterpret_cast<uintptr_t>(m.w) & 15u) || (w2 && (reinterpret_cast<uintptr_t>(w2) & 15u))) return false;
+    if (!takes_tma(m.rows, m.cols, nmat, m.q4_k)) return false;
+    const Plan pl = plan_for(m.cols, nmat, m.q4_k, true);
+    if (!pl.ok || pl.warps != kFusedWarps || pl.stages != kFusedStages) return false;
+    const int64_t units = (m.rows + 7) / 8;
+    const int64_t per_block_rows = ((units + blocks - 1) / blocks) * 8;
+    if (per_block_rows > int64_t(kMaxTilesPerBlock) * kTileRows) return false;      // the table of per-warp sums would not hold the block's tiles
+    GemvQ40Params p{};
+    p.W = static_cast<const uint8_t *>(m.w);
+    p.W2 = static_cast<const uint8_t *>(w2);
+    p.rows = m.rows;
+    p.cols = int(m.cols);
+    p.cbk = pl.cbk; p.nchunks = pl.nchunks; p.stride = pl.stride;
+    p.upr = pl.cbk * kBlockBytes / 16;
+    p.row_unit = 8;
+    p.rows_q = int(units / blocks);
+    p.rows_r = int(units % blocks);
+    p.inv_upr = 65536u / uint32_t(p.upr) + 1u;
+    p.inv_nchunks = 65536u / uint32_t(pl.nchunks) + 1u;
+    *out = p;
+    *smem = std::max(*smem, pl.smem);
+    return true;
+}
+
+template <int D>
+cudaError_t launch_fused_group(const DecodeLayersPlan & pl, const FusedArgs & fa, cudaStream_t stream) {
+    void * args[] = {const_cast<FusedArgs *>(&fa)};
+    auto go = [&](auto kernel) -> cudaError_t {
+        static std::atomic<uint64_t> configured{0};
+        if (const cudaError_t e = allow_dynamic_smem(kernel, int(kSmemLimit), configured); e != cudaSuccess) return e;
+        return cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), dim3(unsigned(pl.blocks)), dim3(kFusedThreads), args, pl.smem, stream);
+    };
+    switch (pl.gp) {
+        case 1: return go(k_decode_layers<D, 1>);
+        case 2: return go(k_decode_layers<D, 2>);
+        case 4: return go(k_decode_layers<D, 4>);
+        default: return go(k_decode_layers<D, 8>);
+    }
+}
+
+}  // namespace
+
+cudaError_t decode_layers_create(const FusedLayer * layers, int n_layers, const FusedBuffers & b, DecodeLayersPlan ** out) {
+    *out = nullptr;
+    int dev = 0, coop = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    const AttnShape & s = b.shape;
+    if (!coop || n_layers < 1 || !attention_gqa_supported(s) || s.head_dim % 32 != 0) return cudaErrorNotSupported;
+    const int blocks = sm_count();
+    const int G = s.n_head / s.n_head_kv, gp = G == 1 ? 1 : G == 2 ? 2 : G <= 4 ? 4 : 8;
+    const int splits = std::min(b.max_splits, blocks / s.n_head_kv);
+    if (splits < 1) return cudaErrorNotSupported;
+    std::vector<FusedPhase> phases;
+    std::vector<CUtensorMap> maps;
+    size_t smem = s.head_dim == 64 ? attn_decode::attention_decode_smem_bytes<64, 8>() : attn_decode::attention_decode_smem_bytes<128, 8>();
+    auto add_map = [&](const FusedMatrix & m, const void * w) -> int {
+        CUtensorMap tm;
+        if (make_rows_map(reinterpret_cast<TensorMap *>(&tm), w, m.rows, m.cols / 32 * kBlockBytes, 8 * kBlockBytes, 8) != cudaSuccess) return -1;
+        maps.push_back(tm);
+        return int(maps.size()) - 1;
+    };
+    for (int l = 0; l < n_layers; l++) {
+        const FusedLayer & L = layers[l];
+        if (L.ffn_gate.rows != L.ffn_up.rows || L.ffn_gate.cols != L.ffn_up.cols || L.ffn_gate.q4_k != L.ffn_up.q4_k) return cudaErrorNotSupported;
+        if (L.attn_output.rows % 32 != 0 || L.ffn_gate.rows % 32 != 0 || L.ffn_down.rows % 32 != 0 || !L.next_norm) return cudaErrorNotSupported;
+        FusedPhase q{}, at{}, o{}, gu{}, dn{};
+        // qkv: the first layer normalizes and splits x itself; the others take what the ffn_down before them prepared
+        if (!fused_projection(L.qkv, nullptr, blocks, &q.g, &smem)) return cudaErrorNotSupported;
+        q.k4 = L.qkv.q4_k;
+        q.map_w = q.map_w2 = add_map(L.qkv, L.qkv.w);
+        q.g.eps = b.eps;
+        if (l == 0) { q.g.x = b.x; q.g.gamma = L.attn_norm; }
+        else { q.g.xq = static_cast<const uint8_t *>(b.xq2); q.g.ss_in = b.norm_ss; q.g.ss_n = blocks; }
+        q.g.y = b.qkv;
+        q.g.bias = L.qkv_bias;
+        q.g.flags = L.qkv_bias ? kFlagBias : 0u;
+        q.g.error = b.error;
+        // attention: rotation, cache write, ranges, merge; leaves the row split for attn_output
+        at.kind = 1;
+        at.a = attn_decode::AttnDecodeParams{b.qkv, static_cast<__half *>(L.kc), static_cast<__half *>(L.vc), b.part, b.state, b.inv_freq, 0, splits, s, b.attn_counters, b.attn,
+                                             static_cast<uint8_t *>(b.xq), static_cast<const float2 *>(b.rope_cs), nullptr, nullptr, 0, 0, 0, nullptr};
+        // attn_output: x += W attn; leaves x * (ffn_norm's gains) split, and the sums of squares, for gate / up
+        if (!fused_projection(L.attn_output, nullptr, blocks, &o.g, &smem)) return cudaErrorNotSupported;
+        o.k4 = L.attn_output.q4_k;
+        o.map_w = o.map_w2 = add_map(L.attn_output, L.attn_output.w);
+        o.g.eps = b.eps;
+        o.g.xq = static_cast<const uint8_t *>(b.xq);
+        o.g.y = b.x;
+        o.g.flags = kFlagAccumulate;
+        o.g.xq_out = static_cast<uint8_t *>(b.xq2); o.g.out_counters = b.norm_counters; o.g.gamma_out = L.ffn_norm; o.g.ss_out = b.norm_ss;
+        o.g.error = b.error;
+        // gate / up: h = silu(Wg xn) * (Wu xn); leaves h split for ffn_down
+        if (!fused_projection(L.ffn_gate, L.ffn_up.w, blocks, &gu.g, &smem)) return cudaErrorNotSupported;
+        gu.k4 = L.ffn_gate.q4_k;
+        gu.map_w = add_map(L.ffn_gate, L.ffn_gate.w);
+        gu.map_w2 = add_map(L.ffn_up, L.ffn_up.w);
+        gu.g.eps = b.eps;
+        gu.g.xq = static_cast<const uint8_t *>(b.xq2); gu.g.ss_in = b.norm_ss; gu.g.ss_n = blocks;
+        gu.g.y = b.h;
+        gu.g.xq_out = static_cast<uint8_t *>(b.xq); gu.g.out_counters = b.split_counters;
+        gu.g.error = b.error;
+        // ffn_down: x += W h; prepares the next norm (the next layer's attn_norm, or the output norm)
+        if (!fused_projection(L.ffn_down, nullptr, blocks, &dn.g, &smem)) return cudaErrorNotSupported;
+        dn.k4 = L.ffn_down.q4_k;
+        dn.map_w = dn.map_w2 = add_map(L.ffn_down, L.ffn_down.w);
+        dn.g.eps = b.eps;
+        dn.g.xq = static_cast<const uint8_t *>(b.xq);
+        dn.g.y = b.x;
+        dn.g.flags = kFlagAccumulate;
+        dn.g.xq_out = static_cast<uint8_t *>(b.xq2); dn.g.out_counters = b.norm_counters; dn.g.gamma_out = L.next_norm; dn.g.ss_out = b.norm_ss;
+        dn.g.error = b.error;
+        for (const FusedPhase * f : {&q, &o, &gu, &dn}) if (f->map_w < 0 || f->map_w2 < 0) return cudaErrorNotSupported;
+        phases.insert(phases.end(), {q, at, o, gu, dn});
+    }
+    if (smem > kSmemLimit) return cudaErrorNotSupported;
+    auto plan = std::make_unique<DecodeLayersPlan>();
+    plan->n_phases = int(phases.size());
+    plan->blocks = blocks;
+    plan->head_dim = s.head_dim;
+    plan->gp = gp;
+    plan->smem = smem;
+    plan->error = b.error;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&plan->phases), phases.size() * sizeof(FusedPhase));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&plan->maps), maps.size() * sizeof(CUtensorMap));
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&plan->barrier), 256);
+    if (e == cudaSuccess) e = cudaMemcpy(plan->phases, phases.data(), phases.size() * sizeof(FusedPhase), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(plan->maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(plan->barrier, 0, 256);
+    if (e != cudaSuccess) { decode_layers_destroy(plan.release()); return e; }
+    *out = plan.release();
+    return cudaSuccess;
+}
+
+void decode_layers_destroy(DecodeLayersPlan * plan) {
+    if (!plan) return;
+    for (void * p : {(void *)plan->phases, (void *)plan->maps, (void *)plan->barrier}) if (p) cudaFree(p);
+    delete plan;
+}
+
+int decode_layers_blocks(const DecodeLayersPlan * plan) { return plan->blocks; }
+unsigned * decode_layers_barrier(const DecodeLayersPlan * plan) { return plan->barrier; }
+
+cudaError_t launch_decode_layers(const DecodeLayersPlan * plan, cudaStream_t stream) {
+    const FusedArgs fa{plan->phases, plan->maps, plan->n_phases, plan->barrier, plan->error};
+    return plan->head_dim == 64 ? launch_fused_group<64>(*plan, fa, stream) : launch_fused_group<128>(*plan, fa, stream);
 }
 
 }  // namespace cuda

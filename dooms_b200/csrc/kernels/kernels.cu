@@ -247,8 +247,9 @@ __global__ void k_add(float * x, const float * y, int64_t n) {
 
 // cs[i] = (cos, sin)(st->pos * inv_freq[i]) for the head_dim / 2 rotary pairs, in double precision, rounded to f32: what every head of every layer of one
 // decode step rotates by, computed once per step instead of in every attention launch.
-__global__ void k_rope_table(const DevState * st, const double * inv_freq, float2 * cs, int pairs) {
+__global__ void k_rope_table(const DevState * st, const double * inv_freq, float2 * cs, int pairs, unsigned * zero) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0 && zero) { zero[0] = 0u; zero[32] = 0u; }      // the fused step's barrier words
     if (i >= pairs) return;
     double sd, cd;
     sincos(double(st->pos) * inv_freq[i], &sd, &cd);
@@ -546,9 +547,9 @@ cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t strea
     return cudaGetLastError();
 }
 
-cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream) {
+cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream, unsigned * zero) {
     const int pairs = head_dim / 2;
-    k_rope_table<<<(pairs + 127) / 128, 128, 0, stream>>>(st, inv_freq, static_cast<float2 *>(cs), pairs);
+    k_rope_table<<<(pairs + 127) / 128, 128, 0, stream>>>(st, inv_freq, static_cast<float2 *>(cs), pairs, zero);
     return cudaGetLastError();
 }
 

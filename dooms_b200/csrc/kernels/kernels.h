@@ -76,7 +76,8 @@ cudaError_t launch_attention_combine(const float * part, float * out, void * xq,
 // the key itself and writes key and value into the cache at st->pos (no launch_rope_store before it); without, q is used as it is, the cache is only read
 // and n_keys_fixed gives the number of positions. Leaves part[n_head][splits][2 + head_dim] for launch_attention_combine.
 // cs[i] = (cos, sin)(st->pos * inv_freq[i]) as float2 for the head_dim / 2 rotary pairs: one decode step's rotation, shared by its layers.
-cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream);
+// zero (optional): a device word the kernel clears (the barrier counter of the fused decode step that follows it).
+cudaError_t launch_rope_table(const DevState * st, const double * inv_freq, void * cs, int head_dim, cudaStream_t stream, unsigned * zero = nullptr);
 bool attention_gqa_supported(const AttnShape & s);
 int attention_gqa_splits(int n_head_kv, int n_ctx);
 // With counters (n_head_kv zeroed ints, left zeroed) the last block of each key/value head merges the ranges itself into out (and xq): no combine launch.
@@ -145,6 +146,39 @@ cudaError_t launch_gemv_q4_0(const void * W, const void * W2, const void * xq, c
                              int64_t rows, int64_t cols, uint32_t flags, bool q4_k, cudaStream_t stream, void * xq_out = nullptr, int * out_counters = nullptr,
                              int32_t * error = nullptr,    // error: optional mapped host word, set to 4 if a bounded wait for a tensor copy ran out
                              const GemvNormLink * link = nullptr);
+
+// ---- the fused decode step (gemv_q4_0.cu): all layers of a one-sequence decode step in one cooperative launch ----
+// Takes models whose layer matrices are all q4_0 / q4_K rows that the tensor-copy variant of the GEMV above streams (rows of whole 256-element groups,
+// one q/k/v matrix per layer) and whose attention the grouped-query kernel handles; anything else is refused with cudaErrorNotSupported and runs kernel
+// by kernel. The step around it stays as it is: embedding and rotary table before (the rotary table kernel also zeroes the barrier word), output
+// projection and argmax after.
+struct FusedMatrix { const void * w; int64_t rows, cols; bool q4_k; };
+struct FusedLayer {
+    FusedMatrix qkv, attn_output, ffn_gate, ffn_up, ffn_down;
+    const float * attn_norm, * ffn_norm, * qkv_bias;      // qkv_bias: nullptr = none
+    const float * next_norm;                               // gains of the norm after this layer: the next layer's attn_norm, or the output norm
+    void * kc, * vc;                                       // this layer's key / value cache
+};
+struct FusedBuffers {
+    float * x, * qkv, * attn, * h;
+    void * xq, * xq2;                                      // split rows: attention / feed-forward output, and the residual row times the next norm's gains
+    float * norm_ss;
+    int * norm_counters, * split_counters, * attn_counters;
+    float * part;                                          // max_splits x n_head x (2 + head_dim) floats
+    const DevState * state;
+    const double * inv_freq;
+    const void * rope_cs;
+    int32_t * error;
+    float eps;
+    AttnShape shape;
+    int max_splits;
+};
+struct DecodeLayersPlan;
+cudaError_t decode_layers_create(const FusedLayer * layers, int n_layers, const FusedBuffers & buffers, DecodeLayersPlan ** out);
+void decode_layers_destroy(DecodeLayersPlan * plan);
+int decode_layers_blocks(const DecodeLayersPlan * plan);            // blocks of the launch = entries of norm_ss its last projection leaves
+unsigned * decode_layers_barrier(const DecodeLayersPlan * plan);    // the word the kernel before the launch has to zero
+cudaError_t launch_decode_layers(const DecodeLayersPlan * plan, cudaStream_t stream);
 
 // ---- the decode step's all-reduce + residual add over peer memory (allreduce_peer.cu) ----
 constexpr int kPeerMaxRanks = 8, kPeerMaxBlocks = 64;

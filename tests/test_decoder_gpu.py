@@ -258,3 +258,29 @@ def test_bf16_operands_are_refused(model_dir):
         CudaLlamaDecoder.load(path, 64, 32, operand_bf16=True)
     assert e.value.code == L.UNSUPPORTED
 
+
+
+def test_fused_decode_step_gives_the_same_tokens(model_dir):
+    """All layers of a decode step as one cooperative launch (opt-in, DOOMS_FUSED_STEP=1) against the chain of kernels: same greedy tokens, logits within the
+    one-token tolerance of each other and of the checker. The model is wide enough for the tensor-copy GEMV the fused step is built from (rows of whole
+    256-element groups, 16 warps x 2 stages: 4096 columns)."""
+    import os
+    import subprocess
+    import sys
+    spec = synth.ModelSpec("wide", "llama", 2, 4096, 32, 8, 8192, 512, 5e5, 1e-5, 4096, False, False, synth.pure(L.Q4_0))
+    path = write(model_dir, "fused_wide_q4_0", spec, 9)
+    prog = ("import sys, json, numpy as np; sys.path.insert(0, %r); from dooms_b200 import CudaLlamaDecoder;"
+            "d = CudaLlamaDecoder.load(%r, 256, 64); d.eval_tokens([5, 9, 300, 2, 77, 140]); toks = [];"
+            "d.generate(12, 3, lambda t: toks.append(t) or True); d.eval_tokens([toks[-1]]);"
+            "print(json.dumps({'tokens': toks, 'logits': d.logits()[:64].tolist(), 'launches': d.timings()['last_generate_launches']}))") % (str(model_dir.parent), path)
+    import json
+    root = str(__import__("pathlib").Path(__file__).resolve().parent.parent)
+    prog = prog.replace(repr(str(model_dir.parent)), repr(root))
+    runs = {}
+    for mode in ("0", "1"):
+        out = subprocess.run([sys.executable, "-c", prog], env={**os.environ, "DOOMS_FUSED_STEP": mode}, capture_output=True, text=True, check=True).stdout
+        runs[mode] = json.loads(out.strip().splitlines()[-1])
+    assert runs["1"]["launches"] < runs["0"]["launches"] / 2          # the fused step really ran
+    assert runs["0"]["tokens"] == runs["1"]["tokens"]
+    a, b = np.array(runs["0"]["logits"]), np.array(runs["1"]["logits"])
+    assert np.abs(a - b).max() < 1e-3
