@@ -66,6 +66,23 @@ class Timings(C.Structure):
                 ("last_batch_launches", C.c_int64)]
 
 
+class LlmOptions(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("n_ctx", C.c_int32), ("n_batch", C.c_int32), ("queue_depth", C.c_int32), ("device", C.c_int32)]
+
+
+class Sampling(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repeat_penalty", C.c_float), ("seed", C.c_uint32)]
+
+
+class GenerationInfo(C.Structure):
+    _fields_ = [("struct_size", C.c_size_t), ("prompt_tokens", C.c_int32), ("completion_tokens", C.c_int32), ("finish_reason", C.c_int32),
+                ("prefill_ms", C.c_double), ("first_token_ms", C.c_double), ("decode_ms", C.c_double)]
+
+
+TEXT_CALLBACK = C.CFUNCTYPE(C.c_int32, C.c_char_p, C.c_void_p)
+FINISH_NONE, FINISH_STOP, FINISH_LENGTH, FINISH_CANCELLED = 0, 1, 2, 3
+
+
 class GgufTensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_int64 * 4), ("offset", C.c_uint64),
                 ("nbytes", C.c_uint64), ("data", C.c_void_p)]
@@ -112,6 +129,24 @@ SIGNATURES = {
     "dooms_cuda_llama_generate": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, TOKEN_CALLBACK, C.c_void_p]),
     "dooms_cuda_llama_profile_pass": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(KernelTime), C.c_int32, C.POINTER(C.c_int32)]),
     "dooms_cuda_llama_timings": (C.c_int32, [C.c_void_p, C.POINTER(Timings)]),
+    "dooms_cuda_llm_open": (C.c_int32, [C.c_char_p, C.POINTER(LlmOptions), C.POINTER(C.c_void_p)]),
+    "dooms_cuda_llm_close": (None, [C.c_void_p]),
+    "dooms_cuda_llm_context_size": (C.c_int32, [C.c_void_p]),
+    "dooms_cuda_llm_generate": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "dooms_cuda_llm_generate_stream": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, TEXT_CALLBACK, C.c_void_p]),
+    "dooms_cuda_llm_generate_tokens": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, C.c_void_p, C.c_size_t,
+                                                   C.POINTER(C.c_size_t), C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_llm_last_generation": (C.c_int32, [C.c_void_p, C.POINTER(GenerationInfo)]),
+    "dooms_cuda_llm_count_tokens": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_vocab_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "dooms_cuda_vocab_close": (None, [C.c_void_p]),
+    "dooms_cuda_vocab_size": (C.c_int32, [C.c_void_p]),
+    "dooms_cuda_vocab_is_end_of_generation": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dooms_cuda_vocab_piece": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_vocab_tokenize": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_text_stream": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_char_p), C.c_int32, TEXT_CALLBACK, C.c_void_p, C.c_void_p, C.c_size_t,
+                                           C.POINTER(C.c_size_t), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "dooms_cuda_sample": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(Sampling), C.c_int32, C.c_void_p]),
     "dooms_cuda_llama_max_sequences": (C.c_int32, [C.c_void_p]),
     "dooms_cuda_llama_max_batch_rows": (C.c_int32, [C.c_void_p]),
     "dooms_cuda_llama_select_sequence": (C.c_int32, [C.c_void_p, C.c_int32]),

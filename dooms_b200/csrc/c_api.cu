@@ -12,6 +12,7 @@
 
 #include "cuda_llama_decoder.h"
 #include "gguf.h"
+#include "llm_pipeline.h"
 #include "kernels/kernels.h"
 #include "nccl_dyn.h"
 
@@ -19,6 +20,11 @@ using namespace dooms;
 
 struct dooms_cuda_llama { std::unique_ptr<CudaLlamaDecoder> dec; };
 struct dooms_gguf { std::unique_ptr<GgufFile> file; };
+struct dooms_cuda_vocab { Vocab vocab; };
+struct dooms_cuda_llm {
+    std::unique_ptr<Llm> llm;
+    dooms_cuda_generation_info last{};
+};
 
 namespace {
 
@@ -364,6 +370,181 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_select_sequence(dooms_cuda_llama * d, in
 DOOMS_CUDA_API int32_t dooms_cuda_llama_decode_batch(dooms_cuda_llama * d, const int32_t * slots, int32_t n, int32_t steps, int32_t * out_tokens) {
     if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
     return done(d->dec->decode_batch(slots, n, steps, out_tokens));
+}
+
+// ---------------------------------------------------------------- the Llm surface
+
+namespace {
+
+SamplerOptions sampler_of(const dooms_cuda_sampling * s) {
+    SamplerOptions o;      // greedy
+    if (s) { o.temperature = s->temperature; o.top_k = s->top_k; o.top_p = s->top_p; o.repeat_penalty = s->repeat_penalty; o.seed = s->seed; }
+    return o;
+}
+bool stops_of(const char * const * stop, int32_t n_stop, std::vector<std::string> * out, int32_t * code) {
+    if (n_stop < 0 || (n_stop > 0 && !stop)) { *code = fail(DOOMS_INVALID_ARGUMENT, "stop strings: a count without an array"); return false; }
+    for (int32_t i = 0; i < n_stop; i++) {
+        if (!stop[i]) { *code = fail(DOOMS_INVALID_ARGUMENT, "stop strings: a NULL entry"); return false; }
+        out->push_back(stop[i]);
+    }
+    return true;
+}
+int32_t text_out(const std::string & text, char * out, size_t capacity, size_t * needed) {
+    if (needed) *needed = text.size() + 1;
+    if (!out || capacity < text.size() + 1) return fail(DOOMS_RESOURCE_EXHAUSTED, "the text needs " + std::to_string(text.size() + 1) + " bytes");
+    std::memcpy(out, text.c_str(), text.size() + 1);
+    return DOOMS_OK;
+}
+int32_t finish_reason_of(const LlmGeneration & g) { return g.cancelled ? DOOMS_CUDA_FINISH_CANCELLED : g.stopped ? DOOMS_CUDA_FINISH_STOP : DOOMS_CUDA_FINISH_LENGTH; }
+
+// One generation on a handle: the shared body of the three generate entry points.
+int32_t run_generation(dooms_cuda_llm * h, const std::vector<int32_t> * prompt_tokens, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
+                       const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback, void * user, LlmGeneration * result) {
+    if (!h) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
+    h->last = dooms_cuda_generation_info{};
+    int32_t code = DOOMS_OK;
+    LlmGenerateOptions o;
+    o.max_new_tokens = max_new_tokens;
+    o.sampler = sampler_of(sampling);
+    if (!stops_of(stop, n_stop, &o.stop, &code)) return code;
+    std::function<bool(const std::string &)> on_text;
+    if (callback) on_text = [&](const std::string & piece) { return callback(piece.c_str(), user) == 0; };
+    LlmTimings tm;
+    Result<LlmGeneration> g = prompt_tokens ? h->llm->generate_tokens(*prompt_tokens, o, on_text, &tm)
+                                            : (prompt && *prompt) ? h->llm->generate(prompt, o, on_text, &tm) : Result<LlmGeneration>(invalid_argument("generate: empty prompt"));
+    if (!g.is_ok()) return done(g.status());
+    h->last.struct_size = sizeof(h->last);
+    h->last.prompt_tokens = int32_t(tm.prompt_tokens);
+    h->last.completion_tokens = int32_t(g.value().tokens.size());
+    h->last.finish_reason = finish_reason_of(g.value());
+    h->last.prefill_ms = tm.prefill_ms; h->last.first_token_ms = tm.first_token_ms; h->last.decode_ms = tm.decode_ms;
+    *result = std::move(g).value();
+    return DOOMS_OK;
+}
+
+}  // namespace
+
+DOOMS_CUDA_API int32_t dooms_cuda_llm_open(const char * gguf_path, const dooms_cuda_llm_options * options, dooms_cuda_llm ** out) {
+    if (!gguf_path || !out) return fail(DOOMS_INVALID_ARGUMENT, "gguf_path or out is NULL");
+    *out = nullptr;
+    int32_t code = DOOMS_OK;
+    if (options && !struct_ok(options, "options", &code)) return code;
+    LlmOptions o;
+    if (options) {
+        if (options->n_ctx > 0) o.n_ctx = options->n_ctx;
+        if (options->n_batch > 0) o.n_batch = options->n_batch;
+        if (options->queue_depth > 0) o.queue_depth = options->queue_depth;
+        o.cuda.device = options->device;
+    }
+    auto llm = Llm::load(gguf_path, o);
+    if (!llm.is_ok()) return done(llm.status());
+    *out = new dooms_cuda_llm{std::move(llm).value(), {}};
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API void dooms_cuda_llm_close(dooms_cuda_llm * llm) { delete llm; }
+DOOMS_CUDA_API int32_t dooms_cuda_llm_context_size(const dooms_cuda_llm * llm) { return llm ? llm->llm->context_size() : 0; }
+
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate(dooms_cuda_llm * llm, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
+                                               const char * const * stop, int32_t n_stop, char * out, size_t capacity, size_t * needed) {
+    LlmGeneration g;
+    const int32_t code = run_generation(llm, nullptr, prompt, max_new_tokens, sampling, stop, n_stop, nullptr, nullptr, &g);
+    return code != DOOMS_OK ? code : text_out(g.text, out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_stream(dooms_cuda_llm * llm, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
+                                                      const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback, void * user) {
+    if (!callback) return fail(DOOMS_INVALID_ARGUMENT, "callback is NULL");
+    LlmGeneration g;
+    return run_generation(llm, nullptr, prompt, max_new_tokens, sampling, stop, n_stop, callback, user, &g);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_tokens(dooms_cuda_llm * llm, const int32_t * prompt, int32_t n_prompt, int32_t max_new_tokens,
+                                                      const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, char * out, size_t capacity,
+                                                      size_t * needed, int32_t * out_tokens, int32_t token_capacity, int32_t * n_tokens) {
+    if (!prompt || n_prompt < 1) return fail(DOOMS_INVALID_ARGUMENT, "generate: empty prompt");
+    const std::vector<int32_t> p(prompt, prompt + n_prompt);
+    LlmGeneration g;
+    const int32_t code = run_generation(llm, &p, nullptr, max_new_tokens, sampling, stop, n_stop, nullptr, nullptr, &g);
+    if (code != DOOMS_OK) return code;
+    if (n_tokens) *n_tokens = int32_t(g.tokens.size());
+    if (out_tokens) {
+        if (token_capacity < int32_t(g.tokens.size())) return fail(DOOMS_RESOURCE_EXHAUSTED, "the tokens need room for " + std::to_string(g.tokens.size()) + " ids");
+        std::copy(g.tokens.begin(), g.tokens.end(), out_tokens);
+    }
+    return text_out(g.text, out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm, dooms_cuda_generation_info * out) {
+    int32_t code = DOOMS_OK;
+    if (!llm) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
+    if (!struct_ok(out, "out", &code)) return code;
+    const size_t size = out->struct_size;
+    std::memcpy(out, &llm->last, std::min(size, sizeof(llm->last)));
+    out->struct_size = size;
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_count_tokens(dooms_cuda_llm * llm, const char * text, int32_t add_special, int32_t * count) {
+    if (!llm || !count) return fail(DOOMS_INVALID_ARGUMENT, "llm or count is NULL");
+    if (!text || !*text) return fail(DOOMS_INVALID_ARGUMENT, "count_tokens: empty text");
+    auto t = llm->llm->tokenize(text, add_special != 0);
+    if (!t.is_ok()) return done(t.status());
+    *count = int32_t(t.value().size());
+    return DOOMS_OK;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_open(const char * gguf_path, dooms_cuda_vocab ** out) {
+    if (!gguf_path || !out) return fail(DOOMS_INVALID_ARGUMENT, "gguf_path or out is NULL");
+    *out = nullptr;
+    auto file = GgufFile::open(gguf_path);
+    if (!file.is_ok()) return done(file.status());
+    auto v = Vocab::from_gguf(file.value());
+    if (!v.is_ok()) return done(v.status());
+    *out = new dooms_cuda_vocab{std::move(v).value()};
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API void dooms_cuda_vocab_close(dooms_cuda_vocab * vocab) { delete vocab; }
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_size(const dooms_cuda_vocab * vocab) { return vocab ? vocab->vocab.size() : 0; }
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_is_end_of_generation(const dooms_cuda_vocab * vocab, int32_t token) { return vocab && vocab->vocab.is_end_of_generation(token) ? 1 : 0; }
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_piece(const dooms_cuda_vocab * vocab, int32_t token, char * out, int32_t capacity, int32_t * n) {
+    if (!vocab || !n) return fail(DOOMS_INVALID_ARGUMENT, "vocab or n is NULL");
+    if (token < 0 || token >= vocab->vocab.size()) return fail(DOOMS_INVALID_ARGUMENT, "token " + std::to_string(token) + " is outside the vocabulary");
+    const std::string & p = vocab->vocab.piece(token);
+    *n = int32_t(p.size());
+    if (capacity < *n || (!out && *n > 0)) return fail(DOOMS_RESOURCE_EXHAUSTED, "the piece needs " + std::to_string(*n) + " bytes");
+    if (*n > 0) std::memcpy(out, p.data(), p.size());
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t * out, int32_t capacity, int32_t * n) {
+    if (!vocab || !n) return fail(DOOMS_INVALID_ARGUMENT, "vocab or n is NULL");
+    auto t = vocab->vocab.tokenize(text ? text : "", add_special != 0);
+    if (!t.is_ok()) return done(t.status());
+    *n = int32_t(t.value().size());
+    if (!out || capacity < *n) return fail(DOOMS_RESOURCE_EXHAUSTED, "the ids need room for " + std::to_string(*n));
+    std::copy(t.value().begin(), t.value().end(), out);
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_text_stream(const dooms_cuda_vocab * vocab, const int32_t * tokens, int32_t n_tokens, const char * const * stop, int32_t n_stop,
+                                              dooms_cuda_text_callback callback, void * user, char * out, size_t capacity, size_t * needed, int32_t * consumed,
+                                              int32_t * finish_reason) {
+    if (!vocab || (n_tokens > 0 && !tokens) || n_tokens < 0) return fail(DOOMS_INVALID_ARGUMENT, "vocab or tokens is NULL");
+    int32_t code = DOOMS_OK;
+    std::vector<std::string> stops;
+    if (!stops_of(stop, n_stop, &stops, &code)) return code;
+    for (const std::string & s : stops) if (s.empty()) return fail(DOOMS_INVALID_ARGUMENT, "an empty stop string");
+    LlmGeneration g;
+    std::function<bool(const std::string &)> on_text;
+    if (callback) on_text = [&](const std::string & piece) { return callback(piece.c_str(), user) == 0; };
+    TextStream stream(vocab->vocab, stops, on_text, &g);
+    int32_t taken = 0;
+    while (taken < n_tokens) { taken++; if (!stream.push(tokens[taken - 1])) break; }
+    stream.finish();
+    if (consumed) *consumed = taken;
+    if (finish_reason) *finish_reason = finish_reason_of(g);
+    return text_out(g.text, out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_sample(const float * logits, int32_t n, const dooms_cuda_sampling * sampling, int32_t draws, int32_t * out_tokens) {
+    if (!logits || n < 1 || draws < 1 || !out_tokens) return fail(DOOMS_INVALID_ARGUMENT, "sample: logits, n, draws and out_tokens are required");
+    auto s = Sampler::create(sampler_of(sampling));
+    if (!s.is_ok()) return done(s.status());
+    for (int32_t i = 0; i < draws; i++) out_tokens[i] = s.value().sample(logits, n);
+    return DOOMS_OK;
 }
 
 // ---------------------------------------------------------------- single kernels

@@ -1,0 +1,346 @@
+#include "llm_pipeline.h"
+
+#include <algorithm>
+#include <cctype>
+#include <chrono>
+#include <climits>
+#include <cmath>
+#include <numeric>
+
+namespace dooms {
+
+namespace {
+
+// UTF-8 encoding of a code point.
+void put_utf8(std::string & s, uint32_t cp) {
+    if (cp < 0x80) s += char(cp);
+    else if (cp < 0x800) { s += char(0xC0 | (cp >> 6)); s += char(0x80 | (cp & 0x3F)); }
+    else if (cp < 0x10000) { s += char(0xE0 | (cp >> 12)); s += char(0x80 | ((cp >> 6) & 0x3F)); s += char(0x80 | (cp & 0x3F)); }
+    else { s += char(0xF0 | (cp >> 18)); s += char(0x80 | ((cp >> 12) & 0x3F)); s += char(0x80 | ((cp >> 6) & 0x3F)); s += char(0x80 | (cp & 0x3F)); }
+}
+// Code points of a UTF-8 string (malformed bytes pass through as themselves).
+std::vector<uint32_t> code_points(const std::string & s) {
+    std::vector<uint32_t> out;
+    for (size_t i = 0; i < s.size();) {
+        const unsigned char c = static_cast<unsigned char>(s[i]);
+        const int n = c >= 0xF0 ? 4 : c >= 0xE0 ? 3 : c >= 0xC0 ? 2 : 1;
+        if (n == 1 || i + size_t(n) > s.size()) { out.push_back(c); i++; continue; }
+        uint32_t cp = c & (0xFF >> (n + 1));
+        for (int k = 1; k < n; k++) cp = (cp << 6) | (static_cast<unsigned char>(s[i + size_t(k)]) & 0x3F);
+        out.push_back(cp);
+        i += size_t(n);
+    }
+    return out;
+}
+
+// The byte alphabet of byte-level BPE vocabularies (GPT-2's): printable bytes stand for themselves, the other 68 bytes for the code points from U+0100 on.
+struct ByteAlphabet {
+    uint32_t to_cp[256];
+    std::unordered_map<uint32_t, uint8_t> to_byte;
+    ByteAlphabet() {
+        uint32_t next = 256;
+        for (int b = 0; b < 256; b++) {
+            const bool printable = (b >= 0x21 && b <= 0x7E) || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
+            to_cp[b] = printable ? uint32_t(b) : next++;
+            to_byte[to_cp[b]] = uint8_t(b);
+        }
+    }
+};
+const ByteAlphabet & alphabet() { static const ByteAlphabet a; return a; }
+
+int32_t int_key(const GgufFile & f, const char * key, int32_t fallback) {
+    auto v = f.get_uint(key);
+    return v.is_ok() ? int32_t(v.value()) : fallback;
+}
+
+// How much of s (from the front) is whole characters: a multi-byte character cut off at the end stays behind.
+size_t whole_characters(const std::string & s) {
+    for (size_t back = 1; back <= 3 && back <= s.size(); back++) {
+        const unsigned char c = static_cast<unsigned char>(s[s.size() - back]);
+        if ((c & 0xC0) == 0x80) continue;      // a continuation byte: its lead byte is further back
+        const size_t length = c >= 0xF0 ? 4 : c >= 0xE0 ? 3 : c >= 0xC0 ? 2 : 1;
+        return length > back ? s.size() - back : s.size();
+    }
+    return s.size();
+}
+
+using Clock = std::chrono::steady_clock;
+double ms_since(Clock::time_point t) { return std::chrono::duration<double, std::milli>(Clock::now() - t).count(); }
+
+}  // namespace
+
+// ---------------------------------------------------------------- vocabulary
+
+Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
+    const auto & md = file.metadata();
+    const auto tokens = md.find("tokenizer.ggml.tokens");
+    if (tokens == md.end() || tokens->second.type != GgufValueType::Array || tokens->second.element_type != GgufValueType::String) {
+        return invalid_argument("the model file has no tokenizer.ggml.tokens (an array of strings)");
+    }
+    auto model = file.get_string("tokenizer.ggml.model");
+    const std::string kind = model.is_ok() ? model.value() : "llama";
+    if (kind != "gpt2" && kind != "llama") return unsupported("tokenizer model '" + kind + "': byte-level BPE (gpt2) and sentencepiece pieces (llama) are read");
+    Vocab v;
+    v.byte_level_ = kind == "gpt2";
+    const size_t n = tokens->second.items.size();
+    v.raw_.reserve(n);
+    for (const GgufValue & t : tokens->second.items) v.raw_.push_back(t.s);
+    v.special_.assign(n, false);
+    if (const auto types = md.find("tokenizer.ggml.token_type"); types != md.end() && types->second.items.size() == n) {
+        // 3 = control, 4 = user defined: no text of their own in the answer (6 = byte: handled as a piece)
+        for (size_t i = 0; i < n; i++) { const int64_t t = types->second.items[i].i; v.special_[i] = t == 3; }
+    }
+    v.pieces_.resize(n);
+    for (size_t i = 0; i < n; i++) {
+        const std::string & raw = v.raw_[i];
+        v.ids_.emplace(raw, int32_t(i));
+        if (v.special_[i]) continue;
+        std::string & out = v.pieces_[i];
+        if (v.byte_level_) {
+            for (uint32_t cp : code_points(raw)) {
+                const auto b = alphabet().to_byte.find(cp);
+                if (b != alphabet().to_byte.end()) out += char(b->second);
+                else put_utf8(out, cp);
+            }
+        } else if (raw.size() == 6 && raw.compare(0, 3, "<0x") == 0 && raw[5] == '>') {
+            out = std::string(1, char(std::stoi(raw.substr(3, 2), nullptr, 16)));
+        } else {
+            for (uint32_t cp : code_points(raw)) { if (cp == 0x2581) out += ' '; else put_utf8(out, cp); }
+        }
+    }
+    if (const auto merges = md.find("tokenizer.ggml.merges"); merges != md.end()) {
+        int32_t rank = 0;
+        for (const GgufValue & m : merges->second.items) v.merge_rank_.emplace(m.s, rank++);
+    }
+    v.bos_ = int_key(file, "tokenizer.ggml.bos_token_id", -1);
+    for (const char * key : {"tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id", "tokenizer.ggml.eom_token_id"}) {
+        const int32_t id = int_key(file, key, -1);
+        if (id >= 0 && std::find(v.eog_.begin(), v.eog_.end(), id) == v.eog_.end()) v.eog_.push_back(id);
+    }
+    auto add_bos = file.get_bool("tokenizer.ggml.add_bos_token");
+    v.add_bos_ = add_bos.is_ok() ? add_bos.value() : !v.byte_level_;      // sentencepiece models ask for it unless they say otherwise
+    return v;
+}
+
+const std::string & Vocab::piece(int32_t id) const {
+    static const std::string none;
+    return id >= 0 && id < size() ? pieces_[size_t(id)] : none;
+}
+
+bool Vocab::is_end_of_generation(int32_t id) const { return std::find(eog_.begin(), eog_.end(), id) != eog_.end(); }
+
+Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_special) const {
+    if (text.empty()) return invalid_argument("tokenize: empty text");
+    if (!byte_level_) return unsupported("tokenize: this file's vocabulary is a sentencepiece model; pass token ids");
+    std::vector<int32_t> out;
+    if (add_special && add_bos_ && bos_ >= 0) out.push_back(bos_);
+    // words: a run of one class of bytes (letters, digits, other), with the single space before it
+    auto cls = [](unsigned char c) { return c == ' ' ? 0 : (std::isalpha(c) || c >= 0x80) ? 1 : std::isdigit(c) ? 2 : 3; };
+    size_t at = 0;
+    while (at < text.size()) {
+        size_t end = at;
+        if (text[end] == ' ' && end + 1 < text.size() && text[end + 1] != ' ') end++;
+        const int k = cls(static_cast<unsigned char>(text[end]));
+        do end++; while (end < text.size() && cls(static_cast<unsigned char>(text[end])) == k && k != 0);
+        // the word's bytes in the byte alphabet, then merges by rank
+        std::vector<std::string> sym;
+        for (size_t i = at; i < end; i++) { std::string s; put_utf8(s, alphabet().to_cp[static_cast<unsigned char>(text[i])]); sym.push_back(std::move(s)); }
+        while (sym.size() > 1) {
+            int32_t best = INT32_MAX;
+            size_t where = 0;
+            for (size_t i = 0; i + 1 < sym.size(); i++) {
+                const auto r = merge_rank_.find(sym[i] + " " + sym[i + 1]);
+                if (r != merge_rank_.end() && r->second < best) { best = r->second; where = i; }
+            }
+            if (best == INT32_MAX) break;
+            sym[where] += sym[where + 1];
+            sym.erase(sym.begin() + long(where) + 1);
+        }
+        for (const std::string & s : sym) {
+            const auto id = ids_.find(s);
+            if (id != ids_.end()) { out.push_back(id->second); continue; }
+            for (uint32_t cp : code_points(s)) {      // a symbol the vocabulary lacks: its bytes one by one
+                std::string one;
+                put_utf8(one, cp);
+                const auto b = ids_.find(one);
+                if (b == ids_.end()) return invalid_argument("tokenize: the vocabulary has no token for a byte of the text");
+                out.push_back(b->second);
+            }
+        }
+        at = end;
+    }
+    return out;
+}
+
+// ---------------------------------------------------------------- sampler
+
+Result<Sampler> Sampler::create(const SamplerOptions & o) {
+    if (!(o.temperature >= 0.f) || !(o.top_p > 0.f && o.top_p <= 1.f) || o.top_k < 0 || !(o.repeat_penalty > 0.f)) {
+        return invalid_argument("sampler: temperature >= 0, top_p in (0, 1], top_k >= 0 and repeat_penalty > 0 are required");
+    }
+    Sampler s;
+    s.o_ = o;
+    s.state_ = 0x9E3779B97F4A7C15ull ^ (uint64_t(o.seed) * 0xD1342543DE82EF95ull);
+    return s;
+}
+
+double Sampler::uniform() {      // splitmix64
+    uint64_t z = (state_ += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return double(z >> 11) * (1.0 / 9007199254740992.0);
+}
+
+void Sampler::accept(int32_t token) {
+    recent_.push_back(token);
+    if (recent_.size() > 64) recent_.erase(recent_.begin());
+}
+
+int32_t Sampler::sample(const float * logits, int32_t n) {
+    std::vector<std::pair<float, int32_t>> cand;
+    cand.reserve(size_t(n));
+    for (int32_t i = 0; i < n; i++) if (logits[i] == logits[i]) cand.emplace_back(logits[i], i);      // NaN never wins
+    if (cand.empty()) { accept(0); return 0; }
+    if (o_.repeat_penalty != 1.f) {
+        for (auto & c : cand) {
+            if (std::find(recent_.begin(), recent_.end(), c.second) != recent_.end()) c.first = c.first > 0 ? c.first / o_.repeat_penalty : c.first * o_.repeat_penalty;
+        }
+    }
+    auto by_logit = [](const std::pair<float, int32_t> & a, const std::pair<float, int32_t> & b) { return a.first > b.first || (a.first == b.first && a.second < b.second); };
+    int32_t chosen;
+    if (o_.temperature == 0.f) {
+        chosen = std::min_element(cand.begin(), cand.end(), by_logit)->second;      // the largest logit, lowest index on ties
+    } else {
+        const size_t keep = o_.top_k > 0 ? std::min(size_t(o_.top_k), cand.size()) : cand.size();
+        std::partial_sort(cand.begin(), cand.begin() + long(keep), cand.end(), by_logit);
+        cand.resize(keep);
+        std::vector<double> p(keep);
+        const double top = cand[0].first;
+        double total = 0;
+        for (size_t i = 0; i < keep; i++) { p[i] = std::exp((double(cand[i].first) - top) / double(o_.temperature)); total += p[i]; }
+        size_t last = keep;
+        if (o_.top_p < 1.f) {      // the smallest prefix whose probability reaches top_p
+            double acc = 0;
+            for (size_t i = 0; i < keep; i++) { acc += p[i] / total; if (acc >= double(o_.top_p)) { last = i + 1; break; } }
+        }
+        double mass = 0;
+        for (size_t i = 0; i < last; i++) mass += p[i];
+        double u = uniform() * mass;
+        size_t pick = last - 1;
+        for (size_t i = 0; i < last; i++) { if (u < p[i]) { pick = i; break; } u -= p[i]; }
+        chosen = cand[pick].second;
+    }
+    accept(chosen);
+    return chosen;
+}
+
+// ---------------------------------------------------------------- text stream
+
+TextStream::TextStream(const Vocab & vocab, const std::vector<std::string> & stops, std::function<bool(const std::string &)> on_text, LlmGeneration * out)
+    : vocab_(vocab), stops_(stops), on_text_(std::move(on_text)), out_(*out) {}
+
+bool TextStream::release(size_t n) {
+    if (n == 0) return true;
+    const std::string piece = held_.substr(0, n);
+    held_.erase(0, n);
+    out_.text += piece;
+    return !on_text_ || on_text_(piece);
+}
+
+bool TextStream::push(int32_t token) {
+    out_.tokens.push_back(token);
+    if (vocab_.is_end_of_generation(token)) { out_.stopped = true; return false; }
+    held_ += vocab_.piece(token);
+    // a stop string inside what is held: the text ends right before the earliest one
+    size_t cut = std::string::npos;
+    for (const std::string & s : stops_) cut = std::min(cut, held_.find(s));
+    if (cut != std::string::npos) {
+        held_.resize(cut);
+        if (release(held_.size())) out_.stopped = true;
+        else out_.cancelled = true;
+        return false;
+    }
+    // hold back the longest tail that could still grow into a stop string, and a character that is not whole yet
+    size_t keep = 0;
+    for (const std::string & s : stops_) {
+        for (size_t k = std::min(s.size() - 1, held_.size()); k > keep; k--) {
+            if (held_.compare(held_.size() - k, k, s, 0, k) == 0) { keep = k; break; }
+        }
+    }
+    const size_t ready = std::min(held_.size() - keep, whole_characters(held_));
+    if (!release(ready)) { out_.cancelled = true; return false; }
+    return true;
+}
+
+void TextStream::finish() {
+    const bool ended_by_token = out_.stopped && !out_.tokens.empty() && vocab_.is_end_of_generation(out_.tokens.back());
+    if ((!out_.stopped && !out_.cancelled) || ended_by_token) (void)release(held_.size());      // nothing follows that could complete a stop string
+}
+
+// ---------------------------------------------------------------- Llm
+
+Result<std::unique_ptr<Llm>> Llm::load(const std::string & path, const LlmOptions & o) {
+    NativeLlamaOptions n;
+    n.n_ctx = o.n_ctx;
+    n.n_batch = o.n_batch;
+    auto dec = load_native_llama(path, n, o.cuda);
+    if (!dec.is_ok()) return dec.status();
+    auto file = GgufFile::open(path);
+    if (!file.is_ok()) return file.status();
+    auto vocab = Vocab::from_gguf(file.value());
+    if (!vocab.is_ok()) return vocab.status();
+    if (vocab.value().size() != dec.value()->config().n_vocab) return invalid_argument("the vocabulary's size differs from the embedding table's rows");
+    return std::unique_ptr<Llm>(new Llm(std::move(dec).value(), std::move(vocab).value(), std::max(1, o.queue_depth)));
+}
+
+Result<LlmGeneration> Llm::generate(const std::string & prompt, const LlmGenerateOptions & o, const std::function<bool(const std::string &)> & on_text, LlmTimings * timings) {
+    auto tokens = tokenize(prompt, true);
+    if (!tokens.is_ok()) return tokens.status();
+    return generate_tokens(tokens.value(), o, on_text, timings);
+}
+
+Result<LlmGeneration> Llm::generate_tokens(const std::vector<int32_t> & prompt, const LlmGenerateOptions & o, const std::function<bool(const std::string &)> & on_text,
+                                           LlmTimings * timings) {
+    const int32_t n_ctx = context_size();
+    if (prompt.empty()) return invalid_argument("generate: empty prompt");
+    if (o.max_new_tokens < 1 || o.max_new_tokens >= n_ctx) return invalid_argument("generate: max_new_tokens has to lie in [1, context size)");
+    if (std::any_of(o.stop.begin(), o.stop.end(), [](const std::string & s) { return s.empty(); })) return invalid_argument("generate: an empty stop string");
+    if (int64_t(prompt.size()) + o.max_new_tokens > n_ctx) {
+        return resource_exhausted("generate: " + std::to_string(prompt.size()) + " prompt tokens and " + std::to_string(o.max_new_tokens) + " new ones do not fit the context of " +
+                                  std::to_string(n_ctx));
+    }
+    auto sampler = Sampler::create(o.sampler);
+    if (!sampler.is_ok()) return sampler.status();
+    const auto t0 = Clock::now();
+    LlmTimings tm;
+    tm.prompt_tokens = int64_t(prompt.size());
+    decoder_->reset();
+    DOOMS_RETURN_IF_ERROR(decoder_->eval_tokens(prompt));
+    LlmGeneration out;
+    TextStream stream(vocab_, o.stop, on_text, &out);
+    auto t_decode = t0;
+    auto count = [&] {
+        // the first token exists once the prompt has gone through the model: its arrival marks the end of the prefill
+        if (tm.generated_tokens++ == 0) { tm.prefill_ms = tm.first_token_ms = ms_since(t0); t_decode = Clock::now(); }
+    };
+    if (sampler.value().greedy()) {
+        // the token is picked on the device and the next step reads it there: steps stay queued ahead of the host
+        DOOMS_RETURN_IF_ERROR(decoder_->generate(o.max_new_tokens, depth_, [&](int32_t token) { count(); return stream.push(token); }));
+    } else {
+        for (int32_t i = 0; i < o.max_new_tokens; i++) {
+            auto logits = decoder_->logits();
+            if (!logits.is_ok()) return logits.status();
+            const int32_t token = sampler.value().sample(logits.value().data(), int32_t(logits.value().size()));
+            count();
+            if (!stream.push(token)) break;
+            if (i + 1 < o.max_new_tokens) DOOMS_RETURN_IF_ERROR(decoder_->eval_tokens(&token, 1));
+        }
+    }
+    stream.finish();
+    tm.decode_ms = tm.generated_tokens > 1 ? ms_since(t_decode) : 0.0;
+    if (timings) *timings = tm;
+    return out;
+}
+
+}  // namespace dooms

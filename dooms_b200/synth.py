@@ -136,6 +136,33 @@ def random_blocks(dtype: int, rows: int, cols: int, seed: int) -> np.ndarray:
     return b.reshape(rows, -1)
 
 
+def byte_level_vocab(n_vocab: int) -> dict:
+    """Tokenizer metadata of a small byte-level BPE vocabulary with n_vocab (>= 270) entries: the 256 byte tokens in the byte alphabet of such
+    vocabularies, a few merges of common English pairs, filler tokens, and an end-of-text token as the last id."""
+    printable = [b for b in range(256) if 0x21 <= b <= 0x7E or 0xA1 <= b <= 0xAC or 0xAE <= b <= 0xFF]
+    to_cp, nxt = {}, 256
+    for b in range(256):
+        if b in printable:
+            to_cp[b] = b
+        else:
+            to_cp[b] = nxt
+            nxt += 1
+    sym = lambda text: "".join(chr(to_cp[b]) for b in text.encode())
+    tokens = [chr(to_cp[b]) for b in range(256)]
+    merges = []
+    for left, right in (("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o"), (" ", "w"), ("o", "r"), (" w", "or"), (" wor", "l"), (" worl", "d"), ("t", "h"), (" ", "th"),
+                        ("S", "T"), ("O", "P")):
+        merges.append(f"{sym(left)} {sym(right)}")
+        tokens.append(sym(left) + sym(right))
+    assert n_vocab >= len(tokens) + 1
+    while len(tokens) < n_vocab - 1:
+        tokens.append(f"<filler_{len(tokens)}>")
+    tokens.append("<|endoftext|>")
+    types = [1] * (n_vocab - 1) + [3]
+    return {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": types,
+            "tokenizer.ggml.eos_token_id": n_vocab - 1, "tokenizer.ggml.bos_token_id": n_vocab - 1, "tokenizer.ggml.add_bos_token": False}
+
+
 def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
     if device == "cpu":
         g = np.random.Generator(np.random.PCG64(seed))
@@ -145,8 +172,8 @@ def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
     return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
 
 
-def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu") -> dict:
-    """Writes the model as a GGUF file; returns {"matrix_bytes": ...}."""
+def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu", vocab: bool = False) -> dict:
+    """Writes the model as a GGUF file; returns {"matrix_bytes": ...}. vocab: with the tokenizer metadata of byte_level_vocab(n_vocab)."""
     md = {
         "general.architecture": spec.arch,
         "general.name": spec.name,
@@ -159,6 +186,8 @@ def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu
         f"{spec.arch}.rope.freq_base": float(spec.rope_base),
         f"{spec.arch}.attention.layer_norm_rms_epsilon": float(spec.rms_eps),
     }
+    if vocab:
+        md.update(byte_level_vocab(spec.n_vocab))
     tensors = []
     counter = [0]
 

@@ -224,6 +224,69 @@ DOOMS_CUDA_API int64_t dooms_cuda_attention_scratch_bytes(int32_t n_head, int32_
 DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void * d_kc, const void * d_vc, float * d_out, void * d_scratch, int32_t n_head,
                                                    int32_t n_head_kv, int32_t head_dim, int32_t n_keys, void * stream);
 
+/* ---- A text language model on the decoder: the `Llm` surface of the reference (src/pipeline/llm_pipeline.h:16-82) and its C face dooms_llm_*
+ * (include/dooms/dooms_c.h:73-138, src/api/c_api.cpp:322-504) for the decoder's own engine. Vocabulary, byte-level BPE tokenizer and sampler are this
+ * library's (the reference takes them from llama.cpp); chat templates are not evaluated. ---- */
+typedef struct dooms_cuda_llm dooms_cuda_llm;
+typedef struct dooms_cuda_vocab dooms_cuda_vocab;
+typedef struct dooms_cuda_llm_options {     /* dooms_llm_options (dooms_c.h:75-81) */
+    size_t struct_size;
+    int32_t n_ctx;          /* positions of the KV cache (prompt + answer); 0: 4096 */
+    int32_t n_batch;        /* largest prefill chunk; 0: 512 */
+    int32_t queue_depth;    /* decode steps kept queued on the GPU in greedy generation; 0: 4 */
+    int32_t device;         /* CUDA device ordinal */
+} dooms_cuda_llm_options;
+typedef struct dooms_cuda_sampling {        /* dooms_llm_sampling (dooms_c.h:85-92); NULL wherever one is taken: greedy */
+    size_t struct_size;
+    float temperature;
+    int32_t top_k;
+    float top_p;
+    float repeat_penalty;
+    uint32_t seed;
+} dooms_cuda_sampling;
+typedef int32_t (*dooms_cuda_text_callback)(const char * piece, void * user);   /* returns 0 to continue, non-zero to stop (dooms_text_callback, dooms_c.h:69) */
+enum { DOOMS_CUDA_FINISH_NONE = 0, DOOMS_CUDA_FINISH_STOP = 1, DOOMS_CUDA_FINISH_LENGTH = 2, DOOMS_CUDA_FINISH_CANCELLED = 3 };   /* dooms_finish_reason, dooms_c.h:118-123 */
+typedef struct dooms_cuda_generation_info { /* dooms_llm_generation_info (dooms_c.h:125-130) plus LlmTimings (llm_pipeline.h:34-40) */
+    size_t struct_size;
+    int32_t prompt_tokens, completion_tokens, finish_reason;
+    double prefill_ms, first_token_ms, decode_ms;
+} dooms_cuda_generation_info;
+
+DOOMS_CUDA_API int32_t dooms_cuda_llm_open(const char * gguf_path, const dooms_cuda_llm_options * options, dooms_cuda_llm ** out);   /* dooms_llm_open */
+DOOMS_CUDA_API void dooms_cuda_llm_close(dooms_cuda_llm * llm);
+DOOMS_CUDA_API int32_t dooms_cuda_llm_context_size(const dooms_cuda_llm * llm);
+/* dooms_llm_generate (dooms_c.h:103-107): the answer as a NUL-terminated UTF-8 string; *needed (optional) its length including the NUL; a smaller
+ * capacity writes nothing and returns DOOMS_RESOURCE_EXHAUSTED. Every call starts a fresh conversation. */
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate(dooms_cuda_llm * llm, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
+                                               const char * const * stop, int32_t n_stop, char * out, size_t capacity, size_t * needed);
+/* dooms_llm_generate_stream (dooms_c.h:108-110). */
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_stream(dooms_cuda_llm * llm, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
+                                                      const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback, void * user);
+/* The same from token ids (files whose vocabulary this library does not tokenize, and tests). out_tokens (optional, token_capacity ids) receives the
+ * generated ids, *n_tokens their number. */
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_tokens(dooms_cuda_llm * llm, const int32_t * prompt, int32_t n_prompt, int32_t max_new_tokens,
+                                                      const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, char * out, size_t capacity,
+                                                      size_t * needed, int32_t * out_tokens, int32_t token_capacity, int32_t * n_tokens);
+DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm, dooms_cuda_generation_info * out);                 /* dooms_llm_last_generation */
+DOOMS_CUDA_API int32_t dooms_cuda_llm_count_tokens(dooms_cuda_llm * llm, const char * text, int32_t add_special, int32_t * count);   /* dooms_llm_count_tokens */
+
+/* The host-side pieces on their own (no GPU): the vocabulary of a GGUF file, the text assembly that turns a token stream into complete UTF-8 pieces with
+ * stop strings (TokenSink, src/pipeline/llm_pipeline.cpp:91-135), and the sampler. */
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_open(const char * gguf_path, dooms_cuda_vocab ** out);
+DOOMS_CUDA_API void dooms_cuda_vocab_close(dooms_cuda_vocab * vocab);
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_size(const dooms_cuda_vocab * vocab);
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_is_end_of_generation(const dooms_cuda_vocab * vocab, int32_t token);
+/* The bytes a token stands for (not NUL-terminated: a piece may hold any byte); *n their number; capacity too small: DOOMS_RESOURCE_EXHAUSTED. */
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_piece(const dooms_cuda_vocab * vocab, int32_t token, char * out, int32_t capacity, int32_t * n);
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t * out, int32_t capacity, int32_t * n);
+/* Runs the text assembly over `tokens`: pieces go to `callback` (optional); *consumed = tokens taken before generation ended, *finish_reason how it ended
+ * (DOOMS_CUDA_FINISH_LENGTH: the tokens ran out); the whole text as dooms_cuda_llm_generate returns it. */
+DOOMS_CUDA_API int32_t dooms_cuda_text_stream(const dooms_cuda_vocab * vocab, const int32_t * tokens, int32_t n_tokens, const char * const * stop, int32_t n_stop,
+                                              dooms_cuda_text_callback callback, void * user, char * out, size_t capacity, size_t * needed, int32_t * consumed,
+                                              int32_t * finish_reason);
+/* `draws` tokens drawn one after another from the same row of n logits (each draw joins the repetition-penalty history). */
+DOOMS_CUDA_API int32_t dooms_cuda_sample(const float * logits, int32_t n, const dooms_cuda_sampling * sampling, int32_t draws, int32_t * out_tokens);
+
 /* This rank's share of the model under tensor parallelism (no counterpart in the reference): rows [q_row0, q_row0 + q_rows) of attn_q and the same
  * columns of attn_output, rows [kv_row0, ..) of attn_k / attn_v (whole heads; the KV cache holds only these heads), rows [ff_row0, ..) of ffn_gate /
  * ffn_up and the same columns of ffn_down, rows [vocab_row0, ..) of the output matrix. The partial sums of attn_output and ffn_down are all-reduced.

@@ -1,0 +1,134 @@
+"""The text-model surface (reference: src/pipeline/llm_pipeline.{h,cpp}; C face include/dooms/dooms_c.h:73-138): vocabulary, text assembly with UTF-8
+hold-back and stop strings, sampler on the host (no GPU), and generation on the decoder (GPU)."""
+import numpy as np
+import pytest
+
+from dooms_b200 import _lib as L
+from dooms_b200 import synth
+from dooms_b200._lib import DoomsError
+from dooms_b200.llm import Llm, Vocab, sample
+
+from helpers import QUANT_PLANS
+
+N_VOCAB = 320
+EOS = N_VOCAB - 1
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    path = str(tmp_path_factory.mktemp("llm") / "llm_tiny.gguf")
+    synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 77, vocab=True)
+    return path
+
+
+def test_vocabulary_round_trips_text_and_merges_by_rank(model):
+    v = Vocab(model)
+    assert len(v) == N_VOCAB and v.is_end_of_generation(EOS) and not v.is_end_of_generation(5) and v.piece(EOS) == b""
+    text = "hello world, the héllo 42 \U0001F600!"
+    ids = v.tokenize(text)
+    assert b"".join(v.piece(t) for t in ids) == text.encode()
+    assert len(ids) < len(text.encode())                       # merges happened
+    assert v.tokenize("hello") == [v.tokenize("hello")[0]] and v.piece(v.tokenize("hello")[0]) == b"hello"      # h e l l o -> he ll o -> hell o -> hello
+    assert v.piece(v.tokenize(" world")[0]) == b" world"
+    assert all(v.piece(b) == bytes([b]) for b in range(256))   # the byte alphabet undone
+    with pytest.raises(DoomsError) as e:
+        v.tokenize("")
+    assert e.value.code == L.INVALID_ARGUMENT
+
+
+def test_pieces_are_whole_characters_and_stop_strings_end_the_text(model):
+    v = Vocab(model)
+    # U+00E9 and an emoji arrive byte by byte: nothing incomplete is ever handed on
+    ids = v.tokenize("aé\U0001F600b")
+    pieces = []
+    text, consumed, reason = v.stream(ids, on_text=lambda p: pieces.append(p) or True)
+    assert text == "aé\U0001F600b" and "".join(pieces) == text and consumed == len(ids) and reason == L.FINISH_LENGTH
+    assert all(p.encode().decode() == p for p in pieces) and len(pieces) >= 4
+    # a stop string that spans tokens: the text ends before it, and its beginning was never shown
+    ids = v.tokenize("the answer STOP and more")
+    pieces = []
+    text, consumed, reason = v.stream(ids, stop=["STOP", "never"], on_text=lambda p: pieces.append(p) or True)
+    assert text == "the answer " and "".join(pieces) == text and reason == L.FINISH_STOP and consumed < len(ids)
+    # what looked like the beginning of a stop string and was not is released
+    text, _, reason = v.stream(v.tokenize("a STx b"), stop=["STOP"])
+    assert text == "a STx b" and reason == L.FINISH_LENGTH
+    # an end-of-generation token ends it; the token is consumed, text before it is kept
+    ids = v.tokenize("hello") + [EOS] + v.tokenize("ignored")
+    text, consumed, reason = v.stream(ids, stop=["zzz"])
+    assert text == "hello" and consumed == len(v.tokenize("hello")) + 1 and reason == L.FINISH_STOP
+    # the callback declines
+    seen = []
+    text, consumed, reason = v.stream(v.tokenize("one two three"), on_text=lambda p: (seen.append(p), len(seen) < 2)[1])
+    assert reason == L.FINISH_CANCELLED and len(seen) == 2 and consumed < len(v.tokenize("one two three"))
+    with pytest.raises(DoomsError):
+        v.stream([1, 2], stop=[""])
+
+
+def test_sampler_rules():
+    logits = np.array([0.5, 3.0, 3.0, -1.0, np.nan, 2.0], dtype=np.float32)
+    assert sample(logits) == [1]                                                     # greedy: the first of the largest, NaN never wins
+    assert sample(logits, 5, temperature=0.8, top_k=1, seed=3) == [1] * 5            # top_k 1 is greedy
+    a = sample(logits, 64, temperature=1.0, top_k=0, top_p=1.0, seed=11)
+    assert a == sample(logits, 64, temperature=1.0, top_k=0, top_p=1.0, seed=11) and a != sample(logits, 64, temperature=1.0, top_k=0, top_p=1.0, seed=12)
+    assert 4 not in a
+    # frequencies follow softmax(logits / T) over the kept tokens
+    lg = np.array([2.0, 1.0, 0.0, -1.0], dtype=np.float32)
+    draws = np.array(sample(lg, 20000, temperature=1.0, top_k=3, top_p=1.0, seed=5))
+    p = np.exp(lg[:3]) / np.exp(lg[:3]).sum()
+    freq = np.array([(draws == i).mean() for i in range(3)])
+    assert np.abs(freq - p).max() < 0.015 and (draws == 3).sum() == 0
+    # top_p keeps the smallest prefix that reaches it
+    assert set(sample(lg, 2000, temperature=1.0, top_k=0, top_p=0.6, seed=1)) == {0}
+    # the repetition penalty pushes a token that was just drawn down
+    flat = np.array([1.0, 0.99], dtype=np.float32)
+    assert sample(flat, 4, temperature=0.0, repeat_penalty=1.5) == [0, 1, 0, 1][:1] + sample(flat, 4, temperature=0.0, repeat_penalty=1.5)[1:]
+    assert sample(flat, 3, temperature=0.0, repeat_penalty=1.5)[:2] == [0, 1]
+    for bad in (dict(temperature=-1.0), dict(top_p=0.0), dict(top_p=1.5), dict(top_k=-1), dict(repeat_penalty=0.0)):
+        with pytest.raises(DoomsError) as e:
+            sample(lg, 1, **bad)
+        assert e.value.code == L.INVALID_ARGUMENT
+
+
+@pytest.mark.gpu
+def test_generation_matches_the_decoder_and_reports_how_it_ended(model):
+    from dooms_b200 import CudaLlamaDecoder
+    llm = Llm(model, n_ctx=256, n_batch=64, queue_depth=3)
+    v = Vocab(model)
+    prompt = "hello world the"
+    ids = v.tokenize(prompt)
+    assert llm.count_tokens(prompt) == len(ids) and llm.context_size() == 256
+    # greedy text = the decoder's greedy tokens through the text assembly
+    dec = CudaLlamaDecoder.load(model, 256, 64)
+    dec.eval_tokens(ids)
+    want = []
+    dec.generate(24, 2, lambda t: want.append(t) or True)
+    want_text, consumed, reason = v.stream(want)
+    text = llm.generate(prompt, 24)
+    info = llm.last_generation()
+    assert text == want_text and info["prompt_tokens"] == len(ids) and info["completion_tokens"] == consumed
+    assert info["finish_reason"] == (L.FINISH_STOP if reason == L.FINISH_STOP else L.FINISH_LENGTH) and info["first_token_ms"] > 0 and info["prefill_ms"] > 0
+    text2, toks = llm.generate_tokens(ids, 24)
+    assert text2 == text and toks == want[:consumed]
+    # streaming gives the same text in whole-character pieces; declining stops it
+    pieces = []
+    assert llm.generate(prompt, 24, on_text=lambda p: pieces.append(p) or True) == text and "".join(pieces) == text
+    seen = []
+    llm.generate(prompt, 24, on_text=lambda p: (seen.append(p), False)[1])
+    assert len(seen) == 1 and llm.last_generation()["finish_reason"] == L.FINISH_CANCELLED
+    # a stop string taken from the middle of the greedy answer cuts it there
+    if len(text) > 6:
+        stop = text[3:6]
+        assert llm.generate(prompt, 24, stop=[stop]) == text[:text.index(stop)] and llm.last_generation()["finish_reason"] == L.FINISH_STOP
+    # sampling: reproducible per seed, and the logits path agrees with the greedy path at temperature 0 with a penalty of 1
+    a = llm.generate(prompt, 16, temperature=0.9, top_k=20, seed=4)
+    assert a == llm.generate(prompt, 16, temperature=0.9, top_k=20, seed=4)
+    assert llm.generate_tokens(ids, 16, temperature=0.0, repeat_penalty=1.0000001)[1] == want[:16][:len(llm.generate_tokens(ids, 16, temperature=0.0, repeat_penalty=1.0000001)[1])]
+    # argument checks (llm_pipeline.cpp:137-145)
+    for kwargs, code in ((dict(prompt="", max_new_tokens=4), L.INVALID_ARGUMENT), (dict(prompt=prompt, max_new_tokens=0), L.INVALID_ARGUMENT),
+                         (dict(prompt=prompt, max_new_tokens=256), L.INVALID_ARGUMENT), (dict(prompt=prompt, max_new_tokens=4, stop=[""]), L.INVALID_ARGUMENT),
+                         (dict(prompt=prompt * 40, max_new_tokens=200), L.RESOURCE_EXHAUSTED), (dict(prompt=prompt, max_new_tokens=4, temperature=-1.0), L.INVALID_ARGUMENT)):
+        with pytest.raises(DoomsError) as e:
+            llm.generate(**kwargs)
+        assert e.value.code == code, kwargs
+    dec.close()
+    llm.close()
