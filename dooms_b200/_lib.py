@@ -63,7 +63,7 @@ class KernelTime(C.Structure):
 class Timings(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("last_eval_ms", C.c_double), ("last_generate_ms", C.c_double), ("last_eval_launches", C.c_int64),
                 ("last_generate_launches", C.c_int64), ("weight_bytes", C.c_int64), ("kv_bytes", C.c_int64), ("last_batch_ms", C.c_double),
-                ("last_batch_launches", C.c_int64)]
+                ("last_batch_launches", C.c_int64), ("tp_peer_allreduce", C.c_int64)]
 
 
 class LlmOptions(C.Structure):
@@ -136,6 +136,9 @@ SIGNATURES = {
     "dooms_cuda_llm_generate_stream": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, TEXT_CALLBACK, C.c_void_p]),
     "dooms_cuda_llm_generate_tokens": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, C.c_void_p, C.c_size_t,
                                                    C.POINTER(C.c_size_t), C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_llm_generate_from_embeddings": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, TEXT_CALLBACK, C.c_void_p,
+                                                            C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "dooms_cuda_llama_embed_tokens": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "dooms_cuda_llm_last_generation": (C.c_int32, [C.c_void_p, C.POINTER(GenerationInfo)]),
     "dooms_cuda_llm_count_tokens": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(C.c_int32)]),
     "dooms_cuda_vocab_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),

@@ -319,6 +319,10 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_embeddings(dooms_cuda_llama * d, co
     if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
     return done(d->dec->eval_embeddings(embeddings, n));
 }
+DOOMS_CUDA_API int32_t dooms_cuda_llama_embed_tokens(dooms_cuda_llama * d, const int32_t * tokens, int32_t n, float * out) {
+    if (!d) return fail(DOOMS_INVALID_ARGUMENT, "decoder is NULL");
+    return done(d->dec->embed_tokens(tokens, n, out));
+}
 DOOMS_CUDA_API int32_t dooms_cuda_llama_pending_token(dooms_cuda_llama * d, int32_t * out) {
     if (!d || !out) return fail(DOOMS_INVALID_ARGUMENT, "decoder or out is NULL");
     auto r = d->dec->pending_token();
@@ -358,6 +362,7 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, doom
         out->last_batch_ms = t.last_batch_ms;
         out->last_batch_launches = t.last_batch_launches;
     }
+    if (out->struct_size >= offsetof(dooms_cuda_timings, tp_peer_allreduce) + sizeof(int64_t)) out->tp_peer_allreduce = t.tp_peer_allreduce;
     return DOOMS_OK;
 }
 
@@ -470,6 +475,25 @@ DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_tokens(dooms_cuda_llm * llm, cons
         std::copy(g.tokens.begin(), g.tokens.end(), out_tokens);
     }
     return text_out(g.text, out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_from_embeddings(dooms_cuda_llm * llm, const int32_t * before, int32_t n_before, const float * image, int32_t image_rows,
+                                                               const int32_t * after, int32_t n_after, int32_t max_new_tokens, dooms_cuda_text_callback callback,
+                                                               void * user, char * out, size_t capacity, size_t * needed) {
+    if (!llm) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
+    if (n_before < 0 || n_after < 0 || (n_before > 0 && !before) || (n_after > 0 && !after)) return fail(DOOMS_INVALID_ARGUMENT, "token counts without arrays");
+    llm->last = dooms_cuda_generation_info{};
+    std::function<bool(const std::string &)> on_text;
+    if (callback) on_text = [&](const std::string & piece) { return callback(piece.c_str(), user) == 0; };
+    LlmTimings tm;
+    auto g = llm->llm->generate_from_embeddings(std::vector<int32_t>(before, before + n_before), image, image_rows, std::vector<int32_t>(after, after + n_after), max_new_tokens,
+                                                on_text, &tm);
+    if (!g.is_ok()) return done(g.status());
+    llm->last.struct_size = sizeof(llm->last);
+    llm->last.prompt_tokens = int32_t(tm.prompt_tokens);
+    llm->last.completion_tokens = int32_t(g.value().tokens.size());
+    llm->last.finish_reason = finish_reason_of(g.value());
+    llm->last.prefill_ms = tm.prefill_ms; llm->last.first_token_ms = tm.first_token_ms; llm->last.decode_ms = tm.decode_ms;
+    return text_out(g.value().text, out, capacity, needed);
 }
 DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm, dooms_cuda_generation_info * out) {
     int32_t code = DOOMS_OK;

@@ -98,6 +98,8 @@ struct CudaLlamaDecoder::Impl {
     float * host_x = nullptr;     // pinned staging for eval_embeddings
     DevState * state = nullptr;
     int32_t * host_error = nullptr;   // mapped pinned word a kernel sets when a bounded wait ran out
+    int32_t * tp_pairs = nullptr;  // tensor parallelism: every rank's (best logit, its index) of the current position
+    bool logits_gathered = true;   // logits_buf holds every rank's rows (always true on one GPU)
     int splits = 1;
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
     int gqa_splits = 1;
@@ -153,7 +155,7 @@ struct CudaLlamaDecoder::Impl {
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
         if (ev_b) cudaEventDestroy(ev_b);
-        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, rope_cs, (void *)attn_counters, (void *)split_counters, (void *)xq2, (void *)norm_ss, (void *)norm_counters, w16,
+        for (void * p : {(void *)weights, (void *)kc, (void *)vc, (void *)x, (void *)xn, (void *)qkv, (void *)attn, (void *)h, (void *)red, (void *)logits_buf, (void *)part, (void *)inv_freq, rope_cs, (void *)attn_counters, (void *)split_counters, (void *)xq2, (void *)norm_ss, (void *)norm_counters, (void *)tp_pairs, w16,
                          argmax_part, (void *)xq, (void *)xn16, (void *)attn16, (void *)h16, (void *)tokens, (void *)in_tokens, (void *)state}) {
             if (p) cudaFree(p);
         }
@@ -503,11 +505,14 @@ struct CudaLlamaDecoder::Impl {
         // The logits of the last row only (metal_llama_decoder.mm:375).
         if (output.rows > 0) matvec("output", output, x + size_t(M - 1) * E, output_norm, logits_buf + vocab_row0, nullptr, 0u);
         if (tp > 1) {
-            run("all_gather", [&] {
-                return nccl.AllGather(logits_buf + vocab_row0, logits_buf, size_t(vocab_stride), NcclApi::kFloat32, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown;
-            });
+            // every rank reduces its own rows to one (value, index) pair; 8 bytes per rank are gathered instead of the logits (those only in logits())
+            run("argmax", [&] { return cuda::launch_argmax_local_pair(logits_buf + vocab_row0, vocab_rows, vocab_row0, tp_pairs + rank * 2, argmax_part, stream); });
+            run("all_gather", [&] { return nccl.AllGather(tp_pairs + rank * 2, tp_pairs, 8, NcclApi::kInt8, comm, stream) == 0 ? cudaSuccess : cudaErrorUnknown; });
+            run("argmax", [&] { return cuda::launch_argmax_pairs(tp_pairs, tp, tokens, host_tokens, state, advance ? 1 : 0, stream); });
+            logits_gathered = false;
+        } else {
+            run("argmax", [&] { return cuda::launch_argmax(logits_buf, int64_t(vocab_stride) * tp, tokens, host_tokens, state, argmax_part, advance ? 1 : 0, stream); });
         }
-        run("argmax", [&] { return cuda::launch_argmax(logits_buf, int64_t(vocab_stride) * tp, tokens, host_tokens, state, argmax_part, advance ? 1 : 0, stream); });
     }
 
     void embed(const int32_t * ids, const int32_t * index, int rows) {
@@ -616,6 +621,7 @@ struct CudaLlamaDecoder::Impl {
     template <class Stage> Status append_positions(int32_t n, bool from_tokens, Stage && stage);
 
     void queue_decode_step() {
+        logits_gathered = tp == 1;
         if (step_graph) {
             launches += step_launches;
             (void)check(cudaGraphLaunch(step_graph, stream), "cudaGraphLaunch");
@@ -853,6 +859,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h), B * size_t(m.ff) * 4, "the feed-forward rows"));
     if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
+    if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tp_pairs), size_t(tp) * 8, "the ranks' argmax pairs"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
     {
         std::vector<double> freq(size_t(c.head_dim / 2));
@@ -935,6 +942,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     }
     if (tp > 1) m.setup_peer_allreduce();
     if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
+    m.tm.tp_peer_allreduce = m.use_par ? 1 : 0;
     m.tm.weight_bytes = int64_t(m.matrix_bytes);
     m.tm.kv_bytes = int64_t(m.kv_bytes);
     return std::unique_ptr<CudaLlamaDecoder>(new CudaLlamaDecoder(std::move(impl)));
@@ -1010,6 +1018,25 @@ Status CudaLlamaDecoder::eval_tokens(const int32_t * ids, int32_t n) {
     });
 }
 
+Status CudaLlamaDecoder::embed_tokens(const int32_t * ids, int32_t n, float * out) {
+    Impl & m = *impl_;
+    if (ids == nullptr || out == nullptr || n < 1) return invalid_argument("embed_tokens: no tokens given, or no room for their rows");
+    const int32_t * bad = std::find_if(ids, ids + n, [&](int32_t t) { return t < 0 || t >= m.cfg.n_vocab; });
+    if (bad != ids + n) return invalid_argument("embed_tokens: id " + std::to_string(*bad) + " is not in the vocabulary of " + std::to_string(m.cfg.n_vocab));
+    DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    cudaSetDevice(m.opt.device);
+    const size_t E = size_t(m.cfg.n_embd);
+    for (int32_t done = 0; done < n; done += m.cfg.n_batch) {      // through the chunk buffers: nothing is pending on them while the stream is idle
+        const int32_t rows = std::min(m.cfg.n_batch, n - done);
+        std::memcpy(m.host_in, ids + done, size_t(rows) * sizeof(int32_t));
+        (void)m.check(cudaMemcpyAsync(m.in_tokens, m.host_in, size_t(rows) * sizeof(int32_t), cudaMemcpyHostToDevice, m.stream), "copying the tokens to the device");
+        m.embed(m.in_tokens, nullptr, rows);
+        (void)m.check(cudaMemcpyAsync(out + size_t(done) * E, m.x, size_t(rows) * E * sizeof(float), cudaMemcpyDeviceToHost, m.stream), "reading the embedding rows");
+        DOOMS_RETURN_IF_ERROR(m.wait_idle());
+    }
+    return Status();
+}
+
 Result<int32_t> CudaLlamaDecoder::pending_token() {
     Impl & m = *impl_;
     if (!m.has_pending) return invalid_argument(kNothingPending);
@@ -1024,6 +1051,15 @@ Status CudaLlamaDecoder::logits_into(float * out, int64_t capacity) {
     if (m.logits_slot != m.cur) return invalid_argument("logits: another sequence (or a batched step) was evaluated since this one; only the last evaluation's logits are kept");
     DOOMS_RETURN_IF_ERROR(m.wait_idle());
     cudaSetDevice(m.opt.device);
+    if (m.tp > 1 && !m.logits_gathered) {
+        // Under tensor parallelism a rank holds its own rows only; the other ranks' arrive here. Collective: every rank of the group calls logits() at
+        // the same point (as it calls eval_tokens and generate).
+        if (m.nccl.AllGather(m.logits_buf + m.vocab_row0, m.logits_buf, size_t(m.vocab_stride), NcclApi::kFloat32, m.comm, m.stream) != 0) {
+            return m.check(cudaErrorUnknown, "gathering the logits");
+        }
+        DOOMS_RETURN_IF_ERROR(m.wait_idle());
+        m.logits_gathered = true;
+    }
     return m.check(cudaMemcpy(out, m.logits_buf, size_t(m.cfg.n_vocab) * sizeof(float), cudaMemcpyDeviceToHost), "reading the logits");
 }
 

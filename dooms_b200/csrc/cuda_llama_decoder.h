@@ -77,6 +77,10 @@ public:
     Status eval_embeddings(const float * embeddings, int32_t n);
     Status eval_tokens(const std::vector<int32_t> & tokens);
     Status eval_tokens(const int32_t * tokens, int32_t n);
+    // Rows of the embedding table as f32 (n x n_embd floats into out), looked up and dequantized on the device by the kernel that eval_tokens uses: what
+    // a caller that mixes token rows with rows of its own (image embeddings, src/pipeline/vlm_pipeline.cpp:180-189) hands to eval_embeddings.
+    //   InvalidArgument  no ids, no room, an id outside the vocabulary
+    Status embed_tokens(const int32_t * tokens, int32_t n, float * out);
     Result<int32_t> pending_token();
     Result<std::vector<float>> logits();
     Status logits_into(float * out, int64_t capacity);
@@ -106,6 +110,7 @@ public:
         int64_t last_eval_launches = 0, last_generate_launches = 0, weight_bytes = 0, kv_bytes = 0;
         double last_batch_ms = 0;            // device time of the last decode_batch call's steps
         int64_t last_batch_launches = 0;
+        int64_t tp_peer_allreduce = 0;       // 1: decode steps reduce over peer memory (kernels/allreduce_peer.cu); 0: NCCL, or one GPU
     };
     Timings timings() const;
 

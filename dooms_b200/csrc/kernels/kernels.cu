@@ -445,6 +445,25 @@ __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_final(const Best * pa
     }
 }
 
+// Tensor parallelism, two stages: every rank reduces its own slice of the vocabulary to one (value, global index) pair (k_argmax_part, then this kernel
+// with `offset` = the slice's first row); the pairs of all ranks are gathered (8 bytes per rank instead of the logits) and k_argmax_pairs picks among them
+// by the same rule, lowest global index on ties, so that every rank writes the same token.
+__global__ void __launch_bounds__(kArgmaxThreads) k_argmax_pair(const Best * part, int nparts, int32_t offset, Best * pair) {
+    Best b{0.f, -1};
+    for (int i = threadIdx.x; i < nparts; i += kArgmaxThreads) if (better(part[i].v, part[i].i, b.v, b.i)) b = part[i];
+    b = block_best(b);
+    if (threadIdx.x == 0) *pair = Best{b.v, b.i < 0 ? -1 : b.i + offset};
+}
+__global__ void k_argmax_pairs(const Best * pairs, int n, int32_t * tokens, int32_t * host_tokens, DevState * st, int advance) {
+    Best b{0.f, -1};
+    for (int r = 0; r < n; r++) if (better(pairs[r].v, pairs[r].i, b.v, b.i)) b = pairs[r];
+    const int32_t tok = b.i < 0 ? 0 : b.i;
+    const int32_t o = st->tok_out;
+    tokens[o] = tok;
+    if (host_tokens) host_tokens[o] = tok;
+    if (advance) { st->pos += 1; st->tok_in += 1; st->tok_out = o + 1; }
+}
+
 // The same reduction for every row of a batched decode step: grid (blocks per row, rows), then one block per row.
 __global__ void __launch_bounds__(kArgmaxThreads) k_argmax_rows_part(const float * logits, int64_t n, int64_t stride, const int32_t * slot, Best * part) {
     const int row = blockIdx.y;
@@ -603,6 +622,18 @@ cudaError_t launch_argmax_rows(const float * logits, int64_t n, int64_t stride, 
     k_argmax_rows_part<<<dim3(blocks, n_rows), kArgmaxThreads, 0, stream>>>(logits, n, stride, rows.slot, static_cast<Best *>(part));
     k_argmax_rows_final<<<n_rows, kArgmaxThreads, 0, stream>>>(static_cast<const Best *>(part), blocks, rows.slot, rows.pos, rows.tok, out, step);
     k_bump<<<1, 1, 0, stream>>>(step);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_local_pair(const float * logits, int64_t n, int32_t offset, void * pair, void * part, cudaStream_t stream) {
+    const int blocks = argmax_blocks(std::max<int64_t>(n, 1));
+    if (n > 0) k_argmax_part<<<blocks, kArgmaxThreads, 0, stream>>>(logits, n, static_cast<Best *>(part));
+    k_argmax_pair<<<1, kArgmaxThreads, 0, stream>>>(static_cast<const Best *>(part), n > 0 ? blocks : 0, offset, static_cast<Best *>(pair));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_pairs(const void * pairs, int n, int32_t * tokens, int32_t * host_tokens, DevState * st, int advance, cudaStream_t stream) {
+    k_argmax_pairs<<<1, 1, 0, stream>>>(static_cast<const Best *>(pairs), n, tokens, host_tokens, st, advance);
     return cudaGetLastError();
 }
 

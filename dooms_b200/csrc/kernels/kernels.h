@@ -113,6 +113,10 @@ cudaError_t launch_attention_flash(const float * qkv, const void * kc, const voi
 // (mapped pinned memory). With advance the state moves one decode step forward (pos, tok_in, tok_out += 1). part: argmax_blocks(n) x 2 words.
 int argmax_blocks(int64_t n);
 cudaError_t launch_argmax(const float * logits, int64_t n, int32_t * tokens, int32_t * host_tokens, DevState * st, void * part, int advance, cudaStream_t stream);
+// Two stages for a vocabulary split over tensor-parallel ranks: *pair (8 bytes: value, index + offset; index -1 when the slice holds no number) = the
+// best of this rank's logits[0..n); then, over the gathered pairs of all ranks, the token by the same first-index rule.
+cudaError_t launch_argmax_local_pair(const float * logits, int64_t n, int32_t offset, void * pair, void * part, cudaStream_t stream);
+cudaError_t launch_argmax_pairs(const void * pairs, int n_ranks, int32_t * tokens, int32_t * host_tokens, DevState * st, int advance, cudaStream_t stream);
 // The same reduction without a state: *out = argmax.
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream);
 

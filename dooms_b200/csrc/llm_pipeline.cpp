@@ -343,4 +343,38 @@ Result<LlmGeneration> Llm::generate_tokens(const std::vector<int32_t> & prompt, 
     return out;
 }
 
+Result<LlmGeneration> Llm::generate_from_embeddings(const std::vector<int32_t> & before, const float * image, int32_t image_rows, const std::vector<int32_t> & after,
+                                                    int32_t max_new_tokens, const std::function<bool(const std::string &)> & on_text, LlmTimings * timings) {
+    const int32_t n_ctx = context_size();
+    const size_t E = size_t(decoder_->config().n_embd);
+    const size_t rows = before.size() + size_t(std::max(image_rows, 0)) + after.size();
+    if (rows == 0 || image_rows < 0 || (image_rows > 0 && image == nullptr)) return invalid_argument("generate_from_embeddings: no rows to evaluate");
+    if (max_new_tokens < 1 || max_new_tokens >= n_ctx) return invalid_argument("generate_from_embeddings: max_new_tokens has to lie in [1, context size)");
+    if (int64_t(rows) + max_new_tokens > n_ctx) {
+        return resource_exhausted("generate_from_embeddings: " + std::to_string(rows) + " rows and " + std::to_string(max_new_tokens) + " new tokens do not fit the context of " +
+                                  std::to_string(n_ctx));
+    }
+    const auto t0 = Clock::now();
+    std::vector<float> all(rows * E);
+    if (!before.empty()) DOOMS_RETURN_IF_ERROR(decoder_->embed_tokens(before.data(), int32_t(before.size()), all.data()));
+    if (image_rows > 0) std::copy(image, image + size_t(image_rows) * E, all.begin() + long(before.size() * E));
+    if (!after.empty()) DOOMS_RETURN_IF_ERROR(decoder_->embed_tokens(after.data(), int32_t(after.size()), all.data() + (before.size() + size_t(image_rows)) * E));
+    LlmTimings tm;
+    tm.prompt_tokens = int64_t(rows);
+    decoder_->reset();
+    DOOMS_RETURN_IF_ERROR(decoder_->eval_embeddings(all.data(), int32_t(rows)));
+    LlmGeneration out;
+    static const std::vector<std::string> no_stops;
+    TextStream stream(vocab_, no_stops, on_text, &out);
+    auto t_decode = t0;
+    DOOMS_RETURN_IF_ERROR(decoder_->generate(max_new_tokens, depth_, [&](int32_t token) {
+        if (tm.generated_tokens++ == 0) { tm.prefill_ms = tm.first_token_ms = ms_since(t0); t_decode = Clock::now(); }
+        return stream.push(token);
+    }));
+    stream.finish();
+    tm.decode_ms = tm.generated_tokens > 1 ? ms_since(t_decode) : 0.0;
+    if (timings) *timings = tm;
+    return out;
+}
+
 }  // namespace dooms

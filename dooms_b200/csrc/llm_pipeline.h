@@ -122,6 +122,13 @@ public:
     Result<LlmGeneration> generate_tokens(const std::vector<int32_t> & prompt, const LlmGenerateOptions & options = LlmGenerateOptions(),
                                           const std::function<bool(const std::string &)> & on_text = nullptr, LlmTimings * timings = nullptr);
 
+    // The text side of a vision-language pipeline (generate_native, src/pipeline/vlm_pipeline.cpp:177-212): the whole prompt as ONE embedding sequence -
+    // the rows of the tokens before the image, the image's embedding rows as the vision model produced them (image_rows x n_embd floats), the rows of the
+    // tokens after it - through eval_embeddings, then greedy decoding with steps queued on the GPU.
+    //   InvalidArgument  no rows at all, non-finite embeddings, max_new_tokens outside [1, n_ctx)     ResourceExhausted  the context
+    Result<LlmGeneration> generate_from_embeddings(const std::vector<int32_t> & before, const float * image, int32_t image_rows, const std::vector<int32_t> & after,
+                                                   int32_t max_new_tokens, const std::function<bool(const std::string &)> & on_text = nullptr, LlmTimings * timings = nullptr);
+
 private:
     Llm(std::unique_ptr<CudaLlamaDecoder> d, Vocab v, int32_t depth) : decoder_(std::move(d)), vocab_(std::move(v)), depth_(depth) {}
     std::unique_ptr<CudaLlamaDecoder> decoder_;

@@ -150,6 +150,13 @@ class CudaLlamaDecoder:
         a = np.ascontiguousarray(embeddings, dtype=np.float32)
         L.check(L.lib().dooms_cuda_llama_eval_embeddings(self._h, a.ctypes.data_as(C.POINTER(C.c_float)), a.shape[0] if n is None else n))
 
+    def embed_tokens(self, tokens: Sequence[int]) -> np.ndarray:
+        """The tokens' rows of the embedding table as float32 [n][n_embd]."""
+        a = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        out = np.empty((a.size, self.config().n_embd), dtype=np.float32)
+        L.check(L.lib().dooms_cuda_llama_embed_tokens(self._h, a.ctypes.data, a.size, out.ctypes.data))
+        return out
+
     def pending_token(self) -> int:
         v = C.c_int32()
         L.check(L.lib().dooms_cuda_llama_pending_token(self._h, C.byref(v)))

@@ -1,5 +1,7 @@
 """The text-model surface over the C ABI (include/dooms_cuda.h: dooms_cuda_llm_*, dooms_cuda_vocab_*, dooms_cuda_text_stream, dooms_cuda_sample): the
-reference's `Llm` (src/pipeline/llm_pipeline.h) for the CUDA decoder. Vocabulary, text assembly and sampler run on the host and need no GPU."""
+reference's `Llm` (src/pipeline/llm_pipeline.h) for the CUDA decoder. Vocabulary, text assembly and sampler run on the host and need no GPU.
+Text crosses the boundary as UTF-8 bytes; a model may emit bytes that are no valid UTF-8 (a random-weight model does), so they are carried through Python
+strings with the surrogateescape error handler: what comes back encodes to exactly the bytes the library produced."""
 from __future__ import annotations
 
 import ctypes as C
@@ -19,7 +21,7 @@ def _sampling(temperature=0.0, top_k=40, top_p=0.95, repeat_penalty=1.0, seed=0)
 
 def _stops(stop: Sequence[str] | None):
     stop = list(stop or [])
-    arr = (C.c_char_p * max(1, len(stop)))(*[s.encode() for s in stop])
+    arr = (C.c_char_p * max(1, len(stop)))(*[s.encode("utf-8", "surrogateescape") for s in stop])
     return arr, len(stop)
 
 
@@ -32,7 +34,7 @@ def _text(call) -> str:
         buf = C.create_string_buffer(needed.value)
         code = call(buf, len(buf), C.byref(needed))
     L.check(code)
-    return buf.value.decode("utf-8", "replace")
+    return buf.value.decode("utf-8", "surrogateescape")
 
 
 def sample(logits: np.ndarray, draws: int = 1, **sampling) -> list[int]:
@@ -82,7 +84,7 @@ class Vocab:
         """The text assembly over `tokens`: (text, tokens consumed, finish reason). on_text receives each piece and returns False to cancel."""
         a = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
         arr, n_stop = _stops(stop)
-        cb = L.TEXT_CALLBACK(lambda piece, _u: 0 if (on_text is None or on_text(piece.decode("utf-8")) is not False) else 1)
+        cb = L.TEXT_CALLBACK(lambda piece, _u: 0 if (on_text is None or on_text(piece.decode("utf-8", "surrogateescape")) is not False) else 1)
         consumed, reason = C.c_int32(), C.c_int32()
         text = _text(lambda buf, cap, needed: L.lib().dooms_cuda_text_stream(self._h, a.ctypes.data, a.size, arr, n_stop, cb, None, buf, cap, needed, C.byref(consumed),
                                                                             C.byref(reason)))
@@ -121,14 +123,14 @@ class Llm:
         s = _sampling(**sampling) if sampling else None
         sp = C.byref(s) if s else None
         if on_text is None:
-            return _text(lambda buf, cap, needed: L.lib().dooms_cuda_llm_generate(self._h, prompt.encode(), max_new_tokens, sp, arr, n_stop, buf, cap, needed))
+            return _text(lambda buf, cap, needed: L.lib().dooms_cuda_llm_generate(self._h, prompt.encode("utf-8", "surrogateescape"), max_new_tokens, sp, arr, n_stop, buf, cap, needed))
         pieces: list[str] = []
 
         def cb(piece, _u):
-            text = piece.decode("utf-8")
+            text = piece.decode("utf-8", "surrogateescape")
             pieces.append(text)
             return 0 if on_text(text) is not False else 1
-        L.check(L.lib().dooms_cuda_llm_generate_stream(self._h, prompt.encode(), max_new_tokens, sp, arr, n_stop, L.TEXT_CALLBACK(cb), None))
+        L.check(L.lib().dooms_cuda_llm_generate_stream(self._h, prompt.encode("utf-8", "surrogateescape"), max_new_tokens, sp, arr, n_stop, L.TEXT_CALLBACK(cb), None))
         return "".join(pieces)
 
     def generate_tokens(self, prompt: Sequence[int], max_new_tokens: int = 128, stop: Sequence[str] | None = None, **sampling):
@@ -141,6 +143,16 @@ class Llm:
         text = _text(lambda buf, cap, needed: L.lib().dooms_cuda_llm_generate_tokens(self._h, a.ctypes.data, a.size, max_new_tokens, C.byref(s) if s else None, arr, n_stop, buf, cap,
                                                                                     needed, toks.ctypes.data, toks.size, C.byref(n)))
         return text, [int(t) for t in toks[:n.value]]
+
+    def generate_from_embeddings(self, before: Sequence[int], image: np.ndarray | None, after: Sequence[int], max_new_tokens: int = 128,
+                                 on_text: Callable[[str], bool] | None = None) -> str:
+        """The text side of a vision-language pipeline: token rows, the image's embedding rows ([rows][n_embd] floats) and more token rows as one sequence."""
+        b = np.ascontiguousarray(np.asarray(before, dtype=np.int32))
+        a = np.ascontiguousarray(np.asarray(after, dtype=np.int32))
+        img = np.ascontiguousarray(image, dtype=np.float32) if image is not None else np.zeros((0, 1), dtype=np.float32)
+        cb = L.TEXT_CALLBACK(lambda piece, _u: 0 if (on_text is None or on_text(piece.decode("utf-8", "surrogateescape")) is not False) else 1)
+        return _text(lambda buf, cap, needed: L.lib().dooms_cuda_llm_generate_from_embeddings(self._h, b.ctypes.data, b.size, img.ctypes.data, img.shape[0], a.ctypes.data, a.size,
+                                                                                             max_new_tokens, cb, None, buf, cap, needed))
 
     def last_generation(self) -> dict:
         info = L.GenerationInfo()

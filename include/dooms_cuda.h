@@ -155,6 +155,9 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_position(const dooms_cuda_llama * d);   
 DOOMS_CUDA_API int32_t dooms_cuda_llama_reset(dooms_cuda_llama * d);                                     /* reset(), .mm:691-695 */
 DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_tokens(dooms_cuda_llama * d, const int32_t * tokens, int32_t n);        /* .mm:712-724 */
 DOOMS_CUDA_API int32_t dooms_cuda_llama_eval_embeddings(dooms_cuda_llama * d, const float * embeddings, int32_t n);  /* .mm:697-710 */
+/* Rows of the embedding table as f32 (n x n_embd floats into out, host memory), dequantized on the device (embedq<Q>, llama_kernels.h:1289-1296): what a
+ * caller that mixes token rows with rows of its own hands to eval_embeddings (vocab.embed_tokens in src/pipeline/vlm_pipeline.cpp:180-181). */
+DOOMS_CUDA_API int32_t dooms_cuda_llama_embed_tokens(dooms_cuda_llama * d, const int32_t * tokens, int32_t n, float * out);
 DOOMS_CUDA_API int32_t dooms_cuda_llama_pending_token(dooms_cuda_llama * d, int32_t * out);                           /* .mm:726-731 */
 /* logits() (.mm:733-739): n_vocab floats of the last evaluated position into out (capacity floats; too small: DOOMS_RESOURCE_EXHAUSTED). */
 DOOMS_CUDA_API int32_t dooms_cuda_llama_logits(dooms_cuda_llama * d, float * out, int64_t capacity);
@@ -176,6 +179,7 @@ typedef struct dooms_cuda_timings {
     int64_t kv_bytes;            /* bytes of the KV cache on this GPU */
     double last_batch_ms;        /* device time of the steps of the last dooms_cuda_llama_decode_batch call (written only when struct_size covers it) */
     int64_t last_batch_launches;
+    int64_t tp_peer_allreduce;   /* 1: the tensor-parallel decode steps reduce over peer memory; 0: NCCL's all-reduce, or one GPU */
 } dooms_cuda_timings;
 DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, dooms_cuda_timings * out);
 
@@ -267,6 +271,12 @@ DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_stream(dooms_cuda_llm * llm, cons
 DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_tokens(dooms_cuda_llm * llm, const int32_t * prompt, int32_t n_prompt, int32_t max_new_tokens,
                                                       const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, char * out, size_t capacity,
                                                       size_t * needed, int32_t * out_tokens, int32_t token_capacity, int32_t * n_tokens);
+/* The text side of the reference's vision-language pipeline (generate_native, src/pipeline/vlm_pipeline.cpp:177-212): the prompt as one embedding sequence
+ * (rows of the tokens `before`, then image_rows x n_embd floats of image embeddings as given, then the rows of the tokens `after`) through
+ * eval_embeddings, then greedy decoding. callback optional (as dooms_cuda_llm_generate_stream); the whole answer in out as dooms_cuda_llm_generate. */
+DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_from_embeddings(dooms_cuda_llm * llm, const int32_t * before, int32_t n_before, const float * image, int32_t image_rows,
+                                                               const int32_t * after, int32_t n_after, int32_t max_new_tokens, dooms_cuda_text_callback callback,
+                                                               void * user, char * out, size_t capacity, size_t * needed);
 DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm, dooms_cuda_generation_info * out);                 /* dooms_llm_last_generation */
 DOOMS_CUDA_API int32_t dooms_cuda_llm_count_tokens(dooms_cuda_llm * llm, const char * text, int32_t add_special, int32_t * count);   /* dooms_llm_count_tokens */
 

@@ -93,6 +93,18 @@ part[: s.vocab_rows] = torch.from_numpy(logits[s.vocab_row0:s.vocab_row0 + s.voc
 parts = [torch.empty_like(part) for _ in range(tp)]
 dist.all_gather(parts, part)
 assert int(torch.cat(parts).argmax()) == int(np.argmax(logits))
+# what the decoder does instead of gathering logits: every rank sends one (value, global index) pair of its slice; the pick among the pairs takes the
+# lowest index on ties and never a NaN (llama_kernels.h:949-975, src/core/argmax.h:15-16), so it equals the first-index argmax of the whole vector
+for case in (logits, np.where(np.arange(cfg.n_vocab) % 7 == 0, logits.max(), logits), np.where(np.arange(cfg.n_vocab) < 60, np.nan, logits)):
+    mine = case[s.vocab_row0:s.vocab_row0 + s.vocab_rows]
+    ok = ~np.isnan(mine)
+    pair = torch.tensor([mine[ok].max(), float(s.vocab_row0 + int(np.flatnonzero(ok & (mine == mine[ok].max()))[0]))] if ok.any() else [0.0, -1.0], dtype=torch.float64)
+    pairs = [torch.empty_like(pair) for _ in range(tp)]
+    dist.all_gather(pairs, pair)
+    cand = [(float(p[0]), int(p[1])) for p in pairs if int(p[1]) >= 0]
+    best = min(cand, key=lambda c: (-c[0], c[1]))[1]
+    want = int(np.flatnonzero(case == np.nanmax(case))[0])
+    assert best == want, (best, want)
 dist.destroy_process_group()
 os.write(1, f"ok {rank}\n".encode())      # one write per rank: the two ranks share the pipe
 """
@@ -128,6 +140,8 @@ dec = CudaLlamaDecoder.load(path, 512, 128, device=local, tp_rank=rank, tp_size=
 dec.eval_tokens(prompt)
 lg = dec.logits(); toks = []
 dec.generate(12, 2, lambda t: toks.append(t) or True)
+peer = dec.timings()["tp_peer_allreduce"]
+assert peer == (1 if os.environ.get("DOOMS_TP_ALLREDUCE") == "peer" else 0), peer      # the variant under test is the one that ran
 if rank == 0:
     ref = CudaLlamaDecoder.load(path, 512, 128, device=local)
     ref.eval_tokens(prompt)
