@@ -2,6 +2,7 @@
 
     python bench_kernels.py gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
     python bench_kernels.py gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
+    python bench_kernels.py attention [--config 2 --layers 2 --prompt 2048 --steps 8]  prefill and decode attention inside a decoder cut to a few layers
     python bench_kernels.py launches <ncu csv>                                     per-kernel totals and shares of an ncu launch list
 
 The GEMV case walks over several distinct matrices so that every launch reads its weights from device memory, not from L2.
@@ -101,6 +102,47 @@ def _gemm(args):
         print(f'{ms * 1e3:.1f} us per call, {flops / ms / 1e9:.1f} TFLOP/s')
 
 
+def _attention(args):
+    """A decoder of the configuration's shape cut to a few layers and a small vocabulary: one prompt call (k_attention_flash once per layer) and a few greedy
+    steps (k_attention_decode once per layer and step), checked against a second run fed token by token."""
+    import dataclasses
+    import os
+    import tempfile
+    import torch
+    from dooms_b200 import CudaLlamaDecoder, synth
+    spec = dataclasses.replace(synth.config_spec(args.config), n_layer=args.layers, n_vocab=4096, tied=False)
+    path = os.path.join(tempfile.gettempdir(), f'dooms_attention_case_{args.config}_{args.layers}.gguf')
+    synth.write_model(spec, path, 77, device='cuda')
+    prompt = [int(t) for t in synth.prompt_tokens(args.prompt, spec.n_vocab, 78)]
+    n_ctx = args.prompt + args.steps + 8
+    dec = CudaLlamaDecoder.load(path, n_ctx, min(args.prompt, 2048))
+    a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    for rep in range(args.reps):
+        dec.reset()
+        torch.cuda.synchronize()
+        a.record()
+        dec.eval_tokens(prompt)
+        dec.pending_token()
+        b.record()
+        out = []
+        dec.generate(args.steps, 2, lambda tok: out.append(tok) is None)
+        c.record()
+        torch.cuda.synchronize()
+        kv = 2 * (args.prompt + args.steps / 2) * spec.n_head_kv * spec.head_dim * 2
+        print(f'prompt of {args.prompt}: {a.elapsed_time(b):.2f} ms; {args.steps} steps: {b.elapsed_time(c) / args.steps * 1e3:.1f} us each '
+              f'({kv / 1e6:.2f} MB of keys and values per layer and step)')
+    dec.reset()
+    dec.eval_tokens(prompt[:-64])
+    for t in prompt[-64:]:
+        dec.eval_tokens([t])                         # the last 64 positions through the decode attention kernel
+    again = []
+    dec.generate(args.steps, 2, lambda tok: again.append(tok) is None)
+    print('tokens', out, 'token by token', again)
+    assert out == again or args.prompt < 65, (out, again)
+    dec.close()
+    os.remove(path)
+
+
 def summarize_launches(path, out=sys.stdout):
     """Totals per kernel of an `ncu --metrics gpu__time_duration.sum --csv` launch list."""
     header, agg = None, collections.OrderedDict()
@@ -145,6 +187,12 @@ def main(argv=None):
     m.add_argument('--gate', action='store_true')
     m.add_argument('--reps', type=int, default=3)
     m.add_argument('--dtype', default='q4_0')
+    t = sub.add_parser('attention')
+    t.add_argument('--config', type=int, default=2)
+    t.add_argument('--layers', type=int, default=2)
+    t.add_argument('--prompt', type=int, default=2048)
+    t.add_argument('--steps', type=int, default=8)
+    t.add_argument('--reps', type=int, default=2)
     l = sub.add_parser('launches')
     l.add_argument('csv')
     args = ap.parse_args(argv)
@@ -152,6 +200,8 @@ def main(argv=None):
         _gemv(args)
     elif args.case == 'gemm':
         _gemm(args)
+    elif args.case == 'attention':
+        _attention(args)
     else:
         summarize_launches(args.csv)
 

@@ -110,6 +110,18 @@ Status scratch_for(size_t bytes, void ** out) {
     return Status();
 }
 
+// The error word of the single-kernel entry points: kernels with bounded waits (tensor copies, mbarriers) set it instead of waiting for ever. One word of
+// mapped pinned host memory per process, never freed, read and cleared by dooms_cuda_kernel_status.
+int32_t * kernel_error_word() {
+    static int32_t * word = [] {
+        int32_t * w = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&w), 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { (void)cudaGetLastError(); return static_cast<int32_t *>(nullptr); }
+        *w = 0;
+        return w;
+    }();
+    return word;
+}
+
 int32_t launch_result(cudaError_t e, const char * what) {
     if (e == cudaSuccess) return DOOMS_OK;
     (void)cudaGetLastError();
@@ -122,12 +134,13 @@ int32_t launch_result(cudaError_t e, const char * what) {
 // inputs are split once by a kernel into the per-device scratch (shared by every call on the device, so such calls must not overlap on different streams).
 int32_t fast_q4_0(const void * w, const void * w2, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, bool q4_k,
                   cudaStream_t st, const char * what) {
-    if (cols < 8192) return launch_result(cuda::launch_gemv_q4_0(w, w2, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st), what);
+    int32_t * err = kernel_error_word();
+    if (cols < 8192) return launch_result(cuda::launch_gemv_q4_0(w, w2, nullptr, x, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st, nullptr, nullptr, err), what);
     void * scratch = nullptr;
     const Status ss = scratch_for((cuda::quantized_x_bytes(cols) + 15) & ~size_t(15), &scratch);
     if (!ss.is_ok()) return done(ss);
     cudaError_t e = cuda::launch_quantize_x(x, cols, scratch, st);
-    if (e == cudaSuccess) e = cuda::launch_gemv_q4_0(w, w2, scratch, nullptr, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st);
+    if (e == cudaSuccess) e = cuda::launch_gemv_q4_0(w, w2, scratch, nullptr, nullptr, 0.f, y, bias, rows, cols, flags, q4_k, st, nullptr, nullptr, err);
     return launch_result(e, what);
 }
 
@@ -629,12 +642,26 @@ DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const 
     cuda::TensorMap map;
     cudaError_t e = cuda::make_activation_map(&map, d_x16, tokens, cols);
     if (e != cudaSuccess) return launch_result(e, "matmul (tensor map)");
-    e = cudaMemsetAsync(scratch, 0, 4, st);
-    if (e == cudaSuccess) {
-        e = cuda::launch_gemm_tc(dtype, d_w, d_w2, &map, d_y, nullptr, d_bias, tokens, rows, cols, rows, 0, flags, static_cast<int32_t *>(scratch), st,
+    int32_t * err = kernel_error_word();
+    if (!err) return fail(DOOMS_RESOURCE_EXHAUSTED, "matmul: could not allocate the kernel error word");
+    {
+        e = cuda::launch_gemm_tc(dtype, d_w, d_w2, &map, d_y, nullptr, d_bias, tokens, rows, cols, rows, 0, flags, err, st,
                                  w16_bytes ? static_cast<uint8_t *>(scratch) + 256 : nullptr, w16_bytes);
     }
     return launch_result(e, "matmul");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_kernel_status(void * stream, int32_t * flag) {
+    if (flag) *flag = 0;
+    const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return launch_result(e, "kernel_status");
+    int32_t * err = kernel_error_word();
+    const int32_t seen = err ? *err : 0;
+    if (err) *err = 0;
+    if (flag) *flag = seen;
+    if (seen == 0) return DOOMS_OK;
+    return fail(DOOMS_INTERNAL, "a kernel gave up a bounded wait (flag " + std::to_string(seen) + (seen == 2 ? ": matmul" : seen == 4 ? ": matvec / gate_up tensor copy" : "") +
+                                    "); its output is not valid");
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream) {

@@ -327,26 +327,25 @@ struct CudaLlamaDecoder::Impl {
 
     // Maps every rank's inbox and flags into this process (CUDA IPC handles exchanged with an NCCL all-gather) for the peer-memory all-reduce of the decode
     // steps. Any failure on any rank leaves the whole group on NCCL: the ranks agree on that with one more all-reduce.
-    void setup_peer_allreduce() {
+    struct PeerHandles { cudaIpcMemHandle_t inbox, flags; };
+    static size_t peer_setup_scratch_bytes(int ranks) { return sizeof(PeerHandles) * size_t(ranks) + 256; }
+    // scratch: peer_setup_scratch_bytes(tp) of device memory, allocated by create() like every other buffer, so that no rank can leave before the
+    // collectives below: each rank takes part in both of them whether or not its own setup worked.
+    void setup_peer_allreduce(void * scratch) {
+        using Handles = PeerHandles;
         const char * env = getenv("DOOMS_TP_ALLREDUCE");
         const int E = cfg.n_embd;
         // Opt-in (DOOMS_TP_ALLREDUCE=peer): on two B200s the 8B decode step measured 2.72 ms with it against 2.60 ms with NCCL's 16 KB all-reduce plus the
         // add kernel, so NCCL stays the default until this path is faster.
         bool ok = env && std::string(env) == "peer" && tp <= cuda::kPeerMaxRanks && E % 4 == 0 && (E + 1023) / 1024 <= cuda::kPeerMaxBlocks;
-        struct Handles { cudaIpcMemHandle_t inbox, flags; };
         std::vector<Handles> all(size_t(tp), Handles{});
-        Handles * d_all = nullptr;
-        float * d_ok = nullptr;
+        Handles * d_all = static_cast<Handles *>(scratch);
+        float * d_ok = reinterpret_cast<float *>(static_cast<char *>(scratch) + sizeof(Handles) * size_t(tp));
         const size_t inbox_bytes = cuda::peer_allreduce_inbox_bytes(tp, E), flag_bytes = cuda::peer_allreduce_flag_bytes(tp);
         ok = ok && cudaMalloc(&par_inbox, inbox_bytes) == cudaSuccess && cudaMalloc(&par_flags, flag_bytes) == cudaSuccess && cudaMalloc(&par_words, 64) == cudaSuccess;
         ok = ok && cudaMemset(par_inbox, 0, inbox_bytes) == cudaSuccess && cudaMemset(par_flags, 0, flag_bytes) == cudaSuccess && cudaMemset(par_words, 0, 64) == cudaSuccess;
         ok = ok && cudaIpcGetMemHandle(&all[size_t(rank)].inbox, par_inbox) == cudaSuccess && cudaIpcGetMemHandle(&all[size_t(rank)].flags, par_flags) == cudaSuccess;
-        // the exchange itself is collective: every rank takes part whether or not its own setup worked
-        if (cudaMalloc(reinterpret_cast<void **>(&d_all), sizeof(Handles) * size_t(tp)) != cudaSuccess || cudaMalloc(reinterpret_cast<void **>(&d_ok), 4) != cudaSuccess) {
-            cudaGetLastError();
-            if (d_all) cudaFree(d_all);
-            return;      // out of device memory at this point fails the creation later anyway
-        }
+        (void)cudaGetLastError();
         cudaMemcpy(d_all + rank, &all[size_t(rank)], sizeof(Handles), cudaMemcpyHostToDevice);
         bool exchanged = nccl.AllGather(d_all + rank, d_all, sizeof(Handles), NcclApi::kInt8, comm, stream) == 0 && cudaStreamSynchronize(stream) == cudaSuccess;
         exchanged = exchanged && cudaMemcpy(all.data(), d_all, sizeof(Handles) * size_t(tp), cudaMemcpyDeviceToHost) == cudaSuccess;
@@ -370,8 +369,6 @@ struct CudaLlamaDecoder::Impl {
         if (nccl.AllReduce(d_ok, d_ok, 1, NcclApi::kFloat32, NcclApi::kSum, comm, stream) == 0 && cudaStreamSynchronize(stream) == cudaSuccess) {
             cudaMemcpy(&sum, d_ok, 4, cudaMemcpyDeviceToHost);
         }
-        cudaFree(d_all);
-        cudaFree(d_ok);
         par.round = static_cast<uint32_t *>(par_words);
         par.ticket = par.round + 1;
         par.state = state;
@@ -940,7 +937,12 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
             return resource_exhausted("could not allocate pinned host memory for the batched decode step");
         }
     }
-    if (tp > 1) m.setup_peer_allreduce();
+    if (tp > 1) {
+        void * scratch = nullptr;
+        DOOMS_RETURN_IF_ERROR(dev_alloc(&scratch, Impl::peer_setup_scratch_bytes(tp), "the exchange of the ranks' memory handles"));
+        m.setup_peer_allreduce(scratch);
+        cudaFree(scratch);
+    }
     if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
     m.tm.tp_peer_allreduce = m.use_par ? 1 : 0;
     m.tm.weight_bytes = int64_t(m.matrix_bytes);

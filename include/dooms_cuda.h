@@ -210,6 +210,11 @@ DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, cons
  * With d_w2: Y[t][r] = silu(X[t] . W[r]) * (X[t] . W2[r]). Y is f32 [tokens][rows]. flags as dooms_cuda_matvec. */
 DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const void * d_w2, const void * d_x16, float * d_y, const float * d_bias,
                                          int32_t tokens, int64_t rows, int64_t cols, uint32_t flags, void * stream);
+/* No counterpart in the reference (Metal command buffers report their own errors). The matvec / gate_up / matmul kernels above wait for their tensor copies
+ * and tensor-core stages with a limit; a wait that runs out sets a process-wide error word instead of hanging the GPU, and the kernel's output is then
+ * not valid. This call waits for `stream`, reads the word into *flag (may be NULL; 0: none, 2: matmul, 4: matvec / gate_up) and clears it; it returns
+ * DOOMS_OK when the word was 0 and DOOMS_INTERNAL otherwise. */
+DOOMS_CUDA_API int32_t dooms_cuda_kernel_status(void * stream, int32_t * flag);
 /* norm_vec (llama_kernels.h:1272-1286): xn = x * rsqrt(mean(x^2) + eps) * gamma for `rows` rows of `cols`. */
 DOOMS_CUDA_API int32_t dooms_cuda_rms_norm(const float * d_x, const float * d_gamma, float * d_out, int64_t rows, int64_t cols, float eps, void * stream);
 /* argmax (llama_kernels.h:949-975) with the host rule that NaN never wins (src/core/argmax.h:15-16): *d_out = lowest index of the maximum. */

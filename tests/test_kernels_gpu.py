@@ -203,7 +203,9 @@ def test_tensor_core_matmul_matches_the_oracle(dtype, shape, gate):
         d_y = dev(y0.copy())
         L.check(L.lib().dooms_cuda_matmul(dtype, d_w.data_ptr(), d_w2.data_ptr() if gate else None, d_x.data_ptr(), d_y.data_ptr(), d_b.data_ptr(), tokens,
                                           rows, cols, flags, None))
-        torch.cuda.synchronize()
+        flag = C.c_int32(-1)
+        L.check(L.lib().dooms_cuda_kernel_status(None, C.byref(flag)))       # waits for the stream; no bounded wait gave up
+        assert flag.value == 0
         got = d_y.cpu().numpy().astype(np.float64)
         assert np.isfinite(got).all()
         assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 2e-5, flags
