@@ -44,7 +44,7 @@ WORKLOAD_NAMES = {0: "qwen2.5-0.5b-arch q4_0, 512-token prompt + 128 greedy toke
 
 def config_dict(config: int, world: int, depth: int, matrix_bytes: int) -> dict:
     """The workload description both arms print, key for key."""
-    return {"workload": WORKLOAD_NAMES[config] + (" [all matrices f16]" if WEIGHTS == "f16" else ""), "parallelism": f"dp{world}" if config == 4 else f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
+    return {"workload": WORKLOAD_NAMES[config] + (" [all matrices f16]" if WEIGHTS == "f16" else "") + (f" [cut to {LAYERS} layers]" if LAYERS else ""), "parallelism": f"dp{world}" if config == 4 else f"tp{world}", "l2": "inputs larger than L2: a decode step streams "
             f"{matrix_bytes / 1e9:.2f} GB of weights, {matrix_bytes / 126e6:.0f}x the 126 MB L2", "queue_depth": depth}
 
 
@@ -106,6 +106,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+LAYERS = 0            # --layers N: the configuration's shape cut to its first N layers (a check of a large shape on few GPUs, not a benchmark line)
 WEIGHTS = "plan"      # --weights f16: the configuration's architecture with every matrix as f16 (the reference's default published form of its models)
 
 
@@ -120,6 +121,9 @@ def model_file(config: int, rank: int, world: int, dist) -> tuple[str, object]:
     if WEIGHTS == "f16":
         spec = dataclasses.replace(spec, plan=synth.pure(L.F16), name=spec.name + "-f16")
         tag = "_f16"
+    if LAYERS:
+        spec = dataclasses.replace(spec, n_layer=LAYERS, name=f"{spec.name}-{LAYERS}-layers")
+        tag += f"_{LAYERS}layers"
     path = os.path.join(os.environ.get("DOOMS_BENCH_DIR", tempfile.gettempdir()), f"dooms_bench_config{config}{tag}_seed{1000 + config}.gguf")
     if rank == 0 and not os.path.exists(path):
         device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -393,10 +397,12 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[0, 1, 2, 3, 4])
     ap.add_argument("--depth", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="cut the configuration's model to its first N layers (0: all)")
     ap.add_argument("--weights", default="plan", choices=["plan", "f16"], help="f16: every matrix of the configuration as f16 instead of its quantization plan")
     args = ap.parse_args()
-    global WEIGHTS
+    global WEIGHTS, LAYERS
     WEIGHTS = args.weights
+    LAYERS = max(0, args.layers)
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if os.environ.get("DOOMS_BENCH_WATCHDOG"):      # dump every thread's stack and exit if the run is still going after this many seconds
         import faulthandler

@@ -3,6 +3,7 @@
     python bench_kernels.py gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
     python bench_kernels.py gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
     python bench_kernels.py attention [--config 2 --layers 2 --prompt 2048 --steps 8]  prefill and decode attention inside a decoder cut to a few layers
+    python bench_kernels.py batch [--config 0 --sequences 256 --steps 8]           a batched decode step over many sequences of mixed lengths
     python bench_kernels.py launches <ncu csv>                                     per-kernel totals and shares of an ncu launch list
 
 The GEMV case walks over several distinct matrices so that every launch reads its weights from device memory, not from L2.
@@ -23,7 +24,7 @@ def _gemv(args):
     from dooms_b200.quantize import quantize
     lib = L.lib()
     gen = torch.Generator(device='cuda').manual_seed(1)
-    dt = L.DTYPE_NAMES.index(args.dtype)
+    dt = L.DTYPE_NAMES.index(args.dtype.lower())
     mats = []
     for _ in range(args.mats):
         g = quantize(dt, torch.randn(args.rows, args.cols, device='cuda', generator=gen) * 0.02)
@@ -69,7 +70,7 @@ def _gemm(args):
     from dooms_b200.quantize import quantize
     lib = L.lib()
     gen = torch.Generator(device='cuda').manual_seed(1)
-    dt = L.DTYPE_NAMES.index(args.dtype)
+    dt = L.DTYPE_NAMES.index(args.dtype.lower())
     M, N, K = args.tokens, args.rows, args.cols
     w = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02)
     w2 = quantize(dt, torch.randn(N, K, device='cuda', generator=gen) * 0.02) if args.gate else None
@@ -143,6 +144,41 @@ def _attention(args):
     os.remove(path)
 
 
+def _batch(args):
+    """The serving load's decode step: `sequences` slots filled with prompts of U[32, 4096] tokens, then a few batched greedy steps. The steps sit inside
+    cudaProfilerStart / Stop, so that a profiler run with --profile-from-start off sees only them."""
+    import os
+    import tempfile
+    import numpy as np
+    import torch
+    from dooms_b200 import CudaLlamaDecoder, synth
+    spec = synth.config_spec(args.config)
+    path = os.path.join(os.environ.get('DOOMS_BENCH_DIR', tempfile.gettempdir()), f'dooms_bench_config{args.config}_seed{1000 + args.config}.gguf')
+    if not os.path.exists(path):
+        synth.write_model(spec, path + '.part', 1000 + args.config, device='cuda')
+        os.replace(path + '.part', path)
+    g = np.random.Generator(np.random.PCG64(9))
+    lengths = g.integers(32, 4097, args.sequences)
+    dec = CudaLlamaDecoder.load(path, 4096 + args.steps * (args.reps + 1) + 8, 2048, max_sequences=args.sequences)
+    for s, n in enumerate(lengths):
+        dec.select_sequence(s)
+        dec.eval_tokens([int(t) for t in synth.prompt_tokens(int(n), spec.n_vocab, 100 + s)])
+    slots = list(range(args.sequences))
+    dec.decode_batch(slots, args.steps)                       # captures the graph
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(args.reps):
+        out = dec.decode_batch(slots, args.steps)
+        t = dec.timings()
+        kv = 2 * 2 * spec.n_layer * spec.n_head_kv * spec.head_dim * float(lengths.sum())
+        print(f'{t["last_batch_ms"] / args.steps * 1e3:.0f} us per step of {args.sequences} rows, {t["last_batch_launches"] // args.steps} launches; '
+              f'{kv / 1e9:.2f} GB of keys and values per step: {kv / (t["last_batch_ms"] / args.steps * 1e-3) / 1e9:.0f} GB/s')
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print('tokens of the last step', out[-1][:8])
+    dec.close()
+
+
 def summarize_launches(path, out=sys.stdout):
     """Totals per kernel of an `ncu --metrics gpu__time_duration.sum --csv` launch list."""
     header, agg = None, collections.OrderedDict()
@@ -193,6 +229,11 @@ def main(argv=None):
     t.add_argument('--prompt', type=int, default=2048)
     t.add_argument('--steps', type=int, default=8)
     t.add_argument('--reps', type=int, default=2)
+    b = sub.add_parser('batch')
+    b.add_argument('--config', type=int, default=0)
+    b.add_argument('--sequences', type=int, default=256)
+    b.add_argument('--steps', type=int, default=8)
+    b.add_argument('--reps', type=int, default=2)
     l = sub.add_parser('launches')
     l.add_argument('csv')
     args = ap.parse_args(argv)
@@ -202,6 +243,8 @@ def main(argv=None):
         _gemm(args)
     elif args.case == 'attention':
         _attention(args)
+    elif args.case == 'batch':
+        _batch(args)
     else:
         summarize_launches(args.csv)
 

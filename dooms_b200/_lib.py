@@ -89,7 +89,8 @@ class GgufTensor(C.Structure):
 
 
 class TpShare(C.Structure):
-    _fields_ = [("struct_size", C.c_size_t)] + [(n, C.c_int64) for n in ("q_row0", "q_rows", "kv_row0", "kv_rows", "ff_row0", "ff_rows", "vocab_row0", "vocab_rows")]
+    _fields_ = [("struct_size", C.c_size_t)] + [(n, C.c_int64) for n in ("q_row0", "q_rows", "kv_row0", "kv_rows", "ff_row0", "ff_rows", "vocab_row0", "vocab_rows",
+                                                                      "attn_col0", "attn_cols")]
 
 
 TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int32, C.c_int32, C.c_void_p)
@@ -165,6 +166,7 @@ SIGNATURES = {
     "dooms_cuda_attention_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "dooms_cuda_attention_decode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "dooms_cuda_tp_share": (C.c_int32, [C.POINTER(LlamaConfig), C.c_int32, C.c_int32, C.POINTER(TpShare)]),
+    "dooms_cuda_tp_share_blocks": (C.c_int32, [C.POINTER(LlamaConfig), C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(TpShare)]),
     "dooms_cuda_nccl_unique_id": (C.c_int32, [C.c_char_p, C.c_void_p]),
 }
 

@@ -730,17 +730,23 @@ DOOMS_CUDA_API int32_t dooms_cuda_attention_decode(const float * d_q, const void
                                                        static_cast<cudaStream_t>(stream)), "attention_decode");
 }
 
-DOOMS_CUDA_API int32_t dooms_cuda_tp_share(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, dooms_tp_share * out) {
+DOOMS_CUDA_API int32_t dooms_cuda_tp_share_blocks(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, int64_t attn_block, int64_t ffn_block,
+                                                  dooms_tp_share * out) {
     int32_t code = DOOMS_OK;
     if (!struct_ok(config, "config", &code) || !struct_ok(out, "out", &code)) return code;
     LlamaDecoderConfig c;
     c.n_head = config->n_head; c.n_head_kv = config->n_head_kv; c.head_dim = config->head_dim; c.n_ff = config->n_ff; c.n_vocab = config->n_vocab;
-    auto r = tp_share(c, tp_rank, tp_size);
+    auto r = tp_share(c, tp_rank, tp_size, attn_block, ffn_block);
     if (!r.is_ok()) return done(r.status());
     const TpShare & s = r.value();
     out->q_row0 = s.q_row0; out->q_rows = s.q_rows; out->kv_row0 = s.kv_row0; out->kv_rows = s.kv_rows; out->ff_row0 = s.ff_row0; out->ff_rows = s.ff_rows;
     out->vocab_row0 = s.vocab_row0; out->vocab_rows = s.vocab_rows;
+    if (out->struct_size >= offsetof(dooms_tp_share, attn_cols) + sizeof(int64_t)) { out->attn_col0 = s.attn_col0; out->attn_cols = s.attn_cols; }
     return DOOMS_OK;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_tp_share(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, dooms_tp_share * out) {
+    return dooms_cuda_tp_share_blocks(config, tp_rank, tp_size, 1, 1, out);
 }
 
 DOOMS_CUDA_API int32_t dooms_cuda_nccl_unique_id(const char * nccl_library, void * out128) {

@@ -60,6 +60,9 @@ struct CudaLlamaDecoder::Impl {
     CudaOptions opt;
     int tp = 1, rank = 0;
     // this rank's share
+    // attn_width / attn_pad: the attention rows are as wide as the blocks of attn_output this rank holds; its heads' columns start attn_pad into a row and
+    // the rest stays zero (one GPU, or shards on block boundaries: attn_width = q_width, attn_pad = 0)
+    int32_t attn_width = 0, attn_pad = 0;
     int32_t nh = 0, nkv = 0, q_width = 0, kv_width = 0, qkv_width = 0, ff = 0, vocab_rows = 0, vocab_row0 = 0, vocab_stride = 0;
     cudaStream_t stream = nullptr;
     uint8_t * weights = nullptr;
@@ -207,7 +210,7 @@ struct CudaLlamaDecoder::Impl {
     }
 
     AttnShape attn_shape() const {
-        return AttnShape{nh, nkv, cfg.head_dim, qkv_width, kv_width, q_width, cfg.rope_neox ? 1 : 0, cfg.rope_base};
+        return AttnShape{nh, nkv, cfg.head_dim, qkv_width, kv_width, attn_width, cfg.rope_neox ? 1 : 0, cfg.rope_base};
     }
 
     void all_reduce(float * buf, size_t count) {
@@ -296,9 +299,9 @@ struct CudaLlamaDecoder::Impl {
     // otherwise, or when prefill_tile = 1 asks for the plain kernels.
     void prefill_attention(__half * kcl, __half * vcl, __half * out16, int M, const AttnShape & as) {
         if (cfg.prefill_tile != 1 && cuda::attention_flash_supported(as)) {
-            run("attention", [&] { return cuda::launch_attention_flash(qkv, kcl, vcl, attn, out16, state, M, as, stream); });
+            run("attention", [&] { return cuda::launch_attention_flash(qkv, kcl, vcl, attn + attn_pad, out16 ? out16 + attn_pad : nullptr, state, M, as, stream); });
         } else {
-            run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn, out16, state, M, as, stream); });
+            run("attention", [&] { return cuda::launch_attention_prefill(qkv, kcl, vcl, attn + attn_pad, out16 ? out16 + attn_pad : nullptr, state, M, as, stream); });
         }
     }
     // Y[m][row0 + n] (+)= X16[m] . W[n] on the tensor cores; X16 is the f16 activation buffer behind map.
@@ -447,14 +450,15 @@ struct CudaLlamaDecoder::Impl {
                 for (const QkvPart & q : L.qkv) {
                     matvec("qkv", q.w, x, L.attn_norm, qkv + q.row0, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, L.qkv_bias ? kFlagBias : 0u);
                 }
-                const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1);
+                // (a padded attention row is split by the projection itself: its zero columns are not the attention kernel's to write)
+                const bool split_attn = fast(L.attn_output) && cfg.head_dim % 32 == 0 && (gqa || splits > 1) && attn_width == q_width;
                 if (gqa) {
                     run("attention", [&] {
-                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn, split_attn ? xq : nullptr, stream, rope_cs);
+                        return cuda::launch_attention_gqa(qkv, kcl, vcl, part, state, inv_freq, 0, gqa_splits, as, attn_counters, attn + attn_pad, split_attn ? xq : nullptr, stream, rope_cs);
                     });
                 } else {
                     run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, 1, as, stream); });
-                    run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
+                    run("attention", [&] { return cuda::launch_attention_decode(qkv, kcl, vcl, attn + attn_pad, part, split_attn ? xq : nullptr, state, 0, splits, as, stream); });
                 }
                 xq_of = split_attn ? attn : nullptr;
                 // the projections that finish x also prepare the norm of the projection after them, when that one is a kernel that can take it
@@ -491,7 +495,7 @@ struct CudaLlamaDecoder::Impl {
                 }
                 run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, M, as, stream); });
                 prefill_attention(kcl, vcl, nullptr, M, as);
-                matmul("attn_output", L.attn_output, nullptr, attn, q_width, o_dst, E, nullptr, M, o_flags);
+                matmul("attn_output", L.attn_output, nullptr, attn, attn_width, o_dst, E, nullptr, M, o_flags);
                 reduce_into_x(M);
                 norm(x, L.ffn_norm, M, false);
                 matmul("gate_up", L.ffn_gate, &L.ffn_up, xn, E, h, ff, nullptr, M, 0u);
@@ -632,18 +636,27 @@ namespace cuda {
 cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream);
 }
 
-Result<TpShare> tp_share(const LlamaDecoderConfig & c, int32_t rank, int32_t tp) {
+Result<TpShare> tp_share(const LlamaDecoderConfig & c, int32_t rank, int32_t tp, int64_t attn_block, int64_t ffn_block) {
     if (tp < 1 || rank < 0 || rank >= tp) return invalid_argument("tp_rank must be in [0, tp_size)");
-    if (c.n_head < 1 || c.n_head_kv < 1 || c.n_head % tp != 0 || c.n_head_kv % tp != 0 || c.n_ff % tp != 0) {
-        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs needs n_head, n_head_kv and n_ff to be multiples of it");
+    if (attn_block < 1 || ffn_block < 1) return invalid_argument("block sizes must be at least 1");
+    if (c.n_head < 1 || c.n_head_kv < 1 || c.n_head % tp != 0 || c.n_head_kv % tp != 0) {
+        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs needs n_head and n_head_kv to be multiples of it");
+    }
+    const int64_t q_width = int64_t(c.n_head) * c.head_dim;
+    if (c.n_ff % ffn_block != 0 || c.n_ff / ffn_block < tp || q_width % attn_block != 0) {
+        return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs: n_ff has to be at least that many whole blocks of " + std::to_string(ffn_block) +
+                           " columns, and the attention width whole blocks of " + std::to_string(attn_block));
     }
     TpShare s;
     s.q_rows = int64_t(c.n_head / tp) * c.head_dim;
     s.q_row0 = s.q_rows * rank;
     s.kv_rows = int64_t(c.n_head_kv / tp) * c.head_dim;
     s.kv_row0 = s.kv_rows * rank;
-    s.ff_rows = c.n_ff / tp;
-    s.ff_row0 = s.ff_rows * rank;
+    const int64_t units = c.n_ff / ffn_block, each = units / tp, more = units % tp;
+    s.ff_row0 = (each * rank + std::min<int64_t>(rank, more)) * ffn_block;
+    s.ff_rows = (each + (rank < more ? 1 : 0)) * ffn_block;
+    s.attn_col0 = s.q_row0 / attn_block * attn_block;
+    s.attn_cols = (s.q_row0 + s.q_rows + attn_block - 1) / attn_block * attn_block - s.attn_col0;
     const int64_t stride = (int64_t(c.n_vocab) + tp - 1) / tp;
     s.vocab_row0 = stride * rank;
     s.vocab_rows = std::max<int64_t>(0, std::min<int64_t>(stride, int64_t(c.n_vocab) - s.vocab_row0));
@@ -662,15 +675,17 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     if (opt.tp_size < 1 || opt.tp_rank < 0 || opt.tp_rank >= opt.tp_size) return invalid_argument("CUDA options: tp_rank has to lie in [0, tp_size)");
     const int64_t E = c.n_embd, F = c.n_ff, V = c.n_vocab, Qw = int64_t(c.n_head) * c.head_dim, KVw = int64_t(c.n_head_kv) * c.head_dim;
 
-    // This rank's share under tensor parallelism: whole heads, and column shards that are whole blocks.
+    // This rank's share under tensor parallelism: whole heads, and column shards that are whole blocks of the coarsest format any layer uses.
     const int tp = opt.tp_size;
-    const Result<TpShare> share = tp_share(c, opt.tp_rank, tp);
-    if (!share.is_ok()) return share.status();
+    int64_t attn_block = 1, ffn_block = 1;
     for (const LlamaLayerWeights & L : w.layers) {
-        if ((Qw / tp) % dtype_block_elems(L.attn_output.dtype) != 0 || (F / tp) % dtype_block_elems(L.ffn_down.dtype) != 0) {
-            return unsupported("tensor parallelism over " + std::to_string(tp) + " GPUs would cut attn_output or ffn_down inside a quantization block");
-        }
+        attn_block = std::max<int64_t>(attn_block, dtype_block_elems(L.attn_output.dtype));
+        ffn_block = std::max<int64_t>(ffn_block, dtype_block_elems(L.ffn_down.dtype));
     }
+    const Result<TpShare> share = tp == 1 ? tp_share(c, 0, 1) : tp_share(c, opt.tp_rank, tp, attn_block, ffn_block);
+    if (!share.is_ok()) return share.status();
+    const int64_t attn_pad = share.value().q_row0 - share.value().attn_col0;
+    if (attn_pad % 8 != 0) return unsupported("tensor parallelism: a rank's heads start " + std::to_string(attn_pad) + " columns into a block of attn_output; multiples of 8 are taken");
 
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) { (void)cudaGetLastError(); return unsupported("no CUDA device"); }
@@ -692,6 +707,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.kv_width = m.nkv * c.head_dim;
     m.qkv_width = m.q_width + 2 * m.kv_width;
     m.ff = int32_t(share.value().ff_rows);
+    m.attn_width = int32_t(share.value().attn_cols);
+    m.attn_pad = int32_t(attn_pad);
     m.vocab_stride = int32_t((V + tp - 1) / tp);
     m.vocab_row0 = int32_t(share.value().vocab_row0);
     m.vocab_rows = int32_t(share.value().vocab_rows);
@@ -775,11 +792,11 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         } else if (L.attn_q_bias.data) {
             plan_vec({cols_of(L.attn_q_bias, q0, ql), cols_of(L.attn_k_bias, kv0, kvl), cols_of(L.attn_v_bias, kv0, kvl)}, &o.qkv_bias);
         }
-        plan_mat({cols_of(L.attn_output, q0, ql)}, &o.attn_output);
+        plan_mat({cols_of(L.attn_output, share.value().attn_col0, m.attn_width)}, &o.attn_output);
         plan_vec({whole(L.ffn_norm)}, &o.ffn_norm);
-        plan_mat({rows_of(L.ffn_gate, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_gate);
-        plan_mat({rows_of(L.ffn_up, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_up);
-        plan_mat({cols_of(L.ffn_down, int64_t(m.rank) * m.ff, m.ff)}, &o.ffn_down);
+        plan_mat({rows_of(L.ffn_gate, share.value().ff_row0, m.ff)}, &o.ffn_gate);
+        plan_mat({rows_of(L.ffn_up, share.value().ff_row0, m.ff)}, &o.ffn_up);
+        plan_mat({cols_of(L.ffn_down, share.value().ff_row0, m.ff)}, &o.ffn_down);
     }
     total += kWeightTail;
     m.weight_bytes = total;
@@ -852,7 +869,8 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.x), B * size_t(E) * 4, "the residual rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xn), B * size_t(E) * 4, "the normalized rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.qkv), B * size_t(m.qkv_width) * 4, "the q/k/v rows"));
-    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn), B * size_t(m.q_width) * 4, "the attention rows"));
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn), B * size_t(m.attn_width) * 4, "the attention rows"));
+    cudaMemset(m.attn, 0, B * size_t(m.attn_width) * 4);
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h), B * size_t(m.ff) * 4, "the feed-forward rows"));
     if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
@@ -873,14 +891,15 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.norm_ss), 4096 * sizeof(float), "the sums of squares of the residual row"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.norm_counters), (size_t(E) / 32 + 1) * sizeof(int), "the residual split counters"));
     cudaMemset(m.norm_counters, 0, (size_t(E) / 32 + 1) * sizeof(int));
-    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.q_width)})) + 64,
+    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xq), cuda::quantized_x_bytes(std::max<int64_t>({E, int64_t(m.ff), int64_t(m.attn_width)})) + 64,
                                     "the split projection input"));
-    if (E % 64 == 0 && m.q_width % 64 == 0 && m.ff % 64 == 0) {
+    if (E % 64 == 0 && m.attn_width % 64 == 0 && m.ff % 64 == 0) {
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xn16), B * size_t(E) * 2, "the f16 normalized rows"));
-        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn16), B * size_t(m.q_width) * 2, "the f16 attention rows"));
+        DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn16), B * size_t(m.attn_width) * 2, "the f16 attention rows"));
+        cudaMemset(m.attn16, 0, B * size_t(m.attn_width) * 2);
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h16), B * size_t(m.ff) * 2, "the f16 feed-forward rows"));
         m.tc_capable = cuda::make_activation_map(&m.map_xn, m.xn16, int64_t(B), E) == cudaSuccess &&
-                       cuda::make_activation_map(&m.map_attn, m.attn16, int64_t(B), m.q_width) == cudaSuccess &&
+                       cuda::make_activation_map(&m.map_attn, m.attn16, int64_t(B), m.attn_width) == cudaSuccess &&
                        cuda::make_activation_map(&m.map_h, m.h16, int64_t(B), m.ff) == cudaSuccess;
         size_t largest = 0;
         for (const LayerDev & L : m.layers) {

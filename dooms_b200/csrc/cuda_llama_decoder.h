@@ -56,9 +56,17 @@ struct CudaOptions {
 };
 
 // A rank's share of the model under tensor parallelism: whole heads, a slice of the feed-forward width, a slice of the vocabulary.
-struct TpShare { int64_t q_row0 = 0, q_rows = 0, kv_row0 = 0, kv_rows = 0, ff_row0 = 0, ff_rows = 0, vocab_row0 = 0, vocab_rows = 0; };
-//   InvalidArgument  tp_rank outside [0, tp_size)     Unsupported  n_head, n_head_kv or n_ff is not a multiple of tp_size
-Result<TpShare> tp_share(const LlamaDecoderConfig & config, int32_t tp_rank, int32_t tp_size);
+// Column shards have to be whole quantization blocks. The feed-forward width is therefore dealt in units of ffn_block columns, the first n_ff / ffn_block %
+// tp_size ranks taking one unit more. The columns of attn_output follow the heads, which no choice can move; where a rank's columns [q_row0, q_row0 +
+// q_rows) start or end inside a block, the rank holds the blocks that cover them, [attn_col0, attn_col0 + attn_cols), and multiplies them with an input
+// that is zero outside its own columns: a block on the boundary is held by both neighbours, each using its own part of it.
+struct TpShare {
+    int64_t q_row0 = 0, q_rows = 0, kv_row0 = 0, kv_rows = 0, ff_row0 = 0, ff_rows = 0, vocab_row0 = 0, vocab_rows = 0;
+    int64_t attn_col0 = 0, attn_cols = 0;
+};
+//   InvalidArgument  tp_rank outside [0, tp_size), a block size < 1
+//   Unsupported  n_head or n_head_kv is not a multiple of tp_size, n_ff or the attention width is not whole blocks, fewer feed-forward units than ranks
+Result<TpShare> tp_share(const LlamaDecoderConfig & config, int32_t tp_rank, int32_t tp_size, int64_t attn_block = 1, int64_t ffn_block = 1);
 
 class CudaLlamaDecoder {
 public:

@@ -305,12 +305,19 @@ DOOMS_CUDA_API int32_t dooms_cuda_sample(const float * logits, int32_t n, const 
 /* This rank's share of the model under tensor parallelism (no counterpart in the reference): rows [q_row0, q_row0 + q_rows) of attn_q and the same
  * columns of attn_output, rows [kv_row0, ..) of attn_k / attn_v (whole heads; the KV cache holds only these heads), rows [ff_row0, ..) of ffn_gate /
  * ffn_up and the same columns of ffn_down, rows [vocab_row0, ..) of the output matrix. The partial sums of attn_output and ffn_down are all-reduced.
- * Host only. DOOMS_UNSUPPORTED when the heads or n_ff do not divide by tp_size. */
+ * Column shards are whole quantization blocks: the feed-forward width is dealt in units of ffn_block columns (the first n_ff / ffn_block % tp_size ranks
+ * take one unit more), and of attn_output a rank holds the blocks [attn_col0, attn_col0 + attn_cols) that cover its heads' columns, multiplied with an
+ * input that is zero outside them (a block on a boundary is held by both neighbours). dooms_cuda_tp_share is the case of both block sizes 1; a decoder
+ * uses the largest block size among its layers' attn_output and ffn_down types (dooms_dtype_block_elems).
+ * Host only. DOOMS_UNSUPPORTED when the heads do not divide by tp_size, or n_ff is not at least tp_size whole blocks. */
 typedef struct dooms_tp_share {
     size_t struct_size;
     int64_t q_row0, q_rows, kv_row0, kv_rows, ff_row0, ff_rows, vocab_row0, vocab_rows;
+    int64_t attn_col0, attn_cols;      /* written when struct_size covers them */
 } dooms_tp_share;
 DOOMS_CUDA_API int32_t dooms_cuda_tp_share(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, dooms_tp_share * out);
+DOOMS_CUDA_API int32_t dooms_cuda_tp_share_blocks(const dooms_llama_config * config, int32_t tp_rank, int32_t tp_size, int64_t attn_block, int64_t ffn_block,
+                                                  dooms_tp_share * out);
 
 /* Tensor-parallel set-up helper: fills 128 bytes with a fresh ncclUniqueId (rank 0 calls it and sends the bytes to the other ranks). */
 DOOMS_CUDA_API int32_t dooms_cuda_nccl_unique_id(const char * nccl_library, void * out128);

@@ -15,10 +15,10 @@ from dooms_b200 import _lib as L
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def share(cfg, rank, tp):
+def share(cfg, rank, tp, attn_block=1, ffn_block=1):
     s = L.TpShare()
     s.struct_size = C.sizeof(L.TpShare)
-    L.check(L.lib().dooms_cuda_tp_share(C.byref(cfg), rank, tp, C.byref(s)))
+    L.check(L.lib().dooms_cuda_tp_share_blocks(C.byref(cfg), rank, tp, attn_block, ffn_block, C.byref(s)))
     return s
 
 
@@ -48,6 +48,42 @@ def test_shares_partition_the_model():
     s.struct_size = C.sizeof(L.TpShare)
     assert lib.dooms_cuda_tp_share(C.byref(config()), 0, 3, C.byref(s)) == L.UNSUPPORTED          # 8 heads over 3 GPUs
     assert lib.dooms_cuda_tp_share(C.byref(config()), 2, 2, C.byref(s)) == L.INVALID_ARGUMENT
+
+
+def test_column_shards_are_whole_blocks_where_the_heads_are_not():
+    """The 32B shape over 8 GPUs (40 / 8 heads of 128, n_ff 27648, 256-element super-blocks): 640 attention columns per rank are two and a half
+    super-blocks, 3456 feed-forward columns thirteen and a half. The feed-forward width is dealt in whole blocks (14 or 13 per rank); of attn_output every
+    rank holds the three blocks that cover its heads and multiplies them with its attention row padded with zeros, and the ranks' sums add up to the
+    unsharded product. Also a small shape over two ranks."""
+    g = np.random.default_rng(3)
+    for (nh, nkv, hd, ff, tp, blk) in ((40, 8, 128, 27648, 8, 256), (10, 2, 128, 1792, 2, 256), (8, 4, 16, 160, 4, 32), (6, 2, 16, 160, 2, 32)):
+        cfg = config(n_head=nh, n_head_kv=nkv, head_dim=hd, n_ff=ff)
+        qw = nh * hd
+        shares = [share(cfg, r, tp, blk, blk) for r in range(tp)]
+        # feed-forward: whole blocks, consecutive, complete, sizes differing by at most one block
+        assert [s.ff_row0 for s in shares] == [sum(t.ff_rows for t in shares[:r]) for r in range(tp)] and sum(s.ff_rows for s in shares) == ff
+        assert all(s.ff_rows % blk == 0 and s.ff_row0 % blk == 0 for s in shares)
+        assert max(s.ff_rows for s in shares) - min(s.ff_rows for s in shares) <= blk
+        # attention: the cover is whole blocks inside the matrix and contains the rank's heads
+        att = g.standard_normal(qw)
+        wo = g.standard_normal((7, qw))
+        total = np.zeros(7)
+        for s in shares:
+            assert s.attn_col0 % blk == 0 and s.attn_cols % blk == 0 and s.attn_col0 + s.attn_cols <= qw
+            assert s.attn_col0 <= s.q_row0 and s.q_row0 + s.q_rows <= s.attn_col0 + s.attn_cols
+            assert s.attn_cols < s.q_rows + 2 * blk
+            padded = np.zeros(s.attn_cols)
+            padded[s.q_row0 - s.attn_col0:s.q_row0 - s.attn_col0 + s.q_rows] = att[s.q_row0:s.q_row0 + s.q_rows]
+            total += wo[:, s.attn_col0:s.attn_col0 + s.attn_cols] @ padded
+        assert np.allclose(total, wo @ att, rtol=1e-12, atol=1e-12)
+    s32 = [share(config(n_head=40, n_head_kv=8, head_dim=128, n_ff=27648), r, 8, 256, 256) for r in range(8)]
+    assert [s.ff_rows // 256 for s in s32] == [14, 14, 14, 14, 13, 13, 13, 13] and all(s.attn_cols == 768 for s in s32)
+    lib = L.lib()
+    s = L.TpShare()
+    s.struct_size = C.sizeof(L.TpShare)
+    assert lib.dooms_cuda_tp_share_blocks(C.byref(config(n_ff=96)), 0, 4, 32, 32, C.byref(s)) == L.UNSUPPORTED      # three blocks of 32 for four ranks
+    assert lib.dooms_cuda_tp_share_blocks(C.byref(config(n_ff=100)), 0, 2, 32, 32, C.byref(s)) == L.UNSUPPORTED     # not whole blocks
+    assert lib.dooms_cuda_tp_share_blocks(C.byref(config()), 0, 2, 0, 32, C.byref(s)) == L.INVALID_ARGUMENT
 
 
 GLOO_CHILD = r"""
@@ -129,7 +165,11 @@ from dooms_b200.decoder import nccl_unique_id
 rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
 torch.cuda.set_device(local)
 dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-spec = synth.tiny_spec(synth.pure(L.Q4_0), arch="qwen2", n_embd=512, n_head=8, n_head_kv=4, n_ff=2048, n_vocab=1001, n_layer=3)
+if os.environ.get("DOOMS_TP_CASE") == "cover":
+    # 640 attention columns and 3.5 feed-forward super-blocks per rank: column shards that do not fall on the 256-element blocks of q4_K / q6_K
+    spec = synth.tiny_spec(synth.q4_k_m_large, arch="qwen2", n_embd=1280, n_head=10, n_head_kv=2, n_ff=1792, n_vocab=1001, n_layer=3)
+else:
+    spec = synth.tiny_spec(synth.pure(L.Q4_0), arch="qwen2", n_embd=512, n_head=8, n_head_kv=4, n_ff=2048, n_vocab=1001, n_layer=3)
 path = os.environ["DOOMS_TP_MODEL"]
 if rank == 0: synth.write_model(spec, path, 5)
 dist.barrier()
@@ -159,16 +199,18 @@ dist.destroy_process_group()
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("allreduce", ["nccl", "peer"])
-def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, allreduce):
-    """Two ranks against one GPU: last-position logits and greedy tokens; with NCCL's all-reduce and with the peer-memory all-reduce + add kernel."""
+@pytest.mark.parametrize("allreduce,case", [("nccl", "even"), ("peer", "even"), ("nccl", "cover")])
+def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, allreduce, case):
+    """Two ranks against one GPU: last-position logits and greedy tokens; with NCCL's all-reduce and with the peer-memory all-reduce + add kernel; and
+    on a model whose column shards do not fall on block boundaries (every rank holds the covering blocks of attn_output, the feed-forward width is dealt
+    in whole blocks)."""
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "child.py"
     script.write_text(NCCL_CHILD)
-    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0", DOOMS_TP_ALLREDUCE=allreduce)
+    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0", DOOMS_TP_ALLREDUCE=allreduce, DOOMS_TP_CASE=case)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                         "29534", str(script)], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
