@@ -66,7 +66,8 @@ bool attention_gqa_supported(const AttnShape & s) {
 
 int attention_gqa_splits(int n_head_kv, int n_ctx) {
     // about one block per SM, and no more ranges than the context has tiles
-    const int want = std::max(1, (sm_count() + n_head_kv - 1) / n_head_kv);
+    static const int per_sm = [] { const char * e = getenv("DOOMS_GQA_PER_SM"); return e ? std::max(1, atoi(e)) : 1; }();
+    const int want = std::max(1, (sm_count() * per_sm + n_head_kv - 1) / n_head_kv);
     return std::max(1, std::min(want, (n_ctx + kTileKeys - 1) / kTileKeys));
 }
 

@@ -389,6 +389,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 if (m0 + c0 >= p.M) break;      // warp-uniform
                 uint32_t acc[32], acc2[32];
                 const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0);
+                // what the results are added to: all 32 loads of a lane are asked for before the first is used (one after another, each behind the store
+                // before it, they cost a memory latency apiece: 4 x 32 of them per tile)
+                float old[32];
+                const bool adds = p.Y && (p.flags & kFlagAccumulate) && n < p.N;
+                #pragma unroll
+                for (int j = 0; j < 32; j++) old[j] = (adds && m0 + c0 + j < p.M) ? __ldcg(p.Y + int64_t(m0 + c0 + j) * p.y_stride + n) : 0.f;
                 tc_ld32(taddr, acc);
                 if (GATE) tc_ld32(taddr + 256u, acc2);
                 if (n < p.N) {
@@ -399,10 +405,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                         float v = __uint_as_float(acc[j]);
                         if (GATE) v = v / (1.f + expf(-v)) * __uint_as_float(acc2[j]);
                         else v += bias;
-                        if (p.Y) {
-                            float * y = p.Y + int64_t(m) * p.y_stride + n;
-                            *y = (p.flags & kFlagAccumulate) ? *y + v : v;
-                        }
+                        v += old[j];
+                        if (p.Y) p.Y[int64_t(m) * p.y_stride + n] = v;
                         if (p.Y16) p.Y16[int64_t(m) * p.y16_stride + n] = __float2half_rn(v);
                     }
                 }
