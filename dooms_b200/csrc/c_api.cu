@@ -633,8 +633,8 @@ DOOMS_CUDA_API int32_t dooms_cuda_matmul(int32_t dtype, const void * d_w, const 
         ((flags & cuda::kFlagBias) && !d_bias) || (flags & ~(cuda::kFlagAccumulate | cuda::kFlagBias)) || (d_w2 && flags)) {
         return fail(DOOMS_INVALID_ARGUMENT, "matmul: NULL pointer, unknown flag, or rows that are not whole blocks and a multiple of 64 elements");
     }
-    // 512 tokens or more: room for the matrix (both, for gate/up) as f16 rows, so that it is dequantized once and both operands arrive by TMA
-    const size_t w16_bytes = tokens >= 512 && dtype != DOOMS_F16 ? size_t(rows) * size_t(cols) * 2 * (d_w2 ? 2 : 1) : 0;
+    // 128 tokens or more: room for the matrix (both, for gate/up) as f16 rows, so that it is dequantized once and both operands arrive by TMA
+    const size_t w16_bytes = tokens >= 128 && dtype != DOOMS_F16 ? size_t(rows) * size_t(cols) * 2 * (d_w2 ? 2 : 1) : 0;
     void * scratch = nullptr;
     const Status ss = scratch_for(256 + w16_bytes, &scratch);
     if (!ss.is_ok()) return done(ss);

@@ -104,12 +104,13 @@ struct CudaLlamaDecoder::Impl {
     int32_t * tp_pairs = nullptr;  // tensor parallelism: every rank's (best logit, its index) of the current position
     bool logits_gathered = true;   // logits_buf holds every rank's rows (always true on one GPU)
     int splits = 1;
+    bool rows_tc = false;        // batched decode steps: attention on the tensor cores (attention_rows.cu)
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
     int gqa_splits = 1;
     double * inv_freq = nullptr;   // head_dim / 2 rotary frequencies
     void * rope_cs = nullptr;      // head_dim / 2 (cos, sin) pairs of the current decode step's position
     int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
-    void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 512 tokens or more dequantize a matrix once per call
+    void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 128 tokens or more dequantize a matrix once per call
     size_t w16_bytes = 0;
     int * split_counters = nullptr; // one per 32 rows of h: rows written by the gate/up GEMV's blocks (zero between launches)
     // The norm between two projections of a decode step, folded into the producer (kernels.h, GemvNormLink): the projection that finishes the residual row
@@ -576,6 +577,10 @@ struct CudaLlamaDecoder::Impl {
                 gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, n, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
             }
             run("attention", [&] {
+                if (rows_tc) {
+                    return cuda::launch_attention_rows_tc(qkv, kc + l * cache_layer_elems, vc + l * cache_layer_elems, b_part, inv_freq, b_splits, cfg.n_ctx, as, b_counters,
+                                                          attn, attn16, rows, n, stream);
+                }
                 return cuda::launch_attention_gqa_rows(qkv, kc + l * cache_layer_elems, vc + l * cache_layer_elems, b_part, inv_freq, b_splits, as, b_counters, attn, attn16,
                                                        rows, n, stream);
             });
@@ -861,6 +866,10 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     m.kv_bytes = 2 * size_t(c.n_layer) * m.cache_layer_elems * sizeof(__half);
     m.splits = cuda::attention_splits(m.nh, c.n_ctx);
     m.gqa = cuda::attention_gqa_supported(m.attn_shape());
+    {
+        const char * e = getenv("DOOMS_ROWS_TC");
+        m.rows_tc = cuda::attention_rows_tc_supported(m.attn_shape()) && !(e && *e == '0');
+    }
     m.gqa_splits = cuda::attention_gqa_splits(m.nkv, c.n_ctx);
     const size_t part_floats = size_t(std::max(m.splits, m.gqa_splits)) * size_t(m.nh) * size_t(2 + c.head_dim);
     const size_t logits_floats = size_t(m.vocab_stride) * size_t(tp);
@@ -907,7 +916,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
             largest = std::max({largest, size_t(L.attn_output.rows) * size_t(L.attn_output.cols) * 2, size_t(L.ffn_down.rows) * size_t(L.ffn_down.cols) * 2,
                                 size_t(L.ffn_gate.rows) * size_t(L.ffn_gate.cols) * 4});
         }
-        if (B >= 512 && largest > 0 && cudaMalloc(&m.w16, largest) == cudaSuccess) m.w16_bytes = largest;      // optional: without it the GEMM dequantizes per tile
+        if (B >= 128 && largest > 0 && cudaMalloc(&m.w16, largest) == cudaSuccess) m.w16_bytes = largest;      // optional: without it the GEMM dequantizes per tile
         else { (void)cudaGetLastError(); m.w16 = nullptr; }
         for (const LayerDev & L : m.layers) {
             for (const QkvPart & q : L.qkv) m.tc_capable = m.tc_capable && cuda::gemm_tc_supported(int(q.w.dt), q.w.ptr, q.w.rows, q.w.cols);

@@ -201,6 +201,7 @@ struct GemmTcParams {
     uint32_t flags;
     int T;                     // tokens per block: 128 or 256
     int wide;                  // q4_0 / q4_K rows of whole 256-element groups at 16-byte aligned addresses: the producers load 144-byte groups with 16-byte loads
+    int pair;                  // (the two-matrix kernel) the second matrix is the next 128 rows of W: one block computes 256 weight rows against its token tile
     int32_t * error;
 };
 
@@ -221,7 +222,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const uint32_t full_x = bars, full_w = bars + 8 * STAGES, empty = bars + 16 * STAGES, acc_full = bars + 24 * STAGES, tmem_slot = acc_full + 8;
     const uint32_t consumed = tmem_slot + 4;       // steps whose stage is free again, counted by the tracker lane
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int64_t n0 = int64_t(blockIdx.x) * kRowsW;
+    const bool pair = GATE && p.pair;
+    const int64_t n0 = int64_t(blockIdx.x) * (pair ? 2 * kRowsW : kRowsW);
     const int m0 = blockIdx.y * p.T;
     const int ksteps = p.K / kStepK;
     const uint32_t ncols = GATE ? 512u : 256u;
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         const int64_t RB = row_bytes_of(DT, p.K);
         const uint8_t * wrow[NMAT];
         wrow[0] = p.W + row * RB;
-        if (GATE) wrow[NMAT - 1] = p.W2 + row * RB;
+        if (GATE) wrow[NMAT - 1] = pair ? p.W + min(n0 + kRowsW + r, p.N - 1) * RB : p.W2 + row * RB;
         const uint32_t dst_row = uint32_t(r) * 128u;
         const int groups = ksteps / 4;
         for (int g = half; g < groups && ok; g += 2) {
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         const int64_t RB = row_bytes_of(DT, p.K);
         const uint8_t * wrow[NMAT];
         wrow[0] = p.W + row * RB;
-        if (GATE) wrow[NMAT - 1] = p.W2 + row * RB;
+        if (GATE) wrow[NMAT - 1] = pair ? p.W + min(n0 + kRowsW + r, p.N - 1) * RB : p.W2 + row * RB;
         const uint32_t dst_row = uint32_t(r) * 128u;
         for (int ks = 0; ks < ksteps && ok; ks++) {
             const int s = ks % STAGES;
@@ -338,7 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, ks * kStepK, m0 + part * 128, full_x + 8 * s);
                 if (PRE) {
                     tma_load_2d(smem0 + s * stage_bytes, &wmap, ks * kStepK, int(n0), full_x + 8 * s);
-                    if (GATE) tma_load_2d(smem0 + s * stage_bytes + kTileWBytes, &w2map, ks * kStepK, int(n0), full_x + 8 * s);
+                    if (GATE) tma_load_2d(smem0 + s * stage_bytes + kTileWBytes, &w2map, ks * kStepK, int(n0) + (pair ? kRowsW : 0), full_x + 8 * s);
                 }
             }
         } else if (lane == 1 && p.wide) {
@@ -382,32 +384,35 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         if (ok) {
             tc_fence_after();
             const int q = warp & 3, colhalf = warp >> 2;
-            const int64_t n = n0 + q * 32 + lane;
             const int cols_per_warp = p.T / 2;
-            const float bias = (p.flags & kFlagBias) && n < p.N ? p.bias[n] : 0.f;
-            for (int c0 = colhalf * cols_per_warp; c0 < (colhalf + 1) * cols_per_warp; c0 += 32) {
-                if (m0 + c0 >= p.M) break;      // warp-uniform
-                uint32_t acc[32], acc2[32];
-                const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0);
-                // what the results are added to: all 32 loads of a lane are asked for before the first is used (one after another, each behind the store
-                // before it, they cost a memory latency apiece: 4 x 32 of them per tile)
-                float old[32];
-                const bool adds = p.Y && (p.flags & kFlagAccumulate) && n < p.N;
-                #pragma unroll
-                for (int j = 0; j < 32; j++) old[j] = (adds && m0 + c0 + j < p.M) ? __ldcg(p.Y + int64_t(m0 + c0 + j) * p.y_stride + n) : 0.f;
-                tc_ld32(taddr, acc);
-                if (GATE) tc_ld32(taddr + 256u, acc2);
-                if (n < p.N) {
+            // pair: the second accumulator holds the next 128 weight rows, with the same epilogue as the first
+            for (int part = 0; part < (pair ? 2 : 1); part++) {
+                const int64_t n = n0 + part * kRowsW + q * 32 + lane;
+                const float bias = (p.flags & kFlagBias) && n < p.N ? p.bias[n] : 0.f;
+                for (int c0 = colhalf * cols_per_warp; c0 < (colhalf + 1) * cols_per_warp; c0 += 32) {
+                    if (m0 + c0 >= p.M) break;      // warp-uniform
+                    uint32_t acc[32], acc2[32];
+                    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0) + uint32_t(part) * 256u;
+                    // what the results are added to: all 32 loads of a lane are asked for before the first is used (one after another, each behind the
+                    // store before it, they cost a memory latency apiece: 4 x 32 of them per tile)
+                    float old[32];
+                    const bool adds = p.Y && (p.flags & kFlagAccumulate) && n < p.N;
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + c0 + j;
-                        if (m >= p.M) continue;
-                        float v = __uint_as_float(acc[j]);
-                        if (GATE) v = v / (1.f + expf(-v)) * __uint_as_float(acc2[j]);
-                        else v += bias;
-                        v += old[j];
-                        if (p.Y) p.Y[int64_t(m) * p.y_stride + n] = v;
-                        if (p.Y16) p.Y16[int64_t(m) * p.y16_stride + n] = __float2half_rn(v);
+                    for (int j = 0; j < 32; j++) old[j] = (adds && m0 + c0 + j < p.M) ? __ldcg(p.Y + int64_t(m0 + c0 + j) * p.y_stride + n) : 0.f;
+                    tc_ld32(taddr, acc);
+                    if (GATE && !pair) tc_ld32(taddr + 256u, acc2);
+                    if (n < p.N) {
+                        #pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int m = m0 + c0 + j;
+                            if (m >= p.M) continue;
+                            float v = __uint_as_float(acc[j]);
+                            if (GATE && !pair) v = v / (1.f + expf(-v)) * __uint_as_float(acc2[j]);
+                            else v += bias;
+                            v += old[j];
+                            if (p.Y) p.Y[int64_t(m) * p.y_stride + n] = v;
+                            if (p.Y16) p.Y16[int64_t(m) * p.y16_stride + n] = __float2half_rn(v);
+                        }
                     }
                 }
             }
@@ -439,7 +444,8 @@ template <int DT, bool PRE>
 cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const CUtensorMap & w2map, const GemmTcParams & p, bool gate, cudaStream_t stream) {
     const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
     const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
-    const dim3 grid(unsigned((p.N + kRowsW - 1) / kRowsW), unsigned((p.M + p.T - 1) / p.T));
+    const int64_t rows_per_block = p.pair ? 2 * kRowsW : kRowsW;
+    const dim3 grid(unsigned((p.N + rows_per_block - 1) / rows_per_block), unsigned((p.M + p.T - 1) / p.T));
     static std::atomic<uint64_t> configured[2];
     if (const cudaError_t e = gate ? allow_dynamic_smem(k_gemm_tc<DT, true, PRE>, 220 * 1024, configured[1])
                                    : allow_dynamic_smem(k_gemm_tc<DT, false, PRE>, 220 * 1024, configured[0]); e != cudaSuccess) return e;
@@ -505,14 +511,16 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
                            int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, void * w16_scratch, size_t w16_bytes) {
     if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
-                   flags, M > 128 ? 256 : 128, 0, error};
+                   flags, M > 128 ? 256 : 128, 0, 0, error};
     p.wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
     // Many tokens: dequantize the matrix once to f16 rows and let TMA feed both operands (the reference does the same from 320 tokens on,
     // metal_llama_decoder.mm:31); otherwise every token tile would redo the dequantization in its producer warps.
     const size_t need = size_t(N) * size_t(K) * 2 * (gate ? 2 : 1);
-    static const int pre_from = [] { const char * e = getenv("DOOMS_GEMM_PRE_FROM"); return e ? atoi(e) : 512; }();
+    // (from 128 tokens: a batched decode step of 256 rows on the 0.5B shape measured 6.4 ms with the weights dequantized by each block's producer warps
+    // and 5.5 ms from f16 rows; with few blocks per matrix the producers' loads are a chain of memory latencies)
+    static const int pre_from = [] { const char * e = getenv("DOOMS_GEMM_PRE_FROM"); return e ? atoi(e) : 128; }();
     // Measured on the 8B shapes: q4_0 / q4_K gate/up is faster fused (875 against 836 TFLOP/s: no f16 copy to write and read), everything else is faster
     // or much faster from f16 rows (ffn_down 961 against 925; q6_K 754 against 83).
     if (w16_scratch && need <= w16_bytes && M >= pre_from && dt != kF16 && !(p.wide && gate)) {
@@ -525,7 +533,17 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
         if (e == cudaSuccess) e = make_activation_map(&w2map, gate ? w16 + size_t(N) * size_t(K) : w16, N, K);
         if (e != cudaSuccess) return e;
         p.wide = 0;
-        return launch_dt<kF16, true>(map, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate, stream);
+        // One matrix: a block may take 256 weight rows (two accumulators that share the token tile), which cuts what a block pulls out of L2 per flop by
+        // a third; the plain tile stays where pairs would leave more of the last wave idle than that is worth.
+        if (!gate) {
+            static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // -1: by the estimate below
+            const int64_t token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
+            const int64_t waves_single = ((N + kRowsW - 1) / kRowsW * token_tiles + sms - 1) / sms;
+            const int64_t waves_pair = ((N + 2 * kRowsW - 1) / (2 * kRowsW) * token_tiles + sms - 1) / sms;
+            p.pair = pair_mode >= 0 ? pair_mode : (waves_pair * 3 < waves_single * 2 ? 1 : 0);      // a pair tile is taken to cost 1.5 plain tiles
+            if (N <= kRowsW) p.pair = 0;
+        }
+        return launch_dt<kF16, true>(map, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate || p.pair, stream);
     }
     switch (dt) {
         case kF16: return launch_dt<kF16, false>(map, map, map, p, gate, stream);

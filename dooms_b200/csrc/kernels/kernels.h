@@ -94,6 +94,11 @@ struct BatchRows { const int32_t * slot; int32_t * pos; int32_t * tok; int64_t s
 // its own position and appends key and value to its own slot's cache.
 cudaError_t launch_attention_gqa_rows(const float * qkv, void * kc, void * vc, float * part, const double * inv_freq, int splits, const AttnShape & s, int * counters,
                                       float * out, void * out16, const BatchRows & rows, int n_rows, cudaStream_t stream);
+// The same step on the tensor cores (attention_rows.cu) for head_dim 64 / 128 and at most 16 query heads per key/value head: ranges of a fixed number of
+// positions (ceil(n_ctx / splits), rounded up to whole tiles), so that a row has as many blocks as its length asks for. Same buffers as above.
+bool attention_rows_tc_supported(const AttnShape & s);
+cudaError_t launch_attention_rows_tc(const float * qkv, void * kc, void * vc, float * part, const double * inv_freq, int splits, int n_ctx, const AttnShape & s,
+                                     int * counters, float * out, void * out16, const BatchRows & rows, int n_rows, cudaStream_t stream);
 // Greedy token of every row: logits [n_rows][stride], first n of each row. Active rows (slot >= 0): tok[r] = argmax, pos[r] += 1, and the token also goes
 // to out[(*step) * n_rows + r]; idle rows write -1 there. *step is incremented once per launch. part: n_rows x argmax_blocks(n) x 2 words.
 cudaError_t launch_argmax_rows(const float * logits, int64_t n, int64_t stride, const BatchRows & rows, int n_rows, int32_t * out, int32_t * step, void * part,
