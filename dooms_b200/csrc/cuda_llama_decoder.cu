@@ -104,6 +104,8 @@ struct CudaLlamaDecoder::Impl {
     int32_t * tp_pairs = nullptr;  // tensor parallelism: every rank's (best logit, its index) of the current position
     bool logits_gathered = true;   // logits_buf holds every rank's rows (always true on one GPU)
     int splits = 1;
+    static constexpr int kMaxShares = 32;
+    float * b_shares = nullptr;  // batched decode steps: [share][max_rows][n_embd] sums of the blocks that share a tile's reduction
     bool rows_tc = false;        // batched decode steps: attention on the tensor cores (attention_rows.cu)
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
     int gqa_splits = 1;
@@ -151,7 +153,7 @@ struct CudaLlamaDecoder::Impl {
         if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
         cuda::decode_layers_destroy(fused);
         for (auto & g : batch_graphs) cudaGraphExecDestroy(g.second);
-        for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters}) if (p) cudaFree(p);
+        for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters, (void *)b_shares}) if (p) cudaFree(p);
         for (void * p : {(void *)h_rows, (void *)h_out}) if (p) cudaFreeHost(p);
         for (void * p : par_opened) cudaIpcCloseMemHandle(p);
         for (void * p : {par_inbox, par_flags, par_words}) if (p) cudaFree(p);
@@ -312,6 +314,19 @@ struct CudaLlamaDecoder::Impl {
             return cuda::launch_gemm_tc(int(w.dt), w.ptr, w2 ? w2->ptr : nullptr, &map, out, out16, bias, M, w.rows, w.cols, out_stride, out16_stride, flags,
                                         host_error, stream, w16, w16_bytes);
         });
+    }
+    // x[m] += X16[m] . W[n] for the rows of a batched step. Few weight rows against one token tile would run on a handful of SMs, so the reduction
+    // dimension is dealt over several blocks per tile where that pays; their sums are added onto x in a fixed order.
+    void gemm_tc_into_x(const char * kind, const MatDev & w, const cuda::TensorMap & map, int M) {
+        const int E = cfg.n_embd;
+        const int shares = b_shares ? cuda::gemm_tc_k_splits(int(w.dt), M, w.rows, w.cols, false, w16 ? w16_bytes : 0) : 1;
+        if (shares <= 1 || shares > kMaxShares) { gemm_tc(kind, w, nullptr, map, x, nullptr, nullptr, M, E, 0, kFlagAccumulate); return; }
+        const int64_t share_stride = int64_t(max_rows) * E;
+        run(kind, [&] {
+            return cuda::launch_gemm_tc(int(w.dt), w.ptr, nullptr, &map, b_shares, nullptr, nullptr, M, w.rows, w.cols, E, 0, 0u, host_error, stream, w16, w16_bytes, shares,
+                                        share_stride);
+        });
+        run("residual", [&] { return cuda::launch_add_shares(x, b_shares, shares, int64_t(M) * E, share_stride, stream); });
     }
     // x += partial sums of the other ranks' shares: with one GPU the projection accumulated into x directly.
     void reduce_into_x(int M) {
@@ -584,10 +599,10 @@ struct CudaLlamaDecoder::Impl {
                 return cuda::launch_attention_gqa_rows(qkv, kc + l * cache_layer_elems, vc + l * cache_layer_elems, b_part, inv_freq, b_splits, as, b_counters, attn, attn16,
                                                        rows, n, stream);
             });
-            gemm_tc("attn_output", L.attn_output, nullptr, map_attn, x, nullptr, nullptr, n, E, 0, kFlagAccumulate);
+            gemm_tc_into_x("attn_output", L.attn_output, map_attn, n);
             norm(x, L.ffn_norm, n, false, true);
             gemm_tc("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, n, 0, ff, 0u);
-            gemm_tc("ffn_down", L.ffn_down, nullptr, map_h, x, nullptr, nullptr, n, E, 0, kFlagAccumulate);
+            gemm_tc_into_x("ffn_down", L.ffn_down, map_h, n);
         }
         norm(x, output_norm, n, false, true);
         gemm_tc("output", output, nullptr, map_xn, b_logits, nullptr, nullptr, n, cfg.n_vocab, 0, 0u);
@@ -958,6 +973,10 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_part), R * size_t(m.b_splits) * size_t(m.nh) * size_t(2 + c.head_dim) * sizeof(float), "the batched attention partial results"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(&m.b_argmax_part, R * size_t(cuda::argmax_blocks(c.n_vocab)) * 8, "the batched argmax partial results"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_counters), R * size_t(m.nkv) * sizeof(int), "the batched attention counters"));
+        if (cudaMalloc(reinterpret_cast<void **>(&m.b_shares), size_t(Impl::kMaxShares) * R * size_t(E) * sizeof(float)) != cudaSuccess) {      // optional
+            (void)cudaGetLastError();
+            m.b_shares = nullptr;
+        }
         cudaMemset(m.b_counters, 0, R * size_t(m.nkv) * sizeof(int));
         if (cudaHostAlloc(reinterpret_cast<void **>(&m.h_rows), 3 * R * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess ||
             cudaHostAlloc(reinterpret_cast<void **>(&m.h_out), size_t(Impl::kMaxBatchSteps) * R * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {

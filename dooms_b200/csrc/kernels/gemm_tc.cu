@@ -202,6 +202,8 @@ struct GemmTcParams {
     int T;                     // tokens per block: 128 or 256
     int wide;                  // q4_0 / q4_K rows of whole 256-element groups at 16-byte aligned addresses: the producers load 144-byte groups with 16-byte loads
     int pair;                  // (the two-matrix kernel) the second matrix is the next 128 rows of W: one block computes 256 weight rows against its token tile
+    int ks_per;                // k steps per block along gridDim.z (0: all of them, one block per tile); block z writes its sum to Y + z * split_stride
+    int64_t split_stride;
     int32_t * error;
 };
 
@@ -225,7 +227,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const bool pair = GATE && p.pair;
     const int64_t n0 = int64_t(blockIdx.x) * (pair ? 2 * kRowsW : kRowsW);
     const int m0 = blockIdx.y * p.T;
-    const int ksteps = p.K / kStepK;
+    // a share of the reduction (f16-row path only): k steps ks0 .. ks0 + ksteps - 1
+    const int ks0 = p.ks_per > 0 ? int(blockIdx.z) * p.ks_per : 0;
+    const int ksteps = p.ks_per > 0 ? min(p.K / kStepK - ks0, p.ks_per) : p.K / kStepK;
     const uint32_t ncols = GATE ? 512u : 256u;
 
     if (threadIdx.x == 0) {
@@ -337,10 +341,10 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 if (!ok) break;
                 const uint32_t dst = smem0 + s * stage_bytes + NMAT * kTileWBytes;
                 mbar_arrive_expect_tx(full_x + 8 * s, tile_x_bytes + (PRE ? NMAT * kTileWBytes : 0u));
-                for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, ks * kStepK, m0 + part * 128, full_x + 8 * s);
+                for (int part = 0; part < p.T / 128; part++) tma_load_2d(dst + part * 16384u, &xmap, (ks0 + ks) * kStepK, m0 + part * 128, full_x + 8 * s);
                 if (PRE) {
-                    tma_load_2d(smem0 + s * stage_bytes, &wmap, ks * kStepK, int(n0), full_x + 8 * s);
-                    if (GATE) tma_load_2d(smem0 + s * stage_bytes + kTileWBytes, &w2map, ks * kStepK, int(n0) + (pair ? kRowsW : 0), full_x + 8 * s);
+                    tma_load_2d(smem0 + s * stage_bytes, &wmap, (ks0 + ks) * kStepK, int(n0), full_x + 8 * s);
+                    if (GATE) tma_load_2d(smem0 + s * stage_bytes + kTileWBytes, &w2map, (ks0 + ks) * kStepK, int(n0) + (pair ? kRowsW : 0), full_x + 8 * s);
                 }
             }
         } else if (lane == 1 && p.wide) {
@@ -385,6 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             tc_fence_after();
             const int q = warp & 3, colhalf = warp >> 2;
             const int cols_per_warp = p.T / 2;
+            float * const Y = p.Y ? p.Y + (p.ks_per > 0 ? int64_t(blockIdx.z) * p.split_stride : 0) : nullptr;
             // pair: the second accumulator holds the next 128 weight rows, with the same epilogue as the first
             for (int part = 0; part < (pair ? 2 : 1); part++) {
                 const int64_t n = n0 + part * kRowsW + q * 32 + lane;
@@ -396,9 +401,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                     // what the results are added to: all 32 loads of a lane are asked for before the first is used (one after another, each behind the
                     // store before it, they cost a memory latency apiece: 4 x 32 of them per tile)
                     float old[32];
-                    const bool adds = p.Y && (p.flags & kFlagAccumulate) && n < p.N;
+                    const bool adds = Y && (p.flags & kFlagAccumulate) && n < p.N;
                     #pragma unroll
-                    for (int j = 0; j < 32; j++) old[j] = (adds && m0 + c0 + j < p.M) ? __ldcg(p.Y + int64_t(m0 + c0 + j) * p.y_stride + n) : 0.f;
+                    for (int j = 0; j < 32; j++) old[j] = (adds && m0 + c0 + j < p.M) ? __ldcg(Y + int64_t(m0 + c0 + j) * p.y_stride + n) : 0.f;
                     tc_ld32(taddr, acc);
                     if (GATE && !pair) tc_ld32(taddr + 256u, acc2);
                     if (n < p.N) {
@@ -410,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                             if (GATE && !pair) v = v / (1.f + expf(-v)) * __uint_as_float(acc2[j]);
                             else v += bias;
                             v += old[j];
-                            if (p.Y) p.Y[int64_t(m) * p.y_stride + n] = v;
+                            if (Y) Y[int64_t(m) * p.y_stride + n] = v;
                             if (p.Y16) p.Y16[int64_t(m) * p.y16_stride + n] = __float2half_rn(v);
                         }
                     }
@@ -445,7 +450,8 @@ cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const C
     const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
     const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
     const int64_t rows_per_block = p.pair ? 2 * kRowsW : kRowsW;
-    const dim3 grid(unsigned((p.N + rows_per_block - 1) / rows_per_block), unsigned((p.M + p.T - 1) / p.T));
+    const int k_blocks = p.ks_per > 0 ? (p.K / kStepK + p.ks_per - 1) / p.ks_per : 1;
+    const dim3 grid(unsigned((p.N + rows_per_block - 1) / rows_per_block), unsigned((p.M + p.T - 1) / p.T), unsigned(k_blocks));
     static std::atomic<uint64_t> configured[2];
     if (const cudaError_t e = gate ? allow_dynamic_smem(k_gemm_tc<DT, true, PRE>, 220 * 1024, configured[1])
                                    : allow_dynamic_smem(k_gemm_tc<DT, false, PRE>, 220 * 1024, configured[0]); e != cudaSuccess) return e;
@@ -501,6 +507,28 @@ cudaError_t make_rows_map(TensorMap * out, const void * base, int64_t rows, int6
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// The f16-row path is taken from this many tokens on (see launch_gemm_tc).
+static int pre_from_tokens() {
+    static const int v = [] { const char * e = getenv("DOOMS_GEMM_PRE_FROM"); return e ? atoi(e) : 128; }();
+    return v;
+}
+
+int gemm_tc_k_splits(int dt, int M, int64_t N, int64_t K, bool gate, size_t w16_bytes) {
+    static const bool off = [] { const char * e = getenv("DOOMS_GEMM_SPLIT_K"); return e && *e == '0'; }();
+    const bool wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0;
+    const bool pre = w16_bytes >= size_t(N) * size_t(K) * 2 * (gate ? 2 : 1) && M >= pre_from_tokens() && dt != kF16 && !(wide && gate);
+    if (off || gate || !pre || K % kStepK != 0) return 1;
+    const int T = M > 128 ? 256 : 128;
+    const int64_t tiles = (N + kRowsW - 1) / kRowsW * ((M + T - 1) / T);
+    const int ksteps = int(K / kStepK);
+    // worth it when the tiles leave most SMs idle and every share still has a few k steps; shares of equal size, none empty
+    int want = int(std::min<int64_t>(sm_count() / std::max<int64_t>(tiles, 1), ksteps / 4));
+    if (tiles * 2 > sm_count() || want < 2) return 1;
+    want = std::min(want, 32);
+    const int per = (ksteps + want - 1) / want;
+    return (ksteps + per - 1) / per;
+}
+
 bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
     (void)W;
     const bool type_ok = dt == kF16 || dt == kQ4_0 || dt == kQ5_0 || dt == kQ8_0 || dt == kQ4_K || dt == kQ6_K;
@@ -508,10 +536,14 @@ bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
 }
 
 cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
-                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, void * w16_scratch, size_t w16_bytes) {
+                           int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, void * w16_scratch, size_t w16_bytes, int k_splits,
+                           int64_t split_stride) {
     if (!gemm_tc_supported(dt, W, N, K) || M < 1) return cudaErrorInvalidValue;
+    if (k_splits > 1 && (k_splits != gemm_tc_k_splits(dt, M, N, K, W2 != nullptr, w16_scratch ? w16_bytes : 0) || !Y || Y16 || flags || split_stride < int64_t(M) * y_stride)) {
+        return cudaErrorInvalidValue;
+    }
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
-                   flags, M > 128 ? 256 : 128, 0, 0, error};
+                   flags, M > 128 ? 256 : 128, 0, 0, 0, 0, error};
     p.wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
@@ -520,7 +552,7 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
     const size_t need = size_t(N) * size_t(K) * 2 * (gate ? 2 : 1);
     // (from 128 tokens: a batched decode step of 256 rows on the 0.5B shape measured 6.4 ms with the weights dequantized by each block's producer warps
     // and 5.5 ms from f16 rows; with few blocks per matrix the producers' loads are a chain of memory latencies)
-    static const int pre_from = [] { const char * e = getenv("DOOMS_GEMM_PRE_FROM"); return e ? atoi(e) : 128; }();
+    const int pre_from = pre_from_tokens();
     // Measured on the 8B shapes: q4_0 / q4_K gate/up is faster fused (875 against 836 TFLOP/s: no f16 copy to write and read), everything else is faster
     // or much faster from f16 rows (ffn_down 961 against 925; q6_K 754 against 83).
     if (w16_scratch && need <= w16_bytes && M >= pre_from && dt != kF16 && !(p.wide && gate)) {
@@ -533,9 +565,14 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
         if (e == cudaSuccess) e = make_activation_map(&w2map, gate ? w16 + size_t(N) * size_t(K) : w16, N, K);
         if (e != cudaSuccess) return e;
         p.wide = 0;
+        if (k_splits > 1) {
+            const int ksteps = int(K / kStepK);
+            p.ks_per = (ksteps + k_splits - 1) / k_splits;
+            p.split_stride = split_stride;
+        }
         // One matrix: a block may take 256 weight rows (two accumulators that share the token tile), which cuts what a block pulls out of L2 per flop by
         // a third; the plain tile stays where pairs would leave more of the last wave idle than that is worth.
-        if (!gate) {
+        if (!gate && k_splits <= 1) {
             static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // -1: by the estimate below
             const int64_t token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
             const int64_t waves_single = ((N + kRowsW - 1) / kRowsW * token_tiles + sms - 1) / sms;

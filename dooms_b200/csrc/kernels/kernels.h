@@ -220,7 +220,12 @@ bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K);
 // per call and both operands arrive by TMA.
 cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
                            int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream,
-                           void * w16_scratch = nullptr, size_t w16_bytes = 0);
+                           void * w16_scratch = nullptr, size_t w16_bytes = 0, int k_splits = 1, int64_t split_stride = 0);
+// A product whose tiles would leave most SMs idle (few weight rows against one token tile: a batched decode step) can deal its reduction dimension over
+// k_splits blocks per tile: gemm_tc_k_splits says how many (1: do not split), launch_gemm_tc with that k_splits then writes the shares' sums to
+// Y + z * split_stride (flags 0, no f16 output), and launch_add_shares adds them onto x in a fixed order, so the result does not depend on timing.
+int gemm_tc_k_splits(int dt, int M, int64_t N, int64_t K, bool gate, size_t w16_bytes);
+cudaError_t launch_add_shares(float * x, const float * shares, int k_splits, int64_t n, int64_t split_stride, cudaStream_t stream);
 
 }  // namespace cuda
 }  // namespace dooms

@@ -31,9 +31,9 @@ def model(model_dir):
     return write(model_dir, "batch_mix", synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=200), 41)
 
 
-def checker_tokens(path, prompt, steps):
+def checker_tokens(path, prompt, steps, n_ctx=512):
     """(pending token, [(token, logits)] of `steps` steps) of one sequence alone: the prompt as one chunk, then single positions through the chunk tiles."""
-    o = ob.OracleDecoder(path, 512, round_operands=True)
+    o = ob.OracleDecoder(path, n_ctx, round_operands=True)
     logits = o.eval_tokens(prompt)
     o.set_round_operands(2)
     pending = ob.argmax(logits)
@@ -80,6 +80,32 @@ def test_batched_steps_match_each_sequence_alone(model):
         dec.select_sequence(s)
         assert dec.position() == len(ps[s]) + 9 and dec.pending_token() == int(got[-1, row])
     assert agreed >= 6 * 9 * 0.8                          # near ties are the exception, not the rule
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_long_rows_spread_over_several_ranges(model_dir, head_dim):
+    """Rows of very different lengths in one step, the longest spread over three ranges of the cache whose results are merged by the last block to finish;
+    key/value heads of 64 and of 128 elements (two tile sizes of the tensor-core attention), three query heads per key/value head."""
+    spec = synth.tiny_spec(QUANT_PLANS["q4_0"], n_embd=6 * head_dim, n_head=6, n_head_kv=2, n_ff=1024, n_vocab=200, context_length=2048)
+    path = write(model_dir, f"batch_long_{head_dim}", spec, 43)
+    lengths = [5, 300, 515, 1100, 1290]
+    ps = [[int(t) for t in synth.prompt_tokens(n, 200, 900 + i)] for i, n in enumerate(lengths)]
+    dec = CudaLlamaDecoder.load(path, 1300, 512, max_sequences=5)
+    pend = []
+    for s, p in enumerate(ps):
+        dec.select_sequence(s)
+        dec.eval_tokens(p)
+        pend.append(dec.pending_token())
+    steps = 5
+    got = dec.decode_batch([4, 3, 2, 1, 0], steps)
+    agreed = 0
+    for row, s in enumerate([4, 3, 2, 1, 0]):
+        pending, want = checker_tokens(path, ps[s], steps, n_ctx=1300)
+        if pend[s] != pending:
+            continue                                      # the prompt itself ended on a near tie: nothing to follow
+        agreed += compare(got[:, row], want)
+    assert agreed >= 5 * steps * 0.8
+    dec.close()
 
 
 def test_batched_steps_match_the_same_sequences_run_singly(model):
