@@ -68,6 +68,8 @@ int attention_gqa_splits(int n_head_kv, int n_ctx) {
     // about one block per SM, and no more ranges than the context has tiles
     static const int per_sm = [] { const char * e = getenv("DOOMS_GQA_PER_SM"); return e ? std::max(1, atoi(e)) : 1; }();
     const int want = std::max(1, (sm_count() * per_sm + n_head_kv - 1) / n_head_kv);
+    static const int fixed = [] { const char * e = getenv("DOOMS_GQA_SPLITS"); return e ? atoi(e) : 0; }();
+    if (fixed > 0) return std::max(1, std::min(fixed, (n_ctx + kTileKeys - 1) / kTileKeys));
     return std::max(1, std::min(want, (n_ctx + kTileKeys - 1) / kTileKeys));
 }
 
