@@ -3,6 +3,7 @@ cache). No collective on the data path. Two ways to run a GPU's share:
   * batched (serve_batched, the default of the command below): the decoder holds one KV-cache slot per sequence, every prompt is evaluated into its slot,
     and then all sequences decode together, one pass over the weights per step for all of them (CudaLlamaDecoder.decode_batch); a sequence that has all
     its tokens leaves its row idle;
+  * continuous (run_continuous): more sequences than slots; finished sequences hand their slots to waiting prompts between batched steps;
   * one at a time (serve): sequences pulled from a shared queue and run one after another, the reference's serving loop (docs/USING.md:103,
     python/dooms/server.py:262-269), optionally several decoders per GPU on their own streams.
 
@@ -70,6 +71,48 @@ def run_batched(dec, sequences, max_steps_per_call: int = 256):
                 need[s] -= k
     t_end = time.perf_counter()
     return tokens, {"prefill_ms": prefill_ms, "decode_ms": decode_ms, "steps": steps_run, "prefill_wall_s": t_decode - t_start, "decode_wall_s": t_end - t_decode}
+
+
+def run_continuous(dec, sequences, max_live: int, max_steps_per_call: int = 64):
+    """More sequences than slots: at most max_live of them are live at a time, each in a KV-cache slot; whenever sequences finish, the next waiting prompts
+    are evaluated into the freed slots and join the following batched steps (continuous batching). A step always has max_live rows (idle ones marked -1),
+    so one captured graph serves the whole run, and a row's arithmetic does not depend on which other sequences share its step: a sequence's tokens are
+    those of run_batched with the same number of rows. Returns (tokens per sequence, {prefill / decode device ms, steps, largest number of live rows})."""
+    n = len(sequences)
+    tokens: list[list[int]] = [[] for _ in range(n)]
+    slot_of = [-1] * max_live                        # the sequence in each slot, -1: free
+    need = [0] * max_live
+    waiting = list(range(n))
+    prefill_ms = decode_ms = 0.0
+    steps_run = most_live = 0
+    while waiting or any(s >= 0 for s in slot_of):
+        for slot in range(max_live):                 # admit
+            if slot_of[slot] < 0 and waiting:
+                i = waiting.pop(0)
+                prompt, n_decode = sequences[i]
+                dec.select_sequence(slot)
+                dec.reset()
+                dec.eval_tokens(prompt)
+                prefill_ms += dec.timings()["last_eval_ms"]
+                tokens[i].append(dec.pending_token())
+                if n_decode > 1:
+                    slot_of[slot], need[slot] = i, n_decode - 1
+        live = [slot for slot in range(max_live) if slot_of[slot] >= 0]
+        if not live:
+            continue
+        most_live = max(most_live, len(live))
+        # as many steps as the first sequence to finish still wants: nothing is generated past a sequence's end, and its slot frees up at once
+        k = min(min(need[slot] for slot in live), max_steps_per_call)
+        rows = [slot if slot_of[slot] >= 0 else -1 for slot in range(max_live)]
+        out = dec.decode_batch(rows, k)
+        decode_ms += dec.timings()["last_batch_ms"]
+        steps_run += k
+        for slot in live:
+            tokens[slot_of[slot]].extend(int(t) for t in out[:, slot])
+            need[slot] -= k
+            if need[slot] == 0:
+                slot_of[slot] = -1
+    return tokens, {"prefill_ms": prefill_ms, "decode_ms": decode_ms, "steps": steps_run, "most_live": most_live}
 
 
 def _batched_worker(device: int, path: str, n_ctx: int, n_batch: int, sequences, mine, done):

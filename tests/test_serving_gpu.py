@@ -50,3 +50,31 @@ def test_sequences_served_as_one_batch_follow_single_runs(model_dir):
         total += n_decode
     assert agree >= 0.8 * total
     dec.close()
+
+
+@pytest.mark.gpu
+def test_continuous_batching_gives_each_sequence_the_tokens_of_a_full_batch(model_dir):
+    """Twelve sequences through four slots: prompts join as others finish. A row's arithmetic does not depend on its neighbours, so every sequence gets
+    exactly the tokens it gets when all rows of a four-row batch are its own group (run_batched over the same four rows, idle rows included)."""
+    path = write(model_dir, "serve_continuous_q4_0", synth.tiny_spec(synth.pure(L.Q4_0), n_vocab=200), 5)
+    seqs = serving.workload(12, 200, 3001, prompt_range=(3, 90), decode_range=(1, 20))
+    dec = CudaLlamaDecoder.load(path, 128, 64, max_sequences=4)
+    tokens, stats = serving.run_continuous(dec, seqs, max_live=4)
+    assert [len(t) for t in tokens] == [d for _, d in seqs]
+    assert 2 <= stats["most_live"] <= 4 and stats["steps"] < sum(d for _, d in seqs)      # steps were shared
+    # the same sequences four at a time, each group as one batch of four rows
+    for g in range(0, 12, 4):
+        want, _ = serving.run_batched(dec, seqs[g:g + 4])
+        for i in range(4):
+            assert tokens[g + i] == want[i][:len(tokens[g + i])], (g, i)
+    # and against single runs: equal up to a near tie
+    one = CudaLlamaDecoder.load(path, 128, 64)
+    agree = total = 0
+    for (prompt, n_decode), got in zip(seqs, tokens):
+        alone = serving.run_sequence(one, prompt, n_decode)[0]
+        assert got[0] == alone[0]
+        agree += next((i for i, (a, b) in enumerate(zip(alone, got)) if a != b), n_decode)
+        total += n_decode
+    assert agree >= 0.8 * total
+    dec.close()
+    one.close()
