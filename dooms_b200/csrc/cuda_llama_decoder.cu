@@ -41,6 +41,7 @@ struct MatDev {
     const uint8_t * ptr = nullptr;
     DType dt = DType::F16;
     int64_t rows = 0, cols = 0;
+    const __half * rows16 = nullptr;      // optional: the same matrix as f16 rows, for the projections of batched steps
     int64_t bytes() const { return rows * static_cast<int64_t>(dtype_bytes(dt, cols).value()); }
 };
 // q, k and v are one concatenated matrix when they share a type; otherwise one part each (rows row0.. of the qkv output).
@@ -105,6 +106,7 @@ struct CudaLlamaDecoder::Impl {
     bool logits_gathered = true;   // logits_buf holds every rank's rows (always true on one GPU)
     int splits = 1;
     static constexpr int kMaxShares = 32;
+    __half * rows16_all = nullptr;   // batched decode steps: the matrices as f16 rows (MatDev::rows16 point into it), when memory allows
     float * b_shares = nullptr;  // batched decode steps: [share][max_rows][n_embd] sums of the blocks that share a tile's reduction
     bool rows_tc = false;        // batched decode steps: attention on the tensor cores (attention_rows.cu)
     bool gqa = false;            // decode attention: the grouped-query kernel (which also rotates and stores the new key / value)
@@ -153,7 +155,7 @@ struct CudaLlamaDecoder::Impl {
         if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
         cuda::decode_layers_destroy(fused);
         for (auto & g : batch_graphs) cudaGraphExecDestroy(g.second);
-        for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters, (void *)b_shares}) if (p) cudaFree(p);
+        for (void * p : {(void *)b_rows, (void *)b_out, (void *)b_step, (void *)b_logits, (void *)b_part, b_argmax_part, (void *)b_counters, (void *)b_shares, (void *)rows16_all}) if (p) cudaFree(p);
         for (void * p : {(void *)h_rows, (void *)h_out}) if (p) cudaFreeHost(p);
         for (void * p : par_opened) cudaIpcCloseMemHandle(p);
         for (void * p : {par_inbox, par_flags, par_words}) if (p) cudaFree(p);
@@ -319,14 +321,26 @@ struct CudaLlamaDecoder::Impl {
     // dimension is dealt over several blocks per tile where that pays; their sums are added onto x in a fixed order.
     void gemm_tc_into_x(const char * kind, const MatDev & w, const cuda::TensorMap & map, int M) {
         const int E = cfg.n_embd;
-        const int shares = b_shares ? cuda::gemm_tc_k_splits(int(w.dt), M, w.rows, w.cols, false, w16 ? w16_bytes : 0) : 1;
-        if (shares <= 1 || shares > kMaxShares) { gemm_tc(kind, w, nullptr, map, x, nullptr, nullptr, M, E, 0, kFlagAccumulate); return; }
+        int shares = 1;
+        if (b_shares) shares = w.rows16 ? cuda::gemm_tc_rows16_k_splits(M, w.rows, w.cols) : cuda::gemm_tc_k_splits(int(w.dt), M, w.rows, w.cols, false, w16 ? w16_bytes : 0);
+        if (shares <= 1 || shares > kMaxShares) { gemm_rows(kind, w, nullptr, map, x, nullptr, nullptr, M, E, 0, kFlagAccumulate); return; }
         const int64_t share_stride = int64_t(max_rows) * E;
         run(kind, [&] {
+            if (w.rows16) {
+                return cuda::launch_gemm_tc_rows16(w.rows16, nullptr, &map, b_shares, nullptr, nullptr, M, w.rows, w.cols, E, 0, 0u, host_error, stream, shares, share_stride);
+            }
             return cuda::launch_gemm_tc(int(w.dt), w.ptr, nullptr, &map, b_shares, nullptr, nullptr, M, w.rows, w.cols, E, 0, 0u, host_error, stream, w16, w16_bytes, shares,
                                         share_stride);
         });
         run("residual", [&] { return cuda::launch_add_shares(x, b_shares, shares, int64_t(M) * E, share_stride, stream); });
+    }
+    // A projection of a batched step: from the decoder's f16 copy of the matrix when it keeps one, else as any chunk's.
+    void gemm_rows(const char * kind, const MatDev & w, const MatDev * w2, const cuda::TensorMap & map, float * out, __half * out16, const float * bias, int M,
+                   int64_t out_stride, int64_t out16_stride, uint32_t flags) {
+        if (!w.rows16 || (w2 && !w2->rows16)) { gemm_tc(kind, w, w2, map, out, out16, bias, M, out_stride, out16_stride, flags); return; }
+        run(kind, [&] {
+            return cuda::launch_gemm_tc_rows16(w.rows16, w2 ? w2->rows16 : nullptr, &map, out, out16, bias, M, w.rows, w.cols, out_stride, out16_stride, flags, host_error, stream);
+        });
     }
     // x += partial sums of the other ranks' shares: with one GPU the projection accumulated into x directly.
     void reduce_into_x(int M) {
@@ -589,7 +603,7 @@ struct CudaLlamaDecoder::Impl {
             const LayerDev & L = layers[l];
             norm(x, L.attn_norm, n, false, true);
             for (const QkvPart & q : L.qkv) {
-                gemm_tc("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, n, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
+                gemm_rows("qkv", q.w, nullptr, map_xn, qkv + q.row0, nullptr, L.qkv_bias ? L.qkv_bias + q.row0 : nullptr, n, qkv_width, 0, L.qkv_bias ? kFlagBias : 0u);
             }
             run("attention", [&] {
                 if (rows_tc) {
@@ -601,11 +615,11 @@ struct CudaLlamaDecoder::Impl {
             });
             gemm_tc_into_x("attn_output", L.attn_output, map_attn, n);
             norm(x, L.ffn_norm, n, false, true);
-            gemm_tc("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, n, 0, ff, 0u);
+            gemm_rows("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, n, 0, ff, 0u);
             gemm_tc_into_x("ffn_down", L.ffn_down, map_h, n);
         }
         norm(x, output_norm, n, false, true);
-        gemm_tc("output", output, nullptr, map_xn, b_logits, nullptr, nullptr, n, cfg.n_vocab, 0, 0u);
+        gemm_rows("output", output, nullptr, map_xn, b_logits, nullptr, nullptr, n, cfg.n_vocab, 0, 0u);
         run("argmax", [&] { return cuda::launch_argmax_rows(b_logits, cfg.n_vocab, cfg.n_vocab, rows, n, b_out, b_step, b_argmax_part, stream); });
     }
     Result<cudaGraphExec_t> batch_graph(int32_t n) {
@@ -963,9 +977,11 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
                      ? std::min<int32_t>({n_seq, c.n_batch, 1024}) : 0;
     if (m.max_rows > 0) {
         const size_t R = size_t(m.max_rows);
-        // Rows attend over very different lengths (a fresh sequence beside one at the end of its context), so the ranges are short: about eight tiles of 64
-        // positions each, which bounds what one block does and lets the long rows spread over many SMs; a short row's later ranges are empty and leave at once.
-        m.b_splits = std::max(1, std::min(64, (c.n_ctx + 511) / 512));
+        // Rows attend over very different lengths (a fresh sequence beside one at the end of its context), so a row is cut into ranges of a fixed number of
+        // positions, which bounds what one block does and lets the long rows spread over many SMs; a short row's later ranges are empty and leave at once.
+        // 1024 positions measured best on 256 rows of 32 .. 4096 positions (4.23 ms per step; 512: 4.48, 256: 5.14).
+        static const int range = [] { const char * e = getenv("DOOMS_ROWS_RANGE"); return e ? std::max(64, atoi(e)) : 1024; }();
+        m.b_splits = std::max(1, std::min(64, (c.n_ctx + range - 1) / range));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_rows), 3 * R * sizeof(int32_t), "the rows of a batched decode step"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_out), size_t(Impl::kMaxBatchSteps) * R * sizeof(int32_t), "the tokens of a batched decode call"));
         DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.b_step), sizeof(int32_t), "the step counter"));
@@ -976,6 +992,38 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         if (cudaMalloc(reinterpret_cast<void **>(&m.b_shares), size_t(Impl::kMaxShares) * R * size_t(E) * sizeof(float)) != cudaSuccess) {      // optional
             (void)cudaGetLastError();
             m.b_shares = nullptr;
+        }
+        // Batched steps run every projection from f16 rows. A copy of the matrices in that form, made once, saves dequantizing them in every step (11 % of
+        // a 256-row step on the 0.5B shape); it is kept when it takes at most a quarter of the memory that is still free (DOOMS_BATCH_F16_ROWS=0: never).
+        std::vector<MatDev *> mats;
+        for (LayerDev & L : m.layers) {
+            for (QkvPart & q : L.qkv) mats.push_back(&q.w);
+            for (MatDev * w : {&L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down}) mats.push_back(w);
+        }
+        mats.push_back(&m.output);
+        size_t halves = 0;
+        for (const MatDev * w : mats) halves += (size_t(w->rows) * size_t(w->cols) + 127) & ~size_t(127);
+        size_t free_bytes = 0, total_bytes = 0;
+        const char * keep = getenv("DOOMS_BATCH_F16_ROWS");
+        if (!(keep && *keep == '0') && cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess && halves * 2 <= free_bytes / 4 &&
+            cudaMalloc(reinterpret_cast<void **>(&m.rows16_all), halves * 2) == cudaSuccess) {
+            size_t at = 0;
+            bool ok = true;
+            for (MatDev * w : mats) {
+                if (w->dt == DType::F16) continue;      // (f16 matrices are their own f16 rows; they stay on the path of any chunk)
+                __half * dst = m.rows16_all + at;
+                ok = ok && cuda::launch_dequant_rows16(int(w->dt), w->ptr, dst, w->rows, w->cols, m.stream) == cudaSuccess;
+                w->rows16 = dst;
+                at += (size_t(w->rows) * size_t(w->cols) + 127) & ~size_t(127);
+            }
+            if (!ok || cudaStreamSynchronize(m.stream) != cudaSuccess) {
+                (void)cudaGetLastError();
+                for (MatDev * w : mats) w->rows16 = nullptr;
+                cudaFree(m.rows16_all);
+                m.rows16_all = nullptr;
+            }
+        } else {
+            (void)cudaGetLastError();
         }
         cudaMemset(m.b_counters, 0, R * size_t(m.nkv) * sizeof(int));
         if (cudaHostAlloc(reinterpret_cast<void **>(&m.h_rows), 3 * R * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess ||

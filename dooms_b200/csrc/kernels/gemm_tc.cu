@@ -513,11 +513,19 @@ static int pre_from_tokens() {
     return v;
 }
 
+static int k_splits_of_rows16(int M, int64_t N, int64_t K);
+
 int gemm_tc_k_splits(int dt, int M, int64_t N, int64_t K, bool gate, size_t w16_bytes) {
-    static const bool off = [] { const char * e = getenv("DOOMS_GEMM_SPLIT_K"); return e && *e == '0'; }();
     const bool wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0;
     const bool pre = w16_bytes >= size_t(N) * size_t(K) * 2 * (gate ? 2 : 1) && M >= pre_from_tokens() && dt != kF16 && !(wide && gate);
-    if (off || gate || !pre || K % kStepK != 0) return 1;
+    if (gate || !pre) return 1;
+    return k_splits_of_rows16(M, N, K);
+}
+int gemm_tc_rows16_k_splits(int M, int64_t N, int64_t K) { return k_splits_of_rows16(M, N, K); }
+
+static int k_splits_of_rows16(int M, int64_t N, int64_t K) {
+    static const bool off = [] { const char * e = getenv("DOOMS_GEMM_SPLIT_K"); return e && *e == '0'; }();
+    if (off || K % kStepK != 0) return 1;
     const int T = M > 128 ? 256 : 128;
     const int64_t tiles = (N + kRowsW - 1) / kRowsW * ((M + T - 1) / T);
     const int ksteps = int(K / kStepK);
@@ -533,6 +541,47 @@ bool gemm_tc_supported(int dt, const void * W, int64_t N, int64_t K) {
     (void)W;
     const bool type_ok = dt == kF16 || dt == kQ4_0 || dt == kQ5_0 || dt == kQ8_0 || dt == kQ4_K || dt == kQ6_K;
     return type_ok && N >= 1 && K >= kStepK && K % kStepK == 0;
+}
+
+// Both operands by TMA: the token rows behind xmap against weights that are f16 rows [N][K] in device memory (w2_16: the second matrix of a gate / up pair).
+static cudaError_t launch_rows16(GemmTcParams p, const CUtensorMap & xmap, const __half * w16, const __half * w2_16, int M, int64_t N, int64_t K, int k_splits,
+                                 int64_t split_stride, cudaStream_t stream) {
+    const bool gate = w2_16 != nullptr;
+    TensorMap wmap, w2map;
+    cudaError_t e = make_activation_map(&wmap, w16, N, K);
+    if (e == cudaSuccess) e = make_activation_map(&w2map, gate ? w2_16 : w16, N, K);
+    if (e != cudaSuccess) return e;
+    p.wide = 0;
+    if (k_splits > 1) {
+        const int ksteps = int(K / kStepK);
+        p.ks_per = (ksteps + k_splits - 1) / k_splits;
+        p.split_stride = split_stride;
+    }
+    // One matrix: a block may take 256 weight rows (two accumulators that share the token tile), which cuts what a block pulls out of L2 per flop by
+    // a third; the plain tile stays where pairs would leave more of the last wave idle than that is worth.
+    if (!gate && k_splits <= 1) {
+        static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // -1: by the estimate below
+        const int64_t token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
+        const int64_t waves_single = ((N + kRowsW - 1) / kRowsW * token_tiles + sms - 1) / sms;
+        const int64_t waves_pair = ((N + 2 * kRowsW - 1) / (2 * kRowsW) * token_tiles + sms - 1) / sms;
+        p.pair = pair_mode >= 0 ? pair_mode : (waves_pair * 3 < waves_single * 2 ? 1 : 0);      // a pair tile is taken to cost 1.5 plain tiles
+        if (N <= kRowsW) p.pair = 0;
+    }
+    return launch_dt<kF16, true>(xmap, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate || p.pair, stream);
+}
+
+cudaError_t launch_gemm_tc_rows16(const void * W16, const void * W2_16, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
+                                  int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, int k_splits, int64_t split_stride) {
+    if (!W16 || N < 1 || K < kStepK || K % kStepK != 0 || M < 1 || (reinterpret_cast<uintptr_t>(W16) & 15u) || (reinterpret_cast<uintptr_t>(W2_16) & 15u)) return cudaErrorInvalidValue;
+    if (k_splits > 1 && (k_splits != k_splits_of_rows16(M, N, K) || W2_16 || !Y || Y16 || flags || split_stride < int64_t(M) * y_stride)) return cudaErrorInvalidValue;
+    GemmTcParams p{nullptr, nullptr, Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride, flags, M > 128 ? 256 : 128, 0, 0, 0, 0, error};
+    return launch_rows16(p, *reinterpret_cast<const CUtensorMap *>(xmap), static_cast<const __half *>(W16), static_cast<const __half *>(W2_16), M, N, K, k_splits,
+                         split_stride, stream);
+}
+
+cudaError_t launch_dequant_rows16(int dt, const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream) {
+    if (!W || !out || rows < 1 || cols < 32 || cols % 32 != 0) return cudaErrorInvalidValue;
+    return dequant_rows_dt(dt, W, out, rows, cols, stream);
 }
 
 cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
@@ -560,27 +609,7 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
         cudaError_t e = dequant_rows_dt(dt, W, w16, N, K, stream);
         if (e == cudaSuccess && gate) e = dequant_rows_dt(dt, W2, w16 + size_t(N) * size_t(K), N, K, stream);
         if (e != cudaSuccess) return e;
-        TensorMap wmap, w2map;
-        e = make_activation_map(&wmap, w16, N, K);
-        if (e == cudaSuccess) e = make_activation_map(&w2map, gate ? w16 + size_t(N) * size_t(K) : w16, N, K);
-        if (e != cudaSuccess) return e;
-        p.wide = 0;
-        if (k_splits > 1) {
-            const int ksteps = int(K / kStepK);
-            p.ks_per = (ksteps + k_splits - 1) / k_splits;
-            p.split_stride = split_stride;
-        }
-        // One matrix: a block may take 256 weight rows (two accumulators that share the token tile), which cuts what a block pulls out of L2 per flop by
-        // a third; the plain tile stays where pairs would leave more of the last wave idle than that is worth.
-        if (!gate && k_splits <= 1) {
-            static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // -1: by the estimate below
-            const int64_t token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
-            const int64_t waves_single = ((N + kRowsW - 1) / kRowsW * token_tiles + sms - 1) / sms;
-            const int64_t waves_pair = ((N + 2 * kRowsW - 1) / (2 * kRowsW) * token_tiles + sms - 1) / sms;
-            p.pair = pair_mode >= 0 ? pair_mode : (waves_pair * 3 < waves_single * 2 ? 1 : 0);      // a pair tile is taken to cost 1.5 plain tiles
-            if (N <= kRowsW) p.pair = 0;
-        }
-        return launch_dt<kF16, true>(map, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate || p.pair, stream);
+        return launch_rows16(p, map, w16, gate ? w16 + size_t(N) * size_t(K) : nullptr, M, N, K, k_splits, split_stride, stream);
     }
     switch (dt) {
         case kF16: return launch_dt<kF16, false>(map, map, map, p, gate, stream);

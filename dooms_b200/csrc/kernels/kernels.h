@@ -225,6 +225,12 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
 // k_splits blocks per tile: gemm_tc_k_splits says how many (1: do not split), launch_gemm_tc with that k_splits then writes the shares' sums to
 // Y + z * split_stride (flags 0, no f16 output), and launch_add_shares adds them onto x in a fixed order, so the result does not depend on timing.
 int gemm_tc_k_splits(int dt, int M, int64_t N, int64_t K, bool gate, size_t w16_bytes);
+// The same product against weights that already lie in device memory as f16 rows [N][K] (W2_16: the second matrix of a gate / up pair): a decoder that
+// runs batched steps keeps such a copy of its matrices, made once with launch_dequant_rows16, instead of dequantizing them in every step.
+cudaError_t launch_dequant_rows16(int dt, const void * W, void * out, int64_t rows, int64_t cols, cudaStream_t stream);
+int gemm_tc_rows16_k_splits(int M, int64_t N, int64_t K);
+cudaError_t launch_gemm_tc_rows16(const void * W16, const void * W2_16, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
+                                  int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, int k_splits = 1, int64_t split_stride = 0);
 cudaError_t launch_add_shares(float * x, const float * shares, int k_splits, int64_t n, int64_t split_stride, cudaStream_t stream);
 
 }  // namespace cuda
