@@ -159,6 +159,9 @@ SIGNATURES = {
     "dooms_cuda_matvec": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
     "dooms_cuda_gate_up": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "dooms_cuda_matmul": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
+    "dooms_cuda_split_input_bytes": (C.c_int64, [C.c_int64]),
+    "dooms_cuda_split_input": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "dooms_cuda_matvec_split": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_uint32, C.c_void_p]),
     "dooms_cuda_kernel_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32)]),
     "dooms_cuda_rms_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
     "dooms_cuda_argmax": (C.c_int32, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),

@@ -609,6 +609,30 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
     return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, st), "matvec");
 }
 
+DOOMS_CUDA_API int64_t dooms_cuda_split_input_bytes(int64_t cols) {
+    return cols >= 32 && cols % 32 == 0 ? int64_t((cuda::quantized_x_bytes(cols) + 15) & ~size_t(15)) : 0;
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_split_input(const float * d_x, int64_t cols, void * d_split, void * stream) {
+    if (!d_x || !d_split || cols < 32 || cols % 32 != 0 || cols > INT32_MAX) return fail(DOOMS_INVALID_ARGUMENT, "split_input: NULL pointer, or a length that is not whole 32-element blocks");
+    return launch_result(cuda::launch_quantize_x(d_x, cols, d_split, static_cast<cudaStream_t>(stream)), "split_input");
+}
+
+DOOMS_CUDA_API int32_t dooms_cuda_matvec_split(int32_t dtype, const void * d_w, const void * d_w2, const void * d_split, float * d_y, const float * d_bias, int64_t rows,
+                                               int64_t cols, uint32_t flags, void * stream) {
+    if (dtype != DOOMS_Q4_0 && dtype != DOOMS_Q4_K) return fail(DOOMS_UNSUPPORTED, "matvec_split takes q4_0 and q4_K rows (the integer tensor-core kernel)");
+    if (!d_w || !d_split || !d_y || rows < 1 || cols < 32 || cols % 32 != 0 || cols > INT32_MAX || ((flags & cuda::kFlagBias) && !d_bias) ||
+        (flags & ~(cuda::kFlagAccumulate | cuda::kFlagBias)) || (d_w2 && flags)) {
+        return fail(DOOMS_INVALID_ARGUMENT, "matvec_split: NULL pointer, unknown flag, or rows that are not whole blocks");
+    }
+    const bool k4 = dtype == DOOMS_Q4_K;
+    const bool ok = k4 ? cuda::gemv_q4_k_supported(d_w, rows, cols) && (!d_w2 || cuda::gemv_q4_k_supported(d_w2, rows, cols))
+                       : cuda::gemv_q4_0_supported(d_w, rows, cols) && (!d_w2 || cuda::gemv_q4_0_supported(d_w2, rows, cols));
+    if (!ok) return fail(DOOMS_UNSUPPORTED, "matvec_split: a shape or alignment the integer tensor-core kernel does not take");
+    return launch_result(cuda::launch_gemv_q4_0(d_w, d_w2, d_split, nullptr, nullptr, 0.f, d_y, d_bias, rows, cols, flags, k4, static_cast<cudaStream_t>(stream), nullptr,
+                                                nullptr, kernel_error_word()), "matvec_split");
+}
+
 DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
                                           void * stream) {
     if (!matrix_dtype(dtype)) return fail(DOOMS_UNSUPPORTED, "gate_up takes f16, q4_0, q5_0, q8_0, q4_K and q6_K");

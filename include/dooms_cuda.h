@@ -205,6 +205,15 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
 /* gate_up1q<Q> (llama_kernels.h:1232-1269): h[r] = silu(Wg[r] . x) * (Wu[r] . x). */
 DOOMS_CUDA_API int32_t dooms_cuda_gate_up(int32_t dtype, const void * d_wg, const void * d_wu, const float * d_x, float * d_h, int64_t rows, int64_t cols,
                                           void * stream);
+/* No counterpart in the reference. The q4_0 / q4_K kernel behind dooms_cuda_matvec / _gate_up multiplies int8 digits on the tensor cores: it works on the
+ * input vector split per 32-element block into a power-of-two scale and four base-128 digits. Given an f32 input it makes that split in its prologue; inside
+ * a decode step the kernel that produced the vector leaves it already split. These entry points are that second form: dooms_cuda_split_input writes the
+ * split of d_x (cols floats) into d_split (dooms_cuda_split_input_bytes(cols) bytes of device memory), dooms_cuda_matvec_split is dooms_cuda_matvec on
+ * it (with d_w2: dooms_cuda_gate_up). Results are bit for bit those of the f32 entry points. DOOMS_UNSUPPORTED for other types or shapes. */
+DOOMS_CUDA_API int64_t dooms_cuda_split_input_bytes(int64_t cols);
+DOOMS_CUDA_API int32_t dooms_cuda_split_input(const float * d_x, int64_t cols, void * d_split, void * stream);
+DOOMS_CUDA_API int32_t dooms_cuda_matvec_split(int32_t dtype, const void * d_w, const void * d_w2, const void * d_split, float * d_y, const float * d_bias, int64_t rows,
+                                               int64_t cols, uint32_t flags, void * stream);
 /* matmul_bigq<Q> / matmul_gate_up_bigq<Q> (llama_kernels.h:1320-1382) on the tcgen05 tensor cores: Y[t][r] (+)= sum_k X[t][k] W[r][k] (+ bias[r]) for
  * `tokens` rows of X, an f16 [tokens][cols] device buffer (cols a multiple of 64; operands are rounded to f16 as the reference's tiles, llama_kernels.h:197).
  * With d_w2: Y[t][r] = silu(X[t] . W[r]) * (X[t] . W2[r]). Y is f32 [tokens][rows]. flags as dooms_cuda_matvec. */

@@ -101,6 +101,29 @@ def test_gate_up_matches_the_oracle(dtype):
     assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 1e-5
 
 
+@pytest.mark.parametrize("dtype,shape", [(L.Q4_0, (300, 4096)), (L.Q4_0, (1152, 896)), (L.Q4_K, (64, 14336)), (L.Q4_0, (4864, 1024))])
+def test_projections_on_an_input_that_is_already_split_give_the_same_bits(dtype, shape):
+    """The integer tensor-core kernel on the split a producer kernel would leave (dooms_cuda_split_input) against the same kernel splitting the f32 input
+    itself: identical results, plain and gate / up."""
+    rows, cols = shape
+    lib = L.lib()
+    bw, bu = random_blocks(dtype, rows, cols, 21), random_blocks(dtype, rows, cols, 22)
+    x = np.random.default_rng(9).standard_normal(cols).astype(np.float32)
+    d_w, d_u, d_x = dev(bw), dev(bu), dev(x)
+    d_split = torch.empty(lib.dooms_cuda_split_input_bytes(cols), dtype=torch.uint8, device="cuda")
+    L.check(lib.dooms_cuda_split_input(d_x.data_ptr(), cols, d_split.data_ptr(), None))
+    a, b = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    L.check(lib.dooms_cuda_matvec(dtype, d_w.data_ptr(), d_x.data_ptr(), a.data_ptr(), None, rows, cols, 0, None))
+    L.check(lib.dooms_cuda_matvec_split(dtype, d_w.data_ptr(), None, d_split.data_ptr(), b.data_ptr(), None, rows, cols, 0, None))
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    L.check(lib.dooms_cuda_gate_up(dtype, d_w.data_ptr(), d_u.data_ptr(), d_x.data_ptr(), a.data_ptr(), rows, cols, None))
+    L.check(lib.dooms_cuda_matvec_split(dtype, d_w.data_ptr(), d_u.data_ptr(), d_split.data_ptr(), b.data_ptr(), None, rows, cols, 0, None))
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    assert lib.dooms_cuda_matvec_split(L.Q8_0, d_w.data_ptr(), None, d_split.data_ptr(), b.data_ptr(), None, rows, cols, 0, None) == L.UNSUPPORTED
+
+
 def test_rms_norm_matches_the_oracle():
     g = np.random.default_rng(0)
     x = g.standard_normal((5, 896)).astype(np.float32) * 3
