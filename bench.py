@@ -506,6 +506,7 @@ def main():
         logits_tp = dec.logits()
         tokens.clear()
         dec.generate(n_gen + 1, args.depth, lambda t: tokens.append(t) or True)
+    tp_flags = dec.timings()
     dec.close()      # every rank at the same point: tearing down the tensor-parallel group is collective
     if rank != 0:
         if world > 1:
@@ -553,6 +554,7 @@ def main():
     else:
         line["cpu_baseline"] = None
     if world > 1:
+        line["tp_allreduce"] = {"peer_memory_kernel": int(tp_flags["tp_peer_allreduce"]), "nccl_symmetric_window": int(tp_flags["tp_symmetric_window"])}
         line["tp_check"] = tp_check(path, prompt, n_gen, n_batch, list(tokens), logits_tp, local)
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -63,7 +63,7 @@ class KernelTime(C.Structure):
 class Timings(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("last_eval_ms", C.c_double), ("last_generate_ms", C.c_double), ("last_eval_launches", C.c_int64),
                 ("last_generate_launches", C.c_int64), ("weight_bytes", C.c_int64), ("kv_bytes", C.c_int64), ("last_batch_ms", C.c_double),
-                ("last_batch_launches", C.c_int64), ("tp_peer_allreduce", C.c_int64)]
+                ("last_batch_launches", C.c_int64), ("tp_peer_allreduce", C.c_int64), ("tp_symmetric_window", C.c_int64)]
 
 
 class LlmOptions(C.Structure):

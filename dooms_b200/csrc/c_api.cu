@@ -376,6 +376,7 @@ DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, doom
         out->last_batch_launches = t.last_batch_launches;
     }
     if (out->struct_size >= offsetof(dooms_cuda_timings, tp_peer_allreduce) + sizeof(int64_t)) out->tp_peer_allreduce = t.tp_peer_allreduce;
+    if (out->struct_size >= offsetof(dooms_cuda_timings, tp_symmetric_window) + sizeof(int64_t)) out->tp_symmetric_window = t.tp_symmetric_window;
     return DOOMS_OK;
 }
 

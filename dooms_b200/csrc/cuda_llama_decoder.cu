@@ -102,6 +102,9 @@ struct CudaLlamaDecoder::Impl {
     float * host_x = nullptr;     // pinned staging for eval_embeddings
     DevState * state = nullptr;
     int32_t * host_error = nullptr;   // mapped pinned word a kernel sets when a bounded wait ran out
+    // tensor parallelism: x, red and tp_pairs in one allocation of NCCL's own (sym_base) registered as a symmetric window (sym_win), when the library
+    // offers that; the three pointers then lie inside it and are not freed on their own
+    void * sym_base = nullptr, * sym_win = nullptr;
     int32_t * tp_pairs = nullptr;  // tensor parallelism: every rank's (best logit, its index) of the current position
     bool logits_gathered = true;   // logits_buf holds every rank's rows (always true on one GPU)
     int splits = 1;
@@ -159,6 +162,8 @@ struct CudaLlamaDecoder::Impl {
         for (void * p : {(void *)h_rows, (void *)h_out}) if (p) cudaFreeHost(p);
         for (void * p : par_opened) cudaIpcCloseMemHandle(p);
         for (void * p : {par_inbox, par_flags, par_words}) if (p) cudaFree(p);
+        if (sym_win) nccl.CommWindowDeregister(comm, sym_win);
+        if (sym_base) { nccl.MemFree(sym_base); x = nullptr; red = nullptr; tp_pairs = nullptr; }
         if (comm) nccl.CommDestroy(comm);
         for (cudaEvent_t e : step_events) cudaEventDestroy(e);
         if (ev_a) cudaEventDestroy(ev_a);
@@ -904,15 +909,33 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     const size_t logits_floats = size_t(m.vocab_stride) * size_t(tp);
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.kc), m.kv_bytes / 2, "the key cache"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.vc), m.kv_bytes / 2, "the value cache"));
-    DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.x), B * size_t(E) * 4, "the residual rows"));
+    if (tp > 1) {
+        // The buffers the ranks reduce and gather: from NCCL's allocator, registered as one symmetric window, so that the 16 KB all-reduces of a decode step
+        // run NCCL's low-latency kernels (DOOMS_TP_SYMMETRIC=0: plain device memory). Every rank takes the same branch: the registration is collective, and
+        // whether the library has the entry points is the same for all of them.
+        const char * sym = getenv("DOOMS_TP_SYMMETRIC");
+        const size_t row_bytes = (B * size_t(E) * 4 + NcclApi::kWinAlignment - 1) & ~(NcclApi::kWinAlignment - 1);
+        const size_t sym_bytes = 2 * row_bytes + NcclApi::kWinAlignment;
+        if (m.nccl.has_windows() && !(sym && *sym == '0') && m.nccl.MemAlloc(&m.sym_base, sym_bytes) == 0 && m.sym_base) {
+            if (m.nccl.CommWindowRegister(m.comm, m.sym_base, sym_bytes, &m.sym_win, NcclApi::kWinCollSymmetric) != 0) m.sym_win = nullptr;
+            cudaMemset(m.sym_base, 0, sym_bytes);
+            m.x = static_cast<float *>(m.sym_base);
+            m.red = reinterpret_cast<float *>(static_cast<char *>(m.sym_base) + row_bytes);
+            m.tp_pairs = reinterpret_cast<int32_t *>(static_cast<char *>(m.sym_base) + 2 * row_bytes);
+        } else {
+            m.sym_base = nullptr;
+            (void)cudaGetLastError();
+        }
+    }
+    if (!m.x) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.x), B * size_t(E) * 4, "the residual rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.xn), B * size_t(E) * 4, "the normalized rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.qkv), B * size_t(m.qkv_width) * 4, "the q/k/v rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.attn), B * size_t(m.attn_width) * 4, "the attention rows"));
     cudaMemset(m.attn, 0, B * size_t(m.attn_width) * 4);
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.h), B * size_t(m.ff) * 4, "the feed-forward rows"));
-    if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
+    if (tp > 1 && !m.red) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.red), B * size_t(E) * 4, "the all-reduce rows"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.logits_buf), logits_floats * 4, "the logits"));
-    if (tp > 1) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tp_pairs), size_t(tp) * 8, "the ranks' argmax pairs"));
+    if (tp > 1 && !m.tp_pairs) DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.tp_pairs), size_t(tp) * 8, "the ranks' argmax pairs"));
     DOOMS_RETURN_IF_ERROR(dev_alloc(reinterpret_cast<void **>(&m.part), part_floats * 4, "the attention partial results"));
     {
         std::vector<double> freq(size_t(c.head_dim / 2));
@@ -1040,6 +1063,7 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
     }
     if (cudaDeviceSynchronize() != cudaSuccess) return internal_error(cuda_msg("setting up the decoder", cudaGetLastError()));
     m.tm.tp_peer_allreduce = m.use_par ? 1 : 0;
+    m.tm.tp_symmetric_window = m.sym_win ? 1 : 0;
     m.tm.weight_bytes = int64_t(m.matrix_bytes);
     m.tm.kv_bytes = int64_t(m.kv_bytes);
     return std::unique_ptr<CudaLlamaDecoder>(new CudaLlamaDecoder(std::move(impl)));

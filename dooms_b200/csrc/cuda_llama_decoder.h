@@ -119,6 +119,7 @@ public:
         double last_batch_ms = 0;            // device time of the last decode_batch call's steps
         int64_t last_batch_launches = 0;
         int64_t tp_peer_allreduce = 0;       // 1: decode steps reduce over peer memory (kernels/allreduce_peer.cu); 0: NCCL, or one GPU
+        int64_t tp_symmetric_window = 0;     // 1: the buffers NCCL reduces lie in a registered symmetric window (its low-latency kernels apply)
     };
     Timings timings() const;
 

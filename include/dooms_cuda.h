@@ -180,6 +180,7 @@ typedef struct dooms_cuda_timings {
     double last_batch_ms;        /* device time of the steps of the last dooms_cuda_llama_decode_batch call (written only when struct_size covers it) */
     int64_t last_batch_launches;
     int64_t tp_peer_allreduce;   /* 1: the tensor-parallel decode steps reduce over peer memory; 0: NCCL's all-reduce, or one GPU */
+    int64_t tp_symmetric_window; /* 1: the buffers NCCL reduces are NCCL's own memory registered as a symmetric window (NCCL 2.27+); 0: plain device memory */
 } dooms_cuda_timings;
 DOOMS_CUDA_API int32_t dooms_cuda_llama_timings(const dooms_cuda_llama * d, dooms_cuda_timings * out);
 

@@ -182,6 +182,8 @@ lg = dec.logits(); toks = []
 dec.generate(12, 2, lambda t: toks.append(t) or True)
 peer = dec.timings()["tp_peer_allreduce"]
 assert peer == (1 if os.environ.get("DOOMS_TP_ALLREDUCE") == "peer" else 0), peer      # the variant under test is the one that ran
+window = dec.timings()["tp_symmetric_window"]
+if os.environ.get("DOOMS_TP_SYMMETRIC") == "0": assert window == 0, window
 if rank == 0:
     ref = CudaLlamaDecoder.load(path, 512, 128, device=local)
     ref.eval_tokens(prompt)
@@ -192,25 +194,25 @@ if rank == 0:
     # ~1e-4 .. 1e-3, the same effect the reference's one-call bound allows for.
     assert err < 3e-3, err
     assert toks == tr, (toks, tr)
-    print("tp ok", world, err)
+    print("tp ok", world, err, "symmetric window", window)
 dist.barrier()
 dist.destroy_process_group()
 """
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("allreduce,case", [("nccl", "even"), ("peer", "even"), ("nccl", "cover")])
-def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, allreduce, case):
+@pytest.mark.parametrize("allreduce,case,symmetric", [("nccl", "even", "1"), ("nccl", "even", "0"), ("peer", "even", "1"), ("nccl", "cover", "1")])
+def test_tensor_parallel_decoder_matches_one_gpu(tmp_path, allreduce, case, symmetric):
     """Two ranks against one GPU: last-position logits and greedy tokens; with NCCL's all-reduce and with the peer-memory all-reduce + add kernel; and
     on a model whose column shards do not fall on block boundaries (every rank holds the covering blocks of attn_output, the feed-forward width is dealt
-    in whole blocks)."""
+    in whole blocks). symmetric: the reduced buffers as a registered NCCL window (where the library has them) or as plain device memory."""
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "child.py"
     script.write_text(NCCL_CHILD)
-    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0", DOOMS_TP_ALLREDUCE=allreduce, DOOMS_TP_CASE=case)
+    env = dict(os.environ, DOOMS_ROOT=str(ROOT), DOOMS_TP_MODEL=str(tmp_path / "tp.gguf"), NCCL_NVLS_ENABLE="0", DOOMS_TP_ALLREDUCE=allreduce, DOOMS_TP_CASE=case, DOOMS_TP_SYMMETRIC=symmetric)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port",
                         "29534", str(script)], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
