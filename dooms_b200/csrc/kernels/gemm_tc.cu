@@ -204,6 +204,8 @@ struct GemmTcParams {
     int pair;                  // (the two-matrix kernel) the second matrix is the next 128 rows of W: one block computes 256 weight rows against its token tile
     int ks_per;                // k steps per block along gridDim.z (0: all of them, one block per tile); block z writes its sum to Y + z * split_stride
     int64_t split_stride;
+    int tile0, tiles_n;        // the block's tile is tile0 + blockIdx.x: row tile = that % tiles_n, token tile = that / tiles_n
+    float * gate_shares;       // (two matrices, ks_per > 0) the raw sums of block (x, z): [x][z][matrix][token of the tile][row of the tile] floats
     int32_t * error;
 };
 
@@ -225,8 +227,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const uint32_t consumed = tmem_slot + 4;       // steps whose stage is free again, counted by the tracker lane
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const bool pair = GATE && p.pair;
-    const int64_t n0 = int64_t(blockIdx.x) * (pair ? 2 * kRowsW : kRowsW);
-    const int m0 = blockIdx.y * p.T;
+    const int tile = p.tile0 + int(blockIdx.x);
+    const int64_t n0 = int64_t(tile % p.tiles_n) * (pair ? 2 * kRowsW : kRowsW);
+    const int m0 = (tile / p.tiles_n) * p.T;
     // a share of the reduction (f16-row path only): k steps ks0 .. ks0 + ksteps - 1
     const int ks0 = p.ks_per > 0 ? int(blockIdx.z) * p.ks_per : 0;
     const int ksteps = p.ks_per > 0 ? min(p.K / kStepK - ks0, p.ks_per) : p.K / kStepK;
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             uint32_t raw[NMAT][36];
             #pragma unroll
             for (int mtx = 0; mtx < NMAT; mtx++) {
-                const uint4 * src = reinterpret_cast<const uint4 *>(wrow[mtx] + size_t(g) * 144);
+                const uint4 * src = reinterpret_cast<const uint4 *>(wrow[mtx] + size_t(ks0 / 4 + g) * 144);
                 #pragma unroll
                 for (int i = 0; i < 9; i++) {
                     const uint4 v = __ldg(src + i);
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             #pragma unroll
             for (int mtx = 0; mtx < NMAT; mtx++) {
                 uint4 v[4];
-                dequant32<DT>(wrow[mtx], uint32_t(ks * kStepK + half * 32), v);
+                dequant32<DT>(wrow[mtx], uint32_t((ks0 + ks) * kStepK + half * 32), v);
                 const uint32_t tile = smem0 + s * stage_bytes + mtx * kTileWBytes + dst_row;
                 #pragma unroll
                 for (int c = 0; c < 4; c++) {
@@ -390,6 +393,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             const int q = warp & 3, colhalf = warp >> 2;
             const int cols_per_warp = p.T / 2;
             float * const Y = p.Y ? p.Y + (p.ks_per > 0 ? int64_t(blockIdx.z) * p.split_stride : 0) : nullptr;
+            if (GATE && !pair && p.gate_shares) {
+                // a share of a gate / up tile's reduction: both raw sums go out as they are; k_gate_up_combine adds the shares and applies silu(g) * u
+                float * dst = p.gate_shares + (int64_t(blockIdx.x) * gridDim.z + blockIdx.z) * 2 * p.T * kRowsW + q * 32 + lane;
+                for (int c0 = colhalf * cols_per_warp; c0 < (colhalf + 1) * cols_per_warp; c0 += 32) {
+                    uint32_t acc[32], acc2[32];
+                    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c0);
+                    tc_ld32(taddr, acc);
+                    tc_ld32(taddr + 256u, acc2);
+                    #pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        dst[int64_t(c0 + j) * kRowsW] = __uint_as_float(acc[j]);
+                        dst[int64_t(p.T + c0 + j) * kRowsW] = __uint_as_float(acc2[j]);
+                    }
+                }
+            } else
             // pair: the second accumulator holds the next 128 weight rows, with the same epilogue as the first
             for (int part = 0; part < (pair ? 2 : 1); part++) {
                 const int64_t n = n0 + part * kRowsW + q * 32 + lane;
@@ -446,17 +464,73 @@ EncodeTiledFn encode_tiled() {
 }
 
 template <int DT, bool PRE>
-cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const CUtensorMap & w2map, const GemmTcParams & p, bool gate, cudaStream_t stream) {
+cudaError_t launch_tiles(const CUtensorMap & map, const CUtensorMap & wmap, const CUtensorMap & w2map, const GemmTcParams & p, bool gate, int n_tiles, cudaStream_t stream) {
     const size_t stage = (gate ? 2 : 1) * size_t(kTileWBytes) + size_t(p.T) * 128;
     const size_t smem = (gate ? 3 : 4) * stage + 1024 + 256;
-    const int64_t rows_per_block = p.pair ? 2 * kRowsW : kRowsW;
     const int k_blocks = p.ks_per > 0 ? (p.K / kStepK + p.ks_per - 1) / p.ks_per : 1;
-    const dim3 grid(unsigned((p.N + rows_per_block - 1) / rows_per_block), unsigned((p.M + p.T - 1) / p.T), unsigned(k_blocks));
+    const dim3 grid(unsigned(n_tiles), 1u, unsigned(k_blocks));
     static std::atomic<uint64_t> configured[2];
     if (const cudaError_t e = gate ? allow_dynamic_smem(k_gemm_tc<DT, true, PRE>, 220 * 1024, configured[1])
                                    : allow_dynamic_smem(k_gemm_tc<DT, false, PRE>, 220 * 1024, configured[0]); e != cudaSuccess) return e;
     if (gate) k_gemm_tc<DT, true, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
     else k_gemm_tc<DT, false, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
+    return cudaGetLastError();
+}
+
+// Adds the shares of the tiles tile0 .. tile0 + gridDim.x - 1 of a gate / up product in a fixed order and writes silu(gate) * up as f16 (the epilogue of
+// the unsplit tile, matmul_gate_up_bigq, src/backend/metal/llama_kernels.h:1351-1382).
+__global__ void __launch_bounds__(256) k_gate_up_combine(const float * shares, int n_shares, int tile0, int tiles_n, int T, float * Y, int64_t y_stride, __half * Y16,
+                                                         int64_t y16_stride, int64_t N, int M) {
+    const int tile = tile0 + int(blockIdx.x);
+    const int64_t n0 = int64_t(tile % tiles_n) * kRowsW;
+    const int m0 = (tile / tiles_n) * T;
+    const int64_t plane = int64_t(T) * kRowsW;
+    const float * mine = shares + int64_t(blockIdx.x) * n_shares * 2 * plane;
+    for (int idx = int(blockIdx.y) * 256 + int(threadIdx.x); idx < T * kRowsW; idx += int(gridDim.y) * 256) {
+        const int j = idx / kRowsW, r = idx % kRowsW;
+        float g = 0.f, u = 0.f;
+        for (int z = 0; z < n_shares; z++) {
+            g += __ldcg(mine + (int64_t(z) * 2) * plane + idx);
+            u += __ldcg(mine + (int64_t(z) * 2 + 1) * plane + idx);
+        }
+        if (m0 + j < M && n0 + r < N) {
+            const float v = g / (1.f + expf(-g)) * u;
+            if (Y) Y[int64_t(m0 + j) * y_stride + n0 + r] = v;
+            if (Y16) Y16[int64_t(m0 + j) * y16_stride + n0 + r] = __float2half_rn(v);
+        }
+    }
+}
+
+// All tiles of a product. A fused gate / up product whose tiles do not fill the last wave of blocks (896 tiles on 148 SMs: six waves and eight tiles) runs
+// its leftover tiles with their reduction dealt over the idle SMs (shares of whole 256-element groups), so that the last wave is short instead of as long
+// as the others; `scratch` holds the shares' raw sums until k_gate_up_combine has applied the epilogue.
+template <int DT, bool PRE>
+cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const CUtensorMap & w2map, GemmTcParams p, bool gate, cudaStream_t stream,
+                      void * scratch = nullptr, size_t scratch_bytes = 0) {
+    const int64_t rows_per_block = p.pair ? 2 * kRowsW : kRowsW;
+    p.tiles_n = int((p.N + rows_per_block - 1) / rows_per_block);
+    const int tiles = p.tiles_n * ((p.M + p.T - 1) / p.T);
+    p.tile0 = 0;
+    p.gate_shares = nullptr;
+    static const bool tail_off = [] { const char * e = getenv("DOOMS_GEMM_TAIL"); return e && *e == '0'; }();
+    const int sms = sm_count(), left = tiles % sms, ksteps = p.K / kStepK;
+    int per = 0, shares = 0;
+    if (!tail_off && gate && !p.pair && !PRE && p.ks_per == 0 && scratch && tiles > sms && left > 0 && left * 4 <= sms && ksteps >= 16 && ksteps % 4 == 0) {
+        const int want = std::min(sms / left, ksteps / 4);
+        per = ((ksteps / 4 + want - 1) / want) * 4;
+        shares = (ksteps + per - 1) / per;
+        if (shares < 2 || size_t(left) * shares * 2 * p.T * kRowsW * sizeof(float) > scratch_bytes) shares = 0;
+    }
+    if (shares == 0) return launch_tiles<DT, PRE>(map, wmap, w2map, p, gate, tiles, stream);
+    cudaError_t e = launch_tiles<DT, PRE>(map, wmap, w2map, p, gate, tiles - left, stream);
+    if (e != cudaSuccess) return e;
+    GemmTcParams t = p;
+    t.tile0 = tiles - left;
+    t.ks_per = per;
+    t.gate_shares = static_cast<float *>(scratch);
+    e = launch_tiles<DT, PRE>(map, wmap, w2map, t, gate, left, stream);
+    if (e != cudaSuccess) return e;
+    k_gate_up_combine<<<dim3(unsigned(left), 16u), 256, 0, stream>>>(t.gate_shares, shares, t.tile0, p.tiles_n, p.T, p.Y, p.y_stride, p.Y16, p.y16_stride, p.N, p.M);
     return cudaGetLastError();
 }
 
@@ -574,7 +648,7 @@ cudaError_t launch_gemm_tc_rows16(const void * W16, const void * W2_16, const Te
                                   int64_t y_stride, int64_t y16_stride, uint32_t flags, int32_t * error, cudaStream_t stream, int k_splits, int64_t split_stride) {
     if (!W16 || N < 1 || K < kStepK || K % kStepK != 0 || M < 1 || (reinterpret_cast<uintptr_t>(W16) & 15u) || (reinterpret_cast<uintptr_t>(W2_16) & 15u)) return cudaErrorInvalidValue;
     if (k_splits > 1 && (k_splits != k_splits_of_rows16(M, N, K) || W2_16 || !Y || Y16 || flags || split_stride < int64_t(M) * y_stride)) return cudaErrorInvalidValue;
-    GemmTcParams p{nullptr, nullptr, Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride, flags, M > 128 ? 256 : 128, 0, 0, 0, 0, error};
+    GemmTcParams p{nullptr, nullptr, Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride, flags, M > 128 ? 256 : 128, 0, 0, 0, 0, 0, 0, nullptr, error};
     return launch_rows16(p, *reinterpret_cast<const CUtensorMap *>(xmap), static_cast<const __half *>(W16), static_cast<const __half *>(W2_16), M, N, K, k_splits,
                          split_stride, stream);
 }
@@ -592,7 +666,7 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
         return cudaErrorInvalidValue;
     }
     GemmTcParams p{static_cast<const uint8_t *>(W), static_cast<const uint8_t *>(W2), Y, static_cast<__half *>(Y16), bias, N, int(K), M, y_stride, y16_stride,
-                   flags, M > 128 ? 256 : 128, 0, 0, 0, 0, error};
+                   flags, M > 128 ? 256 : 128, 0, 0, 0, 0, 0, 0, nullptr, error};
     p.wide = (dt == kQ4_0 || dt == kQ4_K) && K % 256 == 0 && (reinterpret_cast<uintptr_t>(W) & 15u) == 0 && (!W2 || (reinterpret_cast<uintptr_t>(W2) & 15u) == 0) ? 1 : 0;
     const CUtensorMap & map = *reinterpret_cast<const CUtensorMap *>(xmap);
     const bool gate = W2 != nullptr;
@@ -613,10 +687,10 @@ cudaError_t launch_gemm_tc(int dt, const void * W, const void * W2, const Tensor
     }
     switch (dt) {
         case kF16: return launch_dt<kF16, false>(map, map, map, p, gate, stream);
-        case kQ4_0: return launch_dt<kQ4_0, false>(map, map, map, p, gate, stream);
+        case kQ4_0: return launch_dt<kQ4_0, false>(map, map, map, p, gate, stream, w16_scratch, w16_bytes);
         case kQ5_0: return launch_dt<kQ5_0, false>(map, map, map, p, gate, stream);
         case kQ8_0: return launch_dt<kQ8_0, false>(map, map, map, p, gate, stream);
-        case kQ4_K: return launch_dt<kQ4_K, false>(map, map, map, p, gate, stream);
+        case kQ4_K: return launch_dt<kQ4_K, false>(map, map, map, p, gate, stream, w16_scratch, w16_bytes);
         case kQ6_K: return launch_dt<kQ6_K, false>(map, map, map, p, gate, stream);
     }
     return cudaErrorInvalidValue;

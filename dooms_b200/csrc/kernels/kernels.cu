@@ -75,11 +75,13 @@ __global__ void k_embed(const uint8_t * table, const int32_t * ids, const int32_
 // trip to L2 per loop iteration; rows wider than kNormMaxPerThread x 1024 take the looping path. Element i belongs to thread (i / 32) % 32 * 32 + i % 32
 // of pass i / 1024: a warp holds whole 32-element blocks, which is what the split for the staged q4_0 GEMV needs.
 // xq (optional, one row only, E a multiple of 32): the normalized row also split for that kernel (xsplit.cuh).
-constexpr int kNormThreads = 1024, kNormMaxPerThread = 8;
+// Many rows (a prefill chunk, a batched step) take blocks of 256 threads with up to 16 elements each: eight blocks share an SM and cover each other's
+// round trips, where 1024-thread blocks ran in waves of two per SM (22 us for 2048 rows of 4096 floats; the bytes alone are 8 us).
+template <int kNormThreads, int kNormMaxPerThread>
 __global__ void __launch_bounds__(kNormThreads) k_rms_norm(const float * x, const float * gamma, float * out, __half * out16, uint8_t * xq, int E, float eps) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float red[32];
+    __shared__ float red[kNormThreads / 32];
     const float * xr = x + int64_t(blockIdx.x) * E;
     const int64_t obase = int64_t(blockIdx.x) * E;
     const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(kNormThreads) k_rms_norm(const float * x, cons
         __syncthreads();
         float total = 0.f;
         #pragma unroll
-        for (int w = 0; w < 32; w++) total += red[w];
+        for (int w = 0; w < kNormThreads / 32; w++) total += red[w];
         const float inv = rsqrtf(total / float(E) + eps);
         #pragma unroll
         for (int k = 0; k < kNormMaxPerThread; k++) {
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kNormThreads) k_rms_norm(const float * x, cons
     if (lane == 0) red[warp] = ss;
     __syncthreads();
     float total = 0.f;
-    for (int w = 0; w < 32; w++) total += red[w];
+    for (int w = 0; w < kNormThreads / 32; w++) total += red[w];
     const float inv = rsqrtf(total / float(E) + eps);
     for (int i0 = warp * 32; i0 < E; i0 += kNormThreads) {
         const int i = i0 + lane;
@@ -518,7 +520,10 @@ cudaError_t launch_embed(int dt, const void * table, const int32_t * ids, const 
 
 cudaError_t launch_rms_norm(const float * x, const float * gamma, float * out, void * out16, void * xq, int rows, int E, float eps, cudaStream_t stream) {
     if (xq && (rows != 1 || E % 32 != 0)) return cudaErrorInvalidValue;
-    return launch_pdl(k_rms_norm, dim3(rows), dim3(kNormThreads), 0, stream, x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
+    if (rows >= 64 && E <= 256 * 16) {
+        return launch_pdl(k_rms_norm<256, 16>, dim3(rows), dim3(256), 0, stream, x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
+    }
+    return launch_pdl(k_rms_norm<1024, 8>, dim3(rows), dim3(1024), 0, stream, x, gamma, out, static_cast<__half *>(out16), static_cast<uint8_t *>(xq), E, eps);
 }
 
 cudaError_t launch_matvec(int dt, const void * W, const float * x, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream) {

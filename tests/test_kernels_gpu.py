@@ -200,12 +200,14 @@ def test_kernel_entry_points_reject_bad_arguments():
 
 
 @pytest.mark.parametrize("dtype", MATRIX_TYPES)
-@pytest.mark.parametrize("shape", [(45, 300, 256), (130, 128, 512), (1, 129, 64), (257, 256, 1024), (600, 200, 512)])
+@pytest.mark.parametrize("shape", [(45, 300, 256), (130, 128, 512), (1, 129, 64), (257, 256, 1024), (600, 200, 512), (2000, 2500, 1024)])
 @pytest.mark.parametrize("gate", [False, True])
 def test_tensor_core_matmul_matches_the_oracle(dtype, shape, gate):
     """The tcgen05 prefill GEMM against float64 products of the checker's dequantized weights rounded to f16 (the operand rounding of the reference's
-    tiles, src/backend/metal/llama_kernels.h:186-199); tokens and rows that are no multiple of the 128-wide tiles. From 512 tokens on the entry point
-    dequantizes the matrix to f16 rows first and feeds both operands by TMA (the 600-token shape)."""
+    tiles, src/backend/metal/llama_kernels.h:186-199); tokens and rows that are no multiple of the 128-wide tiles. From 128 tokens on the entry point
+    dequantizes the matrix to f16 rows first and feeds both operands by TMA (except q4_0 / q4_K gate / up, which stay fused). The last shape is 160
+    tiles: more than one wave of blocks, so its one-matrix form runs as blocks of 256 weight rows and its fused gate / up form deals the reduction of
+    the tiles left over after the last full wave over the idle SMs."""
     tokens, rows, cols = shape
     if cols % L.BLOCK_ELEMS[dtype]:
         pytest.skip("rows are not whole blocks of this type")
