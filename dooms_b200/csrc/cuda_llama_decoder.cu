@@ -119,6 +119,13 @@ struct CudaLlamaDecoder::Impl {
     int * attn_counters = nullptr; // one per key/value head: blocks of the decode attention that have finished (zero between launches)
     void * w16 = nullptr;           // room for the largest matrix (pair) as f16 rows: chunks of 128 tokens or more dequantize a matrix once per call
     size_t w16_bytes = 0;
+    // Chunks of 128 tokens or more: the f16 rows of the next projection are written on a second stream while the kernels before it run (two buffers taken
+    // in turn; an event per buffer says when it is filled, another when the product that read it is done).
+    cudaStream_t side = nullptr;
+    __half * rows_buf[2] = {nullptr, nullptr};
+    cudaEvent_t rows_filled[2] = {nullptr, nullptr}, rows_freed[2] = {nullptr, nullptr};
+    int rows_next = 0;
+    bool rows_ahead = false;
     int * split_counters = nullptr; // one per 32 rows of h: rows written by the gate/up GEMV's blocks (zero between launches)
     // The norm between two projections of a decode step, folded into the producer (kernels.h, GemvNormLink): the projection that finishes the residual row
     // x leaves x * (the next norm's gains) split in xq2 and its blocks' sums of squares in norm_ss; the next projection takes both instead of reading,
@@ -155,6 +162,12 @@ struct CudaLlamaDecoder::Impl {
 
     ~Impl() {
         if (stream) cudaStreamSynchronize(stream);
+        if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
+        for (int i = 0; i < 2; i++) {
+            if (rows_filled[i]) cudaEventDestroy(rows_filled[i]);
+            if (rows_freed[i]) cudaEventDestroy(rows_freed[i]);
+            if (rows_buf[i]) cudaFree(rows_buf[i]);
+        }
         if (step_graph) cudaGraphExecDestroy(step_graph);      // a graph that holds captured NCCL work has to go before its communicator
         cuda::decode_layers_destroy(fused);
         for (auto & g : batch_graphs) cudaGraphExecDestroy(g.second);
@@ -322,6 +335,21 @@ struct CudaLlamaDecoder::Impl {
                                         host_error, stream, w16, w16_bytes);
         });
     }
+    // Starts writing the f16 rows of w into the next of the two buffers, on the second stream, as soon as the product that last read that buffer is done.
+    int rows_prefetch(const MatDev & w) {
+        const int s = rows_next;
+        rows_next ^= 1;
+        cudaStreamWaitEvent(side, rows_freed[s], 0);
+        run("dequant", [&] { return cuda::launch_dequant_rows16(int(w.dt), w.ptr, rows_buf[s], w.rows, w.cols, side); });
+        cudaEventRecord(rows_filled[s], side);
+        return s;
+    }
+    // The product on the rows that rows_prefetch put into buffer s.
+    void gemm_from_rows(const char * kind, const MatDev & w, int s, const cuda::TensorMap & map, float * out, const float * bias, int M, int64_t out_stride, uint32_t flags) {
+        cudaStreamWaitEvent(stream, rows_filled[s], 0);
+        run(kind, [&] { return cuda::launch_gemm_tc_rows16(rows_buf[s], nullptr, &map, out, nullptr, bias, M, w.rows, w.cols, out_stride, 0, flags, host_error, stream); });
+        cudaEventRecord(rows_freed[s], stream);
+    }
     // x[m] += X16[m] . W[n] for the rows of a batched step. Few weight rows against one token tile would run on a handful of SMs, so the reduction
     // dimension is dealt over several blocks per tile where that pays; their sums are added onto x in a fixed order.
     void gemm_tc_into_x(const char * kind, const MatDev & w, const cuda::TensorMap & map, int M) {
@@ -455,6 +483,7 @@ struct CudaLlamaDecoder::Impl {
     // (encode_forward, metal_llama_decoder.mm:311-385).
     void forward(int M, bool advance) {
         const int E = cfg.n_embd;
+        int rows_slot = 0;
         const AttnShape as = attn_shape();
         const bool single = tp == 1;
         link_ready = false;      // x was just written by the embedding (or by the caller)
@@ -511,6 +540,22 @@ struct CudaLlamaDecoder::Impl {
                 }
                 matvec("ffn_down", L.ffn_down, h, nullptr, o_dst, nullptr, o_flags, after_gamma);
                 reduce_into_x(1);
+            } else if (use_tc && rows_ahead && M >= 128 && !profile) {
+                // (the chunk's norm above wrote xn16) Every projection but the fused gate / up reads f16 rows that were written while the kernels before
+                // it ran: the rows of attn_output during the qkv product, those of ffn_down during attention, the next layer's qkv during gate / up.
+                if (l == 0) rows_slot = rows_prefetch(L.qkv[0].w);
+                const int slot_qkv = rows_slot, slot_o = rows_prefetch(L.attn_output);
+                gemm_from_rows("qkv", L.qkv[0].w, slot_qkv, map_xn, qkv, L.qkv_bias, M, qkv_width, L.qkv_bias ? kFlagBias : 0u);
+                run("rope_store", [&] { return cuda::launch_rope_store(qkv, kcl, vcl, state, inv_freq, M, as, stream); });
+                prefill_attention(kcl, vcl, attn16, M, as);
+                const int slot_down = rows_prefetch(L.ffn_down);
+                gemm_from_rows("attn_output", L.attn_output, slot_o, map_attn, o_dst, nullptr, M, E, o_flags);
+                reduce_into_x(M);
+                norm(x, L.ffn_norm, M, false, true);
+                gemm_tc("gate_up", L.ffn_gate, &L.ffn_up, map_xn, nullptr, h16, nullptr, M, 0, ff, 0u);
+                if (l + 1 < layers.size()) rows_slot = rows_prefetch(layers[l + 1].qkv[0].w);
+                gemm_from_rows("ffn_down", L.ffn_down, slot_down, map_h, o_dst, nullptr, M, E, o_flags);
+                reduce_into_x(M);
             } else if (use_tc) {
                 // (the chunk's norm above wrote xn16)
                 for (const QkvPart & q : L.qkv) {
@@ -970,6 +1015,29 @@ Result<std::unique_ptr<CudaLlamaDecoder>> CudaLlamaDecoder::create(const LlamaDe
         }
         if (B >= 128 && largest > 0 && cudaMalloc(&m.w16, largest) == cudaSuccess) m.w16_bytes = largest;      // optional: without it the GEMM dequantizes per tile
         else { (void)cudaGetLastError(); m.w16 = nullptr; }
+        {
+            // the two buffers of the rows written ahead: when every layer has one qkv matrix and none of these matrices is f16 already
+            size_t single = 0;
+            bool all = B >= 128 && m.w16 != nullptr;
+            for (const LayerDev & L : m.layers) {
+                all = all && L.qkv.size() == 1;
+                for (const MatDev * w : {L.qkv.empty() ? &L.attn_output : &L.qkv[0].w, &L.attn_output, &L.ffn_down}) {
+                    all = all && w->dt != DType::F16;
+                    single = std::max(single, size_t(w->rows) * size_t(w->cols) * 2);
+                }
+            }
+            const char * ahead = getenv("DOOMS_PREFILL_ROWS_AHEAD");
+            if (all && single > 0 && !(ahead && *ahead == '0') && cudaStreamCreateWithFlags(&m.side, cudaStreamNonBlocking) == cudaSuccess) {
+                bool ok = true;
+                for (int i = 0; i < 2; i++) {
+                    ok = ok && cudaMalloc(reinterpret_cast<void **>(&m.rows_buf[i]), single) == cudaSuccess;
+                    ok = ok && cudaEventCreateWithFlags(&m.rows_filled[i], cudaEventDisableTiming) == cudaSuccess;
+                    ok = ok && cudaEventCreateWithFlags(&m.rows_freed[i], cudaEventDisableTiming) == cudaSuccess;
+                }
+                m.rows_ahead = ok;
+            }
+            (void)cudaGetLastError();
+        }
         for (const LayerDev & L : m.layers) {
             for (const QkvPart & q : L.qkv) m.tc_capable = m.tc_capable && cuda::gemm_tc_supported(int(q.w.dt), q.w.ptr, q.w.rows, q.w.cols);
             for (const MatDev * w : {&L.attn_output, &L.ffn_gate, &L.ffn_up, &L.ffn_down}) {
