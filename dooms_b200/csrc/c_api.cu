@@ -607,6 +607,14 @@ DOOMS_CUDA_API int32_t dooms_cuda_matvec(int32_t dtype, const void * d_w, const 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == DOOMS_Q4_0 && cuda::gemv_q4_0_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, false, st, "matvec");
     if (dtype == DOOMS_Q4_K && cuda::gemv_q4_k_supported(d_w, rows, cols)) return fast_q4_0(d_w, nullptr, d_x, d_y, d_bias, rows, cols, flags, true, st, "matvec");
+    if (dtype == DOOMS_Q6_K && cuda::gemv_q6_k_supported(d_w, rows, cols)) {
+        void * scratch = nullptr;
+        const Status ss = scratch_for((cuda::quantized_x_bytes(cols) + 15) & ~size_t(15), &scratch);
+        if (!ss.is_ok()) return done(ss);
+        cudaError_t e = cuda::launch_quantize_x(d_x, cols, scratch, st);
+        if (e == cudaSuccess) e = cuda::launch_gemv_q6_k(d_w, scratch, d_y, d_bias, rows, cols, flags, st);
+        return launch_result(e, "matvec");
+    }
     return launch_result(cuda::launch_matvec(dtype, d_w, d_x, d_y, d_bias, rows, cols, flags, st), "matvec");
 }
 

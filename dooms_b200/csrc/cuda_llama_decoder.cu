@@ -275,6 +275,17 @@ struct CudaLlamaDecoder::Impl {
             return;
         }
         if (writes_x) link_ready = false;
+        if (w.dt == DType::Q6_K && cuda::gemv_q6_k_supported(w.ptr, w.rows, w.cols) && (!gamma || (in == x && cfg.n_embd % 32 == 0))) {
+            // the integer tensor-core kernel for q6_K works on the split input: left by the norm, or made by one small kernel
+            if (gamma) {
+                norm(in, gamma, 1, true);
+            } else if (xq_of != in) {
+                run("split", [&] { return cuda::launch_quantize_x(in, w.cols, xq, stream); });
+                xq_of = in;
+            }
+            run(kind, [&] { return cuda::launch_gemv_q6_k(w.ptr, xq, out, bias, w.rows, w.cols, flags, stream); });
+            return;
+        }
         if (cuda::gemv_blocks_supported(int(w.dt), w.ptr, in, w.rows, w.cols)) {
             run(kind, [&] { return cuda::launch_gemv_blocks(int(w.dt), w.ptr, nullptr, in, gamma, cfg.rms_eps, out, bias, w.rows, w.cols, flags, stream); });
             return;

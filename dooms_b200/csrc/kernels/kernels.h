@@ -126,6 +126,11 @@ cudaError_t launch_argmax_pairs(const void * pairs, int n_ranks, int32_t * token
 cudaError_t launch_argmax_plain(const float * logits, int64_t n, int32_t * out, void * part, cudaStream_t stream);
 
 // ---- the fast decode GEMV on q4_0 rows (gemv_q4_0.cu) ----
+// q6_K rows on the int8 tensor-core path (gemv_q6_k.cu): y (+)= W x (+ bias) on an input that is already split (launch_quantize_x, or a norm that leaves
+// the split). Takes 16-byte aligned matrices with rows of whole super-blocks, up to 40960 columns.
+bool gemv_q6_k_supported(const void * W, int64_t rows, int64_t cols);
+cudaError_t launch_gemv_q6_k(const void * W, const void * xq, float * y, const float * bias, int64_t rows, int64_t cols, uint32_t flags, cudaStream_t stream);
+
 // The streaming GEMV for any block format (gemv_blocks.cu): y (+)= W x (+ bias), or with W2 the fused gate/up h = silu(W x) * (W2 x). Takes 16-byte aligned
 // W and x and rows of whole blocks that fit its shared-memory plan; launch_matvec / launch_gate_up use it whenever it takes the call.
 bool gemv_blocks_supported(int dt, const void * W, const void * x, int64_t rows, int64_t cols);
