@@ -6,11 +6,12 @@
 //   * one m16n8k32 MMA takes 32 consecutive elements of 16 rows; its 8 columns are (16-element sub-block, digit): column c carries digit c % 4 of the
 //     input's first 16 elements (c < 4) or last 16 (c >= 4) and zeros in the other half, so every (row, sub-block, digit) sum comes out on its own and can
 //     take the sub-block's scale;
-//   * the weights go in unsigned and in two parts that add up to q: the low nibbles (0..15) and the high bit pairs shifted into place (0, 16, 32, 48),
-//     two MMAs into the same accumulator, one AND or shift-AND per register instead of assembling q; the offset -32 becomes -32 * sum(x) per sub-block,
-//     with the sums of the input's 16-element sub-blocks computed once per block from its digits;
+//   * the weights go in as two parts that add up to q - 32: the low nibbles, unsigned (0..15), and the high bit pairs shifted into place with the
+//     offset folded in, signed (-32, -16, 0, 16): two MMAs into the same accumulator, a few logic operations per register instead of assembling q;
 //   * rows stream through per-warp rings of shared-memory stages as they lie in the file (210-byte super-blocks at 2-byte alignment: 16-byte asynchronous
-//     copies of the aligned cover; words that end up 2 bytes off a 4-byte boundary are read as two aligned words and a funnel shift).
+//     copies of the aligned cover; words that end up 2 bytes off a 4-byte boundary are read as two aligned words and a funnel shift), and the input's
+//     digits and factors for a unit's super-blocks travel with the unit's rows (1088 bytes per super-block from L2), so that shared memory holds rings
+//     for 16 warps whatever the row length.
 // Integer sums are exact; the only rounding is that of the f32 scale factors and of the f32 accumulation over sub-blocks, as in the q4_0 kernel.
 #include <cuda_fp16.h>
 
@@ -73,13 +74,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
     const int total_units = ntiles * p.nchunks;
     const int my_units = warp < total_units ? (total_units - warp - 1) / WARPS + 1 : 0;
 
-    // shared memory: the input's digits (nb32 x 128), its per-block factors (nb32 x 2 floats), the sums of its 16-element sub-blocks (nb32 x 2 floats), the
-    // warps' stages, the table of the warps' sums
+    // shared memory: the warps' stages (16 rows, then the digits of the chunk's input blocks, then their factors), the table of the warps' sums
     const uint32_t smem_base = smem_u32(smem);
-    const uint32_t xl = smem_base, sxp = xl + uint32_t(nb32) * 128u, sum16 = sxp + uint32_t(nb32) * 8u;
     const uint32_t stride = uint32_t(p.stride);
-    const uint32_t stage_bytes = uint32_t(kTileRows) * stride;
-    const uint32_t stages_off = (uint32_t(nb32) * 144u + 127u) & ~127u;
+    const uint32_t rows_bytes = uint32_t(kTileRows) * stride;
+    const uint32_t x_bytes = uint32_t(p.cbk) * 8u * 136u;             // 8 blocks of 32 elements per super-block: 128 digit bytes and 2 floats each
+    const uint32_t stage_bytes = rows_bytes + x_bytes;
+    const uint32_t stages_off = 0u;
     const uint32_t my_stages = smem_base + stages_off + uint32_t(warp) * STAGES * stage_bytes;
     float * partial = reinterpret_cast<float *>(smem + stages_off + size_t(WARPS) * STAGES * stage_bytes);      // [tile][warp][16]
 
@@ -97,7 +98,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
         piece_rows[k / 8] |= (row & 15u) << (4 * (k % 8));
     }
     const int last_rows = nrows - 1 - (ntiles - 1) * kTileRows;
-    auto fetch = [&]() {
+    // the input's part of a unit: the digits of its 8 cbk blocks (contiguous in xq), then their factors
+    auto fetch_x = [&](int chunk, int slot) {
+        const uint32_t dst = my_stages + uint32_t(slot) * stage_bytes + rows_bytes;
+        const uint32_t blk0 = uint32_t(chunk * p.cbk) * 8u, n_digit = uint32_t(p.cbk) * 64u, n_all = n_digit + uint32_t(p.cbk) * 4u;
+        for (uint32_t i = lane; i < n_all; i += 32u) {
+            const uint8_t * src = i < n_digit ? p.xq + size_t(blk0) * 128 + size_t(i) * 16 : p.xq + size_t(nb32) * 128 + size_t(blk0) * 8 + size_t(i - n_digit) * 16;
+            cp_async16(dst + i * 16u, src);
+        }
+    };
+    auto fetch = [&](bool with_x) {
+        if (with_x) fetch_x(f_chunk, f_slot);
         const uint8_t * base = p.W + (R0 + f_tile * kTileRows) * int64_t(RB) + uint32_t(f_chunk) * CB;
         const uint32_t lo = uint32_t(reinterpret_cast<uintptr_t>(base));
         const uint32_t dst0 = my_stages + uint32_t(f_slot) * stage_bytes;
@@ -116,36 +127,23 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
         if (++f_slot == STAGES) f_slot = 0;
     };
 
+    // The rows of the first STAGES - 1 units are asked for before the wait for the kernel that wrote the input; the input's parts of those units follow it.
     int fetched = 0;
     pdl_trigger();
+    int first_chunk[STAGES - 1];
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        if (fetched < my_units) { fetch(); fetched++; }
-        cp_async_commit();
+        first_chunk[s] = f_chunk;
+        if (fetched < my_units) { fetch(false); fetched++; }
     }
     for (int i = threadIdx.x; i < ntiles * WARPS * kTileRows; i += WARPS * 32) partial[i] = 0.f;
     pdl_wait();
-    for (uint32_t i = threadIdx.x; i < uint32_t(nb32) * 136u / 16u; i += WARPS * 32) cp_async16(xl + i * 16u, p.xq + size_t(i) * 16);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    // sums of the input's 16-element sub-blocks, from the digits: lane l holds word l & 7 of digit l >> 3; even words are the first sub-block's elements
-    for (int blk = warp; blk < nb32; blk += WARPS) {
-        const uint32_t w = lds_u32(xl + uint32_t(blk) * 128u + uint32_t(lane) * 4u);
-        int sd = __dp4a(int(w), 0x01010101, 0);
-        sd += __shfl_xor_sync(0xffffffffu, sd, 2);
-        sd += __shfl_xor_sync(0xffffffffu, sd, 4);      // lanes 8 d (+1): digit d of the first (second) sub-block
-        const int sub = lane & 1;
-        const float s0 = float(__shfl_sync(0xffffffffu, sd, sub)), s1 = float(__shfl_sync(0xffffffffu, sd, 8 + sub));
-        const float s2 = float(__shfl_sync(0xffffffffu, sd, 16 + sub)), s3 = float(__shfl_sync(0xffffffffu, sd, 24 + sub));
-        if (lane < 2) {
-            float f;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(sxp + uint32_t(blk) * 8u));
-            const float total = ((s3 * 128.f + s2) * 128.f + s1) * 128.f + s0;
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(sum16 + uint32_t(blk) * 8u + uint32_t(sub) * 4u), "f"(total * f * 16.f) : "memory");      // f: s 2^-26 / 16
-        }
+    #pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        if (s < fetched) fetch_x(first_chunk[s], s);
+        cp_async_commit();
     }
-    __syncthreads();
+    __syncthreads();      // the table of sums is zeroed
 
     const uint32_t w_lo = uint32_t(reinterpret_cast<uintptr_t>(p.W)) + uint32_t(R0) * RB;
     const int sub = t >> 1;                                  // the 16-element sub-block of an MMA's 32 elements whose sums this lane scales
@@ -168,17 +166,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
     for (int u = 0; u < my_units; u++) {
         cp_async_wait<STAGES - 2>();
         __syncwarp();
-        if (fetched < my_units) { fetch(); fetched++; }
+        if (fetched < my_units) { fetch(true); fetched++; }
         cp_async_commit();
         if (u_tile != acc_tile) { flush(); acc_tile = u_tile; }
         const int last = nrows - 1 - u_tile * kTileRows;      // rows past it are not copied: the lanes of those rows compute on whatever the stage holds and drop it
         const uint32_t lo = w_lo + uint32_t(u_tile * kTileRows) * RB + uint32_t(u_chunk) * CB;
         const uint32_t st = my_stages + uint32_t(u_slot) * stage_bytes;
+        const uint32_t xl = st + rows_bytes, sxp = xl + uint32_t(p.cbk) * 1024u;      // the unit's digits and factors
         const uint32_t src0 = lo + uint32_t(min(g, last)) * RB, src1 = lo + uint32_t(min(g + 8, last)) * RB;      // the rows' addresses in device memory
         uint32_t r0 = st + uint32_t(g) * stride + (src0 & 15u), r1 = st + uint32_t(g + 8) * stride + (src1 & 15u);
         for (int b = 0; b < p.cbk; b++, r0 += kBB, r1 += kBB) {
             const uint32_t sh0 = (r0 & 2u) * 8u, sh1 = (r1 & 2u) * 8u;
-            const int xb = (u_chunk * p.cbk + b) * 8;          // the super-block's first 32-element block of the input
+            const int xb = b * 8;                              // the super-block's first 32-element block among the unit's
             const float d0 = __half2float(__ushort_as_half(uint16_t(word_at(r0 + 208u, sh0)))), d1 = __half2float(__ushort_as_half(uint16_t(word_at(r1 + 208u, sh1))));
             #pragma unroll
             for (int n = 0; n < 2; n++) {                      // the halves of 128 elements
@@ -201,22 +200,25 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
                         const uint32_t b0 = first ? bv.x : 0u, b1 = first ? 0u : bv.y;
                         int c[4] = {0, 0, 0, 0};
                         constexpr uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x30303030u;
-                        // low nibbles, then the high bit pairs at their place (bits 4, 5): (h >> 2 j) << 4
+                        // the low nibbles (unsigned), then the high bit pairs at bits 4, 5 with the offset folded in: (h >> 2 j) << 4 is 0, 16, 32 or 48; flipping
+                        // bit 5 and copying it into bits 6, 7 makes the signed bytes -32, -16, 0, 16
                         mma_u8s8_16832(c, (hi ? q0a >> 4 : q0a) & M4, (hi ? q1a >> 4 : q1a) & M4, (hi ? q0b >> 4 : q0b) & M4, (hi ? q1b >> 4 : q1b) & M4, b0, b1);
                         const int lsh = 4 - 2 * j;             // 4, 2, 0, -2
-                        mma_u8s8_16832(c, (lsh >= 0 ? h0a << lsh : h0a >> 2) & M2, (lsh >= 0 ? h1a << lsh : h1a >> 2) & M2, (lsh >= 0 ? h0b << lsh : h0b >> 2) & M2,
-                                       (lsh >= 0 ? h1b << lsh : h1b >> 2) & M2, b0, b1);
+                        auto high = [&](uint32_t h) {
+                            const uint32_t v = lop3_and_xor(lsh >= 0 ? h << (lsh >= 0 ? lsh : 0) : h >> 2, M2, 0x20202020u);
+                            return v + (v & 0x20202020u) * 6u;
+                        };
+                        mma_s8_16832(c, high(h0a), high(h1a), high(h0b), high(h1b), b0, b1);
                         // scale of sub-block 2 j + sub of the half: byte 2 j + sub of (lo, hi)
                         const int sbyte = 2 * j + sub;         // 0 .. 7; j is a constant after unrolling, sub is not
                         const uint32_t w0 = sbyte < 4 ? s0lo : s0hi, w1 = sbyte < 4 ? s1lo : s1hi;
                         const float sc0 = float(int(int8_t((w0 >> (8 * (sbyte & 3))) & 0xFFu))), sc1 = float(int(int8_t((w1 >> (8 * (sbyte & 3))) & 0xFFu)));
-                        float f, sx;
+                        float f;
                         asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(sxp + uint32_t(blk) * 8u));
-                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(sx) : "r"(sum16 + uint32_t(blk) * 8u + uint32_t(sub) * 4u));
-                        // sum(q x) of this lane's two digits, minus (once per sub-block: the lane of digits 0, 1) 32 sum(x)
-                        const float corr = (t & 1) ? 0.f : 32.f * sx;
-                        acc0 = fmaf(d0 * sc0, float(c[0] + 128 * c[1]) * (f * 16.f * digits) - corr, acc0);
-                        acc1 = fmaf(d1 * sc1, float(c[2] + 128 * c[3]) * (f * 16.f * digits) - corr, acc1);
+                        // sum((q - 32) x) of this lane's two digits (f: the block's s 2^-26 / 16)
+                        const float fx = f * 16.f * digits;
+                        acc0 = fmaf(d0 * sc0 * fx, float(c[0] + 128 * c[1]), acc0);
+                        acc1 = fmaf(d1 * sc1 * fx, float(c[2] + 128 * c[3]), acc1);
                     }
                 }
             }
@@ -244,12 +246,12 @@ struct Plan { int cbk, nchunks, stride, upr, stages, warps; size_t smem; bool ok
 
 constexpr size_t partial_bytes(int warps) { return size_t(kMaxTilesPerBlock) * warps * kTileRows * sizeof(float); }
 
-// Chunks of one or two super-blocks (their aligned cover has to fit the copy table); 16 warps when two stages fit beside the input, else 8.
+// Chunks of one or two super-blocks (their aligned cover has to fit the copy table); 16 warps, as many stages as fit.
 Plan plan_for(int64_t cols) {
     Plan best{};
     if (cols % 256 != 0 || cols > 40960) return best;      // (the copy table packs 15 rows' byte offsets into 19 bits)
     const int nb = int(cols / 256);
-    const size_t fixed = (size_t(cols / 32) * 144 + 127) & ~size_t(127);
+    const size_t fixed = 0;
     int64_t best_score = -1;
     for (int warps : {16, 8}) {
         for (int cbk = 1; cbk <= 2; cbk++) {
@@ -260,12 +262,13 @@ Plan plan_for(int64_t cols) {
             if (stride % 32 != 16) stride += 16;
             if (kTileRows * stride >= (1 << 13)) continue;
             int stages = 0;
-            for (int st = 4; st >= 2; st--) if (fixed + size_t(warps) * st * kTileRows * stride + partial_bytes(warps) <= kSmemLimit) { stages = st; break; }
+            const size_t stage = size_t(kTileRows) * stride + size_t(cbk) * 8 * 136;
+            for (int st = 4; st >= 2; st--) if (fixed + size_t(warps) * st * stage + partial_bytes(warps) <= kSmemLimit) { stages = st; break; }
             if (!stages) continue;
             const int64_t score = (warps == 16 ? 1000 : 0) + cbk * 100 + stages;
             if (score > best_score) {
                 best_score = score;
-                best = Plan{cbk, nb / cbk, stride, upr, stages, warps, fixed + size_t(warps) * stages * kTileRows * stride + partial_bytes(warps), true};
+                best = Plan{cbk, nb / cbk, stride, upr, stages, warps, fixed + size_t(warps) * stages * stage + partial_bytes(warps), true};
             }
         }
     }
