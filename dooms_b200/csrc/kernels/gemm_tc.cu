@@ -632,16 +632,39 @@ static cudaError_t launch_rows16(GemmTcParams p, const CUtensorMap & xmap, const
         p.split_stride = split_stride;
     }
     // One matrix: a block may take 256 weight rows (two accumulators that share the token tile), which cuts what a block pulls out of L2 per flop by
-    // a third; the plain tile stays where pairs would leave more of the last wave idle than that is worth.
-    if (!gate && k_splits <= 1) {
-        static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // -1: by the estimate below
-        const int64_t token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
-        const int64_t waves_single = ((N + kRowsW - 1) / kRowsW * token_tiles + sms - 1) / sms;
-        const int64_t waves_pair = ((N + 2 * kRowsW - 1) / (2 * kRowsW) * token_tiles + sms - 1) / sms;
-        p.pair = pair_mode >= 0 ? pair_mode : (waves_pair * 3 < waves_single * 2 ? 1 : 0);      // a pair tile is taken to cost 1.5 plain tiles
-        if (N <= kRowsW) p.pair = 0;
+    // a third. A block of 256 rows is taken to cost 1.5 plain tiles; the first `pair_tm` token tiles run as such blocks and the rest as plain tiles,
+    // whichever split needs the least time in waves of one block per SM (the 8B qkv product, 48 x 8 plain tiles: six token tiles as 144 blocks of 256
+    // rows, two as 96 plain tiles, 2.5 units of time against 3 either way alone).
+    const CUtensorMap & wm = *reinterpret_cast<const CUtensorMap *>(&wmap), & w2m = *reinterpret_cast<const CUtensorMap *>(&w2map);
+    if (gate || k_splits > 1 || N <= kRowsW) return launch_dt<kF16, true>(xmap, wm, w2m, p, gate, stream);
+    static const int pair_mode = [] { const char * e = getenv("DOOMS_GEMM_PAIR"); return e ? atoi(e) : -1; }();      // 0: never, 1: always, -1: by the estimate
+    const int token_tiles = (M + p.T - 1) / p.T, sms = sm_count();
+    const int tiles_single = int((N + kRowsW - 1) / kRowsW), tiles_pair = int((N + 2 * kRowsW - 1) / (2 * kRowsW));
+    int pair_tm = 0;
+    if (pair_mode > 0) pair_tm = token_tiles;
+    if (pair_mode < 0) {
+        int64_t best = -1;
+        for (int tm = 0; tm <= token_tiles; tm++) {
+            const int64_t cost = int64_t((tiles_pair * tm + sms - 1) / sms) * 3 + int64_t((tiles_single * (token_tiles - tm) + sms - 1) / sms) * 2;
+            if (best < 0 || cost < best) { best = cost; pair_tm = tm; }
+        }
     }
-    return launch_dt<kF16, true>(xmap, *reinterpret_cast<const CUtensorMap *>(&wmap), *reinterpret_cast<const CUtensorMap *>(&w2map), p, gate || p.pair, stream);
+    cudaError_t e2 = cudaSuccess;
+    if (pair_tm > 0) {
+        GemmTcParams q = p;
+        q.pair = 1;
+        q.tiles_n = tiles_pair;
+        q.tile0 = 0;
+        e2 = launch_tiles<kF16, true>(xmap, wm, w2m, q, true, tiles_pair * pair_tm, stream);
+    }
+    if (e2 == cudaSuccess && pair_tm < token_tiles) {
+        GemmTcParams q = p;
+        q.pair = 0;
+        q.tiles_n = tiles_single;
+        q.tile0 = tiles_single * pair_tm;
+        e2 = launch_tiles<kF16, true>(xmap, wm, w2m, q, false, tiles_single * (token_tiles - pair_tm), stream);
+    }
+    return e2;
 }
 
 cudaError_t launch_gemm_tc_rows16(const void * W16, const void * W2_16, const TensorMap * xmap, float * Y, void * Y16, const float * bias, int M, int64_t N, int64_t K,
