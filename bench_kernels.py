@@ -1,6 +1,6 @@
 """Measurement harness beside bench.py: one kernel on one small case, through the C ABI: a correctness check plus CUDA-event timing, sized for a profiler capture.
 
-    python bench_kernels.py gemv  [--rows 14336 --cols 4096 --gate --mats 4]      decode GEMV on q4_0 rows (dooms_cuda_matvec / dooms_cuda_gate_up)
+    python bench_kernels.py gemv  [--rows 14336 --cols 4096 --gate --split --mats 4]   decode GEMV (dooms_cuda_matvec / _gate_up / _matvec_split)
     python bench_kernels.py gemm  [--tokens 2048 --rows 4096 --cols 4096 --gate]  tcgen05 prefill GEMM (dooms_cuda_matmul)
     python bench_kernels.py attention [--config 2 --layers 2 --prompt 2048 --steps 8]  prefill and decode attention inside a decoder cut to a few layers
     python bench_kernels.py batch [--config 0 --sequences 256 --steps 8]           a batched decode step over many sequences of mixed lengths
@@ -34,8 +34,15 @@ def _gemv(args):
     y = torch.empty(args.rows, device='cuda')
     st = torch.cuda.current_stream().cuda_stream
 
+    split = None
+    if args.split:      # the input already split into int8 digits, as the kernels of a decode step hand it to each other
+        split = torch.empty(lib.dooms_cuda_split_input_bytes(args.cols), dtype=torch.uint8, device='cuda')
+        L.check(lib.dooms_cuda_split_input(x.data_ptr(), args.cols, split.data_ptr(), st))
+
     def launch(g, u):
-        if args.gate:
+        if split is not None:
+            L.check(lib.dooms_cuda_matvec_split(dt, g.data_ptr(), u.data_ptr() if args.gate else None, split.data_ptr(), y.data_ptr(), None, args.rows, args.cols, 0, st))
+        elif args.gate:
             L.check(lib.dooms_cuda_gate_up(dt, g.data_ptr(), u.data_ptr(), x.data_ptr(), y.data_ptr(), args.rows, args.cols, st))
         else:
             L.check(lib.dooms_cuda_matvec(dt, g.data_ptr(), x.data_ptr(), y.data_ptr(), None, args.rows, args.cols, 0, st))
@@ -213,6 +220,7 @@ def main(argv=None):
     g.add_argument('--rows', type=int, default=14336)
     g.add_argument('--cols', type=int, default=4096)
     g.add_argument('--gate', action='store_true')
+    g.add_argument('--split', action='store_true', help='q4_0 / q4_k: the input already split (dooms_cuda_matvec_split)')
     g.add_argument('--mats', type=int, default=4)
     g.add_argument('--reps', type=int, default=3)
     g.add_argument('--dtype', default='q4_0')
