@@ -77,6 +77,8 @@ __global__ void __launch_bounds__(kThreads, 3) k_attention_rows_tc(const RowsPar
     int * flag = reinterpret_cast<int *>(smem + 16 * LD * 2 + (D / 2) * 8);
     __half * stages = reinterpret_cast<__half *>(smem + 16 * LD * 2 + (D / 2) * 8 + 16);   // [warp][2][K | V][TK][LD]
 
+    pdl_trigger();
+    pdl_wait();
     const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
     const int slot = p.slot[row];
     if (slot < 0) return;                          // an idle row
@@ -307,8 +309,7 @@ template <int D>
 cudaError_t launch_rows(const RowsParams & p, int n_rows, cudaStream_t stream) {
     static std::atomic<uint64_t> configured{0};
     if (const cudaError_t e = allow_dynamic_smem(k_attention_rows_tc<D>, int(rows_smem_bytes<D>()), configured); e != cudaSuccess) return e;
-    k_attention_rows_tc<D><<<dim3(unsigned(p.s.n_head_kv), unsigned(p.splits), unsigned(n_rows)), kThreads, rows_smem_bytes<D>(), stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(k_attention_rows_tc<D>, dim3(unsigned(p.s.n_head_kv), unsigned(p.splits), unsigned(n_rows)), dim3(kThreads), rows_smem_bytes<D>(), stream, p);
 }
 
 }  // namespace

@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const int ksteps = p.ks_per > 0 ? min(p.K / kStepK - ks0, p.ks_per) : p.K / kStepK;
     const uint32_t ncols = GATE ? 512u : 256u;
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full_x + 8 * s, 1); mbar_init(full_w + 8 * s, p.wide ? kProducerWarps * 16 : kProducerWarps * 32); mbar_init(empty + 8 * s, 1); }
         mbar_init(acc_full, 1);
@@ -251,6 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
     bool ok = true;
+    pdl_wait();      // every thread: from here on the token rows, the residual rows and the weights' f16 copies are those the kernels before this one wrote
 
     if (PRE && warp < kProducerWarps) {
         // nothing to produce: the weight tiles come by TMA
@@ -472,15 +474,17 @@ cudaError_t launch_tiles(const CUtensorMap & map, const CUtensorMap & wmap, cons
     static std::atomic<uint64_t> configured[2];
     if (const cudaError_t e = gate ? allow_dynamic_smem(k_gemm_tc<DT, true, PRE>, 220 * 1024, configured[1])
                                    : allow_dynamic_smem(k_gemm_tc<DT, false, PRE>, 220 * 1024, configured[0]); e != cudaSuccess) return e;
-    if (gate) k_gemm_tc<DT, true, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
-    else k_gemm_tc<DT, false, PRE><<<grid, kThreads, smem, stream>>>(map, wmap, w2map, p);
-    return cudaGetLastError();
+    // launched early: the block's set-up (mbarriers, tensor memory) overlaps the end of the kernel before it
+    if (gate) return launch_pdl(k_gemm_tc<DT, true, PRE>, grid, dim3(kThreads), smem, stream, map, wmap, w2map, p);
+    return launch_pdl(k_gemm_tc<DT, false, PRE>, grid, dim3(kThreads), smem, stream, map, wmap, w2map, p);
 }
 
 // Adds the shares of the tiles tile0 .. tile0 + gridDim.x - 1 of a gate / up product in a fixed order and writes silu(gate) * up as f16 (the epilogue of
 // the unsplit tile, matmul_gate_up_bigq, src/backend/metal/llama_kernels.h:1351-1382).
 __global__ void __launch_bounds__(256) k_gate_up_combine(const float * shares, int n_shares, int tile0, int tiles_n, int T, float * Y, int64_t y_stride, __half * Y16,
                                                          int64_t y16_stride, int64_t N, int M) {
+    pdl_trigger();
+    pdl_wait();
     const int tile = tile0 + int(blockIdx.x);
     const int64_t n0 = int64_t(tile % tiles_n) * kRowsW;
     const int m0 = (tile / tiles_n) * T;
@@ -530,8 +534,8 @@ cudaError_t launch_dt(const CUtensorMap & map, const CUtensorMap & wmap, const C
     t.gate_shares = static_cast<float *>(scratch);
     e = launch_tiles<DT, PRE>(map, wmap, w2map, t, gate, left, stream);
     if (e != cudaSuccess) return e;
-    k_gate_up_combine<<<dim3(unsigned(left), 16u), 256, 0, stream>>>(t.gate_shares, shares, t.tile0, p.tiles_n, p.T, p.Y, p.y_stride, p.Y16, p.y16_stride, p.N, p.M);
-    return cudaGetLastError();
+    return launch_pdl(k_gate_up_combine, dim3(unsigned(left), 16u), dim3(256), 0, stream, static_cast<const float *>(t.gate_shares), shares, t.tile0, p.tiles_n, p.T, p.Y,
+                      p.y_stride, p.Y16, p.y16_stride, p.N, p.M);
 }
 
 template <int DT>

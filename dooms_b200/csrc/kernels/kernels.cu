@@ -567,6 +567,8 @@ cudaError_t launch_dequantize(int dt, const void * blocks, int64_t rows, int64_t
 }
 
 __global__ void __launch_bounds__(256) k_add_shares(float * x, const float * shares, int k_splits, int64_t n, int64_t split_stride) {
+    pdl_trigger();
+    pdl_wait();
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
         float v = x[i];
         for (int s = 0; s < k_splits; s++) v += __ldcg(shares + s * split_stride + i);
@@ -575,8 +577,7 @@ __global__ void __launch_bounds__(256) k_add_shares(float * x, const float * sha
 }
 cudaError_t launch_add_shares(float * x, const float * shares, int k_splits, int64_t n, int64_t split_stride, cudaStream_t stream) {
     if (!x || !shares || k_splits < 1 || n < 1) return cudaErrorInvalidValue;
-    k_add_shares<<<unsigned(std::min<int64_t>((n + 255) / 256, sm_count() * 8)), 256, 0, stream>>>(x, shares, k_splits, n, split_stride);
-    return cudaGetLastError();
+    return launch_pdl(k_add_shares, dim3(unsigned(std::min<int64_t>((n + 255) / 256, sm_count() * 8))), dim3(256), 0, stream, x, shares, k_splits, n, split_stride);
 }
 
 cudaError_t launch_add(float * x, const float * y, int64_t n, cudaStream_t stream) {
