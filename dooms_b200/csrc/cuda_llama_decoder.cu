@@ -518,7 +518,8 @@ struct CudaLlamaDecoder::Impl {
             uint32_t log2_tp = 0;
             while ((1 << log2_tp) < tp) log2_tp++;
             float * o_dst = (single || share) ? x : red;
-            const uint32_t o_flags = single ? kFlagAccumulate : share ? (kFlagAccumulate | (log2_tp << cuda::kFlagShareShift)) : 0u;
+            // (under tensor parallelism the kernel after these projections is a collective: they do not let it start early)
+            const uint32_t o_flags = single ? kFlagAccumulate : (share ? (kFlagAccumulate | (log2_tp << cuda::kFlagShareShift)) : 0u) | cuda::kFlagLateDependents;
             const bool use_tc = M > 1 && tc_capable && cfg.prefill_tile != 1;
             if (M > 1) norm(x, L.attn_norm, M, false, use_tc);
             if (M == 1) {

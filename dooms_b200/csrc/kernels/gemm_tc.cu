@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const int ksteps = p.ks_per > 0 ? min(p.K / kStepK - ks0, p.ks_per) : p.K / kStepK;
     const uint32_t ncols = GATE ? 512u : 256u;
 
-    pdl_trigger();
+    if (!(p.flags & kFlagLateDependents)) pdl_trigger();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full_x + 8 * s, 1); mbar_init(full_w + 8 * s, p.wide ? kProducerWarps * 16 : kProducerWarps * 32); mbar_init(empty + 8 * s, 1); }
         mbar_init(acc_full, 1);

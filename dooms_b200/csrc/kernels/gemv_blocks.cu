@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_blocks(const GemvBlocksP
     };
 
     int fetched = 0;
-    pdl_trigger();
+    if (!(p.flags & kFlagLateDependents)) pdl_trigger();
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (fetched < my_units) { fetch(); fetched++; }

@@ -309,7 +309,7 @@ __device__ __forceinline__ void gemv_q4_0_body(const CUtensorMap * mwp, const CU
     }
     // The first STAGES - 1 stages of weights are asked for at once: they do not depend on the kernel before this one, which may still be running (this
     // kernel is launched early, see launch.cuh). Only then wait for that kernel, and fetch the split input it (or one before it) wrote, as one more group.
-    if constexpr (!FUSED) pdl_trigger();
+    if constexpr (!FUSED) { if (!(p.flags & kFlagLateDependents)) pdl_trigger(); }
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (fetched < my_units) { fetch(); fetched++; }

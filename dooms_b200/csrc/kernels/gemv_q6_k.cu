@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_gemv_q6_k(const GemvQ6kParams
 
     // The rows of the first STAGES - 1 units are asked for before the wait for the kernel that wrote the input; the input's parts of those units follow it.
     int fetched = 0;
-    pdl_trigger();
+    if (!(p.flags & kFlagLateDependents)) pdl_trigger();
     int first_chunk[STAGES - 1];
     #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {

@@ -140,7 +140,7 @@ constexpr int kMvWarps = 4;
 
 template <int DT>
 __global__ void __launch_bounds__(kMvWarps * 32) k_matvec(const uint8_t * W, const float * x, float * y, const float * bias, int64_t rows, int cols, uint32_t flags) {
-    pdl_trigger();
+    if (!(flags & kFlagLateDependents)) pdl_trigger();
     pdl_wait();
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int64_t r = int64_t(blockIdx.x) * kMvWarps + warp;

@@ -20,6 +20,10 @@ enum : uint32_t { kFlagAccumulate = 2, kFlagBias = 4 };   // the reference's Mat
 // One-token projections only, with kFlagAccumulate: bits 8..11 = k > 0 scale the old value by 2^-k first, y = y 2^-k + W x. With 2^k tensor-parallel ranks
 // an in-place all-reduce of y then gives y + the sum of the ranks' products on every rank (the scaling by a power of two is exact), without an add kernel.
 constexpr uint32_t kFlagShareShift = 8;
+// The kernel launched after this one is not one of this library's (an NCCL collective): this kernel then does not let its dependents start early. NCCL's
+// symmetric-memory kernels start on the programmatic trigger of the kernel before them and read their input at once (measured: a tensor-parallel prompt
+// went wrong when the projection before the all-reduce triggered at its start), so a producer of a collective's input triggers only by finishing.
+constexpr uint32_t kFlagLateDependents = 1u << 12;
 __host__ __device__ inline float accumulate_base(float y, uint32_t flags) {
     const uint32_t k = (flags >> kFlagShareShift) & 15u;
 #ifdef __CUDA_ARCH__
