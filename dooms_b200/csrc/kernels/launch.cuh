@@ -3,6 +3,9 @@
 // launched this way calls pdl_wait() before it reads anything an earlier kernel wrote and before it writes anything (weights and other constants may be
 // fetched earlier); it calls pdl_trigger() as soon as the next kernel may start its own prologue. Because each kernel waits for its predecessor to finish
 // before it can finish itself, waiting for the immediate predecessor orders a kernel after everything earlier in the stream.
+// The early trigger is only safe when the kernel that follows is one of these: a kernel of another library that is itself launched as a programmatic
+// dependent but does not wait before it reads (NCCL's symmetric-memory collectives behaved that way) would see half-written input. A kernel whose output
+// such a collective reads therefore skips its trigger (kFlagLateDependents in kernels.h) and releases its dependents by finishing.
 #include <cuda_runtime.h>
 
 #include <atomic>
