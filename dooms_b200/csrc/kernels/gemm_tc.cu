@@ -11,6 +11,12 @@
 //     hanging.
 //   * Epilogue: the producer warps read their TMEM lanes (tcgen05.ld 32x32b), add bias / the residual, or apply silu(gate) * up, and write coalesced
 //     rows of Y (f32) or of the f16 activation buffer the next GEMM reads.
+//   * From 128 tokens per call a matrix is first written out as f16 rows (k_dequant_f16, or a copy the caller keeps) and both operands arrive by TMA; the
+//     producer warps then only run the epilogue. On that route a block may take 256 weight rows (the second accumulator holds rows 128..255 against the
+//     same token tile), the first token tiles of a product running as such blocks and the rest as plain tiles, whichever split needs the fewest waves.
+//   * Two ways to deal a reduction over several blocks: a product of few weight rows against one token tile (a batched decode step) writes per-share sums
+//     that launch_add_shares adds in a fixed order; a fused gate / up product whose tiles leave a nearly empty last wave runs the leftover tiles that way
+//     and k_gate_up_combine applies the epilogue.
 // Replaces matmul_bigq / matmul_gate_up_bigq and the dequant_half + matmul_big pair of the reference (llama_kernels.h:1320-1382, 1474-1480).
 #include <cuda.h>
 #include <cuda_fp16.h>
