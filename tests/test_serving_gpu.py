@@ -16,6 +16,71 @@ def test_workload_is_seeded_and_within_the_ranges():
     assert serving.workload(3, 1000, 1)[0][1] != a[0][1] or not np.array_equal(serving.workload(3, 1000, 1)[0][0], a[0][0])
 
 
+class FakeDecoder:
+    """The decoder's slot interface with arithmetic a test can predict: a sequence's next token depends only on its own history, as the real steps'
+    rows depend only on their own slot."""
+
+    def __init__(self, slots):
+        self.state = [None] * slots
+        self.cur = 0
+        self.calls = []
+
+    @staticmethod
+    def step(history):
+        return (sum(history) * 31 + len(history) * 7) % 1009
+
+    def select_sequence(self, s):
+        self.cur = s
+
+    def reset(self):
+        self.state[self.cur] = []
+
+    def eval_tokens(self, tokens):
+        self.state[self.cur] = list(self.state[self.cur] or []) + [int(t) for t in tokens]
+
+    def pending_token(self):
+        return self.step(self.state[self.cur])
+
+    def timings(self):
+        return {"last_eval_ms": 1.0, "last_batch_ms": 1.0}
+
+    def decode_batch(self, rows, steps):
+        self.calls.append((list(rows), steps))
+        out = np.full((steps, len(rows)), -1, dtype=np.int32)
+        for k in range(steps):
+            for r, slot in enumerate(rows):
+                if slot >= 0:
+                    h = self.state[slot]
+                    h.append(self.step(h))          # the pending token is fed back ...
+                    out[k, r] = self.step(h)        # ... and the next one comes out
+        return out
+
+
+def alone(prompt, n_decode):
+    h = [int(t) for t in prompt]
+    toks = [FakeDecoder.step(h)]
+    for _ in range(n_decode - 1):
+        h.append(toks[-1])
+        toks.append(FakeDecoder.step(h))
+    return toks
+
+
+def test_continuous_batching_schedule_on_a_fake_decoder():
+    """The scheduler alone (no GPU): every sequence gets the tokens it gets alone, no step is run for a finished sequence, slots are reused, and every
+    call has max_live rows."""
+    seqs = serving.workload(23, 1000, 7, prompt_range=(1, 9), decode_range=(1, 14))
+    dec = FakeDecoder(5)
+    tokens, stats = serving.run_continuous(dec, seqs, max_live=5, max_steps_per_call=4)
+    assert tokens == [alone(p, d) for p, d in seqs]
+    assert all(len(rows) == 5 and 1 <= steps <= 4 for rows, steps in dec.calls)
+    assert stats["most_live"] == 5 and stats["steps"] == sum(steps for _, steps in dec.calls)
+    assert sum(steps * sum(r >= 0 for r in rows) for rows, steps in dec.calls) == sum(d - 1 for _, d in seqs)      # no step beyond a sequence's end
+    # the one-batch driver on the same fake
+    dec = FakeDecoder(23)
+    tokens, _ = serving.run_batched(dec, seqs)
+    assert tokens == [alone(p, d) for p, d in seqs]
+
+
 @pytest.mark.gpu
 def test_sequences_served_concurrently_equal_single_runs(model_dir):
     import torch
