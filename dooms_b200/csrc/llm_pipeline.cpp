@@ -6,6 +6,7 @@
 #include <climits>
 #include <cmath>
 #include <numeric>
+#include <queue>
 
 namespace dooms {
 
@@ -112,6 +113,10 @@ Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
         int32_t rank = 0;
         for (const GgufValue & m : merges->second.items) v.merge_rank_.emplace(m.s, rank++);
     }
+    if (const auto scores = md.find("tokenizer.ggml.scores"); scores != md.end() && scores->second.items.size() == n) {
+        v.scores_.resize(n);
+        for (size_t i = 0; i < n; i++) v.scores_[i] = float(scores->second.items[i].f);
+    }
     v.bos_ = int_key(file, "tokenizer.ggml.bos_token_id", -1);
     for (const char * key : {"tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id", "tokenizer.ggml.eom_token_id"}) {
         const int32_t id = int_key(file, key, -1);
@@ -131,9 +136,61 @@ bool Vocab::is_end_of_generation(int32_t id) const { return std::find(eog_.begin
 
 Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_special) const {
     if (text.empty()) return invalid_argument("tokenize: empty text");
-    if (!byte_level_) return unsupported("tokenize: this file's vocabulary is a sentencepiece model; pass token ids");
     std::vector<int32_t> out;
     if (add_special && add_bos_ && bos_ >= 0) out.push_back(bos_);
+    if (!byte_level_) {
+        // sentencepiece: the escaped text as a chain of characters; the pair whose concatenation is the best-scoring piece is merged until none is a piece
+        std::string escaped = "\xE2\x96\x81";
+        for (char c : text) { if (c == ' ') escaped += "\xE2\x96\x81"; else escaped += c; }
+        struct Sym { size_t at, len; int prev, next; };
+        std::vector<Sym> sym;
+        for (size_t i = 0; i < escaped.size();) {
+            const unsigned char c = static_cast<unsigned char>(escaped[i]);
+            size_t len = c < 0x80 ? 1 : c < 0xE0 ? 2 : c < 0xF0 ? 3 : 4;
+            len = std::min(len, escaped.size() - i);
+            sym.push_back({i, len, int(sym.size()) - 1, int(sym.size()) + 1});
+            i += len;
+        }
+        if (!sym.empty()) sym.back().next = -1;
+        // candidate pairs in a heap: best score first, leftmost on ties; a popped pair counts only if both halves still have the lengths it was made with
+        struct Pair { float score; int left, right; size_t left_len, right_len; };
+        auto worse = [](const Pair & a, const Pair & b) { return a.score != b.score ? a.score < b.score : a.left > b.left; };
+        std::priority_queue<Pair, std::vector<Pair>, decltype(worse)> heap(worse);
+        auto offer = [&](int i, int j) {
+            if (i < 0 || j < 0) return;
+            const Sym & a = sym[size_t(i)], & b = sym[size_t(j)];
+            const auto id = ids_.find(escaped.substr(a.at, a.len + b.len));
+            if (id == ids_.end()) return;
+            heap.push({size_t(id->second) < scores_.size() ? scores_[size_t(id->second)] : 0.f, i, j, a.len, b.len});
+        };
+        for (int i = 0; i + 1 < int(sym.size()); i++) offer(i, i + 1);
+        while (!heap.empty()) {
+            const Pair top = heap.top();
+            heap.pop();
+            Sym & a = sym[size_t(top.left)];
+            Sym & b = sym[size_t(top.right)];
+            if (a.len != top.left_len || b.len != top.right_len || a.next != top.right) continue;      // one of them was merged meanwhile
+            a.len += b.len;
+            a.next = b.next;
+            b.len = 0;
+            if (b.next >= 0) sym[size_t(b.next)].prev = top.left;
+            offer(a.prev, top.left);
+            offer(top.left, a.next);
+        }
+        for (int i = sym.empty() ? -1 : 0; i >= 0; i = sym[size_t(i)].next) {
+            const std::string piece = escaped.substr(sym[size_t(i)].at, sym[size_t(i)].len);
+            const auto id = ids_.find(piece);
+            if (id != ids_.end()) { out.push_back(id->second); continue; }
+            for (unsigned char c : piece) {
+                char name[8];
+                snprintf(name, sizeof name, "<0x%02X>", unsigned(c));
+                const auto b = ids_.find(name);
+                if (b == ids_.end()) return invalid_argument("tokenize: the vocabulary has no token for a byte of the text");
+                out.push_back(b->second);
+            }
+        }
+        return out;
+    }
     // words: a run of one class of bytes (letters, digits, other), with the single space before it
     auto cls = [](unsigned char c) { return c == ' ' ? 0 : (std::isalpha(c) || c >= 0x80) ? 1 : std::isdigit(c) ? 2 : 3; };
     size_t at = 0;

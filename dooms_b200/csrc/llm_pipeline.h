@@ -28,7 +28,7 @@ struct SamplerOptions {
 // The vocabulary of a GGUF file: token id <-> bytes.
 class Vocab {
 public:
-    //   InvalidArgument  the file has no tokenizer.ggml.tokens     Unsupported  a tokenizer model other than "gpt2" (byte-level BPE) or "llama" (pieces)
+    //   InvalidArgument  the file has no tokenizer.ggml.tokens     Unsupported  a tokenizer model other than "gpt2" (byte-level BPE) or "llama" (sentencepiece)
     static Result<Vocab> from_gguf(const GgufFile & file);
     int32_t size() const { return int32_t(pieces_.size()); }
     // The bytes token `id` stands for (byte-level BPE: the GPT-2 byte alphabet undone; sentencepiece: U+2581 -> space, <0xHH> -> that byte); special
@@ -37,8 +37,10 @@ public:
     bool is_end_of_generation(int32_t id) const;
     int32_t bos() const { return bos_; }
     bool add_bos() const { return add_bos_; }
-    // Text -> ids. Byte-level BPE only: words are split at the boundary before a run of spaces / letters / digits / other, each word's bytes are merged
-    // pairwise by rank.   Unsupported  a sentencepiece vocabulary (callers pass token ids)     InvalidArgument  empty text
+    // Text -> ids.   InvalidArgument  empty text, or a byte the vocabulary has no token for
+    //   byte-level BPE: words are split at the boundary before a run of spaces / letters / digits / other, each word's bytes are merged pairwise by rank;
+    //   sentencepiece: spaces become U+2581 (one is put in front of the text), the text's characters are merged pairwise, best-scoring vocabulary piece
+    //   first (tokenizer.ggml.scores; leftmost on ties), and what is no piece at the end goes out byte by byte as <0xHH>.
     Result<std::vector<int32_t>> tokenize(const std::string & text, bool add_special) const;
 
 private:
@@ -46,6 +48,7 @@ private:
     std::vector<std::string> raw_;                              // as stored
     std::unordered_map<std::string, int32_t> ids_;              // raw token -> id
     std::unordered_map<std::string, int32_t> merge_rank_;       // "left right" -> rank
+    std::vector<float> scores_;                                 // sentencepiece: per id
     std::vector<bool> special_;
     std::vector<int32_t> eog_;
     int32_t bos_ = -1;

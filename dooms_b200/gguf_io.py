@@ -29,6 +29,8 @@ def _kv(key: str, value) -> bytes:
         return out + struct.pack("<i", _T_STRING) + _s(value)
     if isinstance(value, (list, tuple)) and all(isinstance(v, int) for v in value):
         return out + struct.pack("<iiQ", _T_ARRAY, _T_I32, len(value)) + b"".join(struct.pack("<i", v) for v in value)
+    if isinstance(value, (list, tuple)) and value and all(isinstance(v, float) for v in value):
+        return out + struct.pack("<iiQ", _T_ARRAY, _T_F32, len(value)) + b"".join(struct.pack("<f", v) for v in value)
     if isinstance(value, (list, tuple)) and all(isinstance(v, str) for v in value):
         return out + struct.pack("<iiQ", _T_ARRAY, _T_STRING, len(value)) + b"".join(_s(v) for v in value)
     raise TypeError(f"metadata value of type {type(value)}")

@@ -163,6 +163,25 @@ def byte_level_vocab(n_vocab: int) -> dict:
             "tokenizer.ggml.eos_token_id": n_vocab - 1, "tokenizer.ggml.bos_token_id": n_vocab - 1, "tokenizer.ggml.add_bos_token": False}
 
 
+def sentencepiece_vocab(n_vocab: int) -> dict:
+    """Tokenizer metadata of a small sentencepiece-style vocabulary with n_vocab (>= 300) entries: <unk>, <s>, </s>, the 256 byte tokens <0xHH>, single
+    characters, a few pieces of common English with scores (longer pieces score higher, as trained vocabularies have it), filler tokens."""
+    sp = "\u2581"
+    tokens, scores, types = ["<unk>", "<s>", "</s>"], [0.0, 0.0, 0.0], [2, 3, 3]
+    for b in range(256):
+        tokens.append(f"<0x{b:02X}>"); scores.append(0.0); types.append(6)
+    for ch in [sp] + list("abcdefghijklmnopqrstuvwxyz,.!"):
+        tokens.append(ch); scores.append(-10.0); types.append(1)
+    for piece, score in ((sp + "h", -6.0), ("he", -5.5), ("ll", -5.0), (sp + "he", -4.5), ("llo", -4.0), (sp + "hello", -1.0), ("hell", -3.8), (sp + "w", -6.0), ("or", -5.0),
+                         ("ld", -5.2), (sp + "wor", -3.0), (sp + "world", -1.5), (sp + "t", -6.1), ("th", -4.9), (sp + "th", -3.5), (sp + "the", -2.0)):
+        tokens.append(piece); scores.append(score); types.append(1)
+    assert n_vocab >= len(tokens)
+    while len(tokens) < n_vocab:
+        tokens.append(f"<filler_{len(tokens)}>"); scores.append(-100.0); types.append(1)
+    return {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.scores": scores, "tokenizer.ggml.token_type": types,
+            "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.add_bos_token": True}
+
+
 def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
     if device == "cpu":
         g = np.random.Generator(np.random.PCG64(seed))
@@ -172,8 +191,9 @@ def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
     return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
 
 
-def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu", vocab: bool = False) -> dict:
-    """Writes the model as a GGUF file; returns {"matrix_bytes": ...}. vocab: with the tokenizer metadata of byte_level_vocab(n_vocab)."""
+def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu", vocab=False) -> dict:
+    """Writes the model as a GGUF file; returns {"matrix_bytes": ...}. vocab: True with the tokenizer metadata of byte_level_vocab(n_vocab),
+    "sentencepiece" with that of sentencepiece_vocab(n_vocab)."""
     md = {
         "general.architecture": spec.arch,
         "general.name": spec.name,
@@ -187,7 +207,7 @@ def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu
         f"{spec.arch}.attention.layer_norm_rms_epsilon": float(spec.rms_eps),
     }
     if vocab:
-        md.update(byte_level_vocab(spec.n_vocab))
+        md.update(sentencepiece_vocab(spec.n_vocab) if vocab == "sentencepiece" else byte_level_vocab(spec.n_vocab))
     tensors = []
     counter = [0]
 

@@ -36,6 +36,23 @@ def test_vocabulary_round_trips_text_and_merges_by_rank(model):
     assert e.value.code == L.INVALID_ARGUMENT
 
 
+def test_sentencepiece_vocabulary_merges_by_score_and_falls_back_to_bytes(tmp_path):
+    """A sentencepiece vocabulary (tokenizer.ggml.model = llama): a space in front, spaces as U+2581, pairs merged best score first, characters the
+    vocabulary lacks as <0xHH> byte tokens; the pieces of the ids give the text back (with the space put in front)."""
+    path = str(tmp_path / "spm_tiny.gguf")
+    synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 78, vocab="sentencepiece")
+    v = Vocab(path)
+    tok = {v.piece(i): i for i in range(3 + 256, 3 + 256 + 46) if v.piece(i)}
+    assert v.tokenize("hello world", add_special=False) == [tok[b" hello"], tok[b" world"]]
+    assert v.tokenize("hello world") == [1, tok[b" hello"], tok[b" world"]]                       # the file asks for its <s> in front
+    assert v.tokenize("the hell", add_special=False) == [tok[b" the"], tok[b" "], tok[b"hell"]]   # no piece " hell": a space piece, then the best-scoring split
+    text = "hello w\u00e9 the!"
+    ids = v.tokenize(text, add_special=False)
+    assert b"".join(v.piece(t) for t in ids) == (" " + text).encode()
+    assert [t for t in ids if 3 <= t < 259] == [3 + b for b in "\u00e9".encode()]                  # the accented letter went out as its two bytes
+    assert v.piece(1) == b"" and v.is_end_of_generation(2)
+
+
 def test_pieces_are_whole_characters_and_stop_strings_end_the_text(model):
     v = Vocab(model)
     # U+00E9 and an emoji arrive byte by byte: nothing incomplete is ever handed on
