@@ -74,6 +74,10 @@ class Sampling(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("repeat_penalty", C.c_float), ("seed", C.c_uint32)]
 
 
+class ChatMessage(C.Structure):
+    _fields_ = [("role", C.c_char_p), ("content", C.c_char_p)]
+
+
 class GenerationInfo(C.Structure):
     _fields_ = [("struct_size", C.c_size_t), ("prompt_tokens", C.c_int32), ("completion_tokens", C.c_int32), ("finish_reason", C.c_int32),
                 ("prefill_ms", C.c_double), ("first_token_ms", C.c_double), ("decode_ms", C.c_double)]
@@ -148,6 +152,13 @@ SIGNATURES = {
     "dooms_cuda_vocab_is_end_of_generation": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dooms_cuda_vocab_piece": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
     "dooms_cuda_vocab_tokenize": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_vocab_tokenize_special": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "dooms_cuda_vocab_apply_chat_template": (C.c_int32, [C.c_void_p, C.POINTER(ChatMessage), C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "dooms_cuda_llm_chat": (C.c_int32, [C.c_void_p, C.POINTER(ChatMessage), C.c_int32, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, C.c_void_p, C.c_size_t,
+                                        C.POINTER(C.c_size_t)]),
+    "dooms_cuda_llm_chat_stream": (C.c_int32, [C.c_void_p, C.POINTER(ChatMessage), C.c_int32, C.c_int32, C.POINTER(Sampling), C.POINTER(C.c_char_p), C.c_int32, TEXT_CALLBACK,
+                                               C.c_void_p]),
+    "dooms_cuda_llm_count_chat_tokens": (C.c_int32, [C.c_void_p, C.POINTER(ChatMessage), C.c_int32, C.POINTER(C.c_int32)]),
     "dooms_cuda_text_stream": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_char_p), C.c_int32, TEXT_CALLBACK, C.c_void_p, C.c_void_p, C.c_size_t,
                                            C.POINTER(C.c_size_t), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "dooms_cuda_sample": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(Sampling), C.c_int32, C.c_void_p]),

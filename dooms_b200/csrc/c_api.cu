@@ -417,6 +417,15 @@ int32_t text_out(const std::string & text, char * out, size_t capacity, size_t *
 int32_t finish_reason_of(const LlmGeneration & g) { return g.cancelled ? DOOMS_CUDA_FINISH_CANCELLED : g.stopped ? DOOMS_CUDA_FINISH_STOP : DOOMS_CUDA_FINISH_LENGTH; }
 
 // One generation on a handle: the shared body of the three generate entry points.
+bool messages_of(const dooms_cuda_chat_message * messages, int32_t n, std::vector<ChatMessage> * out, int32_t * code) {
+    if (!messages || n < 1) { *code = fail(DOOMS_INVALID_ARGUMENT, "no messages"); return false; }
+    for (int32_t i = 0; i < n; i++) {
+        if (!messages[i].role || !messages[i].content) { *code = fail(DOOMS_INVALID_ARGUMENT, "a message has a NULL role or content"); return false; }
+        out->push_back({messages[i].role, messages[i].content});
+    }
+    return true;
+}
+
 int32_t run_generation(dooms_cuda_llm * h, const std::vector<int32_t> * prompt_tokens, const char * prompt, int32_t max_new_tokens, const dooms_cuda_sampling * sampling,
                        const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback, void * user, LlmGeneration * result) {
     if (!h) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
@@ -518,6 +527,41 @@ DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm
     out->struct_size = size;
     return DOOMS_OK;
 }
+DOOMS_CUDA_API int32_t dooms_cuda_llm_chat(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t max_new_tokens,
+                                           const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, char * out, size_t capacity, size_t * needed) {
+    if (!llm) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
+    int32_t code = DOOMS_OK;
+    std::vector<ChatMessage> chat;
+    if (!messages_of(messages, n_messages, &chat, &code)) return code;
+    auto tokens = llm->llm->chat_tokens(chat);
+    if (!tokens.is_ok()) return done(tokens.status());
+    LlmGeneration g;
+    code = run_generation(llm, &tokens.value(), nullptr, max_new_tokens, sampling, stop, n_stop, nullptr, nullptr, &g);
+    return code != DOOMS_OK ? code : text_out(g.text, out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_chat_stream(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t max_new_tokens,
+                                                  const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback,
+                                                  void * user) {
+    if (!llm) return fail(DOOMS_INVALID_ARGUMENT, "llm is NULL");
+    if (!callback) return fail(DOOMS_INVALID_ARGUMENT, "callback is NULL");
+    int32_t code = DOOMS_OK;
+    std::vector<ChatMessage> chat;
+    if (!messages_of(messages, n_messages, &chat, &code)) return code;
+    auto tokens = llm->llm->chat_tokens(chat);
+    if (!tokens.is_ok()) return done(tokens.status());
+    LlmGeneration g;
+    return run_generation(llm, &tokens.value(), nullptr, max_new_tokens, sampling, stop, n_stop, callback, user, &g);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_llm_count_chat_tokens(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t * count) {
+    if (!llm || !count) return fail(DOOMS_INVALID_ARGUMENT, "llm or count is NULL");
+    int32_t code = DOOMS_OK;
+    std::vector<ChatMessage> chat;
+    if (!messages_of(messages, n_messages, &chat, &code)) return code;
+    auto tokens = llm->llm->chat_tokens(chat);
+    if (!tokens.is_ok()) return done(tokens.status());
+    *count = int32_t(tokens.value().size());
+    return DOOMS_OK;
+}
 DOOMS_CUDA_API int32_t dooms_cuda_llm_count_tokens(dooms_cuda_llm * llm, const char * text, int32_t add_special, int32_t * count) {
     if (!llm || !count) return fail(DOOMS_INVALID_ARGUMENT, "llm or count is NULL");
     if (!text || !*text) return fail(DOOMS_INVALID_ARGUMENT, "count_tokens: empty text");
@@ -547,6 +591,26 @@ DOOMS_CUDA_API int32_t dooms_cuda_vocab_piece(const dooms_cuda_vocab * vocab, in
     *n = int32_t(p.size());
     if (capacity < *n || (!out && *n > 0)) return fail(DOOMS_RESOURCE_EXHAUSTED, "the piece needs " + std::to_string(*n) + " bytes");
     if (*n > 0) std::memcpy(out, p.data(), p.size());
+    return DOOMS_OK;
+}
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_apply_chat_template(const dooms_cuda_vocab * vocab, const dooms_cuda_chat_message * messages, int32_t n_messages,
+                                                            int32_t add_generation_prompt, char * out, size_t capacity, size_t * needed) {
+    if (!vocab) return fail(DOOMS_INVALID_ARGUMENT, "vocab is NULL");
+    int32_t code = DOOMS_OK;
+    std::vector<ChatMessage> chat;
+    if (!messages_of(messages, n_messages, &chat, &code)) return code;
+    auto text = vocab->vocab.apply_chat_template(chat, add_generation_prompt != 0);
+    if (!text.is_ok()) return done(text.status());
+    return text_out(text.value(), out, capacity, needed);
+}
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize_special(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t parse_special, int32_t * out,
+                                                         int32_t capacity, int32_t * n) {
+    if (!vocab || !n) return fail(DOOMS_INVALID_ARGUMENT, "vocab or n is NULL");
+    auto t = vocab->vocab.tokenize(text ? text : "", add_special != 0, parse_special != 0);
+    if (!t.is_ok()) return done(t.status());
+    *n = int32_t(t.value().size());
+    if (!out || capacity < *n) return fail(DOOMS_RESOURCE_EXHAUSTED, "the ids need room for " + std::to_string(*n));
+    std::copy(t.value().begin(), t.value().end(), out);
     return DOOMS_OK;
 }
 DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t * out, int32_t capacity, int32_t * n) {

@@ -89,8 +89,14 @@ Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
     v.special_.assign(n, false);
     if (const auto types = md.find("tokenizer.ggml.token_type"); types != md.end() && types->second.items.size() == n) {
         // 3 = control, 4 = user defined: no text of their own in the answer (6 = byte: handled as a piece)
-        for (size_t i = 0; i < n; i++) { const int64_t t = types->second.items[i].i; v.special_[i] = t == 3; }
+        for (size_t i = 0; i < n; i++) {
+            const int64_t t = types->second.items[i].i;
+            v.special_[i] = t == 3;
+            if ((t == 3 || t == 4) && !v.raw_[i].empty()) v.marked_.emplace_back(v.raw_[i], int32_t(i));
+        }
+        std::stable_sort(v.marked_.begin(), v.marked_.end(), [](const auto & a, const auto & b) { return a.first.size() > b.first.size(); });
     }
+    if (auto tmpl = file.get_string("tokenizer.chat_template"); tmpl.is_ok()) v.chat_template_ = tmpl.value();
     v.pieces_.resize(n);
     for (size_t i = 0; i < n; i++) {
         const std::string & raw = v.raw_[i];
@@ -134,13 +140,45 @@ const std::string & Vocab::piece(int32_t id) const {
 
 bool Vocab::is_end_of_generation(int32_t id) const { return std::find(eog_.begin(), eog_.end(), id) != eog_.end(); }
 
-Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_special) const {
+Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_special, bool parse_special) const {
     if (text.empty()) return invalid_argument("tokenize: empty text");
     std::vector<int32_t> out;
     if (add_special && add_bos_ && bos_ >= 0) out.push_back(bos_);
+    // the text in stretches between marked tokens; a sentencepiece stretch gets its space in front at the start and after a marked token
+    size_t from = 0, at = 0;
+    bool after_marked = true;
+    auto flush = [&](size_t end) -> Status {
+        if (end > from) {
+            Status s = tokenize_plain(text.substr(from, end - from), after_marked, &out);
+            if (!s.is_ok()) return s;
+            after_marked = false;
+        }
+        return Status();
+    };
+    while (at < text.size() && !marked_.empty()) {
+        const std::pair<std::string, int32_t> * hit = nullptr;
+        for (const auto & m : marked_) {
+            if (!parse_special && special_[size_t(m.second)]) continue;
+            if (text.compare(at, m.first.size(), m.first) == 0) { hit = &m; break; }
+        }
+        if (!hit) { at++; continue; }
+        Status s = flush(at);
+        if (!s.is_ok()) return s;
+        out.push_back(hit->second);
+        after_marked = true;
+        at += hit->first.size();
+        from = at;
+    }
+    Status s = flush(text.size());
+    if (!s.is_ok()) return s;
+    return out;
+}
+
+Status Vocab::tokenize_plain(const std::string & text, bool space_in_front, std::vector<int32_t> * result) const {
+    std::vector<int32_t> & out = *result;
     if (!byte_level_) {
         // sentencepiece: the escaped text as a chain of characters; the pair whose concatenation is the best-scoring piece is merged until none is a piece
-        std::string escaped = "\xE2\x96\x81";
+        std::string escaped = space_in_front ? "\xE2\x96\x81" : "";
         for (char c : text) { if (c == ' ') escaped += "\xE2\x96\x81"; else escaped += c; }
         struct Sym { size_t at, len; int prev, next; };
         std::vector<Sym> sym;
@@ -189,7 +227,7 @@ Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_
                 out.push_back(b->second);
             }
         }
-        return out;
+        return Status();
     }
     // words: a run of one class of bytes (letters, digits, other), with the single space before it
     auto cls = [](unsigned char c) { return c == ' ' ? 0 : (std::isalpha(c) || c >= 0x80) ? 1 : std::isdigit(c) ? 2 : 3; };
@@ -225,6 +263,38 @@ Result<std::vector<int32_t>> Vocab::tokenize(const std::string & text, bool add_
             }
         }
         at = end;
+    }
+    return Status();
+}
+
+// The families below are the ones llama.cpp's llama_chat_apply_template knows by these markers; their formats are the model cards' own.
+Result<std::string> Vocab::apply_chat_template(const std::vector<ChatMessage> & messages, bool add_generation_prompt) const {
+    if (messages.empty()) return invalid_argument("no messages");
+    for (const ChatMessage & m : messages) if (m.role.empty()) return invalid_argument("a message has an empty role");
+    if (chat_template_.empty()) return unsupported("the model file has no chat template");
+    auto has = [&](const char * marker) { return chat_template_.find(marker) != std::string::npos; };
+    auto trimmed = [](const std::string & t) {
+        size_t a = 0, b = t.size();
+        while (a < b && std::isspace(static_cast<unsigned char>(t[a]))) a++;
+        while (b > a && std::isspace(static_cast<unsigned char>(t[b - 1]))) b--;
+        return t.substr(a, b - a);
+    };
+    std::string out;
+    if (has("<|im_start|>") && has("<end_of_utterance>")) {          // SmolVLM: "User: ...<end_of_utterance>\nAssistant:"
+        out = "<|im_start|>";
+        for (const ChatMessage & m : messages) {
+            if (m.role == "system") out += m.content + "\n\n";
+            else out += (m.role == "user" ? "User: " : "Assistant: ") + m.content + "<end_of_utterance>\n";
+        }
+        if (add_generation_prompt) out += "Assistant:";
+    } else if (has("<|im_start|>") && !has("<|im_sep|>")) {          // ChatML (Qwen2 and many others)
+        for (const ChatMessage & m : messages) out += "<|im_start|>" + m.role + "\n" + m.content + "<|im_end|>\n";
+        if (add_generation_prompt) out += "<|im_start|>assistant\n";
+    } else if (has("<|start_header_id|>") && has("<|end_header_id|>")) {      // Llama 3
+        for (const ChatMessage & m : messages) out += "<|start_header_id|>" + m.role + "<|end_header_id|>\n\n" + trimmed(m.content) + "<|eot_id|>";
+        if (add_generation_prompt) out += "<|start_header_id|>assistant<|end_header_id|>\n\n";
+    } else {
+        return unsupported("this model's chat template is of a family this library does not know (ChatML, Llama 3 and SmolVLM are written)");
     }
     return out;
 }
@@ -353,6 +423,19 @@ Result<std::unique_ptr<Llm>> Llm::load(const std::string & path, const LlmOption
 
 Result<LlmGeneration> Llm::generate(const std::string & prompt, const LlmGenerateOptions & o, const std::function<bool(const std::string &)> & on_text, LlmTimings * timings) {
     auto tokens = tokenize(prompt, true);
+    if (!tokens.is_ok()) return tokens.status();
+    return generate_tokens(tokens.value(), o, on_text, timings);
+}
+
+Result<std::vector<int32_t>> Llm::chat_tokens(const std::vector<ChatMessage> & messages) const {
+    auto text = vocab_.apply_chat_template(messages, true);
+    if (!text.is_ok()) return text.status();
+    return vocab_.tokenize(text.value(), /*add_special=*/false, /*parse_special=*/true);
+}
+
+Result<LlmGeneration> Llm::chat(const std::vector<ChatMessage> & messages, const LlmGenerateOptions & o, const std::function<bool(const std::string &)> & on_text,
+                                LlmTimings * timings) {
+    auto tokens = chat_tokens(messages);
     if (!tokens.is_ok()) return tokens.status();
     return generate_tokens(tokens.value(), o, on_text, timings);
 }

@@ -3,7 +3,9 @@
 // tokenization, seeded sampling, streaming with complete UTF-8 pieces and stop strings, timings. The reference takes vocabulary, tokenizer and sampler
 // from llama.cpp (src/models/vlm/text_decoder.*), which is not part of this backend; here they are this file's own: the vocabulary is read from the GGUF
 // metadata (tokenizer.ggml.*), byte-level BPE files are tokenized by merge rank, and the sampler is a plain temperature / top-k / top-p / repetition
-// penalty chain on a seeded generator. Chat templates are not evaluated (chat() of the reference: Unsupported here).
+// penalty chain on a seeded generator. Chat templates are not evaluated as Jinja: as llama.cpp's llama_chat_apply_template does (the call the reference
+// makes, src/models/vlm/text_decoder.cpp:257-278), the file's template is recognised by the markers it contains and the conversation is written in that
+// family's published format (ChatML, Llama 3, SmolVLM); any other template is Unsupported.
 #include <cstdint>
 #include <functional>
 #include <memory>
@@ -25,6 +27,10 @@ struct SamplerOptions {
     uint32_t seed = 0;
 };
 
+struct ChatMessage {             // text_decoder.h:32-35
+    std::string role, content;
+};
+
 // The vocabulary of a GGUF file: token id <-> bytes.
 class Vocab {
 public:
@@ -41,9 +47,21 @@ public:
     //   byte-level BPE: words are split at the boundary before a run of spaces / letters / digits / other, each word's bytes are merged pairwise by rank;
     //   sentencepiece: spaces become U+2581 (one is put in front of the text), the text's characters are merged pairwise, best-scoring vocabulary piece
     //   first (tokenizer.ggml.scores; leftmost on ties), and what is no piece at the end goes out byte by byte as <0xHH>.
-    Result<std::vector<int32_t>> tokenize(const std::string & text, bool add_special) const;
+    // parse_special: a control token's text inside `text` ("<|im_start|>") becomes that token's id instead of being tokenized as characters (what a
+    // chat template's output needs); user-defined tokens are matched either way. The longest token at the earliest position wins.
+    Result<std::vector<int32_t>> tokenize(const std::string & text, bool add_special, bool parse_special = false) const;
+
+    // The conversation in the format of the file's chat template (tokenizer.chat_template), with the opening of the assistant's turn at the end when
+    // add_generation_prompt (TextDecoder::apply_chat_template, text_decoder.cpp:257-278).
+    //   InvalidArgument  no messages, a message with an empty role     Unsupported  the file has no template, or one of a family this library does not know
+    Result<std::string> apply_chat_template(const std::vector<ChatMessage> & messages, bool add_generation_prompt = true) const;
+    bool has_chat_template() const { return apply_chat_template({{"user", "x"}}, true).is_ok(); }      // llm_pipeline.cpp:82
 
 private:
+    Status tokenize_plain(const std::string & text, bool space_in_front, std::vector<int32_t> * out) const;
+    std::vector<std::pair<std::string, int32_t>> marked_;       // control and user-defined tokens that are looked for in text, longest first
+    std::vector<bool> control_;
+    std::string chat_template_;
     std::vector<std::string> pieces_;                           // decoded bytes per id
     std::vector<std::string> raw_;                              // as stored
     std::unordered_map<std::string, int32_t> ids_;              // raw token -> id
@@ -124,6 +142,12 @@ public:
                                    const std::function<bool(const std::string &)> & on_text = nullptr, LlmTimings * timings = nullptr);
     Result<LlmGeneration> generate_tokens(const std::vector<int32_t> & prompt, const LlmGenerateOptions & options = LlmGenerateOptions(),
                                           const std::function<bool(const std::string &)> & on_text = nullptr, LlmTimings * timings = nullptr);
+    // A conversation, formatted with the file's chat template and tokenized with its special tokens parsed and no BOS added: the template's text carries
+    // what it needs (llm_pipeline.h:60-71, llm_pipeline.cpp:233-247).   Unsupported  no template, or an unknown family; otherwise as generate
+    bool has_chat_template() const { return vocab_.has_chat_template(); }
+    Result<std::vector<int32_t>> chat_tokens(const std::vector<ChatMessage> & messages) const;
+    Result<LlmGeneration> chat(const std::vector<ChatMessage> & messages, const LlmGenerateOptions & options = LlmGenerateOptions(),
+                               const std::function<bool(const std::string &)> & on_text = nullptr, LlmTimings * timings = nullptr);
 
     // The text side of a vision-language pipeline (generate_native, src/pipeline/vlm_pipeline.cpp:177-212): the whole prompt as ONE embedding sequence -
     // the rows of the tokens before the image, the image's embedding rows as the vision model produced them (image_rows x n_embd floats), the rows of the

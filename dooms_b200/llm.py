@@ -37,6 +37,15 @@ def _text(call) -> str:
     return buf.value.decode("utf-8", "surrogateescape")
 
 
+def _messages(messages):
+    """[(role, content), ...] or [{"role": ..., "content": ...}, ...] as an array of dooms_cuda_chat_message."""
+    pairs = [(m["role"], m["content"]) if isinstance(m, dict) else tuple(m) for m in messages]
+    arr = (L.ChatMessage * max(1, len(pairs)))()
+    for i, (role, content) in enumerate(pairs):
+        arr[i].role, arr[i].content = role.encode("utf-8", "surrogateescape"), content.encode("utf-8", "surrogateescape")
+    return arr, len(pairs)
+
+
 def sample(logits: np.ndarray, draws: int = 1, **sampling) -> list[int]:
     """`draws` tokens from one row of logits (dooms_cuda_sample); keyword arguments as dooms_cuda_sampling, none: greedy."""
     v = np.ascontiguousarray(logits, dtype=np.float32)
@@ -74,11 +83,16 @@ class Vocab:
     def is_end_of_generation(self, token: int) -> bool:
         return bool(L.lib().dooms_cuda_vocab_is_end_of_generation(self._h, token))
 
-    def tokenize(self, text: str, add_special: bool = True) -> list[int]:
+    def tokenize(self, text: str, add_special: bool = True, parse_special: bool = False) -> list[int]:
         n = C.c_int32()
         out = np.empty(4 * len(text.encode()) + 8, dtype=np.int32)
-        L.check(L.lib().dooms_cuda_vocab_tokenize(self._h, text.encode(), int(add_special), out.ctypes.data, out.size, C.byref(n)))
+        L.check(L.lib().dooms_cuda_vocab_tokenize_special(self._h, text.encode(), int(add_special), int(parse_special), out.ctypes.data, out.size, C.byref(n)))
         return [int(t) for t in out[:n.value]]
+
+    def apply_chat_template(self, messages, add_generation_prompt: bool = True) -> str:
+        """The conversation in the format of the file's chat template; Unsupported without one or with one of an unknown family."""
+        arr, n = _messages(messages)
+        return _text(lambda buf, cap, needed: L.lib().dooms_cuda_vocab_apply_chat_template(self._h, arr, n, int(add_generation_prompt), buf, cap, needed))
 
     def stream(self, tokens: Sequence[int], stop: Sequence[str] | None = None, on_text: Callable[[str], bool] | None = None):
         """The text assembly over `tokens`: (text, tokens consumed, finish reason). on_text receives each piece and returns False to cancel."""
@@ -131,6 +145,29 @@ class Llm:
             pieces.append(text)
             return 0 if on_text(text) is not False else 1
         L.check(L.lib().dooms_cuda_llm_generate_stream(self._h, prompt.encode("utf-8", "surrogateescape"), max_new_tokens, sp, arr, n_stop, L.TEXT_CALLBACK(cb), None))
+        return "".join(pieces)
+
+    def count_chat_tokens(self, messages) -> int:
+        arr, n_messages = _messages(messages)
+        n = C.c_int32()
+        L.check(L.lib().dooms_cuda_llm_count_chat_tokens(self._h, arr, n_messages, C.byref(n)))
+        return n.value
+
+    def chat(self, messages, max_new_tokens: int = 128, stop: Sequence[str] | None = None, on_text: Callable[[str], bool] | None = None, **sampling) -> str:
+        """The assistant's answer to a conversation ([(role, content), ...]) formatted with the file's chat template."""
+        msgs, n_messages = _messages(messages)
+        arr, n_stop = _stops(stop)
+        s = _sampling(**sampling) if sampling else None
+        sp = C.byref(s) if s else None
+        if on_text is None:
+            return _text(lambda buf, cap, needed: L.lib().dooms_cuda_llm_chat(self._h, msgs, n_messages, max_new_tokens, sp, arr, n_stop, buf, cap, needed))
+        pieces: list[str] = []
+
+        def cb(piece, _u):
+            text = piece.decode("utf-8", "surrogateescape")
+            pieces.append(text)
+            return 0 if on_text(text) is not False else 1
+        L.check(L.lib().dooms_cuda_llm_chat_stream(self._h, msgs, n_messages, max_new_tokens, sp, arr, n_stop, L.TEXT_CALLBACK(cb), None))
         return "".join(pieces)
 
     def generate_tokens(self, prompt: Sequence[int], max_new_tokens: int = 128, stop: Sequence[str] | None = None, **sampling):

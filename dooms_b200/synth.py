@@ -136,9 +136,22 @@ def random_blocks(dtype: int, rows: int, cols: int, seed: int) -> np.ndarray:
     return b.reshape(rows, -1)
 
 
-def byte_level_vocab(n_vocab: int) -> dict:
+_CHAT_FAMILIES = {
+    # family: (control tokens, end-of-turn token, a Jinja template of that family: this library looks only for the family's markers in it)
+    "chatml": (["<|im_start|>", "<|im_end|>"], "<|im_end|>",
+               "{% for message in messages %}{{'<|im_start|>' + message['role'] + '\n' + message['content'] + '<|im_end|>' + '\n'}}{% endfor %}"
+               "{% if add_generation_prompt %}{{ '<|im_start|>assistant\n' }}{% endif %}"),
+    "llama3": (["<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"], "<|eot_id|>",
+               "{% for message in messages %}{{ '<|start_header_id|>' + message['role'] + '<|end_header_id|>\n\n' + message['content'] | trim + '<|eot_id|>' }}{% endfor %}"
+               "{% if add_generation_prompt %}{{ '<|start_header_id|>assistant<|end_header_id|>\n\n' }}{% endif %}"),
+    "other": ([], None, "{% for message in messages %}{{ '[TURN] ' + message['content'] }}{% endfor %}"),
+}
+
+
+def byte_level_vocab(n_vocab: int, chat: str | None = None) -> dict:
     """Tokenizer metadata of a small byte-level BPE vocabulary with n_vocab (>= 270) entries: the 256 byte tokens in the byte alphabet of such
-    vocabularies, a few merges of common English pairs, filler tokens, and an end-of-text token as the last id."""
+    vocabularies, a few merges of common English pairs, filler tokens, and an end-of-text token as the last id. chat ("chatml", "llama3", "other"): with
+    that family's control tokens in the ids just below the last one, its end-of-turn token as tokenizer.ggml.eot_token_id and a tokenizer.chat_template."""
     printable = [b for b in range(256) if 0x21 <= b <= 0x7E or 0xA1 <= b <= 0xAC or 0xAE <= b <= 0xFF]
     to_cp, nxt = {}, 256
     for b in range(256):
@@ -159,8 +172,17 @@ def byte_level_vocab(n_vocab: int) -> dict:
         tokens.append(f"<filler_{len(tokens)}>")
     tokens.append("<|endoftext|>")
     types = [1] * (n_vocab - 1) + [3]
-    return {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": types,
-            "tokenizer.ggml.eos_token_id": n_vocab - 1, "tokenizer.ggml.bos_token_id": n_vocab - 1, "tokenizer.ggml.add_bos_token": False}
+    md = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": types,
+          "tokenizer.ggml.eos_token_id": n_vocab - 1, "tokenizer.ggml.bos_token_id": n_vocab - 1, "tokenizer.ggml.add_bos_token": False}
+    if chat is not None:
+        control, end_of_turn, template = _CHAT_FAMILIES[chat]
+        for i, name in enumerate(control):
+            at = n_vocab - 1 - len(control) + i
+            tokens[at], types[at] = name, 3
+            if name == end_of_turn:
+                md["tokenizer.ggml.eot_token_id"] = at
+        md["tokenizer.chat_template"] = template
+    return md
 
 
 def sentencepiece_vocab(n_vocab: int) -> dict:
@@ -193,7 +215,7 @@ def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
 
 def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu", vocab=False) -> dict:
     """Writes the model as a GGUF file; returns {"matrix_bytes": ...}. vocab: True with the tokenizer metadata of byte_level_vocab(n_vocab),
-    "sentencepiece" with that of sentencepiece_vocab(n_vocab)."""
+    "sentencepiece" with that of sentencepiece_vocab(n_vocab), "chatml" / "llama3" / "other" with byte_level_vocab(n_vocab, chat=...)."""
     md = {
         "general.architecture": spec.arch,
         "general.name": spec.name,
@@ -207,7 +229,7 @@ def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu
         f"{spec.arch}.attention.layer_norm_rms_epsilon": float(spec.rms_eps),
     }
     if vocab:
-        md.update(sentencepiece_vocab(spec.n_vocab) if vocab == "sentencepiece" else byte_level_vocab(spec.n_vocab))
+        md.update(sentencepiece_vocab(spec.n_vocab) if vocab == "sentencepiece" else byte_level_vocab(spec.n_vocab, chat=vocab if isinstance(vocab, str) else None))
     tensors = []
     counter = [0]
 

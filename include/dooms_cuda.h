@@ -292,6 +292,20 @@ DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_tokens(dooms_cuda_llm * llm, cons
 DOOMS_CUDA_API int32_t dooms_cuda_llm_generate_from_embeddings(dooms_cuda_llm * llm, const int32_t * before, int32_t n_before, const float * image, int32_t image_rows,
                                                                const int32_t * after, int32_t n_after, int32_t max_new_tokens, dooms_cuda_text_callback callback,
                                                                void * user, char * out, size_t capacity, size_t * needed);
+/* A conversation (dooms_chat_message, dooms_c.h:94-97), formatted with the file's chat template: dooms_llm_chat / dooms_llm_chat_stream /
+ * dooms_llm_count_chat_tokens (dooms_c.h:111-116, 137-138). The template is recognised by the markers it contains, as the llama.cpp call the reference
+ * makes does (src/models/vlm/text_decoder.cpp:268-277): ChatML, Llama 3 and SmolVLM are written; no template or another family: DOOMS_UNSUPPORTED. The
+ * template's text is tokenized with its special tokens parsed and no BOS added (src/pipeline/llm_pipeline.cpp:233-238). */
+typedef struct dooms_cuda_chat_message {
+    const char * role;      /* "system", "user", "assistant" */
+    const char * content;
+} dooms_cuda_chat_message;
+DOOMS_CUDA_API int32_t dooms_cuda_llm_chat(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t max_new_tokens,
+                                           const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, char * out, size_t capacity, size_t * needed);
+DOOMS_CUDA_API int32_t dooms_cuda_llm_chat_stream(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t max_new_tokens,
+                                                  const dooms_cuda_sampling * sampling, const char * const * stop, int32_t n_stop, dooms_cuda_text_callback callback,
+                                                  void * user);
+DOOMS_CUDA_API int32_t dooms_cuda_llm_count_chat_tokens(dooms_cuda_llm * llm, const dooms_cuda_chat_message * messages, int32_t n_messages, int32_t * count);
 DOOMS_CUDA_API int32_t dooms_cuda_llm_last_generation(const dooms_cuda_llm * llm, dooms_cuda_generation_info * out);                 /* dooms_llm_last_generation */
 DOOMS_CUDA_API int32_t dooms_cuda_llm_count_tokens(dooms_cuda_llm * llm, const char * text, int32_t add_special, int32_t * count);   /* dooms_llm_count_tokens */
 
@@ -304,6 +318,12 @@ DOOMS_CUDA_API int32_t dooms_cuda_vocab_is_end_of_generation(const dooms_cuda_vo
 /* The bytes a token stands for (not NUL-terminated: a piece may hold any byte); *n their number; capacity too small: DOOMS_RESOURCE_EXHAUSTED. */
 DOOMS_CUDA_API int32_t dooms_cuda_vocab_piece(const dooms_cuda_vocab * vocab, int32_t token, char * out, int32_t capacity, int32_t * n);
 DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t * out, int32_t capacity, int32_t * n);
+/* The same with parse_special: the text of a control token inside `text` becomes that token's id (TextDecoder::tokenize's parse_special, text_decoder.h:51-53). */
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_tokenize_special(const dooms_cuda_vocab * vocab, const char * text, int32_t add_special, int32_t parse_special, int32_t * out,
+                                                         int32_t capacity, int32_t * n);
+/* TextDecoder::apply_chat_template (text_decoder.cpp:257-278): the conversation as the template's family writes it; the text as dooms_cuda_llm_generate returns one. */
+DOOMS_CUDA_API int32_t dooms_cuda_vocab_apply_chat_template(const dooms_cuda_vocab * vocab, const dooms_cuda_chat_message * messages, int32_t n_messages,
+                                                            int32_t add_generation_prompt, char * out, size_t capacity, size_t * needed);
 /* Runs the text assembly over `tokens`: pieces go to `callback` (optional); *consumed = tokens taken before generation ended, *finish_reason how it ended
  * (DOOMS_CUDA_FINISH_LENGTH: the tokens ran out); the whole text as dooms_cuda_llm_generate returns it. */
 DOOMS_CUDA_API int32_t dooms_cuda_text_stream(const dooms_cuda_vocab * vocab, const int32_t * tokens, int32_t n_tokens, const char * const * stop, int32_t n_stop,

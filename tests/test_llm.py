@@ -53,6 +53,43 @@ def test_sentencepiece_vocabulary_merges_by_score_and_falls_back_to_bytes(tmp_pa
     assert v.piece(1) == b"" and v.is_end_of_generation(2)
 
 
+def _chat_file(tmp_path, family):
+    path = str(tmp_path / f"chat_{family}.gguf")
+    synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 79, vocab=family)
+    return path
+
+
+CONVERSATION = [("system", "the world"), ("user", " hello world \n"), ("assistant", "hello"), ("user", "the")]
+
+
+def test_chat_templates_are_written_by_family_and_their_control_tokens_are_parsed(tmp_path):
+    """apply_chat_template (src/models/vlm/text_decoder.cpp:257-278): the family is read off the template's markers, the conversation is written in that
+    family's format; tokenizing it with parse_special gives the control tokens' own ids around the plainly tokenized text."""
+    v = Vocab(_chat_file(tmp_path, "chatml"))
+    text = v.apply_chat_template(CONVERSATION)
+    assert text == "".join(f"<|im_start|>{r}\n{c}<|im_end|>\n" for r, c in CONVERSATION) + "<|im_start|>assistant\n"
+    assert v.apply_chat_template(CONVERSATION[:2], add_generation_prompt=False) == "<|im_start|>system\nthe world<|im_end|>\n<|im_start|>user\n hello world \n<|im_end|>\n"
+    start, end = N_VOCAB - 3, N_VOCAB - 2
+    ids = v.tokenize("<|im_start|>user\nhello world<|im_end|>\n", add_special=False, parse_special=True)
+    assert ids == [start] + v.tokenize("user\nhello world", add_special=False) + [end] + v.tokenize("\n", add_special=False)
+    plain = v.tokenize("<|im_start|>user", add_special=False)                       # without parse_special the marker is ordinary text
+    assert start not in plain and b"".join(v.piece(t) for t in plain) == b"<|im_start|>user"
+    assert v.is_end_of_generation(end) and v.is_end_of_generation(N_VOCAB - 1) and v.piece(start) == b""
+
+    v3 = Vocab(_chat_file(tmp_path, "llama3"))
+    want = "".join(f"<|start_header_id|>{r}<|end_header_id|>\n\n{c.strip()}<|eot_id|>" for r, c in CONVERSATION) + "<|start_header_id|>assistant<|end_header_id|>\n\n"
+    assert v3.apply_chat_template(CONVERSATION) == want
+    ids3 = v3.tokenize(want, add_special=False, parse_special=True)
+    assert ids3.count(N_VOCAB - 4) == 5 and ids3.count(N_VOCAB - 3) == 5 and ids3.count(N_VOCAB - 2) == 4 and v3.is_end_of_generation(N_VOCAB - 2)
+
+    # refusals: no messages, an empty role, no template in the file, a template of an unknown family (text_decoder.cpp:259-276)
+    for vocab, messages, code in ((v, [], L.INVALID_ARGUMENT), (v, [("", "x")], L.INVALID_ARGUMENT), (Vocab(_chat_file(tmp_path, True)), CONVERSATION, L.UNSUPPORTED),
+                                  (Vocab(_chat_file(tmp_path, "other")), CONVERSATION, L.UNSUPPORTED)):
+        with pytest.raises(DoomsError) as e:
+            vocab.apply_chat_template(messages)
+        assert e.value.code == code
+
+
 def test_pieces_are_whole_characters_and_stop_strings_end_the_text(model):
     v = Vocab(model)
     # U+00E9 and an emoji arrive byte by byte: nothing incomplete is ever handed on
@@ -149,6 +186,32 @@ def test_generation_matches_the_decoder_and_reports_how_it_ended(model):
         assert e.value.code == code, kwargs
     dec.close()
     llm.close()
+
+
+@pytest.mark.gpu
+def test_chat_answers_the_templated_conversation(tmp_path):
+    """Llm::chat (src/pipeline/llm_pipeline.cpp:233-247): the conversation through the file's chat template, tokenized with its control tokens parsed and
+    no BOS, then generation as from any prompt; a file without a template refuses."""
+    path = _chat_file(tmp_path, "chatml")
+    llm, v = Llm(path, n_ctx=256, n_batch=64), Vocab(path)
+    ids = v.tokenize(v.apply_chat_template(CONVERSATION), add_special=False, parse_special=True)
+    assert llm.count_chat_tokens(CONVERSATION) == len(ids)
+    want_text, want_tokens = llm.generate_tokens(ids, 20)
+    assert llm.chat(CONVERSATION, 20) == want_text
+    info = llm.last_generation()
+    assert info["prompt_tokens"] == len(ids) and info["completion_tokens"] == len(want_tokens)
+    pieces = []
+    assert llm.chat([{"role": r, "content": c} for r, c in CONVERSATION], 20, on_text=lambda p: pieces.append(p) or True) == want_text and "".join(pieces) == want_text
+    with pytest.raises(DoomsError) as e:
+        llm.chat([], 4)
+    assert e.value.code == L.INVALID_ARGUMENT
+    llm.close()
+    plain = Llm(_chat_file(tmp_path, True), n_ctx=256, n_batch=64)
+    for call in (lambda: plain.chat(CONVERSATION, 4), lambda: plain.count_chat_tokens(CONVERSATION)):
+        with pytest.raises(DoomsError) as e:
+            call()
+        assert e.value.code == L.UNSUPPORTED
+    plain.close()
 
 
 @pytest.mark.gpu
