@@ -144,13 +144,16 @@ _CHAT_FAMILIES = {
     "llama3": (["<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"], "<|eot_id|>",
                "{% for message in messages %}{{ '<|start_header_id|>' + message['role'] + '<|end_header_id|>\n\n' + message['content'] | trim + '<|eot_id|>' }}{% endfor %}"
                "{% if add_generation_prompt %}{{ '<|start_header_id|>assistant<|end_header_id|>\n\n' }}{% endif %}"),
+    "smolvlm": (["<|im_start|>", "<end_of_utterance>"], "<end_of_utterance>",
+                "<|im_start|>{% for message in messages %}{{ message['role'] | capitalize + ': ' + message['content'] + '<end_of_utterance>\n' }}{% endfor %}"
+                "{% if add_generation_prompt %}{{ 'Assistant:' }}{% endif %}"),
     "other": ([], None, "{% for message in messages %}{{ '[TURN] ' + message['content'] }}{% endfor %}"),
 }
 
 
 def byte_level_vocab(n_vocab: int, chat: str | None = None) -> dict:
     """Tokenizer metadata of a small byte-level BPE vocabulary with n_vocab (>= 270) entries: the 256 byte tokens in the byte alphabet of such
-    vocabularies, a few merges of common English pairs, filler tokens, and an end-of-text token as the last id. chat ("chatml", "llama3", "other"): with
+    vocabularies, a few merges of common English pairs, filler tokens, and an end-of-text token as the last id. chat ("chatml", "llama3", "smolvlm", "other"): with
     that family's control tokens in the ids just below the last one, its end-of-turn token as tokenizer.ggml.eot_token_id and a tokenizer.chat_template."""
     printable = [b for b in range(256) if 0x21 <= b <= 0x7E or 0xA1 <= b <= 0xAC or 0xAE <= b <= 0xFF]
     to_cp, nxt = {}, 256
@@ -215,7 +218,7 @@ def _normal(shape, std: float, seed: int, device: str) -> torch.Tensor:
 
 def write_model(spec: ModelSpec, path: str | Path, seed: int, device: str = "cpu", vocab=False) -> dict:
     """Writes the model as a GGUF file; returns {"matrix_bytes": ...}. vocab: True with the tokenizer metadata of byte_level_vocab(n_vocab),
-    "sentencepiece" with that of sentencepiece_vocab(n_vocab), "chatml" / "llama3" / "other" with byte_level_vocab(n_vocab, chat=...)."""
+    "sentencepiece" with that of sentencepiece_vocab(n_vocab), "chatml" / "llama3" / "smolvlm" / "other" with byte_level_vocab(n_vocab, chat=...)."""
     md = {
         "general.architecture": spec.arch,
         "general.name": spec.name,

@@ -82,6 +82,12 @@ def test_chat_templates_are_written_by_family_and_their_control_tokens_are_parse
     ids3 = v3.tokenize(want, add_special=False, parse_special=True)
     assert ids3.count(N_VOCAB - 4) == 5 and ids3.count(N_VOCAB - 3) == 5 and ids3.count(N_VOCAB - 2) == 4 and v3.is_end_of_generation(N_VOCAB - 2)
 
+    vs = Vocab(_chat_file(tmp_path, "smolvlm"))      # the text model of the reference's vision-language pipeline: system text, then "User:" / "Assistant:" turns
+    assert vs.apply_chat_template(CONVERSATION) == ("<|im_start|>the world\n\nUser:  hello world \n<end_of_utterance>\nAssistant: hello<end_of_utterance>\n"
+                                                    "User: the<end_of_utterance>\nAssistant:")
+    assert vs.tokenize("<|im_start|>User: the<end_of_utterance>", add_special=False, parse_special=True)[::len(vs.tokenize("User: the", add_special=False)) + 1] == \
+        [N_VOCAB - 3, N_VOCAB - 2]
+
     # refusals: no messages, an empty role, no template in the file, a template of an unknown family (text_decoder.cpp:259-276)
     for vocab, messages, code in ((v, [], L.INVALID_ARGUMENT), (v, [("", "x")], L.INVALID_ARGUMENT), (Vocab(_chat_file(tmp_path, True)), CONVERSATION, L.UNSUPPORTED),
                                   (Vocab(_chat_file(tmp_path, "other")), CONVERSATION, L.UNSUPPORTED)):
