@@ -38,6 +38,23 @@ template <int D, int GP>
 __global__ void __launch_bounds__(kThreads) k_attention_decode(const AttnDecodeParams pp) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_trigger();
+    if (pp.l2_hint) {
+        // The cached keys and values of earlier positions do not depend on the projection that runs before this kernel. While that projection's last
+        // blocks drain, ask for this block's range of both caches to be brought to L2 (a hint: nothing is read into the SM). The position is read before
+        // the kernel that may still be writing it is known to be complete, so it can be one step old; that shifts the hinted range by one row at most.
+        const int pos = __ldcg(&pp.st->pos);
+        const int n_keys = pp.n_keys_fixed > 0 ? pp.n_keys_fixed : pos + 1;
+        const int tiles_total = (n_keys + kTileKeys - 1) / kTileKeys, tiles_per = (tiles_total + pp.splits - 1) / pp.splits;
+        const int j_begin = min(n_keys, int(blockIdx.y) * tiles_per * kTileKeys), j_end = min(n_keys, j_begin + tiles_per * kTileKeys);
+        constexpr int LINES = D * 2 / 128 > 0 ? D * 2 / 128 : 1;      // 128-byte lines per cached row of one head
+        if (pos >= 0 && pos < (1 << 28)) {
+            for (int i = threadIdx.x; i < (j_end - j_begin) * LINES; i += kThreads) {
+                const int64_t at = int64_t(j_begin + i / LINES) * pp.s.kv_stride + int(blockIdx.x) * D + (i % LINES) * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.kc + at));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pp.vc + at));
+            }
+        }
+    }
     pdl_wait();
     attention_decode_body<D, GP, true>(pp, int(blockIdx.x), int(blockIdx.y), int(gridDim.y), int(blockIdx.z), smem);
 }
@@ -76,8 +93,10 @@ int attention_gqa_splits(int n_head_kv, int n_ctx) {
 cudaError_t launch_attention_gqa(const float * qkv, void * kc, void * vc, float * part, const DevState * st, const double * inv_freq, int n_keys_fixed,
                                  int splits, const AttnShape & s, int * counters, float * out, void * xq, cudaStream_t stream, const void * rope_cs) {
     if (!attention_gqa_supported(s) || (!inv_freq && n_keys_fixed < 1) || (counters && !out) || (xq && !counters)) return cudaErrorInvalidValue;
-    const AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
-                             static_cast<uint8_t *>(xq), static_cast<const float2 *>(rope_cs), nullptr, nullptr, 0, 0, 0, nullptr};
+    AttnDecodeParams p{qkv, static_cast<__half *>(kc), static_cast<__half *>(vc), part, st, inv_freq, n_keys_fixed, splits, s, counters, out,
+                       static_cast<uint8_t *>(xq), static_cast<const float2 *>(rope_cs), nullptr, nullptr, 0, 0, 0, nullptr, 0};
+    static const bool hint = [] { const char * e = getenv("DOOMS_ATTN_L2_HINT"); return !(e && *e == '0'); }();
+    p.l2_hint = (hint && st && inv_freq) ? 1 : 0;
     return s.head_dim == 64 ? launch_group<64>(p, s.n_head / s.n_head_kv, stream) : launch_group<128>(p, s.n_head / s.n_head_kv, stream);
 }
 

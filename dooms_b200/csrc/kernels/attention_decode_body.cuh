@@ -41,6 +41,7 @@ struct AttnDecodeParams {
     int64_t slot_elems;       // f16 elements between the caches of consecutive slots
     int64_t part_row_floats;  // floats of `part` per row
     __half * out16;           // optional: the merged rows as f16 as well ([row][n_head * head_dim]), the tensor-core GEMM's operand
+    int l2_hint;              // single-row decode: before waiting for the projection in front of it, a block asks for its range of the caches to be brought to L2
 };
 
 __device__ __forceinline__ void cp16(uint32_t dst, const void * src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
