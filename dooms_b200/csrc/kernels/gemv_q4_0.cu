@@ -210,6 +210,12 @@ __device__ __forceinline__ void gemv_q4_0_body(const CUtensorMap * mwp, const CU
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane >> 2, t = lane & 3;
     const int nb = p.cols / 32;
     const int nmat = p.W2 ? 2 : 1;
+    if constexpr (TMA) {      // the copy descriptors are on their way to the SM while the indices and the barriers are set up
+        if (threadIdx.x == 32) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(mwp) : "memory");
+            if (nmat == 2) asm volatile("prefetch.tensormap [%0];" ::"l"(mw2p) : "memory");
+        }
+    }
     const uint32_t RB = uint32_t(nb) * kBlockBytes;
     const uint32_t CB = uint32_t(p.cbk) * kBlockBytes;
 
