@@ -53,6 +53,26 @@ def test_sentencepiece_vocabulary_merges_by_score_and_falls_back_to_bytes(tmp_pa
     assert v.piece(1) == b"" and v.is_end_of_generation(2)
 
 
+def test_sentencepiece_tokenizer_matches_the_sentencepiece_library(tmp_path):
+    """The ids the sentencepiece library itself gives for a BPE model with byte fallback trained on synthetic text (tests/golden/sentencepiece_tiny.json,
+    written by tests/golden/make_sentencepiece_fixture.py) are what Vocab.tokenize gives for the same pieces and scores read from a GGUF file: the
+    reference gets this tokenizer from llama.cpp (src/models/vlm/text_decoder.cpp:123-145), whose "llama" tokenizer follows the same library."""
+    import json
+    from pathlib import Path
+    from dooms_b200.gguf_io import GgufWriter
+    fx = json.loads((Path(__file__).parent / "golden" / "sentencepiece_tiny.json").read_text())
+    path = str(tmp_path / "spm_golden.gguf")
+    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": fx["pieces"],
+                              "tokenizer.ggml.scores": [float(x) for x in fx["scores"]], "tokenizer.ggml.token_type": fx["types"],
+                              "tokenizer.ggml.bos_token_id": fx["bos"], "tokenizer.ggml.eos_token_id": fx["eos"], "tokenizer.ggml.add_bos_token": True}, [])
+    v = Vocab(path)
+    assert len(v) == len(fx["pieces"])
+    for case in fx["cases"]:
+        assert v.tokenize(case["text"], add_special=False) == case["ids"], case["text"]
+        assert b"".join(v.piece(t) for t in case["ids"]) == (" " + case["text"]).encode()      # and the pieces give the text back, with the space put in front
+    assert v.tokenize("hello world") == [fx["bos"]] + fx["cases"][0]["ids"]
+
+
 def _chat_file(tmp_path, family):
     path = str(tmp_path / f"chat_{family}.gguf")
     synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 79, vocab=family)
