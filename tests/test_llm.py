@@ -73,6 +73,26 @@ def test_sentencepiece_tokenizer_matches_the_sentencepiece_library(tmp_path):
     assert v.tokenize("hello world") == [fx["bos"]] + fx["cases"][0]["ids"]
 
 
+def test_byte_level_bpe_tokenizer_matches_the_tokenizers_library(tmp_path):
+    """The ids the `tokenizers` library gives for a byte-level BPE vocabulary trained on synthetic text (tests/golden/byte_bpe_tiny.json, written by
+    tests/golden/make_byte_bpe_fixture.py) are what Vocab.tokenize gives for the same tokens and merges read from a GGUF file, on texts that this
+    backend's word splitter and the GPT-2 pre-tokenizer split alike (the fixture's script says which)."""
+    import json
+    from pathlib import Path
+    from dooms_b200.gguf_io import GgufWriter
+    fx = json.loads((Path(__file__).parent / "golden" / "byte_bpe_tiny.json").read_text())
+    n, eot = len(fx["tokens"]), fx["end_of_text"]
+    path = str(tmp_path / "bpe_golden.gguf")
+    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": fx["tokens"], "tokenizer.ggml.merges": fx["merges"],
+                              "tokenizer.ggml.token_type": [3 if i == eot else 1 for i in range(n)], "tokenizer.ggml.eos_token_id": eot,
+                              "tokenizer.ggml.bos_token_id": eot, "tokenizer.ggml.add_bos_token": False}, [])
+    v = Vocab(path)
+    for case in fx["cases"]:
+        assert v.tokenize(case["text"], add_special=False) == case["ids"], case["text"]
+        assert b"".join(v.piece(t) for t in case["ids"]) == case["text"].encode()
+    assert v.tokenize("hello<|endoftext|>", add_special=False, parse_special=True) == fx["cases"][2]["ids"] + [eot] and v.is_end_of_generation(eot)
+
+
 def _chat_file(tmp_path, family):
     path = str(tmp_path / f"chat_{family}.gguf")
     synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 79, vocab=family)
