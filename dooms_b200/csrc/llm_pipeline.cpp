@@ -8,9 +8,28 @@
 #include <numeric>
 #include <queue>
 
+#include "unicode_ranges.h"
+
 namespace dooms {
 
 namespace {
+
+template <size_t N> bool in_ranges(const CodePointRange (&ranges)[N], uint32_t cp) {
+    size_t lo = 0, hi = N;
+    while (lo < hi) {
+        const size_t mid = (lo + hi) / 2;
+        if (cp > ranges[mid].last) lo = mid + 1;
+        else if (cp < ranges[mid].first) hi = mid;
+        else return true;
+    }
+    return false;
+}
+bool is_letter(uint32_t cp) { return cp < 0x80 ? ((cp | 0x20u) >= 'a' && (cp | 0x20u) <= 'z') : in_ranges(kLetterRanges, cp); }      // \p{L}
+bool is_number(uint32_t cp) { return cp < 0x80 ? (cp >= '0' && cp <= '9') : in_ranges(kNumberRanges, cp); }                          // \p{N}
+bool is_space(uint32_t cp) {                                                                                                         // \s (White_Space)
+    return cp == ' ' || (cp >= 9 && cp <= 13) || cp == 0x85 || cp == 0xA0 || cp == 0x1680 || (cp >= 0x2000 && cp <= 0x200A) || cp == 0x2028 || cp == 0x2029 ||
+           cp == 0x202F || cp == 0x205F || cp == 0x3000;
+}
 
 // UTF-8 encoding of a code point.
 void put_utf8(std::string & s, uint32_t cp) {
@@ -70,6 +89,78 @@ double ms_since(Clock::time_point t) { return std::chrono::duration<double, std:
 
 }  // namespace
 
+// The words a byte-level BPE vocabulary merges within, as byte ranges of `text`: what the pre-tokenizer regexes of the model families give, matched by
+// hand (first alternative that matches at a position wins, as in the regex engines; llama.cpp applies the same patterns for tokenizer.ggml.pre):
+//   GPT-2:    's|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+
+//   Llama 3:  (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
+//   Qwen2:    the same with \p{N} (one digit) in place of \p{N}{1,3}
+std::vector<std::pair<size_t, size_t>> split_words(const std::string & text, int kind) {
+    constexpr int kGpt2 = 0, kLlama3 = 1;
+    std::vector<uint32_t> cp;
+    std::vector<size_t> at;
+    for (size_t i = 0; i < text.size();) {
+        const unsigned char c = static_cast<unsigned char>(text[i]);
+        int n = c >= 0xF0 ? 4 : c >= 0xE0 ? 3 : c >= 0xC0 ? 2 : 1;
+        if (i + size_t(n) > text.size()) n = 1;
+        uint32_t v = n == 1 ? c : c & (0xFFu >> (n + 1));
+        for (int k = 1; k < n; k++) v = (v << 6) | (static_cast<unsigned char>(text[i + size_t(k)]) & 0x3F);
+        cp.push_back(v);
+        at.push_back(i);
+        i += size_t(n);
+    }
+    const size_t n = cp.size();
+    at.push_back(text.size());
+    auto L = [&](size_t k) { return k < n && is_letter(cp[k]); };
+    auto N = [&](size_t k) { return k < n && is_number(cp[k]); };
+    auto S = [&](size_t k) { return k < n && is_space(cp[k]); };
+    auto O = [&](size_t k) { return k < n && !is_space(cp[k]) && !is_letter(cp[k]) && !is_number(cp[k]); };
+    auto NL = [&](size_t k) { return k < n && (cp[k] == '\r' || cp[k] == '\n'); };
+    auto low = [&](size_t k) -> uint32_t { return k >= n ? 0u : (kind != kGpt2 && cp[k] >= 'A' && cp[k] <= 'Z') ? cp[k] + 32u : cp[k]; };
+    std::vector<std::pair<size_t, size_t>> words;
+    for (size_t i = 0; i < n;) {
+        size_t j = 0;
+        if (cp[i] == '\'') {      // a contraction
+            const uint32_t a = low(i + 1), b = low(i + 2);
+            if (a == 's' || a == 't' || a == 'm' || a == 'd') j = i + 2;
+            else if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e') || (a == 'l' && b == 'l')) j = i + 3;
+        }
+        if (!j) {                  // letters, with the one character allowed in front of them
+            const bool lead = kind == kGpt2 ? cp[i] == ' ' : (!NL(i) && !L(i) && !N(i));
+            const size_t k = (lead && L(i + 1)) ? i + 1 : i;
+            if (L(k)) { j = k; while (L(j)) j++; }
+        }
+        if (!j) {                  // digits
+            if (kind == kGpt2) {
+                const size_t k = (cp[i] == ' ' && N(i + 1)) ? i + 1 : i;
+                if (N(k)) { j = k; while (N(j)) j++; }
+            } else if (N(i)) {
+                j = i + 1;
+                if (kind == kLlama3) while (N(j) && j - i < 3) j++;
+            }
+        }
+        if (!j) {                  // anything else that is no space, with a space in front (and, outside GPT-2, the line breaks behind)
+            const size_t k = (cp[i] == ' ' && O(i + 1)) ? i + 1 : i;
+            if (O(k)) {
+                j = k;
+                while (O(j)) j++;
+                if (kind != kGpt2) while (NL(j)) j++;
+            }
+        }
+        if (!j && S(i)) {
+            size_t e = i;
+            while (S(e)) e++;
+            if (kind != kGpt2) {   // up to the last line break of the run
+                for (size_t k = e; k > i; k--) if (NL(k - 1)) { j = k; break; }
+            }
+            if (!j) j = (e == n || e - i == 1) ? e : e - 1;      // the run, short of its last character when a word follows (that one goes with the word)
+        }
+        if (!j) j = i + 1;
+        words.emplace_back(at[i], at[j]);
+        i = j;
+    }
+    return words;
+}
+
 // ---------------------------------------------------------------- vocabulary
 
 Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
@@ -83,6 +174,11 @@ Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
     if (kind != "gpt2" && kind != "llama") return unsupported("tokenizer model '" + kind + "': byte-level BPE (gpt2) and sentencepiece pieces (llama) are read");
     Vocab v;
     v.byte_level_ = kind == "gpt2";
+    if (auto pre = file.get_string("tokenizer.ggml.pre"); pre.is_ok()) {
+        const std::string & name = pre.value();
+        if (name == "llama-bpe" || name == "llama3" || name == "llama-v3") { v.pre_ = 1; v.ignore_merges_ = true; }
+        else if (name == "qwen2" || name == "deepseek-r1-qwen") v.pre_ = 2;
+    }
     const size_t n = tokens->second.items.size();
     v.raw_.reserve(n);
     for (const GgufValue & t : tokens->second.items) v.raw_.push_back(t.s);
@@ -229,17 +325,15 @@ Status Vocab::tokenize_plain(const std::string & text, bool space_in_front, std:
         }
         return Status();
     }
-    // words: a run of one class of bytes (letters, digits, other), with the single space before it
-    auto cls = [](unsigned char c) { return c == ' ' ? 0 : (std::isalpha(c) || c >= 0x80) ? 1 : std::isdigit(c) ? 2 : 3; };
-    size_t at = 0;
-    while (at < text.size()) {
-        size_t end = at;
-        if (text[end] == ' ' && end + 1 < text.size() && text[end + 1] != ' ') end++;
-        const int k = cls(static_cast<unsigned char>(text[end]));
-        do end++; while (end < text.size() && cls(static_cast<unsigned char>(text[end])) == k && k != 0);
+    for (const auto & [at, end] : split_words(text, pre_)) {
         // the word's bytes in the byte alphabet, then merges by rank
         std::vector<std::string> sym;
         for (size_t i = at; i < end; i++) { std::string s; put_utf8(s, alphabet().to_cp[static_cast<unsigned char>(text[i])]); sym.push_back(std::move(s)); }
+        if (ignore_merges_) {      // Llama 3 vocabularies: a word that is a token goes out as that token, whatever the merges would build
+            std::string whole;
+            for (const std::string & s : sym) whole += s;
+            if (const auto id = ids_.find(whole); id != ids_.end()) { out.push_back(id->second); continue; }
+        }
         while (sym.size() > 1) {
             int32_t best = INT32_MAX;
             size_t where = 0;
@@ -262,7 +356,6 @@ Status Vocab::tokenize_plain(const std::string & text, bool space_in_front, std:
                 out.push_back(b->second);
             }
         }
-        at = end;
     }
     return Status();
 }

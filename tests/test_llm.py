@@ -73,24 +73,29 @@ def test_sentencepiece_tokenizer_matches_the_sentencepiece_library(tmp_path):
     assert v.tokenize("hello world") == [fx["bos"]] + fx["cases"][0]["ids"]
 
 
-def test_byte_level_bpe_tokenizer_matches_the_tokenizers_library(tmp_path):
+@pytest.mark.parametrize("pre", ["gpt-2", "llama-bpe", "qwen2"])
+def test_byte_level_bpe_tokenizer_matches_the_tokenizers_library(tmp_path, pre):
     """The ids the `tokenizers` library gives for a byte-level BPE vocabulary trained on synthetic text (tests/golden/byte_bpe_tiny.json, written by
-    tests/golden/make_byte_bpe_fixture.py) are what Vocab.tokenize gives for the same tokens and merges read from a GGUF file, on texts that this
-    backend's word splitter and the GPT-2 pre-tokenizer split alike (the fixture's script says which)."""
+    tests/golden/make_byte_bpe_fixture.py) are what Vocab.tokenize gives for the same tokens and merges read from a GGUF file, for each of the three
+    pre-tokenizers a file can name in tokenizer.ggml.pre: fixed texts plus seeded random mixtures of words, digits, punctuation, contractions, spaces,
+    line breaks and non-ASCII characters. The reference gets its tokenizer from llama.cpp (src/models/vlm/text_decoder.cpp:123-145), which applies the
+    same patterns."""
     import json
     from pathlib import Path
     from dooms_b200.gguf_io import GgufWriter
     fx = json.loads((Path(__file__).parent / "golden" / "byte_bpe_tiny.json").read_text())
     n, eot = len(fx["tokens"]), fx["end_of_text"]
     path = str(tmp_path / "bpe_golden.gguf")
-    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": fx["tokens"], "tokenizer.ggml.merges": fx["merges"],
-                              "tokenizer.ggml.token_type": [3 if i == eot else 1 for i in range(n)], "tokenizer.ggml.eos_token_id": eot,
-                              "tokenizer.ggml.bos_token_id": eot, "tokenizer.ggml.add_bos_token": False}, [])
+    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "gpt2", "tokenizer.ggml.pre": pre, "tokenizer.ggml.tokens": fx["tokens"],
+                              "tokenizer.ggml.merges": fx["merges"], "tokenizer.ggml.token_type": [3 if i == eot else 1 for i in range(n)],
+                              "tokenizer.ggml.eos_token_id": eot, "tokenizer.ggml.bos_token_id": eot, "tokenizer.ggml.add_bos_token": False}, [])
     v = Vocab(path)
-    for case in fx["cases"]:
+    cases = [c for c in fx["cases"] if c["pre"] == pre]
+    assert len(cases) > 100
+    for case in cases:
         assert v.tokenize(case["text"], add_special=False) == case["ids"], case["text"]
         assert b"".join(v.piece(t) for t in case["ids"]) == case["text"].encode()
-    assert v.tokenize("hello<|endoftext|>", add_special=False, parse_special=True) == fx["cases"][2]["ids"] + [eot] and v.is_end_of_generation(eot)
+    assert v.tokenize("hello<|endoftext|>", add_special=False, parse_special=True) == v.tokenize("hello", add_special=False) + [eot] and v.is_end_of_generation(eot)
 
 
 def _chat_file(tmp_path, family):
