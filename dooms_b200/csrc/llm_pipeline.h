@@ -2,8 +2,8 @@
 // A text language model on the CUDA decoder: the surface of the reference's `Llm` (src/pipeline/llm_pipeline.h:16-82) for the decoder's own engine:
 // tokenization, seeded sampling, streaming with complete UTF-8 pieces and stop strings, timings. The reference takes vocabulary, tokenizer and sampler
 // from llama.cpp (src/models/vlm/text_decoder.*), which is not part of this backend; here they are this file's own: the vocabulary is read from the GGUF
-// metadata (tokenizer.ggml.*), byte-level BPE files are tokenized by merge rank, and the sampler is a plain temperature / top-k / top-p / repetition
-// penalty chain on a seeded generator. Chat templates are not evaluated as Jinja: as llama.cpp's llama_chat_apply_template does (the call the reference
+// metadata (tokenizer.ggml.*), byte-level BPE files are tokenized by merge rank within the words their pre-tokenizer pattern cuts, sentencepiece files
+// by piece score, and the sampler is a plain temperature / top-k / top-p / repetition penalty chain on a seeded generator. Chat templates are not evaluated as Jinja: as llama.cpp's llama_chat_apply_template does (the call the reference
 // makes, src/models/vlm/text_decoder.cpp:257-278), the file's template is recognised by the markers it contains and the conversation is written in that
 // family's published format (ChatML, Llama 3, SmolVLM); any other template is Unsupported.
 #include <cstdint>
