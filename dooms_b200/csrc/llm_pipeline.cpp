@@ -435,15 +435,17 @@ int32_t Sampler::sample(const float * logits, int32_t n) {
         const size_t keep = o_.top_k > 0 ? std::min(size_t(o_.top_k), cand.size()) : cand.size();
         std::partial_sort(cand.begin(), cand.begin() + long(keep), cand.end(), by_logit);
         cand.resize(keep);
+        // the order of the reference's chain (src/models/vlm/text_decoder.cpp:239-242): top-k, then top-p on the probabilities at temperature 1, then the
+        // temperature, then the draw
         std::vector<double> p(keep);
         const double top = cand[0].first;
-        double total = 0;
-        for (size_t i = 0; i < keep; i++) { p[i] = std::exp((double(cand[i].first) - top) / double(o_.temperature)); total += p[i]; }
         size_t last = keep;
         if (o_.top_p < 1.f) {      // the smallest prefix whose probability reaches top_p
-            double acc = 0;
+            double total = 0, acc = 0;
+            for (size_t i = 0; i < keep; i++) { p[i] = std::exp(double(cand[i].first) - top); total += p[i]; }
             for (size_t i = 0; i < keep; i++) { acc += p[i] / total; if (acc >= double(o_.top_p)) { last = i + 1; break; } }
         }
+        for (size_t i = 0; i < last; i++) p[i] = std::exp((double(cand[i].first) - top) / double(o_.temperature));
         double mass = 0;
         for (size_t i = 0; i < last; i++) mass += p[i];
         double u = uniform() * mass;

@@ -184,6 +184,12 @@ def test_sampler_rules():
     assert np.abs(freq - p).max() < 0.015 and (draws == 3).sum() == 0
     # top_p keeps the smallest prefix that reaches it
     assert set(sample(lg, 2000, temperature=1.0, top_k=0, top_p=0.6, seed=1)) == {0}
+    # ... measured at temperature 1, before the temperature is applied (the order of the reference's chain, src/models/vlm/text_decoder.cpp:239-242): at
+    # temperature 10 the three largest are nearly equally likely, yet the prefix is still the one token that holds 0.64 of the mass at temperature 1
+    assert set(sample(lg, 2000, temperature=10.0, top_k=0, top_p=0.6, seed=1)) == {0}
+    hot = np.array(sample(lg, 6000, temperature=10.0, top_k=0, top_p=0.9, seed=2))      # prefix {0, 1, 2} at temperature 1 (0.64 + 0.24 + 0.09), drawn from at 10
+    want = np.exp(lg[:3] / 10.0) / np.exp(lg[:3] / 10.0).sum()
+    assert set(hot) == {0, 1, 2} and np.abs(np.array([(hot == i).mean() for i in range(3)]) - want).max() < 0.02
     # the repetition penalty pushes a token that was just drawn down
     flat = np.array([1.0, 0.99], dtype=np.float32)
     assert sample(flat, 3, temperature=0.0, repeat_penalty=1.5)[:2] == [0, 1]
