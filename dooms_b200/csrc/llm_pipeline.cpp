@@ -226,6 +226,8 @@ Result<Vocab> Vocab::from_gguf(const GgufFile & file) {
     }
     auto add_bos = file.get_bool("tokenizer.ggml.add_bos_token");
     v.add_bos_ = add_bos.is_ok() ? add_bos.value() : !v.byte_level_;      // sentencepiece models ask for it unless they say otherwise
+    auto space_prefix = file.get_bool("tokenizer.ggml.add_space_prefix");
+    v.space_prefix_ = space_prefix.is_ok() ? space_prefix.value() : true;
     return v;
 }
 
@@ -274,7 +276,7 @@ Status Vocab::tokenize_plain(const std::string & text, bool space_in_front, std:
     std::vector<int32_t> & out = *result;
     if (!byte_level_) {
         // sentencepiece: the escaped text as a chain of characters; the pair whose concatenation is the best-scoring piece is merged until none is a piece
-        std::string escaped = space_in_front ? "\xE2\x96\x81" : "";
+        std::string escaped = (space_in_front && space_prefix_) ? "\xE2\x96\x81" : "";
         for (char c : text) { if (c == ' ') escaped += "\xE2\x96\x81"; else escaped += c; }
         struct Sym { size_t at, len; int prev, next; };
         std::vector<Sym> sym;

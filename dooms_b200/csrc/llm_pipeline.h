@@ -46,7 +46,7 @@ public:
     // Text -> ids.   InvalidArgument  empty text, or a byte the vocabulary has no token for
     //   byte-level BPE: the text is cut into words the way the file's pre-tokenizer does (tokenizer.ggml.pre: the Llama 3 pattern for "llama-bpe", the
     //   Qwen2 pattern for "qwen2", the GPT-2 pattern otherwise), each word's bytes are merged pairwise by rank;
-    //   sentencepiece: spaces become U+2581 (one is put in front of the text), the text's characters are merged pairwise, best-scoring vocabulary piece
+    //   sentencepiece: spaces become U+2581 (one is put in front of the text unless tokenizer.ggml.add_space_prefix says no), the text's characters are merged pairwise, best-scoring vocabulary piece
     //   first (tokenizer.ggml.scores; leftmost on ties), and what is no piece at the end goes out byte by byte as <0xHH>.
     // parse_special: a control token's text inside `text` ("<|im_start|>") becomes that token's id instead of being tokenized as characters (what a
     // chat template's output needs); user-defined tokens are matched either way. The longest token at the earliest position wins.
@@ -72,6 +72,7 @@ private:
     std::vector<int32_t> eog_;
     int32_t bos_ = -1;
     bool add_bos_ = false, byte_level_ = false, ignore_merges_ = false;
+    bool space_prefix_ = true;                                  // sentencepiece: a space goes in front of the text (tokenizer.ggml.add_space_prefix)
     int pre_ = 0;                                               // 0 GPT-2, 1 Llama 3, 2 Qwen2
 };
 

@@ -19,23 +19,32 @@ TEXTS = ["hello world", "the quick brown fox jumps over the lazy dog", "hello", 
          "日本", "trailing space ", "   ", "modelmodel layer.norm"]
 
 
+def train(tmp: str, corpus: Path, dummy_prefix: bool):
+    prefix = str(Path(tmp) / ("tiny" if dummy_prefix else "tiny_noprefix"))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=prefix, vocab_size=400, model_type="bpe", byte_fallback=True, character_coverage=0.98,
+                                   bos_id=1, eos_id=2, unk_id=0, pad_id=-1, normalization_rule_name="identity", add_dummy_prefix=dummy_prefix,
+                                   remove_extra_whitespaces=False, num_threads=1, minloglevel=2)
+    return spm.SentencePieceProcessor(model_file=prefix + ".model")
+
+
+def describe(sp) -> dict:
+    n = sp.get_piece_size()
+    types = [2 if sp.is_unknown(i) else 3 if sp.is_control(i) else 6 if sp.is_byte(i) else 1 for i in range(n)]      # GGUF token types
+    return {"pieces": [sp.id_to_piece(i) for i in range(n)], "scores": [sp.get_score(i) for i in range(n)], "types": types, "bos": sp.bos_id(), "eos": sp.eos_id(),
+            "cases": [{"text": t, "ids": sp.encode(t, out_type=int)} for t in TEXTS]}
+
+
 def main():
     rng = random.Random(5)
     with tempfile.TemporaryDirectory() as tmp:
         corpus = Path(tmp) / "corpus.txt"
         corpus.write_text("\n".join(" ".join(rng.choice(WORDS) for _ in range(rng.randint(3, 12))) for _ in range(3000)), encoding="utf-8")
-        prefix = str(Path(tmp) / "tiny")
-        spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=prefix, vocab_size=400, model_type="bpe", byte_fallback=True, character_coverage=0.98,
-                                       bos_id=1, eos_id=2, unk_id=0, pad_id=-1, normalization_rule_name="identity", add_dummy_prefix=True,
-                                       remove_extra_whitespaces=False, num_threads=1, minloglevel=2)
-        sp = spm.SentencePieceProcessor(model_file=prefix + ".model")
-    n = sp.get_piece_size()
-    types = [2 if sp.is_unknown(i) else 3 if sp.is_control(i) else 6 if sp.is_byte(i) else 1 for i in range(n)]      # GGUF token types
-    out = {"pieces": [sp.id_to_piece(i) for i in range(n)], "scores": [sp.get_score(i) for i in range(n)], "types": types, "bos": sp.bos_id(), "eos": sp.eos_id(),
-           "sentencepiece_version": spm.__version__, "cases": [{"text": t, "ids": sp.encode(t, out_type=int)} for t in TEXTS]}
+        out = describe(train(tmp, corpus, True))
+        out["no_space_prefix"] = describe(train(tmp, corpus, False))      # the same, from a model that puts no space in front (tokenizer.ggml.add_space_prefix = false)
+    out["sentencepiece_version"] = spm.__version__
     path = Path(__file__).resolve().parent / "sentencepiece_tiny.json"
     path.write_text(json.dumps(out, ensure_ascii=True, indent=0), encoding="utf-8")
-    print(f"wrote {path}: {n} pieces, {len(TEXTS)} cases")
+    print(f"wrote {path}: {len(out['pieces'])} pieces, {len(TEXTS)} cases, with and without the space in front")
 
 
 if __name__ == "__main__":

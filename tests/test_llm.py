@@ -60,16 +60,19 @@ def test_sentencepiece_tokenizer_matches_the_sentencepiece_library(tmp_path):
     import json
     from pathlib import Path
     from dooms_b200.gguf_io import GgufWriter
-    fx = json.loads((Path(__file__).parent / "golden" / "sentencepiece_tiny.json").read_text())
-    path = str(tmp_path / "spm_golden.gguf")
-    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": fx["pieces"],
-                              "tokenizer.ggml.scores": [float(x) for x in fx["scores"]], "tokenizer.ggml.token_type": fx["types"],
-                              "tokenizer.ggml.bos_token_id": fx["bos"], "tokenizer.ggml.eos_token_id": fx["eos"], "tokenizer.ggml.add_bos_token": True}, [])
-    v = Vocab(path)
-    assert len(v) == len(fx["pieces"])
-    for case in fx["cases"]:
-        assert v.tokenize(case["text"], add_special=False) == case["ids"], case["text"]
-        assert b"".join(v.piece(t) for t in case["ids"]) == (" " + case["text"]).encode()      # and the pieces give the text back, with the space put in front
+    whole = json.loads((Path(__file__).parent / "golden" / "sentencepiece_tiny.json").read_text())
+    for fx, space_prefix in ((whole["no_space_prefix"], False), (whole, True)):
+        path = str(tmp_path / f"spm_golden_{int(space_prefix)}.gguf")
+        md = {"general.architecture": "llama", "tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": fx["pieces"], "tokenizer.ggml.scores": [float(x) for x in fx["scores"]],
+              "tokenizer.ggml.token_type": fx["types"], "tokenizer.ggml.bos_token_id": fx["bos"], "tokenizer.ggml.eos_token_id": fx["eos"], "tokenizer.ggml.add_bos_token": True}
+        if not space_prefix:
+            md["tokenizer.ggml.add_space_prefix"] = False
+        GgufWriter().write(path, md, [])
+        v = Vocab(path)
+        assert len(v) == len(fx["pieces"])
+        for case in fx["cases"]:
+            assert v.tokenize(case["text"], add_special=False) == case["ids"], (space_prefix, case["text"])
+            assert b"".join(v.piece(t) for t in case["ids"]) == ((" " if space_prefix else "") + case["text"]).encode()      # the pieces give the text back
     assert v.tokenize("hello world") == [fx["bos"]] + fx["cases"][0]["ids"]
 
 
