@@ -101,6 +101,61 @@ def test_byte_level_bpe_tokenizer_matches_the_tokenizers_library(tmp_path, pre):
     assert v.tokenize("hello<|endoftext|>", add_special=False, parse_special=True) == v.tokenize("hello", add_special=False) + [eot] and v.is_end_of_generation(eot)
 
 
+def test_tokenizers_agree_with_their_libraries_on_random_text(tmp_path):
+    """Live differential run where the `tokenizers` and `sentencepiece` packages are installed (skipped otherwise; the committed fixtures above hold without
+    them): seeded random mixtures that include unusual spaces, digits and letters of other scripts, combining marks and long digit runs."""
+    import json
+    import random
+    import sys
+    from pathlib import Path
+    tk = pytest.importorskip("tokenizers")
+    spm = pytest.importorskip("sentencepiece")
+    golden = Path(__file__).parent / "golden"
+    sys.path.insert(0, str(golden))
+    try:
+        import make_byte_bpe_fixture as B
+        import make_sentencepiece_fixture as S
+    finally:
+        sys.path.pop(0)
+    from dooms_b200.gguf_io import GgufWriter
+    rng = random.Random(17)
+    fx = json.loads((golden / "byte_bpe_tiny.json").read_text())
+    tokens, merges, eot = fx["tokens"], fx["merges"], fx["end_of_text"]
+    vocab, pairs = {t: i for i, t in enumerate(tokens)}, [tuple(m.split(" ")) for m in merges]
+    pieces = B.PIECES + ["\u2003", "\u2028", "\u202f", "\u0085", "\v", "\f", "\r", "\u0663\u0664\u0665", "\u216b", "\u01c5", "\u02b0", "\u093c", "\u203f", "\u20ac", "\u200b",
+                         "\ufeff", "a\u0301", "\ufb01", "\U0001d518", "\U0001d7d8", "Z\u00dcRICH", "'Ll", "'T", "'M", "9" * 7, "ab12cd", "x'sy", "\n\n\n ", " \t\n", "\n a",
+                         "  a", "\t\ta", "end\n", "!!\n\nX", " !\r\n\r\nq"]
+    for name, pattern in B.PATTERNS.items():
+        enc = tk.Tokenizer(tk.models.BPE(vocab=vocab, merges=pairs, ignore_merges=(name == "llama-bpe")))
+        if pattern is None:
+            enc.pre_tokenizer = tk.pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+        else:
+            enc.pre_tokenizer = tk.pre_tokenizers.Sequence([tk.pre_tokenizers.Split(tk.Regex(pattern), behavior="isolated", invert=False),
+                                                            tk.pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+        path = str(tmp_path / f"fuzz_{name}.gguf")
+        GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "gpt2", "tokenizer.ggml.pre": name, "tokenizer.ggml.tokens": tokens,
+                                  "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": [3 if i == eot else 1 for i in range(len(tokens))],
+                                  "tokenizer.ggml.eos_token_id": eot, "tokenizer.ggml.bos_token_id": eot, "tokenizer.ggml.add_bos_token": False}, [])
+        v = Vocab(path)
+        for _ in range(1500):
+            text = "".join(rng.choice(pieces) for _ in range(rng.randint(1, 10)))
+            assert v.tokenize(text, add_special=False) == enc.encode(text).ids, (name, text)
+    corpus = tmp_path / "corpus.txt"
+    words = random.Random(5)
+    corpus.write_text("\n".join(" ".join(words.choice(S.WORDS) for _ in range(words.randint(3, 12))) for _ in range(3000)), encoding="utf-8")
+    sp = S.train(str(tmp_path), corpus, True)
+    d = S.describe(sp)
+    path = str(tmp_path / "fuzz_spm.gguf")
+    GgufWriter().write(path, {"general.architecture": "llama", "tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": d["pieces"],
+                              "tokenizer.ggml.scores": [float(x) for x in d["scores"]], "tokenizer.ggml.token_type": d["types"], "tokenizer.ggml.bos_token_id": 1,
+                              "tokenizer.ggml.eos_token_id": 2}, [])
+    v = Vocab(path)
+    pieces = S.WORDS + [" ", " ", "  ", "\n", "\t", "x", "q", "Z", "1", "23", ".", ",", "!", "\u00e9", "\u65e5", "\u672c", "\u2603", "\U0001F600", "ll", "he", "th", "e", "o", "s"]
+    for _ in range(3000):
+        text = "".join(rng.choice(pieces) for _ in range(rng.randint(1, 12)))
+        assert v.tokenize(text, add_special=False) == sp.encode(text, out_type=int), text
+
+
 def _chat_file(tmp_path, family):
     path = str(tmp_path / f"chat_{family}.gguf")
     synth.write_model(synth.tiny_spec(QUANT_PLANS["q4_0"], n_vocab=N_VOCAB), path, 79, vocab=family)
