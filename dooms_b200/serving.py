@@ -1,5 +1,5 @@
 """Many independent sequences over one or more GPUs, data parallel: one worker process per GPU, each with its own decoder (weights replicated, its own KV
-cache). No collective on the data path. Two ways to run a GPU's share:
+cache). No collective on the data path. Three ways to run a GPU's share:
   * batched (serve_batched, the default of the command below): the decoder holds one KV-cache slot per sequence, every prompt is evaluated into its slot,
     and then all sequences decode together, one pass over the weights per step for all of them (CudaLlamaDecoder.decode_batch); a sequence that has all
     its tokens leaves its row idle;
