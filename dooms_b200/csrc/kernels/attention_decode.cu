@@ -2,8 +2,9 @@
 // row is read from device memory once per step, in 16-byte coalesced asynchronous copies, by a grid of (key/value head, range of positions) blocks that
 // covers all SMs. The kernel also does what used to be a launch of its own before it: it rotates the new token's query and key (rope_store,
 // src/backend/metal/llama_kernels.h:521-545), writes the rotated key and the value into the f16 cache, and uses them from shared memory in the same pass.
-// Each block leaves an unnormalised partial result (max, sum, values) per query head; k_attention_combine merges the ranges (attention_split /
-// attention_combine, llama_kernels.h:860-929).
+// Each block leaves an unnormalised partial result (max, sum, values) per query head; the block that finishes a key/value head's last range merges the
+// ranges of its query heads itself (attention_split / attention_combine, llama_kernels.h:860-929), or k_attention_combine does when no counters are given.
+// The scores and the weighted sums run on the tensor cores (attention_decode_body.cuh).
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
