@@ -1,5 +1,5 @@
-// Decode GEMV for the block formats that have no integer tensor-core path here (q5_0, q8_0, q4_K, q6_K, f16; q4_0 when its fast kernel does not take the
-// shape): the same streaming skeleton as gemv_q4_0.cu, with the dot products on the CUDA cores in f32.
+// Decode GEMV for the block formats and shapes that have no integer tensor-core path here (q5_0, q8_0, f16; q4_0, q4_K and q6_K when gemv_q4_0.cu /
+// gemv_q6_k.cu do not take the shape): the same streaming skeleton as gemv_q4_0.cu, with the dot products on the CUDA cores in f32.
 //   * One block per SM with an equal share of the rows; the units of work are (16-row tile, matrix, chunk of the row), dealt round-robin to the block's
 //     warps; every warp streams its units through its own ring of shared-memory stages filled by 16-byte asynchronous copies of the rows' bytes exactly as
 //     they lie in the GGUF file (blocks of 22, 34, 144, 210 bytes at 2-byte alignment: the copies are the aligned cover of the chunk).

@@ -9,9 +9,12 @@
 //     bit), exactly the operand layout mma.m16n8k32.s8 wants for a q4_0 block: low nibbles are elements 0..15, high nibbles 16..31.
 //   * One MMA per block: 16 rows x 32 elements x (4 limbs of this block | 4 limbs of the next block's slot). Two consecutive blocks accumulate into one
 //     8-column fragment so that all 32 lanes have one (row, block, limb pair) to scale: acc += float(c_lo + 128 c_hi) * (d * s * 2^-30 or 2^-16).
-//   * Each warp streams (16 rows x a chunk of the row) units through its own ring of shared-memory stages filled by 16-byte asynchronous copies of the
-//     rows' bytes exactly as they lie in the GGUF file (18-byte blocks, 2-byte aligned): no repacking, 16-byte aligned covers, a row stride in the stage
-//     that keeps the 8 rows of a fragment on different banks. One block-wide barrier after the prologue, one before the epilogue.
+//   * Each warp streams (16 rows x a chunk of the row) units through its own ring of shared-memory stages, filled with the rows' bytes exactly as they
+//     lie in the GGUF file (18-byte blocks, 2-byte aligned; no repacking): by TMA tensor copies of 8 rows x 144 bytes with one mbarrier per stage and
+//     warp (bounded polls) when rows are whole 256-element groups, otherwise by 16-byte asynchronous copies of aligned covers with a row stride in the
+//     stage that keeps the 8 rows of a fragment on different banks. One block-wide barrier after the prologue, one before the epilogue.
+//   * The kernel is launched early (programmatic dependent launch): it asks for its copy descriptors and its first weight stages before it waits for
+//     the kernel that produces its input.
 // The block formulas are the reference's (src/backend/metal/llama_kernels.h:1012-1040: value = d (q - 8)); matvec1q / gate_up1q there are the kernels this
 // replaces (llama_kernels.h:1197-1269).
 #include <cuda.h>
